@@ -1,0 +1,186 @@
+/* C ABI of the library (loaded from Python with ctypes, usable from C/C++).
+ *
+ * Capability parity: the reference's include/ooverlap/comm.h:54-358
+ * (oo_group_* / oo_node_* / oo_buffer_* / oo_ipc_slot_set_* / oo_allreduce* /
+ * oo_reduce_scatter* / oo_all_gather*).  The object model is collapsed to one
+ * communicator per rank process that owns a symmetric heap: every rank maps
+ * every other rank's heap (and, where the driver allows, an NVLink multicast
+ * alias of all of them), so a buffer is identified by (registration id,
+ * byte offset) and no per-call exchange is ever needed.
+ *
+ * All functions return 0 on success or a negative oob_status_t; the message of
+ * the last failure on the calling thread is available from oob_last_error().
+ */
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#pragma GCC visibility push(default)
+
+typedef struct oob_comm oob_comm;
+
+typedef enum {
+  OOB_OK = 0,
+  OOB_ERR_INVALID = -1,
+  OOB_ERR_CUDA = -2,
+  OOB_ERR_BOOTSTRAP = -3,
+  OOB_ERR_UNSUPPORTED = -4,
+  OOB_ERR_NOMEM = -5,
+  OOB_ERR_DEVICE_TIMEOUT = -6, /* a kernel gave up waiting; see oob_comm_status */
+  OOB_ERR_POISONED = -7        /* an earlier device timeout left the flags inconsistent */
+} oob_status_t;
+
+typedef enum { OOB_F16 = 0, OOB_BF16 = 1, OOB_F32 = 2 } oob_dtype_t;
+typedef enum { OOB_SUM = 0, OOB_MIN = 1, OOB_MAX = 2 } oob_op_t;
+
+/* Algorithms; OOB_ALGO_AUTO asks the tuning policy. */
+#define OOB_ALGO_AUTO (-1)
+typedef enum { OOB_AR_ONESHOT_P2P = 0, OOB_AR_TWOSHOT_P2P = 1, OOB_AR_TWOSHOT_NVLS = 2, OOB_AR_ONESHOT_NVLS = 3 } oob_ar_algo_t;
+typedef enum { OOB_RS_P2P = 0, OOB_RS_NVLS = 1 } oob_rs_algo_t;
+typedef enum { OOB_AG_PUSH_P2P = 0, OOB_AG_PUSH_NVLS = 1, OOB_AG_PULL_P2P = 2 } oob_ag_algo_t;
+typedef enum {
+  OOB_NORM_LOCAL = 0,
+  OOB_NORM_AR_ONESHOT = 1,
+  OOB_NORM_AR_TWOSHOT = 2,
+  OOB_NORM_AR_TWOSHOT_NVLS = 3,
+  OOB_NORM_RS = 4,
+  OOB_NORM_RS_NVLS = 5
+} oob_norm_algo_t;
+typedef enum { OOB_GEMM_PLAIN = 0, OOB_GEMM_AR = 1, OOB_GEMM_RS_NORM = 2, OOB_GEMM_AG = 3 } oob_gemm_mode_t;
+
+/* Creation flags */
+#define OOB_FLAG_NO_NVLS 1u        /* never create a multicast object */
+#define OOB_FLAG_LEGACY_IPC 2u     /* cudaMalloc + cudaIpc handles instead of VMM file descriptors */
+
+typedef struct {
+  int rank, world, device;
+  int nvls;            /* 1 when the heap has a multicast alias */
+  int emulated;        /* 1 for the single-GPU emulation group */
+  int memory_kind;     /* 0 = VMM fd, 1 = legacy IPC, 2 = same-process */
+  uint64_t heap_bytes; /* per rank, including the signal pad */
+  uint64_t user_offset;/* first byte available to oob_alloc */
+  uint64_t timeout_ns;
+} oob_comm_info_t;
+
+typedef struct {
+  int code, rank, peer, block;
+  unsigned expected, observed;
+  int where, pad;
+} oob_device_status_t;
+
+const char* oob_last_error(void);
+const char* oob_version(void);
+
+/* One call per rank process.  `key` names the rendezvous (<= 80 chars). */
+int oob_comm_create(int rank, int world, int device, const char* key, uint64_t heap_bytes, unsigned flags,
+                    int timeout_ms, oob_comm** out);
+/* All `world` ranks live in this process on `device`; collectives are run as
+ * ONE cooperative launch whose block rows act as ranks.  For tests and tuning
+ * on a single GPU. */
+int oob_comm_create_emulated(int world, int device, uint64_t heap_bytes, oob_comm** out);
+int oob_comm_destroy(oob_comm* c);
+int oob_comm_info(const oob_comm* c, oob_comm_info_t* info);
+int oob_comm_set_timeout_ms(oob_comm* c, int ms);
+int oob_comm_barrier(oob_comm* c);                       /* host-side, through the rendezvous */
+int oob_comm_status(oob_comm* c, oob_device_status_t* s);/* 0 = clean, OOB_ERR_DEVICE_TIMEOUT otherwise */
+/* Collective: zeroes every rank's signal pad and status after a device
+ * timeout.  No kernel of this communicator may be in flight. */
+int oob_comm_recover(oob_comm* c);
+
+/* Symmetric heap.  Every rank must issue the same sequence of alloc/free
+ * calls; offsets are then identical on all ranks. */
+int oob_alloc(oob_comm* c, uint64_t bytes, uint64_t align, uint64_t* offset);
+int oob_free(oob_comm* c, uint64_t offset);
+void* oob_heap_ptr(const oob_comm* c, int rank, uint64_t offset);
+void* oob_heap_mc_ptr(const oob_comm* c, uint64_t offset);
+
+/* Registers memory that was NOT allocated from the heap (e.g. a torch tensor)
+ * through legacy CUDA IPC: the allocation's base is shared once and kept in an
+ * import cache, the view is base + offset.  Collective.  Returns the
+ * registration id (> 0) in *reg. */
+int oob_register_ipc(oob_comm* c, void* ptr, uint64_t bytes, int* reg);
+int oob_unregister(oob_comm* c, int reg);
+
+/* Buffers are (reg, offset): reg 0 is the heap. */
+int oob_allreduce(oob_comm* c, int dtype, int op, int algo, int in_reg, uint64_t in_off, int out_reg, uint64_t out_off,
+                  void* out_local, uint64_t count, int max_ctas, void* stream);
+int oob_reduce_scatter(oob_comm* c, int dtype, int op, int algo, int in_reg, uint64_t in_off, void* out_local,
+                       uint64_t count, int max_ctas, void* stream);
+int oob_all_gather(oob_comm* c, int dtype, int algo, int out_reg, uint64_t out_off, const void* src_local,
+                   void* dst_local, uint64_t count, int max_ctas, void* stream);
+
+typedef struct {
+  int dtype, rows, hidden;
+  float eps;
+  int x_reg;
+  uint64_t x_off;
+  const void* residual;
+  const void* weight;
+  int y_reg;
+  uint64_t y_off; /* two-shot algorithms: y in registered memory */
+  void* y_local;  /* other algorithms */
+  int res_out_reg;
+  uint64_t res_out_off; /* reg < 0: no residual output */
+  void* res_out_local;
+  uint64_t emu_stride_local; /* emulation: byte stride between ranks of residual / y_local / res_out_local */
+} oob_norm_args_t;
+int oob_fused_norm(oob_comm* c, int algo, const oob_norm_args_t* a, int max_ctas, void* stream);
+
+typedef struct {
+  int mode, dtype;
+  int M, N, K;
+  const void* A;
+  int lda;
+  const void* B;
+  int ldb;
+  void* C;
+  int ldc;
+  uint64_t a_emu_stride, b_emu_stride, c_emu_stride;
+  int comm_ctas, max_ctas;
+  int partial_reg;
+  uint64_t partial_off;
+  int c_reg;
+  uint64_t c_off;
+  int counter_base;
+  const void* residual;
+  const void* weight;
+  float eps;
+  void* y_local;
+  void* res_out_local;
+  uint64_t rs_emu_stride;
+  int a_full_reg;
+  uint64_t a_full_off;
+} oob_gemm_args_t;
+/* c may be NULL for OOB_GEMM_PLAIN. */
+int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream);
+int oob_gemm_counters_needed(int mode, int M, int N, int world);
+uint64_t oob_gemm_partial_bytes(int M, int N);
+
+/* Tuning policy (size -> algorithm, CTA budget). */
+int oob_policy_load(const char* json_path);
+int oob_policy_select(int world, int collective /*0 AR,1 RS,2 AG*/, uint64_t bytes, int nvls, int* algo, int* ctas);
+
+/* Topology probe; writes a JSON document into buf (truncated to cap). */
+int oob_topology_json(char* buf, uint64_t cap, int run_probes);
+
+/* Node-local rendezvous on its own (host only): all-gather of small blobs,
+ * barrier, file-descriptor exchange.  Every call has the creation timeout. */
+typedef struct oob_bootstrap oob_bootstrap;
+int oob_bootstrap_create(int rank, int world, const char* key, int timeout_ms, oob_bootstrap** out);
+int oob_bootstrap_destroy(oob_bootstrap* h);
+int oob_bootstrap_allgather(oob_bootstrap* h, const void* in, void* out, uint64_t bytes);
+int oob_bootstrap_barrier(oob_bootstrap* h);
+int oob_bootstrap_exchange_fds(oob_bootstrap* h, int my_fd, int* fds_out /* world entries */);
+int oob_bootstrap_broadcast_fd(oob_bootstrap* h, int root, int* fd);
+
+/* Test hook: waits on a flag that nobody sets, with the communicator's
+ * timeout, and reports through the status block (bounded-wait self test). */
+int oob_test_bounded_wait(oob_comm* c, void* stream);
+
+#pragma GCC visibility pop
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,235 @@
+// Residual-add + RMSNorm, stand-alone and fused into the tail of the
+// all-reduce / reduce-scatter: the rank that reduces a token row keeps it in
+// registers, adds the residual, computes the row's mean square in fp32,
+// scales by the norm weight and writes (or broadcasts) the result.  The
+// partial sums never make a round trip through memory between the collective
+// and the normalisation.
+//
+// Capability parity: the reference has a stand-alone fp16 RMSNorm and a
+// variant that un-reorders the overlap GEMM's packed tiles
+// (src/rmsnorm/rmsnorm.cuh:11-121); it has no residual add and no fusion with
+// a collective.  Math here is fp32 with a caller-supplied eps.
+#include <cuda_runtime.h>
+#include "../device/reduce.cuh"
+#include "../device/sync.cuh"
+#include "collectives.h"
+
+namespace oob {
+namespace {
+
+constexpr int kNormThreads = 256;
+
+__device__ __forceinline__ float block_sum(float v) {
+  __shared__ float s_part[kNormThreads / 32];
+  __shared__ float s_total;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();  // protects s_part / s_total against the previous row's readers
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < kNormThreads / 32 ? s_part[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) s_total = t;
+  }
+  __syncthreads();
+  return s_total;
+}
+
+__device__ __forceinline__ void row_partition(int rows, int world, int r, int& b, int& e) {
+  const int base = rows / world, rem = rows % world;
+  b = base * r + (r < rem ? r : rem);
+  e = b + base + (r < rem ? 1 : 0);
+}
+
+// PPT = 16-byte packs per thread (hidden <= PPT * 256 * 8).
+template <typename T, int PPT, int NR, int ALGO>
+__global__ void __launch_bounds__(kNormThreads) fused_norm_kernel(CommCtx ctx_param, NormArgs a) {
+  const CommCtx ctx = resolve_ctx(ctx_param);
+  const int world = ctx.world, rank = ctx.rank;
+  using PT = PackTraits<T>;
+  constexpr int E = 8;
+  const int hidden = a.hidden;
+  const int packs_per_row = hidden / E;
+  const size_t row_bytes = size_t(hidden) * sizeof(T);
+
+  constexpr bool kComm = ALGO != kNormLocal;
+  constexpr bool kShard = (ALGO == kNormArTwoShot || ALGO == kNormArTwoShotNvls || ALGO == kNormRs || ALGO == kNormRsNvls);
+  constexpr bool kRs = (ALGO == kNormRs || ALGO == kNormRsNvls);
+  constexpr bool kMc = (ALGO == kNormArTwoShotNvls || ALGO == kNormRsNvls);
+  constexpr bool kPush = (ALGO == kNormArTwoShot || ALGO == kNormArTwoShotNvls);
+
+  if constexpr (kComm) {
+    if (!rank_barrier(ctx, blockIdx.x, 40)) return;
+  }
+
+  int row0 = 0, row1 = a.rows;
+  if constexpr (kShard) row_partition(a.rows, world, rank, row0, row1);
+
+  const char* res = a.residual ? static_cast<const char*>(a.residual) + a.residual_emu_stride * blockIdx.y : nullptr;
+  char* y_local = a.y_local ? static_cast<char*>(a.y_local) + a.y_local_emu_stride * blockIdx.y : nullptr;
+  char* ro_local =
+      a.res_out_local ? static_cast<char*>(a.res_out_local) + a.res_out_local_emu_stride * blockIdx.y : nullptr;
+  const bool want_res_out = kPush ? (a.res_out.p[rank] != nullptr) : (ro_local != nullptr);
+
+  // Norm weight for this thread's packs stays in registers across rows.
+  float w[PPT][E];
+#pragma unroll
+  for (int j = 0; j < PPT; ++j) {
+    const int p = threadIdx.x + j * kNormThreads;
+    if (p < packs_per_row) {
+      const uint4 wv = *reinterpret_cast<const uint4*>(static_cast<const char*>(a.weight) + size_t(p) * 16);
+      PT::unpack(wv, w[j]);
+    }
+  }
+
+  for (int row = row0 + blockIdx.x; row < row1; row += gridDim.x) {
+    const size_t off = size_t(row) * row_bytes;
+    // Residual and outputs of the RS form are indexed by the rank-local row.
+    const size_t loff = kRs ? size_t(row - row0) * row_bytes : off;
+    float v[PPT][E];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PPT; ++j) {
+      const int p = threadIdx.x + j * kNormThreads;
+      if (p < packs_per_row) {
+        uint4 x;
+        if constexpr (!kComm)
+          x = *reinterpret_cast<const uint4*>(static_cast<const char*>(a.x.p[rank]) + off + size_t(p) * 16);
+        else if constexpr (kMc)
+          x = reduce_pack_mc<T, kSum>(static_cast<const char*>(a.x.mc) + off + size_t(p) * 16);
+        else
+          x = reduce_pack_p2p<T, kSum, NR>(a.x, off + size_t(p) * 16, world);
+        PT::unpack(x, v[j]);
+        if (res != nullptr) {
+          const uint4 rv = ptx::ld_nc_v4(res + loff + size_t(p) * 16);
+          float rf[E];
+          PT::unpack(rv, rf);
+#pragma unroll
+          for (int i = 0; i < E; ++i) v[j][i] += rf[i];
+          // The normalisation sees the residual stream as it is stored (rounded).
+          if (want_res_out) {
+            const uint4 ro = PT::pack(v[j]);
+            PT::unpack(ro, v[j]);
+          }
+        }
+        if (want_res_out) {
+          const uint4 ro = PT::pack(v[j]);
+          if constexpr (kPush) {
+            if constexpr (kMc) {
+              ptx::multimem_st_v4(static_cast<char*>(a.res_out.mc) + off + size_t(p) * 16, ro);
+            } else {
+              for (int r = 0; r < world; ++r)
+                ptx::st_v4(static_cast<char*>(a.res_out.p[(rank + r) % world]) + off + size_t(p) * 16, ro);
+            }
+          } else {
+            ptx::st_v4(ro_local + loff + size_t(p) * 16, ro);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < E; ++i) ss += v[j][i] * v[j][i];
+      }
+    }
+    const float total = block_sum(ss);
+    const float scale = rsqrtf(total / float(hidden) + a.eps);
+#pragma unroll
+    for (int j = 0; j < PPT; ++j) {
+      const int p = threadIdx.x + j * kNormThreads;
+      if (p < packs_per_row) {
+        float o[E];
+#pragma unroll
+        for (int i = 0; i < E; ++i) o[i] = v[j][i] * scale * w[j][i];
+        const uint4 yo = PT::pack(o);
+        if constexpr (kPush) {
+          if constexpr (kMc) {
+            ptx::multimem_st_v4(static_cast<char*>(a.y.mc) + off + size_t(p) * 16, yo);
+          } else {
+            for (int r = 0; r < world; ++r)
+              ptx::st_v4(static_cast<char*>(a.y.p[(rank + r) % world]) + off + size_t(p) * 16, yo);
+          }
+        } else {
+          ptx::st_v4(y_local + loff + size_t(p) * 16, yo);
+        }
+      }
+    }
+  }
+
+  if constexpr (kComm) rank_barrier(ctx, blockIdx.x, 41);
+}
+
+template <typename K>
+cudaError_t launch_k(K kernel, const CommCtx& ctx, int ctas, const NormArgs& a, cudaStream_t stream) {
+  if (ctx.emu_table != nullptr) {
+    dim3 grid(ctas, ctx.world);
+    CommCtx c = ctx;
+    NormArgs aa = a;
+    void* argv[] = {(void*)&c, (void*)&aa};
+    return cudaLaunchCooperativeKernel((const void*)kernel, grid, dim3(kNormThreads), argv, 0, stream);
+  }
+  kernel<<<dim3(ctas, 1), kNormThreads, 0, stream>>>(ctx, a);
+  return cudaGetLastError();
+}
+
+template <typename T, int PPT, int NR>
+cudaError_t dispatch_algo(int algo, const CommCtx& ctx, int ctas, const NormArgs& a, cudaStream_t stream) {
+  switch (algo) {
+    case kNormLocal:
+      return launch_k(fused_norm_kernel<T, PPT, 0, kNormLocal>, ctx, ctas, a, stream);
+    case kNormArOneShot:
+      return launch_k(fused_norm_kernel<T, PPT, NR, kNormArOneShot>, ctx, ctas, a, stream);
+    case kNormArTwoShot:
+      return launch_k(fused_norm_kernel<T, PPT, NR, kNormArTwoShot>, ctx, ctas, a, stream);
+    case kNormArTwoShotNvls:
+      return launch_k(fused_norm_kernel<T, PPT, 0, kNormArTwoShotNvls>, ctx, ctas, a, stream);
+    case kNormRs:
+      return launch_k(fused_norm_kernel<T, PPT, NR, kNormRs>, ctx, ctas, a, stream);
+    case kNormRsNvls:
+      return launch_k(fused_norm_kernel<T, PPT, 0, kNormRsNvls>, ctx, ctas, a, stream);
+  }
+  return cudaErrorInvalidValue;
+}
+
+template <typename T, int PPT>
+cudaError_t dispatch_world(int algo, const CommCtx& ctx, int ctas, const NormArgs& a, cudaStream_t stream) {
+  switch (ctx.world) {
+    case 2:
+      return dispatch_algo<T, PPT, 2>(algo, ctx, ctas, a, stream);
+    case 4:
+      return dispatch_algo<T, PPT, 4>(algo, ctx, ctas, a, stream);
+    case 8:
+      return dispatch_algo<T, PPT, 8>(algo, ctx, ctas, a, stream);
+    default:
+      return dispatch_algo<T, PPT, 0>(algo, ctx, ctas, a, stream);
+  }
+}
+
+template <typename T>
+cudaError_t dispatch_ppt(int algo, const CommCtx& ctx, int ctas, const NormArgs& a, cudaStream_t stream) {
+  const int packs = a.hidden / 8;
+  const int ppt = (packs + kNormThreads - 1) / kNormThreads;
+  if (ppt <= 1) return dispatch_world<T, 1>(algo, ctx, ctas, a, stream);
+  if (ppt <= 2) return dispatch_world<T, 2>(algo, ctx, ctas, a, stream);
+  if (ppt <= 4) return dispatch_world<T, 4>(algo, ctx, ctas, a, stream);
+  if (ppt <= 8) return dispatch_world<T, 8>(algo, ctx, ctas, a, stream);
+  return cudaErrorInvalidValue;  // hidden > 16384
+}
+
+}  // namespace
+
+cudaError_t launch_fused_norm(const CommCtx& ctx, int algo, const NormArgs& a, int max_ctas, cudaStream_t stream) {
+  if (a.hidden % 8 != 0 || a.hidden <= 0 || a.rows < 0) return cudaErrorInvalidValue;
+  if (a.dtype != kF16 && a.dtype != kBF16) return cudaErrorInvalidValue;
+  const bool mc = (algo == kNormArTwoShotNvls || algo == kNormRsNvls);
+  if (mc && a.x.mc == nullptr) return cudaErrorInvalidValue;
+  if (algo == kNormArTwoShotNvls && a.y.mc == nullptr) return cudaErrorInvalidValue;
+  int rows = a.rows;
+  if (algo >= kNormArTwoShot) rows = (a.rows + ctx.world - 1) / ctx.world;
+  int ctas = max_ctas < 1 ? 1 : max_ctas;
+  if (ctas > kMaxCommBlocks) ctas = kMaxCommBlocks;
+  if (ctas > rows) ctas = rows < 1 ? 1 : rows;
+  if (a.dtype == kF16) return dispatch_ppt<__half>(algo, ctx, ctas, a, stream);
+  return dispatch_ppt<__nv_bfloat16>(algo, ctx, ctas, a, stream);
+}
+
+}  // namespace oob

@@ -1,0 +1,63 @@
+// Host interface of the tcgen05 GEMM family (plain, GEMM->all-reduce,
+// GEMM->reduce-scatter+residual+RMSNorm, all-gather->GEMM).
+#pragma once
+#include <cuda_runtime.h>
+#include <cstddef>
+#include <cstdint>
+#include "../device/comm_ctx.h"
+
+namespace oob {
+
+enum GemmMode : int {
+  kGemmPlain = 0,   // C = A * B^T
+  kGemmAr = 1,      // C_all_ranks = sum_r A_r * B_r^T               (row-parallel linear)
+  kGemmRsNorm = 2,  // rows of rank: y = rmsnorm(sum_r A_r B_r^T + residual) * w
+  kGemmAg = 3,      // C = allgather_rows(A_shard) * B^T             (column-parallel linear)
+};
+
+constexpr int kTileM = 128;
+constexpr int kTileN = 256;
+constexpr int kTileK = 64;
+constexpr int kTileBytes = kTileM * kTileN * 2;  // one 16-bit output tile
+
+// All matrices are 16-bit (fp16 or bf16), A is [M, K] row-major with leading
+// dimension lda, B is [N, K] row-major (the layout of a torch Linear weight)
+// with leading dimension ldb, C is [M, N] row-major.
+struct GemmArgs {
+  int mode;
+  int fmt;  // 0 = fp16, 1 = bf16
+  int M, N, K;
+  const void* A;
+  int lda;
+  const void* B;
+  int ldb;
+  void* C;  // plain / AG modes: local output
+  int ldc;
+  size_t a_emu_stride, b_emu_stride, c_emu_stride;  // single-GPU emulation: per-rank byte strides of A, B, C
+
+  int comm_ctas;  // CTAs reserved for the communication role (fused modes)
+  int max_ctas;   // 0 = one CTA per SM
+
+  // Fused modes
+  PeerPtrs partial;     // AR / RS: tile-packed partial products, registered; >= tiles * kTileBytes
+  PeerPtrs c_sym;       // AR: output [M, N] in every rank's registered memory
+  int counter_base;     // first general counter of the pad used by this op
+  // RS + norm tail (rows of this rank only; M / world must be a multiple of 128)
+  const void* residual; // [M/world, N] or null
+  const void* weight;   // [N] or null (null: no normalisation, y = sum + residual)
+  float eps;
+  void* y_local;        // [M/world, N]
+  void* res_out_local;  // [M/world, N] or null
+  size_t rs_emu_stride; // emulation stride of residual / y_local / res_out_local
+  // AG: A is this rank's [M/world, K] shard; gathered copy lives in a_full
+  PeerPtrs a_full;      // [M, K] registered on every rank
+};
+
+// Launches on `stream`.  Returns cudaErrorInvalidValue for unsupported shapes
+// (K % 8, N % 8, leading dimensions not multiples of 8 elements, ...).
+cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& args, cudaStream_t stream);
+
+// Number of general counters a fused op needs from counter_base on.
+int gemm_counters_needed(int mode, int M, int N, int world);
+
+}  // namespace oob

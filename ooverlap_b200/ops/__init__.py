@@ -1,0 +1,5 @@
+"""Hot ops: hand-written sm_100a kernels behind small Python entry points."""
+from .gemm import gemm  # noqa: F401
+from .norm import (fused_allreduce_rmsnorm, fused_reduce_scatter_rmsnorm, rmsnorm,  # noqa: F401
+                   rmsnorm_reference)
+from .overlap import AllGatherGemm, GemmAllReduce, GemmReduceScatterNorm, gemm_all_reduce_unfused  # noqa: F401

@@ -1,0 +1,52 @@
+"""Plain tcgen05 GEMM: ``C[M, N] = A[M, K] @ B[N, K]^T`` (B in torch ``Linear.weight`` layout).
+
+Capability parity: ``gemm_plain_sm90_dispatch`` / the cuBLAS column GEMM of the
+reference's legacy binding (src/gemm/gemm_plain_sm90_dispatch.h:19-46,
+src/pybind.cpp:266-324).  One hand-written sm_100a kernel replaces the 122
+generated CUTLASS instances.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from ..utils.dtypes import dtype_code
+
+
+def _check_operands(a: torch.Tensor, b: torch.Tensor) -> None:
+    if a.dtype not in (torch.float16, torch.bfloat16) or a.dtype != b.dtype:
+        raise TypeError("GEMM operands must both be fp16 or both bf16")
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
+        raise ValueError(f"shape mismatch: A {tuple(a.shape)} x B^T {tuple(b.shape)}")
+    if a.stride(1) != 1 or b.stride(1) != 1:
+        raise ValueError("A and B must be row-major (unit stride along K)")
+    if not a.is_cuda or not b.is_cuda:
+        raise ValueError("GEMM operands must be CUDA tensors")
+
+
+def fill_gemm_args(args: _lib.GemmArgs, a: torch.Tensor, b: torch.Tensor) -> None:
+    args.dtype = dtype_code(a.dtype)
+    args.M, args.K = a.shape
+    args.N = b.shape[0]
+    args.A, args.lda = a.data_ptr(), a.stride(0)
+    args.B, args.ldb = b.data_ptr(), b.stride(0)
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, max_ctas: int = 0) -> torch.Tensor:
+    """``out = a @ b.T`` with fp32 accumulation in TMEM."""
+    _check_operands(a, b)
+    M, N = a.shape[0], b.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    elif out.shape != (M, N) or out.dtype != a.dtype or out.stride(1) != 1:
+        raise ValueError("bad output tensor")
+    args = _lib.GemmArgs()
+    args.mode = _lib.GEMM_PLAIN
+    fill_gemm_args(args, a, b)
+    args.C, args.ldc = out.data_ptr(), out.stride(0)
+    args.max_ctas = max_ctas
+    _lib.check(_lib.lib().oob_gemm(None, ctypes.byref(args), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return out

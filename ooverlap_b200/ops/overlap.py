@@ -1,0 +1,178 @@
+"""GEMM + collective overlap ops (one fused sm_100a kernel each).
+
+* :class:`GemmAllReduce` — row-parallel linear: ``C = sum_ranks(A_r @ B_r^T)`` on every rank.
+* :class:`GemmReduceScatterNorm` — ``y_rows_of_rank = rmsnorm(sum_ranks(A_r @ B_r^T) + residual) * w``.
+* :class:`AllGatherGemm` — column-parallel linear: ``C = allgather_rows(A_shard) @ B^T``.
+
+Each object owns the registered buffers (tile-packed partial products, output,
+gathered operand) and the arrival counters of its shape, so calls are a single
+kernel launch with fixed addresses (CUDA-graph friendly).
+
+Capability parity: ``OverlapImpl::GemmAllReduceOverlap`` /
+``GemmReduceScatterOverlap`` of the reference (src/overlap_impl.cu:450-706) and
+its Python driver (test/test.py:509-676).  The segment search, reorder maps and
+the separate wait kernel are gone: the GEMM epilogue signals per tile and
+reducer CTAs of the same launch stream the reduction over NVSwitch.  The
+RMSNorm tail and AllGather->GEMM have no counterpart there.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from ..utils.partition import partition
+from .gemm import _check_operands, fill_gemm_args, gemm
+
+TILE_M = 128
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _emulated(comm) -> bool:
+    return bool(getattr(comm, "emulated", False))
+
+
+def _operands(comm, a: torch.Tensor, b: torch.Tensor):
+    """In emulation ``a`` and ``b`` are stacked ``[world, ...]``; returns (a0, b0, a_stride, b_stride)."""
+    if _emulated(comm):
+        if a.dim() != 3 or b.dim() != 3 or a.shape[0] != comm.world or b.shape[0] != comm.world:
+            raise ValueError("emulated group: operands must be stacked [world, rows, K]")
+        return a[0], b[0], a.stride(0) * a.element_size(), b.stride(0) * b.element_size()
+    return a, b, 0, 0
+
+
+class GemmAllReduce:
+    def __init__(self, comm, M: int, N: int, dtype: torch.dtype, *, comm_ctas: int = 20, max_ctas: int = 0):
+        self.comm, self.M, self.N, self.dtype = comm, M, N, dtype
+        self.comm_ctas, self.max_ctas = comm_ctas, max_ctas
+        self.fused = comm.world > 1
+        if self.fused:
+            lib = _lib.lib()
+            self.partial_off = comm.alloc(int(lib.oob_gemm_partial_bytes(M, N)))
+            self.c_off = comm.alloc(M * N * 2)
+            self.counter_base = comm.reserve_counters(lib.oob_gemm_counters_needed(_lib.GEMM_AR, M, N, comm.world))
+
+    def output(self, rank: Optional[int] = None) -> torch.Tensor:
+        """The [M, N] result buffer in registered memory (of ``rank`` in emulation)."""
+        if _emulated(self.comm):
+            return self.comm.view(self.c_off, (self.M, self.N), self.dtype, rank or 0)
+        return self.comm.view(self.c_off, (self.M, self.N), self.dtype)
+
+    def __call__(self, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+        if not self.fused:
+            return gemm(a, b, max_ctas=self.max_ctas)
+        a0, b0, sa, sb = _operands(self.comm, a, b)
+        _check_operands(a0, b0)
+        if a0.shape[0] != self.M or b0.shape[0] != self.N:
+            raise ValueError("operand shapes do not match this op")
+        args = _lib.GemmArgs()
+        args.mode = _lib.GEMM_AR
+        fill_gemm_args(args, a0, b0)
+        args.a_emu_stride, args.b_emu_stride = sa, sb
+        args.comm_ctas, args.max_ctas = self.comm_ctas, self.max_ctas
+        args.partial_reg, args.partial_off = 0, self.partial_off
+        args.c_reg, args.c_off = 0, self.c_off
+        args.counter_base = self.counter_base
+        _lib.check(_lib.lib().oob_gemm(self.comm._h, ctypes.byref(args), _stream()))
+        return self.output()
+
+
+class GemmReduceScatterNorm:
+    """``weight=None`` gives the plain GEMM->reduce-scatter (+ optional residual add)."""
+
+    def __init__(self, comm, M: int, N: int, dtype: torch.dtype, *, eps: float = 1e-6, comm_ctas: int = 16,
+                 max_ctas: int = 0):
+        if comm.world < 2:
+            raise ValueError("needs at least two ranks")
+        if M % comm.world or (M // comm.world) % TILE_M:
+            raise ValueError(f"M / world must be a multiple of {TILE_M}")
+        self.comm, self.M, self.N, self.dtype, self.eps = comm, M, N, dtype, eps
+        self.comm_ctas, self.max_ctas = comm_ctas, max_ctas
+        lib = _lib.lib()
+        self.partial_off = comm.alloc(int(lib.oob_gemm_partial_bytes(M, N)))
+        self.counter_base = comm.reserve_counters(lib.oob_gemm_counters_needed(_lib.GEMM_RS_NORM, M, N, comm.world))
+        self.rows = M // comm.world
+
+    def __call__(self, a: torch.Tensor, b: torch.Tensor, weight: Optional[torch.Tensor] = None,
+                 residual: Optional[torch.Tensor] = None, *, y: Optional[torch.Tensor] = None,
+                 residual_out: Optional[torch.Tensor] = None):
+        """Returns ``(y, residual_out)``; in emulation both are stacked ``[world, rows, N]``."""
+        a0, b0, sa, sb = _operands(self.comm, a, b)
+        _check_operands(a0, b0)
+        emu = _emulated(self.comm)
+        shape = (self.comm.world, self.rows, self.N) if emu else (self.rows, self.N)
+        if y is None:
+            y = torch.empty(shape, dtype=self.dtype, device=a.device)
+        if residual_out is None and residual is not None:
+            residual_out = torch.empty(shape, dtype=self.dtype, device=a.device)
+        args = _lib.GemmArgs()
+        args.mode = _lib.GEMM_RS_NORM
+        fill_gemm_args(args, a0, b0)
+        args.a_emu_stride, args.b_emu_stride = sa, sb
+        args.comm_ctas, args.max_ctas = self.comm_ctas, self.max_ctas
+        args.partial_reg, args.partial_off = 0, self.partial_off
+        args.counter_base = self.counter_base
+        args.residual = residual.data_ptr() if residual is not None else None
+        args.weight = weight.data_ptr() if weight is not None else None
+        args.eps = self.eps
+        args.y_local = y.data_ptr()
+        args.res_out_local = residual_out.data_ptr() if residual_out is not None else None
+        args.rs_emu_stride = self.rows * self.N * 2 if emu else 0
+        _lib.check(_lib.lib().oob_gemm(self.comm._h, ctypes.byref(args), _stream()))
+        return y, residual_out
+
+
+class AllGatherGemm:
+    def __init__(self, comm, M: int, K: int, dtype: torch.dtype, *, comm_ctas: int = 16, max_ctas: int = 0):
+        if comm.world < 2:
+            raise ValueError("needs at least two ranks")
+        if M % comm.world or (M // comm.world) % TILE_M:
+            raise ValueError(f"M / world must be a multiple of {TILE_M}")
+        self.comm, self.M, self.K, self.dtype = comm, M, K, dtype
+        self.comm_ctas, self.max_ctas = comm_ctas, max_ctas
+        self.a_full_off = comm.alloc(M * K * 2)
+        self.counter_base = comm.reserve_counters(_lib.lib().oob_gemm_counters_needed(_lib.GEMM_AG, M, 8, comm.world))
+
+    def gathered(self, rank: Optional[int] = None) -> torch.Tensor:
+        """The gathered A ([M, K]) as it landed in this rank's registered memory.  Rows of the rank's own
+        shard are only present there when the broadcast went through NVLS."""
+        if _emulated(self.comm):
+            return self.comm.view(self.a_full_off, (self.M, self.K), self.dtype, rank or 0)
+        return self.comm.view(self.a_full_off, (self.M, self.K), self.dtype)
+
+    def __call__(self, a_shard: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``a_shard``: [M / world, K]; ``b``: [N_local, K].  Returns C [M, N_local] (stacked in emulation)."""
+        a0, b0, sa, sb = _operands(self.comm, a_shard, b)
+        _check_operands(a0, b0)
+        emu = _emulated(self.comm)
+        N = b0.shape[0]
+        shape = (self.comm.world, self.M, N) if emu else (self.M, N)
+        if out is None:
+            out = torch.empty(shape, dtype=self.dtype, device=b.device)
+        args = _lib.GemmArgs()
+        args.mode = _lib.GEMM_AG
+        fill_gemm_args(args, a0, b0)
+        args.M = self.M  # logical problem: the gathered operand
+        args.C, args.ldc = out.data_ptr(), N
+        args.a_emu_stride, args.b_emu_stride = sa, sb
+        args.c_emu_stride = self.M * N * 2 if emu else 0
+        args.comm_ctas, args.max_ctas = self.comm_ctas, self.max_ctas
+        args.a_full_reg, args.a_full_off = 0, self.a_full_off
+        args.counter_base = self.counter_base
+        _lib.check(_lib.lib().oob_gemm(self.comm._h, ctypes.byref(args), _stream()))
+        return out
+
+
+def gemm_all_reduce_unfused(comm, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Our GEMM followed by our all-reduce as two kernels (comparison point for the fused op)."""
+    out = comm.empty((a.shape[0], b.shape[0]), a.dtype) if comm.world > 1 else None
+    c = gemm(a, b, out=out)
+    return comm.all_reduce(c) if comm.world > 1 else c
+
+
+__all__ = ["GemmAllReduce", "GemmReduceScatterNorm", "AllGatherGemm", "gemm_all_reduce_unfused", "partition"]

@@ -1,0 +1,60 @@
+"""Environment-variable configuration layer.
+
+Capability parity: the reference is configured through environment variables
+only (OOVERLAP_TUNING_POLICY, OOVERLAP_MAX_CTAS, ... in
+src/comm/tuning/tuning_policy.cpp:25-29 and the VLLM_OOVERLAP_* family in
+patches/vllm/v0.25.0/vllm/distributed/device_communicators/ooverlap_all_reduce.py:44-67).
+All names understood by this package are listed here.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+
+def _int(name: str, default: int) -> int:
+    v = os.environ.get(name)
+    if v is None or v == "":
+        return default
+    try:
+        return int(v)
+    except ValueError:
+        raise ValueError(f"{name} must be an integer, got {v!r}") from None
+
+
+def _flag(name: str, default: bool = False) -> bool:
+    v = os.environ.get(name)
+    if v is None:
+        return default
+    return v.strip().lower() not in ("", "0", "false", "no", "off")
+
+
+@dataclass
+class Config:
+    heap_bytes: int            # OOB_HEAP_BYTES: symmetric heap per rank
+    timeout_ms: int            # OOB_TIMEOUT_MS: budget of device waits and of the rendezvous
+    disable_nvls: bool         # OOB_DISABLE_NVLS
+    legacy_ipc: bool           # OOB_LEGACY_IPC: cudaIpc handles instead of VMM file descriptors
+    max_ctas: int              # OOB_MAX_CTAS: cap of the CTA budget chosen by the policy (0 = none)
+    tuning_policy: str         # OOB_TUNING_POLICY: JSON file
+    log_level: str             # OOB_LOG_LEVEL: error / warning / info / debug / trace
+    ar_slots: int              # OOB_AR_SLOTS, OOB_AR_SLOT_BYTES: round-robin all-reduce pool
+    ar_slot_bytes: int
+    ag_slots: int              # OOB_AG_SLOTS, OOB_AG_SLOT_BYTES: all-gather pool
+    ag_slot_bytes: int
+
+    @staticmethod
+    def from_env() -> "Config":
+        return Config(
+            heap_bytes=_int("OOB_HEAP_BYTES", 1 << 30),
+            timeout_ms=_int("OOB_TIMEOUT_MS", 10000),
+            disable_nvls=_flag("OOB_DISABLE_NVLS"),
+            legacy_ipc=_flag("OOB_LEGACY_IPC"),
+            max_ctas=_int("OOB_MAX_CTAS", 0),
+            tuning_policy=os.environ.get("OOB_TUNING_POLICY", ""),
+            log_level=os.environ.get("OOB_LOG_LEVEL", "warning"),
+            ar_slots=_int("OOB_AR_SLOTS", 8),
+            ar_slot_bytes=_int("OOB_AR_SLOT_BYTES", 8 << 20),
+            ag_slots=_int("OOB_AG_SLOTS", 4),
+            ag_slot_bytes=_int("OOB_AG_SLOT_BYTES", 64 << 20),
+        )

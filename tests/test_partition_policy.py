@@ -1,0 +1,94 @@
+import ctypes
+import json
+
+import pytest
+
+from ooverlap_b200 import _lib
+from ooverlap_b200.utils.partition import bus_bandwidth_gbs, max_shard, partition, partition_sizes
+
+
+@pytest.mark.parametrize("count", [0, 1, 7, 16, 4097, 1048576])
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8, 16])
+def test_partition_covers_everything(count, world):
+    sizes = partition_sizes(count, world)
+    assert sum(sizes) == count
+    assert max(sizes) - min(sizes) <= 1
+    assert sizes == sorted(sizes, reverse=True)  # the first `count % world` ranks get base + 1
+    assert max(sizes) == (max_shard(count, world) if count else 0)
+    prev = 0
+    for r in range(world):
+        b, e = partition(count, world, r)
+        assert b == prev
+        prev = e
+    assert prev == count
+
+
+def test_partition_rejects_bad_rank():
+    with pytest.raises(ValueError):
+        partition(10, 4, 4)
+
+
+def test_bus_bandwidth_definition():
+    # all-reduce: 2(n-1)/n * S / t ; reduce-scatter / all-gather: (n-1)/n * S / t
+    assert bus_bandwidth_gbs("all_reduce", 8, 1 << 30, 1.0) == pytest.approx(2 * 7 / 8 * (1 << 30) / 1e9)
+    assert bus_bandwidth_gbs("reduce_scatter", 4, 1000, 1e-6) == pytest.approx(0.75)
+    assert bus_bandwidth_gbs("all_gather", 2, 1000, 1e-6) == pytest.approx(0.5)
+
+
+def _select(lib, world, coll, nbytes, nvls):
+    algo, ctas = ctypes.c_int(), ctypes.c_int()
+    assert lib.oob_policy_select(world, coll, nbytes, nvls, ctypes.byref(algo), ctypes.byref(ctas)) == 0
+    return algo.value, ctas.value
+
+
+def test_policy_builtin_defaults(lib, monkeypatch):
+    monkeypatch.delenv("OOB_MAX_CTAS", raising=False)
+    assert lib.oob_policy_load(b"") == 0
+    algo, ctas = _select(lib, 8, 0, 16 << 10, 0)
+    assert algo == _lib.AR_ONESHOT_P2P and ctas >= 1
+    algo, _ = _select(lib, 8, 0, 64 << 20, 0)
+    assert algo == _lib.AR_TWOSHOT_P2P
+    algo, _ = _select(lib, 8, 0, 64 << 20, 1)
+    assert algo == _lib.AR_TWOSHOT_NVLS
+    assert _select(lib, 8, 1, 1 << 20, 1)[0] == _lib.RS_NVLS
+    assert _select(lib, 8, 2, 1 << 20, 0)[0] == _lib.AG_PUSH_P2P
+
+
+def test_policy_file_nearest_point_and_cap(lib, tmp_path, monkeypatch):
+    pts = {"comment": "ignored", "points": [
+        {"world": 8, "collective": "allreduce", "nvls": 0, "bytes": 1 << 20, "algo": 1, "ctas": 12},
+        {"world": 8, "collective": "allreduce", "nvls": 0, "bytes": 1 << 26, "algo": 1, "ctas": 40, "extra": [1, {"a": 2}]},
+        {"world": 8, "collective": "all_gather", "nvls": 1, "bytes": 1 << 20, "algo": 1, "ctas": 6},
+    ]}
+    path = tmp_path / "policy.json"
+    path.write_text(json.dumps(pts))
+    monkeypatch.delenv("OOB_MAX_CTAS", raising=False)
+    assert lib.oob_policy_load(str(path).encode()) == 0
+    assert _select(lib, 8, 0, 3 << 20, 0) == (1, 12)   # nearest in log-ratio: 1 MiB
+    assert _select(lib, 8, 0, 1 << 25, 0) == (1, 40)
+    assert _select(lib, 8, 2, 1 << 10, 1) == (1, 6)
+    # no point for this world size -> built-in
+    assert _select(lib, 4, 0, 1 << 10, 0)[0] == _lib.AR_ONESHOT_P2P
+    monkeypatch.setenv("OOB_MAX_CTAS", "5")
+    assert _select(lib, 8, 0, 1 << 25, 0) == (1, 5)
+    monkeypatch.delenv("OOB_MAX_CTAS")
+    assert lib.oob_policy_load(b"") == 0
+
+
+def test_policy_rejects_malformed(lib, tmp_path):
+    bad = tmp_path / "bad.json"
+    bad.write_text('{"points": [{"world": 8, "collective": "allreduce"}]}')
+    assert lib.oob_policy_load(str(bad).encode()) == _lib.ERR_INVALID
+    assert b"missing" in lib.oob_last_error()
+    bad.write_text('{"points": [')
+    assert lib.oob_policy_load(str(bad).encode()) == _lib.ERR_INVALID
+    assert lib.oob_policy_load(b"/nonexistent/policy.json") == _lib.ERR_INVALID
+    assert lib.oob_policy_load(b"") == 0
+
+
+def test_gemm_bookkeeping_helpers(lib):
+    assert lib.oob_gemm_partial_bytes(8192, 8192) == 64 * 32 * 128 * 256 * 2
+    assert lib.oob_gemm_partial_bytes(100, 100) == 128 * 256 * 2
+    assert lib.oob_gemm_counters_needed(_lib.GEMM_AR, 8192, 8192, 8) == 256
+    assert lib.oob_gemm_counters_needed(_lib.GEMM_RS_NORM, 4096, 8192, 8) == 8
+    assert lib.oob_gemm_counters_needed(_lib.GEMM_AG, 4096, 3584, 8) == 33
