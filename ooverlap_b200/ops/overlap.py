@@ -56,12 +56,13 @@ class GemmAllReduce:
             self.partial_off = comm.alloc(int(lib.oob_gemm_partial_bytes(M, N)))
             self.c_off = comm.alloc(M * N * 2)
             self.counter_base = comm.reserve_counters(lib.oob_gemm_counters_needed(_lib.GEMM_AR, M, N, comm.world))
+            self._out = None if _emulated(comm) else comm.view(self.c_off, (M, N), dtype)
 
     def output(self, rank: Optional[int] = None) -> torch.Tensor:
         """The [M, N] result buffer in registered memory (of ``rank`` in emulation)."""
         if _emulated(self.comm):
             return self.comm.view(self.c_off, (self.M, self.N), self.dtype, rank or 0)
-        return self.comm.view(self.c_off, (self.M, self.N), self.dtype)
+        return self._out
 
     def __call__(self, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         if not self.fused:

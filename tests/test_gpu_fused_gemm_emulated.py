@@ -1,0 +1,81 @@
+"""Fused GEMM + collective kernels with emulated ranks on one GPU (every rank = one block row of a single
+cooperative launch).  Oracle: PyTorch fp32 matmul and reductions."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _operands(world, M, N, K, dtype, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    a = torch.randn(world, M, K, device="cuda", generator=g).to(dtype)
+    b = (torch.randn(world, N, K, device="cuda", generator=g) / (K * world) ** 0.5).to(dtype)
+    return a, b
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("shape", [(256, 512, 256), (1024, 1024, 512), (200, 264, 72)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gemm_all_reduce(world, shape, dtype):
+    from ooverlap_b200 import EmulatedGroup
+    from ooverlap_b200.ops import GemmAllReduce
+    M, N, K = shape
+    g = EmulatedGroup(world, heap_bytes=64 << 20)
+    op = GemmAllReduce(g, M, N, dtype, comm_ctas=4)
+    a, b = _operands(world, M, N, K, dtype, seed=M + world)
+    want = sum(a[r].float() @ b[r].float().t() for r in range(world))
+    for it in range(3):  # repeated calls re-arm the tile counters
+        for r in range(world):
+            op.output(r).zero_()
+        op(a, b)
+        g.check_status()
+        for r in range(world):
+            got = op.output(r)
+            assert (got.float() - want).abs().max().item() <= 2e-2 * max(1.0, want.abs().max().item()), (it, r)
+            assert torch.equal(got, op.output(0))
+    g.close()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("with_norm", [True, False])
+def test_gemm_reduce_scatter_residual_rmsnorm(world, with_norm):
+    from ooverlap_b200 import EmulatedGroup
+    from ooverlap_b200.ops import GemmReduceScatterNorm
+    dtype, eps = torch.bfloat16, 1e-6
+    M, N, K = 128 * world * 2, 1024, 256
+    g = EmulatedGroup(world, heap_bytes=64 << 20)
+    op = GemmReduceScatterNorm(g, M, N, dtype, eps=eps, comm_ctas=3)
+    a, b = _operands(world, M, N, K, dtype, seed=7)
+    rows = M // world
+    residual = torch.randn(world, rows, N, device="cuda").to(dtype)
+    w = (1 + 0.02 * torch.randn(N, device="cuda")).to(dtype) if with_norm else None
+    s = sum(a[r].float() @ b[r].float().t() for r in range(world))
+    s = (s + residual.reshape(M, N).float()).to(dtype).float()
+    want = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + eps) * w.float() if with_norm else s
+    for it in range(2):
+        y, ro = op(a, b, w, residual)
+        g.check_status()
+        assert (ro.reshape(M, N).float() - s).abs().max().item() <= 3e-2 * max(1.0, s.abs().max().item())
+        assert (y.reshape(M, N).float() - want).abs().max().item() <= 6e-2 * max(1.0, want.abs().max().item())
+    g.close()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_all_gather_gemm(world):
+    from ooverlap_b200 import EmulatedGroup
+    from ooverlap_b200.ops import AllGatherGemm
+    dtype = torch.bfloat16
+    M, N, K = 128 * world * 2, 520, 320
+    g = EmulatedGroup(world, heap_bytes=64 << 20)
+    op = AllGatherGemm(g, M, K, dtype, comm_ctas=3)
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    a_full = torch.randn(M, K, device="cuda", generator=gen).to(dtype)
+    a_shards = a_full.view(world, M // world, K).contiguous()
+    b = (torch.randn(world, N, K, device="cuda", generator=gen) / K ** 0.5).to(dtype)  # each rank its own columns
+    for it in range(2):
+        out = op(a_shards, b)
+        g.check_status()
+        for r in range(world):
+            want = a_full.float() @ b[r].float().t()
+            assert (out[r].float() - want).abs().max().item() <= 2e-2 * max(1.0, want.abs().max().item()), (it, r)
+    g.close()

@@ -1,0 +1,76 @@
+"""tcgen05 GEMM against a plain PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b):
+    return a.float() @ b.float().t()
+
+
+def _check(M, N, K, dtype, lda_pad=0):
+    from ooverlap_b200.ops import gemm
+    g = torch.Generator(device="cuda").manual_seed(M * 131 + N * 17 + K)
+    a_full = torch.randn(M, K + lda_pad, device="cuda", generator=g).to(dtype)
+    a = a_full[:, :K]
+    b = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).to(dtype)
+    c = gemm(a, b)
+    torch.cuda.synchronize()
+    ref = _ref(a, b)
+    err = (c.float() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err <= 1e-2 * max(1.0, scale), (M, N, K, dtype, err, scale)
+    return c
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (128, 256, 512), (256, 512, 1024), (1024, 2048, 4096)])
+def test_exact_tiles(shape, dtype):
+    _check(*shape, dtype)
+
+
+@pytest.mark.parametrize("shape", [(1, 256, 64), (100, 200, 72), (129, 257 * 8, 8), (300, 1000, 1096), (5000, 264, 200)])
+def test_ragged_shapes(shape):
+    _check(*shape, torch.bfloat16)
+
+
+def test_padded_leading_dimension_and_out():
+    from ooverlap_b200.ops import gemm
+    _check(256, 512, 256, torch.bfloat16, lda_pad=64)
+    a = torch.randn(200, 128, device="cuda").bfloat16()
+    b = torch.randn(96, 128, device="cuda").bfloat16()
+    big = torch.zeros(200, 128, device="cuda", dtype=torch.bfloat16)
+    out = gemm(a, b, out=big[:, :96])
+    assert out.data_ptr() == big.data_ptr()
+    torch.cuda.synchronize()
+    assert (big[:, :96].float() - _ref(a, b)).abs().max().item() < 0.5
+    assert big[:, 96:].abs().max().item() == 0  # nothing written past N
+
+
+def test_many_tiles_per_cta_and_repeatability():
+    # 4096 x 4096 output = 512 tiles on 148 CTAs: exercises the TMEM double buffering and the smem ring wrap.
+    c1 = _check(4096, 4096, 1024, torch.bfloat16)
+    c2 = _check(4096, 4096, 1024, torch.bfloat16)
+    assert torch.equal(c1, c2)
+
+
+def test_cta_budget():
+    from ooverlap_b200.ops import gemm
+    a = torch.randn(1024, 512, device="cuda").bfloat16()
+    b = torch.randn(1024, 512, device="cuda").bfloat16()
+    c_full = gemm(a, b)
+    c_few = gemm(a, b, max_ctas=7)
+    torch.cuda.synchronize()
+    assert torch.equal(c_full, c_few)
+
+
+def test_rejects_bad_operands():
+    from ooverlap_b200 import OobError
+    from ooverlap_b200.ops import gemm
+    a = torch.randn(64, 60, device="cuda").bfloat16()  # K % 8 != 0
+    b = torch.randn(64, 60, device="cuda").bfloat16()
+    with pytest.raises(OobError):
+        gemm(a, b)
+    with pytest.raises(TypeError):
+        gemm(a.float(), b.float())
