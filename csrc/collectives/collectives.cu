@@ -68,7 +68,9 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(CommCtx ctx_param, 
 
   if constexpr (ALGO == 0 || ALGO == 3) {
     char* dst = out_local + out_local_emu_stride * blockIdx.y;
-    const Stripe s = block_stripe(0, packs);
+    // A destination that is not 16-byte aligned takes the element-wise path for everything.
+    const size_t vec_packs = (reinterpret_cast<uintptr_t>(dst) & 15) == 0 ? packs : 0;
+    const Stripe s = block_stripe(0, vec_packs);
     for (size_t p = s.begin + threadIdx.x; p < s.end; p += kThreads) {
       uint4 v;
       if constexpr (ALGO == 0)
@@ -77,10 +79,9 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(CommCtx ctx_param, 
         v = reduce_pack_mc<T, OP>(static_cast<const char*>(in.mc) + p * 16);
       ptx::st_v4(dst + p * 16, v);
     }
-    if (blockIdx.x == 0) {
-      for (size_t e = packs * E + threadIdx.x; e < count; e += kThreads)
-        st_elem<T>(dst + e * sizeof(T), reduce_scalar_p2p<T, OP>(in, e * sizeof(T), world));
-    }
+    for (size_t e = vec_packs * E + blockIdx.x * size_t(kThreads) + threadIdx.x; e < count;
+         e += size_t(gridDim.x) * kThreads)
+      st_elem<T>(dst + e * sizeof(T), reduce_scalar_p2p<T, OP>(in, e * sizeof(T), world));
   } else {
     // Shard r = packs [r*P/n, (r+1)*P/n); the sub-pack tail belongs to the last rank.
     const size_t p0 = packs * rank / world, p1 = packs * (rank + 1) / world;

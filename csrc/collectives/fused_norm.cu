@@ -94,14 +94,15 @@ __global__ void __launch_bounds__(kNormThreads) fused_norm_kernel(CommCtx ctx_pa
     for (int j = 0; j < PPT; ++j) {
       const int p = threadIdx.x + j * kNormThreads;
       if (p < packs_per_row) {
-        uint4 x;
-        if constexpr (!kComm)
-          x = *reinterpret_cast<const uint4*>(static_cast<const char*>(a.x.p[rank]) + off + size_t(p) * 16);
-        else if constexpr (kMc)
-          x = reduce_pack_mc<T, kSum>(static_cast<const char*>(a.x.mc) + off + size_t(p) * 16);
-        else
-          x = reduce_pack_p2p<T, kSum, NR>(a.x, off + size_t(p) * 16, world);
-        PT::unpack(x, v[j]);
+        if constexpr (!kComm) {
+          PT::unpack(*reinterpret_cast<const uint4*>(static_cast<const char*>(a.x.p[rank]) + off + size_t(p) * 16),
+                     v[j]);
+        } else if constexpr (kMc) {
+          PT::unpack(reduce_pack_mc<T, kSum>(static_cast<const char*>(a.x.mc) + off + size_t(p) * 16), v[j]);
+        } else {
+          // fp32 sum stays in registers: one rounding, after the residual add.
+          reduce_pack_p2p_f32<T, kSum, NR>(a.x, off + size_t(p) * 16, world, v[j]);
+        }
         if (res != nullptr) {
           const uint4 rv = ptx::ld_nc_v4(res + loff + size_t(p) * 16);
           float rf[E];

@@ -92,10 +92,10 @@ __device__ __forceinline__ float combine(float a, float b) {
 // loads.  NR > 0 fixes the world size at compile time so that all loads are in
 // flight together; NR == 0 is the generic loop.
 template <typename T, int OP, int NR>
-__device__ __forceinline__ uint4 reduce_pack_p2p(const PeerPtrs& in, size_t off, int world) {
+__device__ __forceinline__ void reduce_pack_p2p_f32(const PeerPtrs& in, size_t off, int world,
+                                                    float (&acc)[PackTraits<T>::kElems]) {
   using PT = PackTraits<T>;
   constexpr int E = PT::kElems;
-  float acc[E];
   if constexpr (NR > 0) {
     uint4 v[NR];
 #pragma unroll
@@ -119,7 +119,13 @@ __device__ __forceinline__ uint4 reduce_pack_p2p(const PeerPtrs& in, size_t off,
       for (int i = 0; i < E; ++i) acc[i] = combine<OP>(acc[i], f[i]);
     }
   }
-  return PT::pack(acc);
+}
+
+template <typename T, int OP, int NR>
+__device__ __forceinline__ uint4 reduce_pack_p2p(const PeerPtrs& in, size_t off, int world) {
+  float acc[PackTraits<T>::kElems];
+  reduce_pack_p2p_f32<T, OP, NR>(in, off, world, acc);
+  return PackTraits<T>::pack(acc);
 }
 
 // Same reduction done inside the NVSwitch.  fp32 min/max have no multimem

@@ -257,12 +257,10 @@ __device__ void rs_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
           const int n_blk = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
           const size_t off =
               size_t(m_blk * sc.tiles_n + n_blk) * kTileBytes + size_t(r_in) * (kTileN * 2) + size_t(cp) * 16;
-          uint4 x;
           if (use_mc)
-            x = reduce_pack_mc<T, kSum>(static_cast<const char*>(a.partial.mc) + off);
+            PT::unpack(reduce_pack_mc<T, kSum>(static_cast<const char*>(a.partial.mc) + off), v[q]);
           else
-            x = reduce_pack_p2p<T, kSum, 0>(a.partial, off, world);
-          PT::unpack(x, v[q]);
+            reduce_pack_p2p_f32<T, kSum, 0>(a.partial, off, world, v[q]);
           if (res != nullptr) {
             const uint4 rv = ptx::ld_nc_v4(res + lrow_off + size_t(p) * 16);
             float rf[8];

@@ -768,8 +768,8 @@ int oob_allreduce(oob_comm* c, int dtype, int op, int algo, int in_reg, uint64_t
   } else if (!c->peer_ptrs(out_reg, out_off, &out)) {
     return set_error(OOB_ERR_INVALID, "two-shot all-reduce needs a registered output buffer");
   }
-  if ((in_off & 15) || (!one_shot && (out_off & 15)) || (one_shot && (reinterpret_cast<uintptr_t>(out_local) & 15)))
-    return set_error(OOB_ERR_INVALID, "all-reduce buffers must be 16-byte aligned");
+  if ((in_off & 15) || (!one_shot && (out_off & 15)))
+    return set_error(OOB_ERR_INVALID, "registered all-reduce buffers must be 16-byte aligned");
   const uint64_t emu_stride = c->emulated ? count * esize : 0;
   cudaError_t e = launch_allreduce(c->make_ctx(), dtype, op, algo, in, out, out_local, emu_stride, count, max_ctas,
                                    static_cast<cudaStream_t>(stream));

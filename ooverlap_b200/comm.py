@@ -120,6 +120,8 @@ class Communicator:
         self.nvls = bool(info.nvls)
         self.heap_bytes = int(info.heap_bytes)
         self._heap_base = int(lib.oob_heap_ptr(self._h, self.rank, 0))
+        # Allocated on EVERY rank up front: heap offsets stay identical only if all ranks allocate alike.
+        self._dummy_off = self.alloc(1024)
         logger.info("rank %d/%d on cuda:%d: heap %d MiB, memory kind %d, NVLS %s", self.rank, self.world, self.device,
                     self.heap_bytes >> 20, info.memory_kind, self.nvls)
 
@@ -238,7 +240,12 @@ class Communicator:
             _lib.check(_lib.lib().oob_comm_status(self._h, None))
 
     def recover(self) -> None:
+        """Collective: clears flags and status on every rank after a device timeout."""
         _lib.check(_lib.lib().oob_comm_recover(self._h))
+
+    def set_timeout_ms(self, ms: int) -> None:
+        """Budget of every device-side wait of this communicator."""
+        _lib.check(_lib.lib().oob_comm_set_timeout_ms(self._h, int(ms)))
 
     # ------------------------------------------------------------- scratch
     def _scratch_for(self, key, nbytes: int) -> int:
@@ -340,7 +347,7 @@ class Communicator:
                                                      ctypes.c_void_p(_current_stream_ptr())))
         else:
             # Nothing owned (more ranks than elements): still take part in the barriers.
-            dummy = self._scratch_for(("rs_dummy",), 16)
+            dummy = self._dummy_off
             _lib.check(_lib.lib().oob_reduce_scatter(self._h, dtype_code(x.dtype), op_code(op), algo, loc[0], loc[1],
                                                      ctypes.c_void_p(self._heap_base + dummy), x.numel(),
                                                      max_ctas or self.config.max_ctas,

@@ -29,7 +29,7 @@ def test_local_rmsnorm(shape, dtype):
     y2, r2 = rmsnorm(x, w, 1e-6, res)
     want2, s2 = _oracle([x], res, w, 1e-6, dtype)
     assert (y2.float() - want2).abs().max().item() <= 3e-2
-    assert (r2.float() - s2).abs().max().item() <= 1e-2 * 4
+    assert ((r2.float() - s2).abs() <= 1e-2 + s2.abs() * 2 ** -7).all()
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
@@ -65,7 +65,7 @@ def test_allreduce_residual_rmsnorm(world, algo, rows):
         rs = [g.view(r_off, (rows, hidden), dtype, r) for r in range(world)]
     for r in range(world):
         assert (ys[r].float() - want_y).abs().max().item() <= 5e-2, (r, algo)
-        assert (rs[r].float() - want_s).abs().max().item() <= 1e-2 * world
+        assert ((rs[r].float() - want_s).abs() <= 1e-2 + want_s.abs() * 2 ** -7).all()  # one bf16 ulp of slack
         assert torch.equal(ys[r], ys[0])
     g.close()
 
@@ -98,5 +98,5 @@ def test_reduce_scatter_residual_rmsnorm(world):
     for r in range(world):
         b, e = partition(rows, world, r)
         assert (y[r, : e - b].float() - want_y[b:e]).abs().max().item() <= 5e-2
-        assert (ro[r, : e - b].float() - want_s[b:e]).abs().max().item() <= 1e-2 * world
+        assert ((ro[r, : e - b].float() - want_s[b:e]).abs() <= 1e-2 + want_s[b:e].abs() * 2 ** -7).all()
     g.close()

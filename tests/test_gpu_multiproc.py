@@ -1,0 +1,252 @@
+"""One process per GPU with the real ``Communicator`` (symmetric heap over VMM file descriptors, NVLS multicast
+where the driver grants it).  Needs at least two GPUs; skipped otherwise.  Oracle: PyTorch fp32 on the host."""
+import uuid
+
+import pytest
+import torch
+
+from mp_util import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _world():
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    return min(n, 8)
+
+
+needs_multi = pytest.mark.skipif(_world() < 2, reason="needs at least 2 GPUs")
+
+
+def _inputs(world, n, dtype, seed):
+    return [(torch.rand(n, generator=torch.Generator().manual_seed(seed * 31 + r)) * 2 - 1).to(dtype)
+            for r in range(world)]
+
+
+def _rank_collectives(rank, world, key, flags_env):
+    import os
+    os.environ.update(flags_env)
+    from ooverlap_b200 import Communicator, _lib
+    from ooverlap_b200.utils.partition import partition
+    torch.cuda.set_device(rank)
+    comm = Communicator(list(range(world)), rank, key, heap_bytes=256 << 20)
+    report = {"nvls": comm.nvls, "memory_kind": comm.info.memory_kind, "checks": []}
+
+    def check(name, got, want, tol):
+        err = (got.float().cpu() - want.float()).abs().max().item() if want.numel() else 0.0
+        report["checks"].append((name, err, tol))
+
+    ar_algos = [_lib.AR_TWOSHOT_P2P] + ([_lib.AR_TWOSHOT_NVLS] if comm.nvls else [])
+    os_algos = [_lib.AR_ONESHOT_P2P] + ([_lib.AR_ONESHOT_NVLS] if comm.nvls else [])
+    for dtype, tol in ((torch.bfloat16, 1e-2 * world), (torch.float16, 1e-2 * world), (torch.float32, 1e-5 * world)):
+        for n in (1, 7, 4097, (1 << 20) + 8):
+            xs = _inputs(world, n, dtype, n)
+            want = torch.stack([x.float() for x in xs]).sum(0)
+            buf = comm.empty((n,), dtype)
+            for algo in ar_algos:
+                buf.copy_(xs[rank].cuda())
+                comm.all_reduce(buf, algo=algo)
+                check(f"ar_inplace algo{algo} {dtype} {n}", buf, want, tol)
+            for algo in os_algos:
+                buf.copy_(xs[rank].cuda())
+                out = torch.empty(n, dtype=dtype, device="cuda")
+                comm.all_reduce_out(buf, out, algo=algo)
+                check(f"ar_oneshot algo{algo} {dtype} {n}", out, want, tol)
+            # policy-selected, unregistered input (copied into the cached scratch)
+            got = comm.all_reduce(xs[rank].cuda())
+            check(f"ar_auto {dtype} {n}", got, want, tol)
+            # reduce-scatter: in place and into a separate tensor, both algorithms
+            b, e = partition(n, world, rank)
+            for algo in [_lib.RS_P2P] + ([_lib.RS_NVLS] if comm.nvls else []):
+                buf.copy_(xs[rank].cuda())
+                got = comm.reduce_scatter(buf, algo=algo)
+                check(f"rs algo{algo} {dtype} {n}", got, want[b:e], tol)
+            out = torch.empty(e - b, dtype=dtype, device="cuda")
+            comm.reduce_scatter(xs[rank].cuda(), out=out)
+            check(f"rs_out {dtype} {n}", out, want[b:e], tol)
+            # all-gather (uneven shards)
+            full = torch.cat([xs[r][slice(*partition(n, world, r))] for r in range(world)])
+            for algo in [_lib.AG_PUSH_P2P] + ([_lib.AG_PUSH_NVLS] if comm.nvls else []):
+                got = comm.all_gather(xs[rank][b:e].cuda(), total=n, algo=algo)
+                check(f"ag algo{algo} {dtype} {n}", got, full, 0.0)
+            torch.cuda.synchronize()
+            comm.check_status()
+    # min / max
+    x = torch.tensor([float(rank), -float(rank), 0.5], device="cuda")
+    check("max", comm.all_reduce(x.clone(), "max"), torch.tensor([world - 1.0, 0.0, 0.5]), 0.0)
+    check("min", comm.all_reduce(x.clone(), "min"), torch.tensor([0.0, 1.0 - world, 0.5]), 0.0)
+    # slot pools: zero-copy producer -> all-reduce, ring wraps
+    comm.init_round_robin_slots(torch.bfloat16, 1 << 20, 3)
+    for it in range(5):
+        slot = comm.acquire_all_reduce_slot((64, 128))
+        slot.fill_(float(rank + it))
+        got = comm.all_reduce_preloaded_slot(slot)
+        check(f"slot {it}", got, torch.full((64, 128), float(sum(r + it for r in range(world)))), 1e-2 * world)
+    got = comm.all_reduce_round_robin(torch.full((10,), 2.0, dtype=torch.bfloat16, device="cuda"))
+    check("rr", got, torch.full((10,), 2.0 * world), 1e-2)
+    comm.init_all_gather_slots(torch.bfloat16, 1 << 20, 2)
+    got = comm.all_gather_round_robin(torch.full((4, 8), float(rank), dtype=torch.bfloat16, device="cuda"))
+    check("ag_rr", got, torch.arange(world).float().repeat_interleave(4).unsqueeze(1).expand(-1, 8), 0.0)
+    # torch-allocated tensor registered through legacy IPC (base + offset inside the caching allocator's block)
+    try:
+        big = torch.zeros(1 << 16, device="cuda")
+        view = big[1000:1000 + 4096]
+        view.fill_(rank + 1.0)
+        comm.all_reduce_inplace(view)
+        check("ipc_inplace", view, torch.full((4096,), float(sum(r + 1 for r in range(world)))), 1e-5 * world)
+        report["ipc"] = "ok"
+    except _lib.OobError as e:  # e.g. expandable segments: reported, not fatal
+        report["ipc"] = f"unsupported: {e}"
+    torch.cuda.synchronize()
+    comm.check_status()
+    comm.barrier()
+    comm.close()
+    return report
+
+
+@needs_multi
+@pytest.mark.parametrize("nvls", [True, False])
+def test_collectives_all_algorithms(nvls):
+    world = _world()
+    env = {} if nvls else {"OOB_DISABLE_NVLS": "1"}
+    res = run_ranks(_rank_collectives, world, ("mp_" + uuid.uuid4().hex[:10], env), timeout=600)
+    assert len(res) == world, res
+    for r in range(world):
+        kind, val = res[r]
+        assert kind == "ok", val
+        if not nvls:
+            assert not val["nvls"]
+        bad = [(n, e, t) for n, e, t in val["checks"] if not e <= t]
+        assert not bad, bad[:10]
+    print("nvls:", res[0][1]["nvls"], "memory kind:", res[0][1]["memory_kind"], "ipc:", res[0][1].get("ipc"))
+
+
+def _rank_fused(rank, world, key):
+    from ooverlap_b200 import Communicator
+    from ooverlap_b200.ops import (AllGatherGemm, GemmAllReduce, GemmReduceScatterNorm, fused_allreduce_rmsnorm,
+                                   fused_reduce_scatter_rmsnorm)
+    torch.cuda.set_device(rank)
+    comm = Communicator(list(range(world)), rank, key, heap_bytes=512 << 20)
+    dt = torch.bfloat16
+    out = []
+
+    def gen(shape, seed, scale=1.0):
+        return (torch.randn(shape, generator=torch.Generator().manual_seed(seed)) * scale).to(dt)
+
+    # fused all-reduce + residual + RMSNorm (one-shot for few tokens, two-shot for many)
+    hidden, eps = 4096, 1e-6
+    w = (1 + 0.02 * torch.randn(hidden, generator=torch.Generator().manual_seed(5))).to(dt)
+    for rows in (4, 512):
+        xs = [gen((rows, hidden), 100 + r) for r in range(world)]
+        res = gen((rows, hidden), 99)
+        x = comm.empty((rows, hidden), dt)
+        x.copy_(xs[rank].cuda())
+        y, ro = fused_allreduce_rmsnorm(comm, x, w.cuda(), eps, res.cuda())
+        s = (torch.stack([t.float() for t in xs]).sum(0) + res.float()).to(dt).float()
+        want = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+        out.append((f"ar_norm {rows}", (y.float().cpu() - want).abs().max().item(), 6e-2))
+        # through NVLS the switch rounds the sum once before the residual is added: two roundings
+        out.append((f"ar_norm_res {rows}", ((ro.float().cpu() - s).abs() - s.abs() * 2 ** -6).max().item(), 1e-2))
+        # sequence-parallel form
+        b, e = rows * rank // world, rows * (rank + 1) // world
+        if rows % world == 0:
+            x.copy_(xs[rank].cuda())
+            y2, _ = fused_reduce_scatter_rmsnorm(comm, x, w.cuda(), eps, res[b:e].cuda())
+            out.append((f"rs_norm {rows}", (y2.float().cpu() - want[b:e]).abs().max().item(), 6e-2))
+    # fused GEMM ops
+    M, N, K = 128 * world * 2, 1024, 512
+    a = [gen((M, K), 200 + r) for r in range(world)]
+    bw = [gen((N, K), 300 + r, (K * world) ** -0.5) for r in range(world)]
+    want = sum(a[r].float() @ bw[r].float().t() for r in range(world))
+    op = GemmAllReduce(comm, M, N, dt, comm_ctas=8)
+    for it in range(3):
+        c = op(a[rank].cuda(), bw[rank].cuda())
+        torch.cuda.synchronize()
+        out.append((f"gemm_ar {it}", (c.float().cpu() - want).abs().max().item(), 3e-2 * max(1, want.abs().max().item())))
+    rs = GemmReduceScatterNorm(comm, M, N, dt, eps=eps, comm_ctas=8)
+    wn = (1 + 0.02 * torch.randn(N, generator=torch.Generator().manual_seed(6))).to(dt)
+    res = gen((M, N), 400)
+    rows = M // world
+    s = (want + res.float()).to(dt).float()
+    wanty = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + eps) * wn.float()
+    for it in range(2):
+        y, ro = rs(a[rank].cuda(), bw[rank].cuda(), wn.cuda(), res[rank * rows:(rank + 1) * rows].cuda())
+        torch.cuda.synchronize()
+        out.append((f"gemm_rs_norm {it}", (y.float().cpu() - wanty[rank * rows:(rank + 1) * rows]).abs().max().item(), 8e-2))
+    ag = AllGatherGemm(comm, M, K, dt, comm_ctas=8)
+    a_full = gen((M, K), 500)
+    for it in range(2):
+        c = ag(a_full[rank * rows:(rank + 1) * rows].cuda(), bw[rank].cuda())
+        torch.cuda.synchronize()
+        wantc = a_full.float() @ bw[rank].float().t()
+        out.append((f"ag_gemm {it}", (c.float().cpu() - wantc).abs().max().item(), 3e-2 * max(1, wantc.abs().max().item())))
+    comm.check_status()
+    comm.barrier()
+    nv = comm.nvls
+    comm.close()
+    return nv, out
+
+
+@needs_multi
+def test_fused_ops_across_gpus():
+    world = _world()
+    res = run_ranks(_rank_fused, world, ("mf_" + uuid.uuid4().hex[:10],), timeout=600)
+    assert len(res) == world, res
+    for r in range(world):
+        kind, val = res[r]
+        assert kind == "ok", val
+        bad = [(n, e, t) for n, e, t in val[1] if not e <= t]
+        assert not bad, bad
+
+
+def _rank_absent_peer(rank, world, key):
+    """Failure detection without faulting a GPU: the last rank sits out one collective (it is between steps,
+    nothing of its own in flight).  The others' kernels give up after the wait budget, return, and the host
+    reads who was missing; after a collective recover() the group works again.  NVLS is off here."""
+    import os
+    os.environ["OOB_DISABLE_NVLS"] = "1"
+    from ooverlap_b200 import Communicator, DeviceTimeout, _lib
+    torch.cuda.set_device(rank)
+    comm = Communicator(list(range(world)), rank, key, heap_bytes=64 << 20)
+    buf = comm.empty((1024,), torch.float32)
+    buf.fill_(1.0)
+    comm.all_reduce(buf, algo=_lib.AR_TWOSHOT_P2P)  # generous default budget: first launches load the kernels
+    torch.cuda.synchronize()
+    comm.check_status()
+    ok_before = buf[0].item() == world
+    comm.set_timeout_ms(500)
+    comm.barrier()
+    detected = None
+    if rank != world - 1:
+        buf.fill_(1.0)
+        comm.all_reduce(buf, algo=_lib.AR_TWOSHOT_P2P)  # the last rank never joins this one
+        torch.cuda.synchronize()  # returns: the kernel's wait is bounded
+        try:
+            comm.check_status()
+        except DeviceTimeout as e:
+            detected = str(e)
+    comm.recover()  # collective, host side
+    comm.set_timeout_ms(10000)
+    comm.barrier()
+    buf.fill_(2.0)
+    comm.all_reduce(buf, algo=_lib.AR_TWOSHOT_P2P)
+    torch.cuda.synchronize()
+    comm.check_status()
+    ok_after = buf[0].item() == 2.0 * world
+    comm.barrier()
+    comm.close()
+    return ok_before, detected, ok_after
+
+
+@needs_multi
+def test_absent_peer_is_detected_and_recovered():
+    world = min(_world(), 4)
+    res = run_ranks(_rank_absent_peer, world, ("ma_" + uuid.uuid4().hex[:10],), timeout=300)
+    assert len(res) == world, res
+    for r in range(world):
+        kind, val = res[r]
+        assert kind == "ok", val
+        ok_before, detected, ok_after = val
+        assert ok_before and ok_after
+        if r != world - 1:
+            assert detected is not None and f"peer {world - 1}" in detected
