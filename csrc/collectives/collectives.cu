@@ -27,6 +27,11 @@ namespace {
 
 constexpr int kThreads = 512;
 
+// Packs per thread and loop iteration.  A P2P reduction of NR ranks holds NR loads per pack in registers, so
+// wide worlds unroll less; multimem loads (one per pack) unroll most.
+template <int NR, bool MC>
+constexpr int kUnroll = MC ? 8 : (NR == 0 ? 1 : (NR >= 8 ? 2 : 4));
+
 struct Stripe {
   size_t begin, end;  // pack indices handled by this block
 };
@@ -71,13 +76,24 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(CommCtx ctx_param, 
     // A destination that is not 16-byte aligned takes the element-wise path for everything.
     const size_t vec_packs = (reinterpret_cast<uintptr_t>(dst) & 15) == 0 ? packs : 0;
     const Stripe s = block_stripe(0, vec_packs);
-    for (size_t p = s.begin + threadIdx.x; p < s.end; p += kThreads) {
-      uint4 v;
-      if constexpr (ALGO == 0)
-        v = reduce_pack_p2p<T, OP, NR>(in, p * 16, world);
-      else
-        v = reduce_pack_mc<T, OP>(static_cast<const char*>(in.mc) + p * 16);
-      ptx::st_v4(dst + p * 16, v);
+    constexpr int U = kUnroll<NR, ALGO == 3>;
+    for (size_t pb = s.begin + threadIdx.x; pb < s.end; pb += size_t(kThreads) * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t p = pb + size_t(u) * kThreads;
+        if (p < s.end) {
+          if constexpr (ALGO == 0)
+            v[u] = reduce_pack_p2p<T, OP, NR>(in, p * 16, world);
+          else
+            v[u] = reduce_pack_mc<T, OP>(static_cast<const char*>(in.mc) + p * 16);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t p = pb + size_t(u) * kThreads;
+        if (p < s.end) ptx::st_v4(dst + p * 16, v[u]);
+      }
     }
     for (size_t e = vec_packs * E + blockIdx.x * size_t(kThreads) + threadIdx.x; e < count;
          e += size_t(gridDim.x) * kThreads)
@@ -86,18 +102,37 @@ __global__ void __launch_bounds__(kThreads) allreduce_kernel(CommCtx ctx_param, 
     // Shard r = packs [r*P/n, (r+1)*P/n); the sub-pack tail belongs to the last rank.
     const size_t p0 = packs * rank / world, p1 = packs * (rank + 1) / world;
     const Stripe s = block_stripe(p0, p1);
-    for (size_t p = s.begin + threadIdx.x; p < s.end; p += kThreads) {
-      if constexpr (ALGO == 1) {
-        const uint4 v = reduce_pack_p2p<T, OP, NR>(in, p * 16, world);
-        if constexpr (NR > 0) {
+    // U packs per thread and iteration: all their remote loads are issued before the first store, which is
+    // what keeps enough bytes in flight to cover the NVLink round trip.
+    constexpr int U = kUnroll<NR, ALGO == 2>;
+    for (size_t pb = s.begin + threadIdx.x; pb < s.end; pb += size_t(kThreads) * U) {
+      uint4 v[U];
 #pragma unroll
-          for (int r = 0; r < NR; ++r) ptx::st_v4(static_cast<char*>(out.p[(rank + r) % NR]) + p * 16, v);
-        } else {
-          for (int r = 0; r < world; ++r) ptx::st_v4(static_cast<char*>(out.p[(rank + r) % world]) + p * 16, v);
+      for (int u = 0; u < U; ++u) {
+        const size_t p = pb + size_t(u) * kThreads;
+        if (p < s.end) {
+          if constexpr (ALGO == 1)
+            v[u] = reduce_pack_p2p<T, OP, NR>(in, p * 16, world);
+          else
+            v[u] = reduce_pack_mc<T, OP>(static_cast<const char*>(in.mc) + p * 16);
         }
-      } else {
-        const uint4 v = reduce_pack_mc<T, OP>(static_cast<const char*>(in.mc) + p * 16);
-        ptx::multimem_st_v4(static_cast<char*>(out.mc) + p * 16, v);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t p = pb + size_t(u) * kThreads;
+        if (p < s.end) {
+          if constexpr (ALGO == 1) {
+            if constexpr (NR > 0) {
+#pragma unroll
+              for (int r = 0; r < NR; ++r) ptx::st_v4(static_cast<char*>(out.p[(rank + r) % NR]) + p * 16, v[u]);
+            } else {
+              for (int r = 0; r < world; ++r)
+                ptx::st_v4(static_cast<char*>(out.p[(rank + r) % world]) + p * 16, v[u]);
+            }
+          } else {
+            ptx::multimem_st_v4(static_cast<char*>(out.mc) + p * 16, v[u]);
+          }
+        }
       }
     }
     if (rank == world - 1 && blockIdx.x == 0) {
@@ -139,13 +174,24 @@ __global__ void __launch_bounds__(kThreads) reduce_scatter_kernel(CommCtx ctx_pa
   const RangeSplit<T> sp(e0, vec_ok ? e1 : e0);
   if (vec_ok) {
     const Stripe s = block_stripe(sp.head_end / E, sp.body_end / E);
-    for (size_t p = s.begin + threadIdx.x; p < s.end; p += kThreads) {
-      uint4 v;
-      if constexpr (ALGO == 0)
-        v = reduce_pack_p2p<T, OP, NR>(in, p * 16, world);
-      else
-        v = reduce_pack_mc<T, OP>(static_cast<const char*>(in.mc) + p * 16);
-      ptx::st_v4(dst + (p * E - e0) * sizeof(T), v);
+    constexpr int U = kUnroll<NR, ALGO == 1>;
+    for (size_t pb = s.begin + threadIdx.x; pb < s.end; pb += size_t(kThreads) * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t p = pb + size_t(u) * kThreads;
+        if (p < s.end) {
+          if constexpr (ALGO == 0)
+            v[u] = reduce_pack_p2p<T, OP, NR>(in, p * 16, world);
+          else
+            v[u] = reduce_pack_mc<T, OP>(static_cast<const char*>(in.mc) + p * 16);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t p = pb + size_t(u) * kThreads;
+        if (p < s.end) ptx::st_v4(dst + (p * E - e0) * sizeof(T), v[u]);
+      }
     }
   }
   // Scalar head and tail (or everything, when the alignments disagree).

@@ -1,614 +1,16 @@
-// tcgen05 / TMEM GEMM for sm_100a with communication fused into the same
-// persistent kernel.
-//
-// Mainloop (all modes): one CTA per SM, 128x256 output tiles, K blocks of 64.
-//   warp 0   TMA producer: cp.async.bulk.tensor (this GPU's memory, 128-byte swizzle) into a 4-stage ring
-//   warp 1   MMA issuer: one thread issues tcgen05.mma (M128 N256 K16, fp32 accumulate in TMEM),
-//            tcgen05.commit releases the smem stage / publishes the accumulator
-//   warps 2-5 epilogue: tcgen05.ld the accumulator (two TMEM stages, so the next tile's mainloop overlaps), convert, store
-// Fused modes add a second role on `comm_ctas` CTAs of the same launch:
-//   GEMM->AR      epilogue writes the partial tile to a registered buffer and bumps an arrival counter on the tile's
-//                 owner rank; owner-side reducer CTAs pull the tile from all ranks (multimem.ld_reduce in the switch, or
-//                 P2P loads, fp32 accumulate) and broadcast the sum into every rank's C (multimem.st / P2P stores)
-//                 while later tiles still compute.
-//   GEMM->RS+norm counters are per 128-row block on the rank that owns the rows; reducers sum the rows, add the
-//                 residual, apply RMSNorm and write the rank's rows.
-//   AG->GEMM      pusher CTAs broadcast this rank's A shard chunk by chunk into every rank's gathered buffer and bump
-//                 per-chunk flags; the TMA producer waits for the flag of the chunk it is about to load from LOCAL memory.
-// All cross-GPU traffic is plain ld/st/red or multimem.*; TMA only ever touches local memory.
-//
-// Capability parity with the reference: signalling GEMM + reorder epilogue + wait kernel + per-segment all-reduce
-// (src/gemm/gemm_with_signal_sm90.h:102-513, src/epilogue/reorder_epilogue.h:324-595, src/wait.cuh:5-9,
-// src/overlap_impl.cu:450-706), row remap for reduce-scatter (src/gemm/scatter_row_remap_sm90.cuh:35-82) and the
-// plain GEMM (src/gemm/gemm_plain_sm90.cu).  The reorder tables / segment search are replaced by a deterministic
-// tile order plus arrival counters; accumulation is fp32 (the reference accumulates in fp16,
-// src/gemm/gemm_signal_sm90.cu:108).
-#include <cuda.h>
-#include <cuda_runtime.h>
+// Host entry of the tcgen05 GEMM family: argument checks, tensor-map cache, the library-owned split-K
+// workspace, and dispatch to the kernels of gemm_kernel.cuh.
 #include <mutex>
 #include <unordered_map>
-#include "../device/reduce.cuh"
-#include "../device/sync.cuh"
+
 #include "../runtime/driver_api.h"
-#include "gemm.h"
+#include "gemm_kernel.cuh"
 
 namespace oob {
 namespace {
 
-constexpr int kStages = 4;
-constexpr int kABytes = kTileM * kTileK * 2;  // 16 KiB
-constexpr int kBBytes = kTileN * kTileK * 2;  // 32 KiB
-constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kAccStages = 2;
-constexpr int kTmemCols = 512;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr int kThreadsPlain = 192;
-constexpr int kThreadsFused = 384;
-constexpr int kPacksPerTile = kTileBytes / 16;  // 4096
-constexpr int kPacksPerTileRow = kTileN / 8;    // 32
+using namespace gemm_detail;
 
-struct SmemCtl {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
-  uint64_t tmem_full[kAccStages];
-  uint64_t tmem_empty[kAccStages];
-  uint32_t tmem_base;
-  int abort;
-  uint32_t epi_count[kAccStages];  // epilogue warps that have stored their rows of the tile in this TMEM stage
-};
-
-struct Sched {
-  int tiles_m, tiles_n, tiles;
-  int mode, world, rank;
-  int bps;  // 128-row blocks per rank shard (RS / AG)
-  // Logical tile (m_blk, n_blk) of schedule position `seq`.  Every rank walks
-  // the same sequence so that arrival counters fill at about the same time.
-  __device__ void coord(int seq, int& m_blk, int& n_blk) const {
-    if (mode == kGemmRsNorm) {
-      // Row-block major; consecutive row blocks belong to consecutive owners.
-      const int i = seq / tiles_n;
-      n_blk = seq % tiles_n;
-      m_blk = (i % world) * bps + i / world;
-    } else if (mode == kGemmAg) {
-      // Own shard first (it is local), then chunk c of every other rank in ring order.
-      const int i = seq / tiles_n;
-      n_blk = seq % tiles_n;
-      if (i < bps) {
-        m_blk = rank * bps + i;
-      } else {
-        const int k = i - bps;
-        const int c = k / (world - 1);
-        const int s = (rank + 1 + k % (world - 1)) % world;
-        m_blk = s * bps + c;
-      }
-    } else {
-      // Grouped raster: 16 tile rows at a time so that concurrently running
-      // CTAs share A and B tiles in L2.
-      constexpr int kGroup = 16;
-      const int per_group = kGroup * tiles_n;
-      const int g = seq / per_group;
-      const int first_m = g * kGroup;
-      const int rows = (tiles_m - first_m) < kGroup ? (tiles_m - first_m) : kGroup;
-      const int in = seq - g * per_group;
-      m_blk = first_m + in % rows;
-      n_blk = in / rows;
-    }
-  }
-};
-
-__device__ __forceinline__ void gemm_report(DeviceStatus* s, int rank, int code, int where) {
-  if (s == nullptr) return;
-  if (atomicCAS(&s->code, 0, code) == 0) {
-    s->rank = rank;
-    s->peer = -1;
-    s->block = static_cast<int>(blockIdx.x);
-    s->where = where;
-    __threadfence_system();
-  }
-}
-
-// Wait until *p == want exactly-or-more (counters are reset by their consumer, so they never overshoot).
-__device__ __forceinline__ bool wait_counter(const CommCtx& ctx, const uint32_t* p, uint32_t want, int code,
-                                             int where) {
-  return wait_word_ge(ctx, p, want, code, -1, where);
-}
-
-template <typename T>
-__device__ __forceinline__ void cvt_store_32(char* dst, const uint32_t (&r)[32], bool full_vec, int valid_cols) {
-  // r holds 32 consecutive fp32 columns of one row.
-  uint32_t packed[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float a = __uint_as_float(r[2 * i]), b = __uint_as_float(r[2 * i + 1]);
-    if constexpr (PackTraits<T>::kDType == kBF16) {
-      __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-      packed[i] = *reinterpret_cast<uint32_t*>(&h);
-    } else {
-      __half2 h = __floats2half2_rn(a, b);
-      packed[i] = *reinterpret_cast<uint32_t*>(&h);
-    }
-  }
-  if (full_vec) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      *reinterpret_cast<uint4*>(dst + i * 16) =
-          make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-  } else {
-    for (int i = 0; i < valid_cols; ++i) {
-      const uint32_t w = packed[i >> 1];
-      *reinterpret_cast<unsigned short*>(dst + i * 2) = static_cast<unsigned short>((i & 1) ? (w >> 16) : (w & 0xffff));
-    }
-  }
-}
-
-template <int THREADS>
-__device__ __forceinline__ float cta_sum(float v, float* s_part, float* s_total) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = v;
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    float t = threadIdx.x < THREADS / 32 ? s_part[threadIdx.x] : 0.f;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    if (threadIdx.x == 0) *s_total = t;
-  }
-  __syncthreads();
-  return *s_total;
-}
-
-// ---------------------------------------------------------------------------
-// Communication roles (run by whole CTAs with blockIdx.x >= gemm_ctas)
-// ---------------------------------------------------------------------------
-
-// GEMM->AR reducer: owned tiles are those at schedule positions seq with seq % world == rank.
-template <typename T, int THREADS>
-__device__ void ar_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sched& sc, int j, int R) {
-  __shared__ int s_ok;
-  const int world = ctx.world, rank = ctx.rank;
-  const bool use_mc = a.partial.mc != nullptr && a.c_sym.mc != nullptr;
-  const size_t row_bytes = size_t(a.N) * 2;
-  bool ok = true;
-  int k = j;
-  for (; ok; k += R) {
-    const int seq = k * world + rank;
-    if (seq >= sc.tiles) break;
-    if (threadIdx.x == 0)
-      s_ok = wait_counter(ctx, counter_ptr(ctx, rank, a.counter_base + k), world, kDevTimeoutCounter, 50) ? 1 : 0;
-    __syncthreads();
-    ok = s_ok != 0;
-    if (!ok) break;
-    if (threadIdx.x == 0) *counter_ptr(ctx, rank, a.counter_base + k) = 0;  // single consumer: re-arm now
-    int m_blk, n_blk;
-    sc.coord(seq, m_blk, n_blk);
-    const size_t tile_off = size_t(m_blk * sc.tiles_n + n_blk) * kTileBytes;
-    const int rows_valid = min(kTileM, a.M - m_blk * kTileM);
-    const int packs_valid_row = min(kPacksPerTileRow, (a.N - n_blk * kTileN) / 8);
-    constexpr int U = 4;
-    for (int base = 0; base < kPacksPerTile; base += THREADS * U) {
-      uint4 v[U];
-      bool live[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int p = base + u * THREADS + threadIdx.x;
-        const int row = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
-        live[u] = p < kPacksPerTile && row < rows_valid && cp < packs_valid_row;
-        if (live[u]) {
-          if (use_mc)
-            v[u] = reduce_pack_mc<T, kSum>(static_cast<const char*>(a.partial.mc) + tile_off + size_t(p) * 16);
-          else
-            v[u] = reduce_pack_p2p<T, kSum, 0>(a.partial, tile_off + size_t(p) * 16, world);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (!live[u]) continue;
-        const int p = base + u * THREADS + threadIdx.x;
-        const int row = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
-        const size_t coff = size_t(m_blk * kTileM + row) * row_bytes + size_t(n_blk * kTileN + cp * 8) * 2;
-        if (use_mc) {
-          ptx::multimem_st_v4(static_cast<char*>(a.c_sym.mc) + coff, v[u]);
-        } else {
-          for (int r = 0; r < world; ++r) ptx::st_v4(static_cast<char*>(a.c_sym.p[(rank + r) % world]) + coff, v[u]);
-        }
-      }
-    }
-  }
-  // Every rank's reducer j is past its last tile: all pushes into this rank's C have been issued and
-  // released, and nobody reads this rank's partial buffer any more.
-  if (ok) rank_barrier(ctx, j, 51);
-}
-
-// GEMM->RS + residual + RMSNorm reducer.  All R reducer CTAs share each owned row block (rows j, j+R, ...).
-template <typename T, int THREADS>
-__device__ void rs_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sched& sc, int j, int R) {
-  __shared__ int s_ok;
-  __shared__ float s_part[THREADS / 32];
-  __shared__ float s_total;
-  using PT = PackTraits<T>;
-  constexpr int PPT = 6;  // N <= 6 * 384 * 8 = 18432
-  const int world = ctx.world, rank = ctx.rank;
-  const bool use_mc = a.partial.mc != nullptr;
-  const int packs_per_row = a.N / 8;
-  const size_t row_bytes = size_t(a.N) * 2;
-  const char* res = a.residual ? static_cast<const char*>(a.residual) + a.rs_emu_stride * blockIdx.y : nullptr;
-  char* y = static_cast<char*>(a.y_local) + a.rs_emu_stride * blockIdx.y;
-  char* ro = a.res_out_local ? static_cast<char*>(a.res_out_local) + a.rs_emu_stride * blockIdx.y : nullptr;
-  const char* wgt = static_cast<const char*>(a.weight);
-  bool ok = true;
-  for (int lb = 0; lb < sc.bps && ok; ++lb) {
-    uint32_t* cnt = counter_ptr(ctx, rank, a.counter_base + lb);
-    uint32_t* done = counter_ptr(ctx, rank, a.counter_base + sc.bps + lb);
-    if (threadIdx.x == 0)
-      s_ok = wait_counter(ctx, cnt, uint32_t(world) * sc.tiles_n, kDevTimeoutCounter, 60) ? 1 : 0;
-    __syncthreads();
-    ok = s_ok != 0;
-    if (!ok) break;
-    const int m_blk = rank * sc.bps + lb;
-    for (int r_in = j; r_in < kTileM; r_in += R) {
-      const size_t lrow_off = size_t(lb * kTileM + r_in) * row_bytes;
-      float v[PPT][8];
-      float ss = 0.f;
-#pragma unroll
-      for (int q = 0; q < PPT; ++q) {
-        const int p = threadIdx.x + q * THREADS;
-        if (p < packs_per_row) {
-          const int n_blk = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
-          const size_t off =
-              size_t(m_blk * sc.tiles_n + n_blk) * kTileBytes + size_t(r_in) * (kTileN * 2) + size_t(cp) * 16;
-          if (use_mc)
-            PT::unpack(reduce_pack_mc<T, kSum>(static_cast<const char*>(a.partial.mc) + off), v[q]);
-          else
-            reduce_pack_p2p_f32<T, kSum, 0>(a.partial, off, world, v[q]);
-          if (res != nullptr) {
-            const uint4 rv = ptx::ld_nc_v4(res + lrow_off + size_t(p) * 16);
-            float rf[8];
-            PT::unpack(rv, rf);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[q][i] += rf[i];
-            const uint4 rounded = PT::pack(v[q]);
-            PT::unpack(rounded, v[q]);
-          }
-          if (ro != nullptr) ptx::st_v4(ro + lrow_off + size_t(p) * 16, PT::pack(v[q]));
-#pragma unroll
-          for (int i = 0; i < 8; ++i) ss += v[q][i] * v[q][i];
-        }
-      }
-      float scale = 1.f;
-      if (wgt != nullptr) {
-        const float total = cta_sum<THREADS>(ss, s_part, &s_total);
-        scale = rsqrtf(total / float(a.N) + a.eps);
-      }
-#pragma unroll
-      for (int q = 0; q < PPT; ++q) {
-        const int p = threadIdx.x + q * THREADS;
-        if (p < packs_per_row) {
-          float o[8];
-          if (wgt != nullptr) {
-            const uint4 wv = *reinterpret_cast<const uint4*>(wgt + size_t(p) * 16);
-            float wf[8];
-            PT::unpack(wv, wf);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = v[q][i] * scale * wf[i];
-          } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) o[i] = v[q][i];
-          }
-          ptx::st_v4(y + lrow_off + size_t(p) * 16, PT::pack(o));
-        }
-      }
-    }
-    // The last reducer to finish this row block re-arms its counters for the next call.
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      if (atomicAdd(done, 1u) == uint32_t(R - 1)) {
-        *cnt = 0;
-        *done = 0;
-        __threadfence();
-      }
-    }
-  }
-  if (ok) rank_barrier(ctx, j, 61);
-}
-
-// AG->GEMM pusher: broadcasts this rank's shard, one 128-row chunk at a time.
-template <int THREADS>
-__device__ void ag_pusher_role(const CommCtx& ctx, const GemmArgs& a, const Sched& sc, int j, int R) {
-  const int world = ctx.world, rank = ctx.rank;
-  const bool use_mc = a.a_full.mc != nullptr && ctx.pad_mc != nullptr;
-  // Previous call's readers of the gathered buffers are done once every rank has entered this call.
-  if (!rank_barrier(ctx, j, 70)) return;
-  const char* src = static_cast<const char*>(a.A) + a.a_emu_stride * blockIdx.y;
-  const size_t row_bytes = size_t(a.K) * 2;  // gathered buffer is dense [M, K]
-  const size_t src_row_bytes = size_t(a.lda) * 2;
-  const int packs_per_row = a.K / 8;
-  const int shard_rows = a.M / world;
-  for (int c = 0; c < sc.bps; ++c) {
-    const int row0 = c * kTileM;
-    const int rows = min(kTileM, shard_rows - row0);
-    const int total = rows * packs_per_row;
-    for (int p = j * THREADS + threadIdx.x; p < total; p += R * THREADS) {
-      const int row = row0 + p / packs_per_row, cp = p % packs_per_row;
-      const uint4 v = ptx::ld_nc_v4(src + size_t(row) * src_row_bytes + size_t(cp) * 16);
-      const size_t doff = size_t(rank * shard_rows + row) * row_bytes + size_t(cp) * 16;
-      if (use_mc) {
-        ptx::multimem_st_v4(static_cast<char*>(a.a_full.mc) + doff, v);
-      } else {
-        for (int r = 1; r < world; ++r) ptx::st_v4(static_cast<char*>(a.a_full.p[(rank + r) % world]) + doff, v);
-      }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      ptx::fence_acq_rel_sys();
-      const int idx = a.counter_base + rank * sc.bps + c;
-      if (use_mc) {
-        ptx::multimem_red_add_u32(ctx.pad_mc + kPadCounterOffset + idx, 1u);
-      } else {
-        for (int r = 1; r < world; ++r) ptx::red_release_sys_add(counter_ptr(ctx, (rank + r) % world, idx), 1u);
-      }
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------
-// The kernel
-// ---------------------------------------------------------------------------
-struct EmuMaps {
-  const CUtensorMap* table;  // [world][3]: A, B, A_local per emulated rank (device memory), or nullptr
-};
-
-template <typename T, int MODE>
-__global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsFused, 1)
-    gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                const __grid_constant__ CUtensorMap tmap_a_local, EmuMaps emu, CommCtx ctx_param, GemmArgs a,
-                int gemm_ctas) {
-  constexpr int THREADS = MODE == kGemmPlain ? kThreadsPlain : kThreadsFused;
-  constexpr int FMT = PackTraits<T>::kDType == kBF16 ? 1 : 0;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem + kStages * kStageBytes);
-
-  const CommCtx ctx = resolve_ctx(ctx_param);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  Sched sc;
-  sc.tiles_m = (a.M + kTileM - 1) / kTileM;
-  sc.tiles_n = (a.N + kTileN - 1) / kTileN;
-  sc.tiles = sc.tiles_m * sc.tiles_n;
-  sc.mode = MODE;
-  sc.world = ctx.world;
-  sc.rank = ctx.rank;
-  sc.bps = (MODE == kGemmRsNorm || MODE == kGemmAg) ? (a.M / ctx.world + kTileM - 1) / kTileM : 0;
-
-  // ---- communication CTAs -------------------------------------------------
-  if constexpr (MODE != kGemmPlain) {
-    if (static_cast<int>(blockIdx.x) >= gemm_ctas) {
-      const int j = blockIdx.x - gemm_ctas, R = gridDim.x - gemm_ctas;
-      if constexpr (MODE == kGemmAr) ar_reducer_role<T, THREADS>(ctx, a, sc, j, R);
-      if constexpr (MODE == kGemmRsNorm) rs_reducer_role<T, THREADS>(ctx, a, sc, j, R);
-      if constexpr (MODE == kGemmAg) ag_pusher_role<THREADS>(ctx, a, sc, j, R);
-      return;
-    }
-  }
-
-  // ---- GEMM CTAs ----------------------------------------------------------
-  const CUtensorMap* ta = emu.table ? &emu.table[3 * blockIdx.y + 0] : &tmap_a;
-  const CUtensorMap* tb = emu.table ? &emu.table[3 * blockIdx.y + 1] : &tmap_b;
-  const CUtensorMap* tal = emu.table ? &emu.table[3 * blockIdx.y + 2] : &tmap_a_local;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(&ctl->full[s], 1);
-      ptx::mbar_init(&ctl->empty[s], 1);
-    }
-    for (int s = 0; s < kAccStages; ++s) {
-      ptx::mbar_init(&ctl->tmem_full[s], 1);
-      ptx::mbar_init(&ctl->tmem_empty[s], 4);  // one arrival per epilogue warp
-    }
-    ctl->abort = 0;
-    for (int s = 0; s < kAccStages; ++s) ctl->epi_count[s] = 0;
-    ptx::mbar_fence_init();
-    ptx::prefetch_tmap(ta);
-    ptx::prefetch_tmap(tb);
-    if constexpr (MODE == kGemmAg) ptx::prefetch_tmap(tal);
-  }
-  if (warp == 1) {
-    ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
-    ptx::tmem_relinquish();
-  }
-  ptx::tc_fence_before_sync();
-  __syncthreads();
-  ptx::tc_fence_after_sync();
-  const uint32_t tmem_base = ctl->tmem_base;
-  volatile int* abort = &ctl->abort;
-
-  const int num_kb = (a.K + kTileK - 1) / kTileK;
-  const int G = gemm_ctas;
-  const int shard_rows = (MODE == kGemmAg) ? a.M / ctx.world : 0;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      // ------------------------- TMA producer -------------------------
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int seq = blockIdx.x; seq < sc.tiles && ok; seq += G) {
-        int m_blk, n_blk;
-        sc.coord(seq, m_blk, n_blk);
-        const CUtensorMap* tma_a_cur = ta;
-        int a_row = m_blk * kTileM;
-        if constexpr (MODE == kGemmAg) {
-          const int owner = m_blk / sc.bps;
-          if (owner == ctx.rank) {
-            tma_a_cur = tal;  // own rows are read from the shard itself
-            a_row = (m_blk - owner * sc.bps) * kTileM;
-          } else {
-            // Gathered rows: wait until all pushers of `owner` delivered this chunk into LOCAL memory.
-            const int R = gridDim.x - G;
-            ok = wait_counter(ctx, counter_ptr(ctx, ctx.rank, a.counter_base + m_blk), R, kDevTimeoutChunkFlag, 71);
-            if (!ok) {
-              *abort = 1;
-              break;
-            }
-            ptx::fence_proxy_async_global();
-          }
-        }
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!ptx::mbar_wait(&ctl->empty[stage], phase ^ 1, abort)) {
-            ok = false;
-            break;
-          }
-          uint8_t* sa = smem + stage * kStageBytes;
-          uint8_t* sb = sa + kABytes;
-          ptx::mbar_arrive_expect_tx(&ctl->full[stage], kStageBytes);
-          ptx::tma_load_2d(sa, tma_a_cur, &ctl->full[stage], kb * kTileK, a_row);
-          ptx::tma_load_2d(sb, tb, &ctl->full[stage], kb * kTileK, n_blk * kTileN);
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1;
-          }
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      // ------------------------- MMA issuer ---------------------------
-      constexpr uint32_t idesc = ptx::umma_idesc_f16(FMT, kTileM, kTileN);
-      int stage = 0;
-      uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      bool ok = true;
-      for (int seq = blockIdx.x; seq < sc.tiles && ok; seq += G) {
-        if (!ptx::mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1, abort)) break;
-        ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * kTileN;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!ptx::mbar_wait(&ctl->full[stage], phase, abort)) {
-            ok = false;
-            break;
-          }
-          ptx::tc_fence_after_sync();
-          const uint32_t sa = ptx::smem_u32(smem + stage * kStageBytes);
-          const uint64_t da = ptx::umma_desc_kmajor_sw128(sa);
-          const uint64_t db = ptx::umma_desc_kmajor_sw128(sa + kABytes);
-#pragma unroll
-          for (int k = 0; k < kTileK / 16; ++k) {
-            // Advancing 16 K-elements = 32 bytes inside the 128-byte swizzle atom: +2 in the (>>4) address field.
-            ptx::umma_f16(d_tmem, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (kb | k) != 0 ? 1u : 0u);
-          }
-          ptx::umma_commit(&ctl->empty[stage]);  // stage reusable once these MMAs have read it
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1;
-          }
-        }
-        if (!ok) break;
-        ptx::umma_commit(&ctl->tmem_full[acc]);  // accumulator complete
-        if (++acc == kAccStages) {
-          acc = 0;
-          acc_phase ^= 1;
-        }
-      }
-    }
-  } else if (warp < 6) {
-    // --------------------------- epilogue -----------------------------
-    const int q = warp & 3;  // TMEM lane quadrant this warp may read
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    char* c_base = nullptr;
-    if constexpr (MODE == kGemmPlain || MODE == kGemmAg) c_base = static_cast<char*>(a.C) + a.c_emu_stride * blockIdx.y;
-    char* p_base = nullptr;
-    if constexpr (MODE == kGemmAr || MODE == kGemmRsNorm) p_base = static_cast<char*>(a.partial.p[ctx.rank]);
-    for (int seq = blockIdx.x; seq < sc.tiles; seq += G) {
-      int m_blk, n_blk;
-      sc.coord(seq, m_blk, n_blk);
-      if (!ptx::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort)) break;
-      ptx::tc_fence_after_sync();
-      const int r_in = q * 32 + lane;
-      const int row = m_blk * kTileM + r_in;
-      const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + acc * kTileN;
-#pragma unroll 2
-      for (int c = 0; c < kTileN / 32; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32b_x32(t_addr + c * 32, r);
-        ptx::tmem_ld_wait();
-        const int col = n_blk * kTileN + c * 32;
-        if constexpr (MODE == kGemmPlain || MODE == kGemmAg) {
-          if (row < a.M && col < a.N) {
-            const int valid = min(32, a.N - col);
-            cvt_store_32<T>(c_base + (size_t(row) * a.ldc + col) * 2, r, valid == 32 && (a.ldc % 8) == 0, valid);
-          }
-        } else {
-          // Tile-packed partial buffer: the whole (padded) tile is written so that reducers can stream it.
-          cvt_store_32<T>(p_base + size_t(m_blk * sc.tiles_n + n_blk) * kTileBytes + size_t(r_in) * (kTileN * 2) + c * 64,
-                          r, true, 32);
-        }
-      }
-      if constexpr (MODE == kGemmAr || MODE == kGemmRsNorm) {
-        // The last of the four epilogue warps to finish its rows publishes one arrival for the tile.  The
-        // count is taken BEFORE the TMEM stage is handed back, so arrivals of the next tile that uses the
-        // same stage cannot mix with this tile's.
-        __syncwarp();
-        if (lane == 0) {
-          __threadfence();
-          if ((atomicAdd(&ctl->epi_count[acc], 1u) & 3u) == 3u) {
-            ptx::fence_acq_rel_sys();
-            if constexpr (MODE == kGemmAr) {
-              const int owner = seq % ctx.world;
-              ptx::red_release_sys_add(counter_ptr(ctx, owner, a.counter_base + seq / ctx.world), 1u);
-            } else {
-              const int owner = m_blk / sc.bps;
-              ptx::red_release_sys_add(counter_ptr(ctx, owner, a.counter_base + (m_blk - owner * sc.bps)), 1u);
-            }
-          }
-        }
-      }
-      // Accumulator drained: hand the TMEM stage back to the MMA warp.
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
-      if (++acc == kAccStages) {
-        acc = 0;
-        acc_phase ^= 1;
-      }
-    }
-  }
-
-  // ---- teardown -----------------------------------------------------------
-  __syncthreads();
-  if (*abort) {
-    // Give copies that may still be in flight time to land before shared memory is released.
-    if (threadIdx.x == 0) {
-      gemm_report(ctx.status, ctx.rank, kDevTimeoutMbarrier, 80);
-      const uint64_t t0 = ptx::globaltimer_ns();
-      while (ptx::globaltimer_ns() - t0 < 200000) __nanosleep(1000);
-    }
-    __syncthreads();
-  }
-  if constexpr (MODE == kGemmAg) {
-    // Last GEMM CTA out re-arms the chunk flags (every flag has reached its final value by now).
-    if (threadIdx.x == 0 && !*abort) {
-      uint32_t* done = counter_ptr(ctx, ctx.rank, a.counter_base + sc.tiles_m);
-      __threadfence();
-      if (atomicAdd(done, 1u) == uint32_t(G - 1)) {
-        for (int i = 0; i < sc.tiles_m; ++i) *counter_ptr(ctx, ctx.rank, a.counter_base + i) = 0;
-        *done = 0;
-        __threadfence();
-      }
-    }
-  }
-  if (warp == 1) {
-    __syncwarp();
-    ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, kTmemCols);
-  }
-}
-
-// ---------------------------------------------------------------------------
-// Host side
-// ---------------------------------------------------------------------------
 struct MapKey {
   const void* p;
   uint64_t rows, cols, ld;
@@ -628,8 +30,9 @@ struct MapKeyHash {
   }
 };
 
-// 2-D map over a row-major [rows, cols] 16-bit matrix; box = box_rows x 64 elements, 128-byte swizzle.
-bool make_tmap(CUtensorMap* out, const void* p, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+// Encoding a tensor map costs a few microseconds of host time; weights and registered buffers keep their
+// addresses, so the encoded maps are cached by (pointer, shape).
+bool make_tmap_cached(CUtensorMap* out, const void* p, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
   static std::mutex mu;
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   const MapKey key{p, rows, cols, ld, box_rows};
@@ -641,6 +44,74 @@ bool make_tmap(CUtensorMap* out, const void* p, uint64_t rows, uint64_t cols, ui
       return true;
     }
   }
+  if (!encode_tmap_2d(out, p, rows, cols, ld, box_rows)) return false;
+  std::lock_guard<std::mutex> g(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return true;
+}
+
+// Library-owned scratch, one per device, grown on demand: the split-K workspace and the tensor-map table of the
+// single-GPU emulation.
+struct DeviceScratch {
+  void* splitk = nullptr;
+  size_t splitk_bytes = 0;
+  CUtensorMap* emu_maps = nullptr;
+};
+DeviceScratch g_scratch[64];
+std::mutex g_scratch_mu;
+
+cudaError_t ensure_splitk(int dev, size_t need, cudaStream_t stream, void** out) {
+  std::lock_guard<std::mutex> g(g_scratch_mu);
+  DeviceScratch& s = g_scratch[dev & 63];
+  if (s.splitk_bytes < need) {
+    // Growing: earlier launches may still use the old block.
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    if (s.splitk) cudaFree(s.splitk);
+    s.splitk = nullptr;
+    s.splitk_bytes = 0;
+    size_t cap = need + (need >> 2);
+    e = cudaMalloc(&s.splitk, cap);
+    if (e != cudaSuccess) return e;
+    e = cudaMemset(s.splitk, 0, kSplitkCounterBytes);
+    if (e != cudaSuccess) return e;
+    s.splitk_bytes = cap;
+  }
+  (void)stream;
+  *out = s.splitk;
+  return cudaSuccess;
+}
+
+cudaError_t ensure_emu_maps(int dev, CUtensorMap** out) {
+  std::lock_guard<std::mutex> g(g_scratch_mu);
+  DeviceScratch& s = g_scratch[dev & 63];
+  if (s.emu_maps == nullptr) {
+    cudaError_t e = cudaMalloc(&s.emu_maps, sizeof(CUtensorMap) * 3 * kMaxRanks);
+    if (e != cudaSuccess) return e;
+  }
+  *out = s.emu_maps;
+  return cudaSuccess;
+}
+
+template <typename T>
+cudaError_t launch_fmt(const CommCtx& ctx, const GemmArgs& a, cudaStream_t stream, CUtensorMap* emu_maps) {
+  switch (a.mode) {
+    case kGemmPlain:
+      return launch_mode<T, kGemmPlain>(ctx, a, stream, make_tmap_cached, emu_maps);
+    case kGemmAr:
+      return launch_mode<T, kGemmAr>(ctx, a, stream, make_tmap_cached, emu_maps);
+    case kGemmRsNorm:
+      return launch_mode<T, kGemmRsNorm>(ctx, a, stream, make_tmap_cached, emu_maps);
+    case kGemmAg:
+      return launch_mode<T, kGemmAg>(ctx, a, stream, make_tmap_cached, emu_maps);
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+bool encode_tmap_2d(CUtensorMap* out, const void* p, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
   const DriverApi* drv = driver_api();
   if (drv == nullptr || drv->cuTensorMapEncodeTiled == nullptr) return false;
   cuuint64_t gdim[2] = {cols, rows};
@@ -650,150 +121,79 @@ bool make_tmap(CUtensorMap* out, const void* p, uint64_t rows, uint64_t cols, ui
   CUresult r = drv->cuTensorMapEncodeTiled(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(p), gdim, gstride,
                                            box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return false;
-  std::lock_guard<std::mutex> g(mu);
-  if (cache.size() > 4096) cache.clear();
-  cache.emplace(key, *out);
-  return true;
+  return r == CUDA_SUCCESS;
 }
-
-int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
-
-template <typename T, int MODE>
-cudaError_t launch_mode(const CommCtx& ctx, const GemmArgs& a, cudaStream_t stream) {
-  constexpr int THREADS = MODE == kGemmPlain ? kThreadsPlain : kThreadsFused;
-  auto kernel = gemm_kernel<T, MODE>;
-  static uint64_t attr_set_mask = 0;  // per device (one bit each)
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!(attr_set_mask >> (dev & 63) & 1)) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) return e;
-    attr_set_mask |= uint64_t(1) << (dev & 63);
-  }
-  const bool emu = ctx.emu_table != nullptr;
-  const int world = ctx.world;
-  const int tiles = ((a.M + kTileM - 1) / kTileM) * ((a.N + kTileN - 1) / kTileN);
-  int budget = a.max_ctas > 0 ? a.max_ctas : sm_count();
-  if (emu) budget = budget / world;
-  int comm = MODE == kGemmPlain ? 0 : (a.comm_ctas > 0 ? a.comm_ctas : 16);
-  if (comm > budget / 2) comm = budget / 2;
-  if (MODE != kGemmPlain && comm < 1) return cudaErrorInvalidValue;
-  int gemm_ctas = budget - comm;
-  if (gemm_ctas > tiles) gemm_ctas = tiles;
-  if (gemm_ctas < 1) return cudaErrorInvalidValue;
-
-  const int shard_rows = a.M / world;
-  CUtensorMap ta, tb, tal;
-  EmuMaps em{nullptr};
-  static CUtensorMap* emu_dev = nullptr;  // emulation only (tests): small device table
-  if (!emu) {
-    const void* a_ptr = MODE == kGemmAg ? a.a_full.p[ctx.rank] : a.A;
-    const uint64_t a_ld = MODE == kGemmAg ? uint64_t(a.K) : uint64_t(a.lda);
-    if (!make_tmap(&ta, a_ptr, a.M, a.K, a_ld, kTileM)) return cudaErrorInvalidValue;
-    if (!make_tmap(&tb, a.B, a.N, a.K, a.ldb, kTileN)) return cudaErrorInvalidValue;
-    if (MODE == kGemmAg) {
-      if (!make_tmap(&tal, a.A, shard_rows, a.K, a.lda, kTileM)) return cudaErrorInvalidValue;
-    } else {
-      tal = ta;
-    }
-  } else {
-    CUtensorMap host[3 * kMaxRanks];
-    for (int r = 0; r < world; ++r) {
-      const char* A_r = static_cast<const char*>(a.A) + a.a_emu_stride * r;
-      const char* B_r = static_cast<const char*>(a.B) + a.b_emu_stride * r;
-      const void* a_ptr = MODE == kGemmAg ? a.a_full.p[r] : static_cast<const void*>(A_r);
-      const uint64_t a_ld = MODE == kGemmAg ? uint64_t(a.K) : uint64_t(a.lda);
-      if (!make_tmap(&host[3 * r + 0], a_ptr, a.M, a.K, a_ld, kTileM)) return cudaErrorInvalidValue;
-      if (!make_tmap(&host[3 * r + 1], B_r, a.N, a.K, a.ldb, kTileN)) return cudaErrorInvalidValue;
-      if (MODE == kGemmAg) {
-        if (!make_tmap(&host[3 * r + 2], A_r, shard_rows, a.K, a.lda, kTileM)) return cudaErrorInvalidValue;
-      } else {
-        host[3 * r + 2] = host[3 * r + 0];
-      }
-    }
-    if (emu_dev == nullptr) {
-      cudaError_t e = cudaMalloc(&emu_dev, sizeof(CUtensorMap) * 3 * kMaxRanks);
-      if (e != cudaSuccess) return e;
-    }
-    // Synchronous on purpose: the emulation path is a test harness.
-    cudaError_t e = cudaStreamSynchronize(stream);
-    if (e != cudaSuccess) return e;
-    e = cudaMemcpy(emu_dev, host, sizeof(CUtensorMap) * 3 * world, cudaMemcpyHostToDevice);
-    if (e != cudaSuccess) return e;
-    em.table = emu_dev;
-    ta = tb = tal = host[0];
-  }
-
-  const int grid_x = gemm_ctas + comm;
-  if (emu) {
-    dim3 grid(grid_x, world);
-    CommCtx c = ctx;
-    GemmArgs aa = a;
-    int g = gemm_ctas;
-    void* argv[] = {(void*)&ta, (void*)&tb, (void*)&tal, (void*)&em, (void*)&c, (void*)&aa, (void*)&g};
-    return cudaLaunchCooperativeKernel((const void*)kernel, grid, dim3(THREADS), argv, kSmemBytes, stream);
-  }
-  kernel<<<dim3(grid_x, 1), THREADS, kSmemBytes, stream>>>(ta, tb, tal, em, ctx, a, gemm_ctas);
-  return cudaGetLastError();
-}
-
-template <typename T>
-cudaError_t launch_fmt(const CommCtx& ctx, const GemmArgs& a, cudaStream_t stream) {
-  switch (a.mode) {
-    case kGemmPlain:
-      return launch_mode<T, kGemmPlain>(ctx, a, stream);
-    case kGemmAr:
-      return launch_mode<T, kGemmAr>(ctx, a, stream);
-    case kGemmRsNorm:
-      return launch_mode<T, kGemmRsNorm>(ctx, a, stream);
-    case kGemmAg:
-      return launch_mode<T, kGemmAg>(ctx, a, stream);
-  }
-  return cudaErrorInvalidValue;
-}
-
-}  // namespace
 
 int gemm_counters_needed(int mode, int M, int N, int world) {
   const int tiles_m = (M + kTileM - 1) / kTileM, tiles_n = (N + kTileN - 1) / kTileN;
   switch (mode) {
     case kGemmAr:
-      return (tiles_m * tiles_n + world - 1) / world;
+      return (tiles_m * tiles_n + world - 1) / world + 1;  // per-tile arrivals + ticket
     case kGemmRsNorm:
-      return 2 * ((M / world + kTileM - 1) / kTileM);
+      return 2 * ((M / world + kTileM - 1) / kTileM) + 1;  // arrivals + finished items per row block + ticket
     case kGemmAg:
-      return tiles_m + 1;
+      return tiles_m + 1;  // chunk flags + finished GEMM CTAs
   }
   return 0;
 }
 
-cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& a, cudaStream_t stream) {
+int gemm_auto_splits(int M, int N, int K, int sms) {
+  const int tiles = ((M + kTileM - 1) / kTileM) * ((N + kTileN - 1) / kTileN);
+  if (tiles * 2 > sms || K < 4 * kTileK) return 1;
+  int s = sms / tiles;
+  if (s > 8) s = 8;
+  // Keep at least four K blocks (256 elements) per split so that the pipeline still fills.
+  const int num_kb = (K + kTileK - 1) / kTileK;
+  if (s > num_kb / 4) s = num_kb / 4;
+  return gemm_detail::normalize_splits(K, s);
+}
+
+cudaError_t validate_gemm(const CommCtx& ctx, const GemmArgs& a) {
   if (a.M <= 0 || a.N <= 0 || a.K <= 0) return cudaErrorInvalidValue;
   if (a.K % 8 != 0 || a.lda % 8 != 0 || a.ldb % 8 != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15)) return cudaErrorInvalidValue;
   if (a.mode != kGemmPlain) {
     if (a.N % 8 != 0) return cudaErrorInvalidValue;
-    if (gemm_counters_needed(a.mode, a.M, a.N, ctx.world) + a.counter_base > kNumCounters) return cudaErrorInvalidValue;
+    if (gemm_counters_needed(a.mode, a.M, a.N, ctx.world) + a.counter_base > kNumCounters - 1)
+      return cudaErrorInvalidValue;
   }
   if (a.mode == kGemmRsNorm || a.mode == kGemmAg) {
     if (a.M % ctx.world != 0 || (a.M / ctx.world) % kTileM != 0) return cudaErrorInvalidValue;
-    if (a.mode == kGemmRsNorm && a.N > 6 * kThreadsFused * 8) return cudaErrorInvalidValue;
+    if (a.mode == kGemmRsNorm && a.N > 6 * gemm_detail::kThreadsFused * 8) return cudaErrorInvalidValue;
     if (a.mode == kGemmAg && ctx.world < 2) return cudaErrorInvalidValue;
   }
   if (a.mode == kGemmPlain || a.mode == kGemmAg) {
     if (reinterpret_cast<uintptr_t>(a.C) & 15) return cudaErrorInvalidValue;
   }
-  return a.fmt == 1 ? launch_fmt<__nv_bfloat16>(ctx, a, stream) : launch_fmt<__half>(ctx, a, stream);
+  return cudaSuccess;
+}
+
+cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& args, cudaStream_t stream) {
+  cudaError_t e = validate_gemm(ctx, args);
+  if (e != cudaSuccess) return e;
+  GemmArgs a = args;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (a.mode == kGemmPlain) {
+    int splits = a.splits;
+    if (splits == 0) splits = gemm_auto_splits(a.M, a.N, a.K, a.max_ctas > 0 ? a.max_ctas : sm_count());
+    splits = normalize_splits(a.K, splits);
+    const size_t tiles = size_t((a.M + kTileM - 1) / kTileM) * ((a.N + kTileN - 1) / kTileN);
+    if (tiles > kSplitkMaxTiles) splits = 1;
+    a.splits = splits;
+    if (splits > 1 && a.splitk_ws == nullptr) {
+      e = ensure_splitk(dev, splitk_workspace_bytes(a.M, a.N, splits), stream, &a.splitk_ws);
+      if (e != cudaSuccess) return e;
+    }
+  } else {
+    a.splits = 1;
+  }
+  CUtensorMap* emu_maps = nullptr;
+  if (ctx.emu_table != nullptr) {
+    e = ensure_emu_maps(dev, &emu_maps);
+    if (e != cudaSuccess) return e;
+  }
+  return a.fmt == 1 ? launch_fmt<__nv_bfloat16>(ctx, a, stream, emu_maps) : launch_fmt<__half>(ctx, a, stream, emu_maps);
 }
 
 }  // namespace oob

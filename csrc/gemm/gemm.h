@@ -37,6 +37,12 @@ struct GemmArgs {
 
   int comm_ctas;  // CTAs reserved for the communication role (fused modes)
   int max_ctas;   // 0 = one CTA per SM
+  int use_nvls;   // fused modes: 0 = peer loads/stores even when a multicast alias exists
+
+  // Plain mode: K split over `splits` CTAs per tile (0 = choose from the shape, 1 = off).  The fp32 partials
+  // and their arrival counters live in splitk_ws (nullptr = the library's own workspace, grown on demand).
+  int splits;
+  void* splitk_ws;
 
   // Fused modes
   PeerPtrs partial;     // AR / RS: tile-packed partial products, registered; >= tiles * kTileBytes
@@ -57,7 +63,13 @@ struct GemmArgs {
 // (K % 8, N % 8, leading dimensions not multiples of 8 elements, ...).
 cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& args, cudaStream_t stream);
 
+// Argument checks shared by every entry point.
+cudaError_t validate_gemm(const CommCtx& ctx, const GemmArgs& args);
+
 // Number of general counters a fused op needs from counter_base on.
 int gemm_counters_needed(int mode, int M, int N, int world);
+
+// Split count the plain GEMM picks for a shape on `sms` SMs (1 = no split).
+int gemm_auto_splits(int M, int N, int K, int sms);
 
 }  // namespace oob

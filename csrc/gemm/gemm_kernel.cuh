@@ -1,0 +1,864 @@
+// tcgen05 / TMEM GEMM for sm_100a with communication fused into the same
+// persistent kernel (device code and the launch helper; included by the
+// translation units that instantiate it).
+//
+// Mainloop (all modes): one CTA per SM, 128x256 output tiles, K blocks of 64.
+//   warp 0    TMA producer: cp.async.bulk.tensor (this GPU's memory, 128-byte swizzle) into a 4-stage ring
+//   warp 1    MMA issuer: one thread issues tcgen05.mma (M128 N256 K16, fp32 accumulate in TMEM);
+//             tcgen05.commit releases the smem stage / publishes the accumulator
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (two TMEM stages, so the next tile's mainloop overlaps),
+//             convert, store
+// Plain mode can split K over several CTAs per tile (small-M problems that would otherwise occupy a fraction of
+// the SMs): partial accumulators go to an fp32 workspace and the last CTA to arrive for a 32-row quadrant of a tile
+// sums the splits in a fixed order and writes C.
+// Fused modes add a communication role.  `comm_ctas` CTAs run it from the start and every GEMM CTA joins when it
+// has finished its tiles, drawing work from a ticket counter:
+//   GEMM->AR      the epilogue writes the partial tile to a registered buffer and bumps an arrival counter on the
+//                 tile's owner rank; the owner pulls the tile from all ranks (multimem.ld_reduce in the switch, or
+//                 P2P loads, fp32 accumulate) and broadcasts the sum into every rank's C (multimem.st / P2P stores)
+//                 while later tiles still compute.
+//   GEMM->RS+norm counters are per 128-row block on the rank that owns the rows; reducers sum the rows, add the
+//                 residual, apply RMSNorm and write the rank's rows.
+//   AG->GEMM      pusher CTAs broadcast this rank's A shard chunk by chunk into every rank's gathered buffer and bump
+//                 per-chunk flags; the TMA producer waits for the flag of the chunk it is about to load from LOCAL
+//                 memory.
+// All cross-GPU traffic is plain ld/st/red or multimem.*; TMA only ever touches local memory.
+//
+// Capability parity with the reference: signalling GEMM + reorder epilogue + wait kernel + per-segment all-reduce
+// (src/gemm/gemm_with_signal_sm90.h:102-513, src/epilogue/reorder_epilogue.h:324-595, src/wait.cuh:5-9,
+// src/overlap_impl.cu:450-706), row remap for reduce-scatter (src/gemm/scatter_row_remap_sm90.cuh:35-82), the plain
+// GEMM (src/gemm/gemm_plain_sm90.cu) and its stream-K instances (src/gemm/gemm_with_signal_sm90.h:238-292).  The
+// reorder tables / segment search are replaced by a deterministic tile order plus arrival counters; accumulation is
+// fp32 (the reference accumulates in fp16, src/gemm/gemm_signal_sm90.cu:108).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include "../device/reduce.cuh"
+#include "../device/sync.cuh"
+#include "gemm.h"
+
+namespace oob {
+
+// Encodes a 2-D tensor map over a row-major [rows, cols] 16-bit matrix with leading dimension ld (elements):
+// box = box_rows x 64 elements, 128-byte swizzle.  Pure host computation through the driver; false on failure.
+bool encode_tmap_2d(CUtensorMap* out, const void* p, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows);
+
+namespace gemm_detail {
+
+constexpr int kStages = 4;
+constexpr int kABytes = kTileM * kTileK * 2;  // 16 KiB
+constexpr int kBBytes = kTileN * kTileK * 2;  // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kAccStages = 2;
+constexpr int kTmemCols = 512;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kThreadsPlain = 192;
+constexpr int kThreadsFused = 384;
+constexpr int kPacksPerTile = kTileBytes / 16;  // 4096
+constexpr int kPacksPerTileRow = kTileN / 8;    // 32
+constexpr int kRsRowsPerItem = 8;               // GEMM->RS: rows of a 128-row block handled per ticket
+constexpr int kRsItemsPerBlock = kTileM / kRsRowsPerItem;
+
+// Split-K workspace layout: kSplitkCounterBytes of arrival counters (one per 32-row tile quadrant, zero between
+// calls), then the fp32 partial tiles [tile][split][128][256].
+constexpr size_t kSplitkMaxTiles = 16384;
+constexpr size_t kSplitkCounterBytes = kSplitkMaxTiles * 4 * sizeof(uint32_t);
+__host__ __device__ __forceinline__ float* splitk_partials(void* ws) {
+  return reinterpret_cast<float*>(static_cast<char*>(ws) + kSplitkCounterBytes);
+}
+
+struct SmemCtl {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[kAccStages];
+  uint64_t tmem_empty[kAccStages];
+  uint32_t tmem_base;
+  int abort;
+  uint32_t epi_count[kAccStages];  // epilogue warps that have stored their rows of the tile in this TMEM stage
+};
+
+struct Sched {
+  int tiles_m, tiles_n, tiles;
+  int splits, items;  // items = tiles * splits (split-K: plain mode only)
+  int kb_per_split;
+  int mode, world, rank;
+  int bps;  // 128-row blocks per rank shard (RS / AG)
+  // Logical tile (m_blk, n_blk) of schedule position `seq`.  Every rank walks
+  // the same sequence so that arrival counters fill at about the same time.
+  __device__ void coord(int seq, int& m_blk, int& n_blk) const {
+    if (mode == kGemmRsNorm) {
+      // Row-block major; consecutive row blocks belong to consecutive owners.
+      const int i = seq / tiles_n;
+      n_blk = seq % tiles_n;
+      m_blk = (i % world) * bps + i / world;
+    } else if (mode == kGemmAg) {
+      // Own shard first (it is local), then chunk c of every other rank in ring order.
+      const int i = seq / tiles_n;
+      n_blk = seq % tiles_n;
+      if (i < bps) {
+        m_blk = rank * bps + i;
+      } else {
+        const int k = i - bps;
+        const int c = k / (world - 1);
+        const int s = (rank + 1 + k % (world - 1)) % world;
+        m_blk = s * bps + c;
+      }
+    } else {
+      // Grouped raster: 16 tile rows at a time so that concurrently running
+      // CTAs share A and B tiles in L2.
+      constexpr int kGroup = 16;
+      const int per_group = kGroup * tiles_n;
+      const int g = seq / per_group;
+      const int first_m = g * kGroup;
+      const int rows = (tiles_m - first_m) < kGroup ? (tiles_m - first_m) : kGroup;
+      const int in = seq - g * per_group;
+      m_blk = first_m + in % rows;
+      n_blk = in / rows;
+    }
+  }
+};
+
+__device__ __forceinline__ void gemm_report(DeviceStatus* s, int rank, int code, int where) {
+  if (s == nullptr) return;
+  if (atomicCAS(&s->code, 0, code) == 0) {
+    s->rank = rank;
+    s->peer = -1;
+    s->block = static_cast<int>(blockIdx.x);
+    s->where = where;
+    __threadfence_system();
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void cvt_store_32(char* dst, const uint32_t (&r)[32], bool full_vec, int valid_cols) {
+  // r holds 32 consecutive fp32 columns of one row.
+  uint32_t packed[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float a = __uint_as_float(r[2 * i]), b = __uint_as_float(r[2 * i + 1]);
+    if constexpr (PackTraits<T>::kDType == kBF16) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+      packed[i] = *reinterpret_cast<uint32_t*>(&h);
+    } else {
+      __half2 h = __floats2half2_rn(a, b);
+      packed[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+  }
+  if (full_vec) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      *reinterpret_cast<uint4*>(dst + i * 16) =
+          make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+  } else {
+    for (int i = 0; i < valid_cols; ++i) {
+      const uint32_t w = packed[i >> 1];
+      *reinterpret_cast<unsigned short*>(dst + i * 2) = static_cast<unsigned short>((i & 1) ? (w >> 16) : (w & 0xffff));
+    }
+  }
+}
+
+template <int THREADS>
+__device__ __forceinline__ float cta_sum(float v, float* s_part, float* s_total) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < THREADS / 32 ? s_part[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) *s_total = t;
+  }
+  __syncthreads();
+  return *s_total;
+}
+
+// Sum of one 16-byte pack over all ranks, fp32 result, through the switch or by peer loads.
+template <typename T>
+__device__ __forceinline__ void reduce_pack_any(bool use_mc, const PeerPtrs& buf, size_t off, int world,
+                                                float (&acc)[8]) {
+  if (use_mc) {
+    PackTraits<T>::unpack(reduce_pack_mc<T, kSum>(static_cast<const char*>(buf.mc) + off), acc);
+  } else if (world == 2) {
+    reduce_pack_p2p_f32<T, kSum, 2>(buf, off, world, acc);
+  } else if (world == 4) {
+    reduce_pack_p2p_f32<T, kSum, 4>(buf, off, world, acc);
+  } else if (world == 8) {
+    reduce_pack_p2p_f32<T, kSum, 8>(buf, off, world, acc);
+  } else {
+    reduce_pack_p2p_f32<T, kSum, 0>(buf, off, world, acc);
+  }
+}
+
+// Draws the next ticket of this launch.  The counter is re-armed by whoever draws the last ticket that can ever
+// be drawn: `total` in-range tickets plus one out-of-range ticket per CTA of the launch.
+__device__ __forceinline__ int draw_ticket(uint32_t* ticket, int total, int* s_slot) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t t = atomicAdd(ticket, 1u);
+    if (t == uint32_t(total) + gridDim.x - 1) {
+      *ticket = 0;
+      __threadfence();
+    }
+    *s_slot = static_cast<int>(t);
+  }
+  __syncthreads();
+  return *s_slot;
+}
+
+// ---------------------------------------------------------------------------
+// Communication roles
+// ---------------------------------------------------------------------------
+
+// GEMM->AR: owned tiles are those at schedule positions seq with seq % world == rank; ticket k is the k-th of them.
+// Counter layout from counter_base: [owned] arrivals per owned tile, then the ticket counter.
+template <typename T, int THREADS>
+__device__ void ar_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sched& sc) {
+  __shared__ int s_ok;
+  __shared__ int s_ticket;
+  const int world = ctx.world, rank = ctx.rank;
+  const bool use_mc = a.partial.mc != nullptr && a.c_sym.mc != nullptr && a.use_nvls != 0;
+  const size_t row_bytes = size_t(a.N) * 2;
+  const int owned = (sc.tiles - rank + world - 1) / world;  // tickets that map to a tile
+  const int owned_max = (sc.tiles + world - 1) / world;
+  uint32_t* ticket = counter_ptr(ctx, rank, a.counter_base + owned_max);
+  bool ok = true;
+  while (true) {
+    const int k = draw_ticket(ticket, owned, &s_ticket);
+    if (k >= owned) break;
+    const int seq = k * world + rank;
+    if (threadIdx.x == 0) {
+      uint32_t* cnt = counter_ptr(ctx, rank, a.counter_base + k);
+      s_ok = wait_word_ge(ctx, cnt, world, kDevTimeoutCounter, -1, 50) ? 1 : 0;
+      *cnt = 0;  // single consumer: re-arm now (next call's arrivals cannot come before this launch ends everywhere)
+    }
+    __syncthreads();
+    if (s_ok == 0) ok = false;
+    if (!ok) continue;  // keep drawing so that the ticket counter still gets re-armed
+    int m_blk, n_blk;
+    sc.coord(seq, m_blk, n_blk);
+    const size_t tile_off = size_t(m_blk * sc.tiles_n + n_blk) * kTileBytes;
+    const int rows_valid = min(kTileM, a.M - m_blk * kTileM);
+    const int packs_valid_row = min(kPacksPerTileRow, (a.N - n_blk * kTileN) / 8);
+    constexpr int U = 4;
+    for (int base = 0; base < kPacksPerTile; base += THREADS * U) {
+      uint4 v[U];
+      bool live[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int p = base + u * THREADS + threadIdx.x;
+        const int row = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
+        live[u] = p < kPacksPerTile && row < rows_valid && cp < packs_valid_row;
+        if (live[u]) {
+          float acc[8];
+          reduce_pack_any<T>(use_mc, a.partial, tile_off + size_t(p) * 16, world, acc);
+          v[u] = PackTraits<T>::pack(acc);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (!live[u]) continue;
+        const int p = base + u * THREADS + threadIdx.x;
+        const int row = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
+        const size_t coff = size_t(m_blk * kTileM + row) * row_bytes + size_t(n_blk * kTileN + cp * 8) * 2;
+        if (use_mc) {
+          ptx::multimem_st_v4(static_cast<char*>(a.c_sym.mc) + coff, v[u]);
+        } else {
+          for (int r = 0; r < world; ++r) ptx::st_v4(static_cast<char*>(a.c_sym.p[(rank + r) % world]) + coff, v[u]);
+        }
+      }
+    }
+  }
+  // Block b of every rank is past its last tile: together (all blocks) this means every push into this rank's C
+  // has been issued and released, and nobody reads this rank's partial buffer any more.
+  if (ok) rank_barrier(ctx, blockIdx.x, 51);
+}
+
+// GEMM->RS + residual + RMSNorm.  Ticket t = (owned row block t / kRsItemsPerBlock, row group t % kRsItemsPerBlock).
+// Counter layout from counter_base: [bps] tile arrivals per row block, [bps] finished items per row block, ticket.
+template <typename T, int THREADS>
+__device__ void rs_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sched& sc) {
+  __shared__ int s_ok;
+  __shared__ int s_ticket;
+  __shared__ float s_part[THREADS / 32];
+  __shared__ float s_total;
+  using PT = PackTraits<T>;
+  constexpr int PPT = 6;  // N <= 6 * 384 * 8 = 18432
+  const int world = ctx.world, rank = ctx.rank;
+  const bool use_mc = a.partial.mc != nullptr && a.use_nvls != 0;
+  const int packs_per_row = a.N / 8;
+  const size_t row_bytes = size_t(a.N) * 2;
+  const char* res = a.residual ? static_cast<const char*>(a.residual) + a.rs_emu_stride * blockIdx.y : nullptr;
+  char* y = static_cast<char*>(a.y_local) + a.rs_emu_stride * blockIdx.y;
+  char* ro = a.res_out_local ? static_cast<char*>(a.res_out_local) + a.rs_emu_stride * blockIdx.y : nullptr;
+  const char* wgt = static_cast<const char*>(a.weight);
+  const int total = sc.bps * kRsItemsPerBlock;
+  uint32_t* ticket = counter_ptr(ctx, rank, a.counter_base + 2 * sc.bps);
+  bool ok = true;
+  while (true) {
+    const int t = draw_ticket(ticket, total, &s_ticket);
+    if (t >= total) break;
+    const int lb = t / kRsItemsPerBlock, grp = t % kRsItemsPerBlock;
+    uint32_t* cnt = counter_ptr(ctx, rank, a.counter_base + lb);
+    uint32_t* done = counter_ptr(ctx, rank, a.counter_base + sc.bps + lb);
+    if (threadIdx.x == 0)
+      s_ok = wait_word_ge(ctx, cnt, uint32_t(world) * sc.tiles_n, kDevTimeoutCounter, -1, 60) ? 1 : 0;
+    __syncthreads();
+    if (s_ok == 0) ok = false;
+    if (ok) {
+      const int m_blk = rank * sc.bps + lb;
+      for (int r_in = grp * kRsRowsPerItem; r_in < (grp + 1) * kRsRowsPerItem; ++r_in) {
+        const size_t lrow_off = size_t(lb * kTileM + r_in) * row_bytes;
+        float v[PPT][8];
+        float ss = 0.f;
+#pragma unroll
+        for (int q = 0; q < PPT; ++q) {
+          const int p = threadIdx.x + q * THREADS;
+          if (p < packs_per_row) {
+            const int n_blk = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
+            const size_t off =
+                size_t(m_blk * sc.tiles_n + n_blk) * kTileBytes + size_t(r_in) * (kTileN * 2) + size_t(cp) * 16;
+            reduce_pack_any<T>(use_mc, a.partial, off, world, v[q]);
+            if (res != nullptr) {
+              const uint4 rv = ptx::ld_nc_v4(res + lrow_off + size_t(p) * 16);
+              float rf[8];
+              PT::unpack(rv, rf);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[q][i] += rf[i];
+              const uint4 rounded = PT::pack(v[q]);
+              PT::unpack(rounded, v[q]);
+            }
+            if (ro != nullptr) ptx::st_v4(ro + lrow_off + size_t(p) * 16, PT::pack(v[q]));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += v[q][i] * v[q][i];
+          }
+        }
+        float scale = 1.f;
+        if (wgt != nullptr) {
+          const float total_ss = cta_sum<THREADS>(ss, s_part, &s_total);
+          scale = rsqrtf(total_ss / float(a.N) + a.eps);
+        }
+#pragma unroll
+        for (int q = 0; q < PPT; ++q) {
+          const int p = threadIdx.x + q * THREADS;
+          if (p < packs_per_row) {
+            float o[8];
+            if (wgt != nullptr) {
+              const uint4 wv = *reinterpret_cast<const uint4*>(wgt + size_t(p) * 16);
+              float wf[8];
+              PT::unpack(wv, wf);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[i] = v[q][i] * scale * wf[i];
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[i] = v[q][i];
+            }
+            ptx::st_v4(y + lrow_off + size_t(p) * 16, PT::pack(o));
+          }
+        }
+      }
+    }
+    // Whoever finishes the last row group of a block re-arms the block's counters for the next call.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if (atomicAdd(done, 1u) == uint32_t(kRsItemsPerBlock - 1)) {
+        *cnt = 0;
+        *done = 0;
+        __threadfence();
+      }
+    }
+  }
+  if (ok) rank_barrier(ctx, blockIdx.x, 61);
+}
+
+// AG->GEMM pusher: broadcasts this rank's shard, one 128-row chunk at a time.
+template <int THREADS>
+__device__ void ag_pusher_role(const CommCtx& ctx, const GemmArgs& a, const Sched& sc, int j, int R) {
+  const int world = ctx.world, rank = ctx.rank;
+  const bool use_mc = a.a_full.mc != nullptr && ctx.pad_mc != nullptr && a.use_nvls != 0;
+  // Previous call's readers of the gathered buffers are done once every rank has entered this call.
+  if (!rank_barrier(ctx, j, 70)) return;
+  const char* src = static_cast<const char*>(a.A) + a.a_emu_stride * blockIdx.y;
+  const size_t row_bytes = size_t(a.K) * 2;  // gathered buffer is dense [M, K]
+  const size_t src_row_bytes = size_t(a.lda) * 2;
+  const int packs_per_row = a.K / 8;
+  const int shard_rows = a.M / world;
+  for (int c = 0; c < sc.bps; ++c) {
+    const int row0 = c * kTileM;
+    const int rows = min(kTileM, shard_rows - row0);
+    const int total = rows * packs_per_row;
+    for (int p = j * THREADS + threadIdx.x; p < total; p += R * THREADS) {
+      const int row = row0 + p / packs_per_row, cp = p % packs_per_row;
+      const uint4 v = ptx::ld_nc_v4(src + size_t(row) * src_row_bytes + size_t(cp) * 16);
+      const size_t doff = size_t(rank * shard_rows + row) * row_bytes + size_t(cp) * 16;
+      if (use_mc) {
+        ptx::multimem_st_v4(static_cast<char*>(a.a_full.mc) + doff, v);
+      } else {
+        for (int r = 1; r < world; ++r) ptx::st_v4(static_cast<char*>(a.a_full.p[(rank + r) % world]) + doff, v);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      ptx::fence_acq_rel_sys();
+      const int idx = a.counter_base + rank * sc.bps + c;
+      if (use_mc) {
+        ptx::multimem_red_add_u32(ctx.pad_mc + kPadCounterOffset + idx, 1u);
+      } else {
+        for (int r = 1; r < world; ++r) ptx::red_release_sys_add(counter_ptr(ctx, (rank + r) % world, idx), 1u);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------
+struct EmuMaps {
+  const CUtensorMap* table;  // [world][3]: A, B, A_local per emulated rank (device memory), or nullptr
+};
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsFused, 1)
+    gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const __grid_constant__ CUtensorMap tmap_a_local, EmuMaps emu, CommCtx ctx_param, GemmArgs a,
+                int gemm_ctas) {
+  constexpr int THREADS = MODE == kGemmPlain ? kThreadsPlain : kThreadsFused;
+  constexpr int FMT = PackTraits<T>::kDType == kBF16 ? 1 : 0;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem + kStages * kStageBytes);
+
+  const CommCtx ctx = resolve_ctx(ctx_param);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_kb = (a.K + kTileK - 1) / kTileK;
+
+  Sched sc;
+  sc.tiles_m = (a.M + kTileM - 1) / kTileM;
+  sc.tiles_n = (a.N + kTileN - 1) / kTileN;
+  sc.tiles = sc.tiles_m * sc.tiles_n;
+  sc.splits = (MODE == kGemmPlain && a.splits > 1) ? a.splits : 1;
+  sc.items = sc.tiles * sc.splits;
+  sc.kb_per_split = (num_kb + sc.splits - 1) / sc.splits;
+  sc.mode = MODE;
+  sc.world = ctx.world;
+  sc.rank = ctx.rank;
+  sc.bps = (MODE == kGemmRsNorm || MODE == kGemmAg) ? (a.M / ctx.world + kTileM - 1) / kTileM : 0;
+
+  // ---- communication CTAs -------------------------------------------------
+  if constexpr (MODE != kGemmPlain) {
+    if (static_cast<int>(blockIdx.x) >= gemm_ctas) {
+      const int j = blockIdx.x - gemm_ctas, R = gridDim.x - gemm_ctas;
+      if constexpr (MODE == kGemmAr) ar_reducer_role<T, THREADS>(ctx, a, sc);
+      if constexpr (MODE == kGemmRsNorm) rs_reducer_role<T, THREADS>(ctx, a, sc);
+      if constexpr (MODE == kGemmAg) ag_pusher_role<THREADS>(ctx, a, sc, j, R);
+      return;
+    }
+  }
+
+  // ---- GEMM CTAs ----------------------------------------------------------
+  const CUtensorMap* ta = emu.table ? &emu.table[3 * blockIdx.y + 0] : &tmap_a;
+  const CUtensorMap* tb = emu.table ? &emu.table[3 * blockIdx.y + 1] : &tmap_b;
+  const CUtensorMap* tal = emu.table ? &emu.table[3 * blockIdx.y + 2] : &tmap_a_local;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(&ctl->full[s], 1);
+      ptx::mbar_init(&ctl->empty[s], 1);
+    }
+    for (int s = 0; s < kAccStages; ++s) {
+      ptx::mbar_init(&ctl->tmem_full[s], 1);
+      ptx::mbar_init(&ctl->tmem_empty[s], 4);  // one arrival per epilogue warp
+      ctl->epi_count[s] = 0;
+    }
+    ctl->abort = 0;
+    ptx::mbar_fence_init();
+    ptx::prefetch_tmap(ta);
+    ptx::prefetch_tmap(tb);
+    if constexpr (MODE == kGemmAg) ptx::prefetch_tmap(tal);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile int* abort = &ctl->abort;
+  const int G = gemm_ctas;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------- TMA producer -------------------------
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < sc.items && ok; item += G) {
+        const int seq = item / sc.splits, split = item - seq * sc.splits;
+        const int kb0 = split * sc.kb_per_split, kb1 = min(num_kb, kb0 + sc.kb_per_split);
+        int m_blk, n_blk;
+        sc.coord(seq, m_blk, n_blk);
+        const CUtensorMap* tma_a_cur = ta;
+        int a_row = m_blk * kTileM;
+        if constexpr (MODE == kGemmAg) {
+          const int owner = m_blk / sc.bps;
+          if (owner == ctx.rank) {
+            tma_a_cur = tal;  // own rows are read from the shard itself
+            a_row = (m_blk - owner * sc.bps) * kTileM;
+          } else {
+            // Gathered rows: wait until all pushers of `owner` delivered this chunk into LOCAL memory.
+            const int R = gridDim.x - G;
+            ok = wait_word_ge(ctx, counter_ptr(ctx, ctx.rank, a.counter_base + m_blk), R, kDevTimeoutChunkFlag, owner,
+                              71);
+            if (!ok) {
+              *abort = 1;
+              break;
+            }
+            ptx::fence_proxy_async_global();
+          }
+        }
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!ptx::mbar_wait(&ctl->empty[stage], phase ^ 1, abort)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          ptx::mbar_arrive_expect_tx(&ctl->full[stage], kStageBytes);
+          ptx::tma_load_2d(sa, tma_a_cur, &ctl->full[stage], kb * kTileK, a_row);
+          ptx::tma_load_2d(sb, tb, &ctl->full[stage], kb * kTileK, n_blk * kTileN);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------- MMA issuer ---------------------------
+      constexpr uint32_t idesc = ptx::umma_idesc_f16(FMT, kTileM, kTileN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < sc.items && ok; item += G) {
+        const int split = item % sc.splits;
+        const int kb0 = split * sc.kb_per_split, kb1 = min(num_kb, kb0 + sc.kb_per_split);
+        if (!ptx::mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1, abort)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kTileN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!ptx::mbar_wait(&ctl->full[stage], phase, abort)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t sa = ptx::smem_u32(smem + stage * kStageBytes);
+          const uint64_t da = ptx::umma_desc_kmajor_sw128(sa);
+          const uint64_t db = ptx::umma_desc_kmajor_sw128(sa + kABytes);
+#pragma unroll
+          for (int k = 0; k < kTileK / 16; ++k) {
+            // Advancing 16 K-elements = 32 bytes inside the 128-byte swizzle atom: +2 in the (>>4) address field.
+            ptx::umma_f16(d_tmem, da + uint64_t(k * 2), db + uint64_t(k * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          ptx::umma_commit(&ctl->empty[stage]);  // stage reusable once these MMAs have read it
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        ptx::umma_commit(&ctl->tmem_full[acc]);  // accumulator complete
+        if (++acc == kAccStages) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else if (warp < 6) {
+    // --------------------------- epilogue -----------------------------
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    char* c_base = nullptr;
+    if constexpr (MODE == kGemmPlain || MODE == kGemmAg) c_base = static_cast<char*>(a.C) + a.c_emu_stride * blockIdx.y;
+    char* p_base = nullptr;
+    if constexpr (MODE == kGemmAr || MODE == kGemmRsNorm) p_base = static_cast<char*>(a.partial.p[ctx.rank]);
+    for (int item = blockIdx.x; item < sc.items; item += G) {
+      const int seq = item / sc.splits, split = item - seq * sc.splits;
+      int m_blk, n_blk;
+      sc.coord(seq, m_blk, n_blk);
+      if (!ptx::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort)) break;
+      ptx::tc_fence_after_sync();
+      const int r_in = q * 32 + lane;
+      const int row = m_blk * kTileM + r_in;
+      const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + acc * kTileN;
+      const int tile_id = m_blk * sc.tiles_n + n_blk;
+      float* ws_tile = nullptr;
+      if constexpr (MODE == kGemmPlain) {
+        if (sc.splits > 1)
+          ws_tile = splitk_partials(a.splitk_ws) + (size_t(tile_id) * sc.splits + split) * (kTileM * kTileN);
+      }
+#pragma unroll 2
+      for (int c = 0; c < kTileN / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32b_x32(t_addr + c * 32, r);
+        ptx::tmem_ld_wait();
+        const int col = n_blk * kTileN + c * 32;
+        if constexpr (MODE == kGemmPlain || MODE == kGemmAg) {
+          if (ws_tile != nullptr) {
+            // split-K: fp32 partial accumulator, tile-packed [128][256]
+            float4* dst = reinterpret_cast<float4*>(ws_tile + size_t(r_in) * kTileN + c * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                   __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+          } else if (row < a.M && col < a.N) {
+            const int valid = min(32, a.N - col);
+            cvt_store_32<T>(c_base + (size_t(row) * a.ldc + col) * 2, r, valid == 32 && (a.ldc % 8) == 0, valid);
+          }
+        } else {
+          // Tile-packed partial buffer: the whole (padded) tile is written so that reducers can stream it.
+          cvt_store_32<T>(p_base + size_t(tile_id) * kTileBytes + size_t(r_in) * (kTileN * 2) + c * 64, r, true, 32);
+        }
+      }
+      if constexpr (MODE == kGemmPlain) {
+        if (ws_tile != nullptr) {
+          // The last CTA to deliver this 32-row quadrant sums the splits in split order and writes C.
+          uint32_t* qcnt = static_cast<uint32_t*>(a.splitk_ws) + tile_id * 4 + q;
+          __syncwarp();
+          uint32_t prev = 0;
+          if (lane == 0) {
+            __threadfence();
+            prev = atomicAdd(qcnt, 1u);
+          }
+          prev = __shfl_sync(0xffffffffu, prev, 0);
+          if (prev == uint32_t(sc.splits - 1)) {
+            __threadfence();
+            if (lane == 0) *qcnt = 0;  // re-arm for the next call
+            const float* base = splitk_partials(a.splitk_ws) + size_t(tile_id) * sc.splits * (kTileM * kTileN);
+            for (int rr = 0; rr < 32; ++rr) {
+              const int grow = m_blk * kTileM + q * 32 + rr;
+              if (grow >= a.M) break;
+#pragma unroll
+              for (int half = 0; half < 2; ++half) {
+                const int cc = half * 128 + lane * 4;
+                float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int sp = 0; sp < sc.splits; ++sp) {
+                  const float4 v = __ldcg(reinterpret_cast<const float4*>(
+                      base + size_t(sp) * (kTileM * kTileN) + size_t(q * 32 + rr) * kTileN + cc));
+                  s.x += v.x;
+                  s.y += v.y;
+                  s.z += v.z;
+                  s.w += v.w;
+                }
+                const int gcol = n_blk * kTileN + cc;
+                if (gcol < a.N) {
+                  const float f[4] = {s.x, s.y, s.z, s.w};
+                  char* dst = c_base + (size_t(grow) * a.ldc + gcol) * 2;
+                  if (gcol + 4 <= a.N && (a.ldc % 4) == 0) {
+                    uint2 o;
+                    if constexpr (PackTraits<T>::kDType == kBF16) {
+                      __nv_bfloat162 h0 = __floats2bfloat162_rn(f[0], f[1]), h1 = __floats2bfloat162_rn(f[2], f[3]);
+                      o.x = *reinterpret_cast<uint32_t*>(&h0);
+                      o.y = *reinterpret_cast<uint32_t*>(&h1);
+                    } else {
+                      __half2 h0 = __floats2half2_rn(f[0], f[1]), h1 = __floats2half2_rn(f[2], f[3]);
+                      o.x = *reinterpret_cast<uint32_t*>(&h0);
+                      o.y = *reinterpret_cast<uint32_t*>(&h1);
+                    }
+                    *reinterpret_cast<uint2*>(dst) = o;
+                  } else {
+                    for (int i = 0; i < 4 && gcol + i < a.N; ++i)
+                      reinterpret_cast<T*>(dst)[i] = PackTraits<T>::from_float(f[i]);
+                  }
+                }
+              }
+            }
+          }
+        }
+      }
+      if constexpr (MODE == kGemmAr || MODE == kGemmRsNorm) {
+        // The last of the four epilogue warps to finish its rows publishes one arrival for the tile.  The
+        // count is taken BEFORE the TMEM stage is handed back, so arrivals of the next tile that uses the
+        // same stage cannot mix with this tile's.
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();
+          if ((atomicAdd(&ctl->epi_count[acc], 1u) & 3u) == 3u) {
+            ptx::fence_acq_rel_sys();
+            if constexpr (MODE == kGemmAr) {
+              const int owner = seq % ctx.world;
+              ptx::red_release_sys_add(counter_ptr(ctx, owner, a.counter_base + seq / ctx.world), 1u);
+            } else {
+              const int owner = m_blk / sc.bps;
+              ptx::red_release_sys_add(counter_ptr(ctx, owner, a.counter_base + (m_blk - owner * sc.bps)), 1u);
+            }
+          }
+        }
+      }
+      // Accumulator drained: hand the TMEM stage back to the MMA warp.
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
+      if (++acc == kAccStages) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // ---- teardown -----------------------------------------------------------
+  __syncthreads();
+  const bool aborted = *abort != 0;
+  if (aborted) {
+    // Give copies that may still be in flight time to land before shared memory is released.
+    if (threadIdx.x == 0) {
+      gemm_report(ctx.status, ctx.rank, kDevTimeoutMbarrier, 80);
+      const uint64_t t0 = ptx::globaltimer_ns();
+      while (ptx::globaltimer_ns() - t0 < 200000) __nanosleep(1000);
+    }
+    __syncthreads();
+  }
+  if constexpr (MODE == kGemmAg) {
+    // Last GEMM CTA out re-arms the chunk flags (every flag has reached its final value by now).
+    if (threadIdx.x == 0 && !aborted) {
+      uint32_t* done = counter_ptr(ctx, ctx.rank, a.counter_base + sc.tiles_m);
+      __threadfence();
+      if (atomicAdd(done, 1u) == uint32_t(G - 1)) {
+        for (int i = 0; i < sc.tiles_m; ++i) *counter_ptr(ctx, ctx.rank, a.counter_base + i) = 0;
+        *done = 0;
+        __threadfence();
+      }
+    }
+  }
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+  // GEMM CTAs that are done computing help with the reduction of what is still in flight.
+  if constexpr (MODE == kGemmAr) {
+    if (!aborted) ar_reducer_role<T, THREADS>(ctx, a, sc);
+  }
+  if constexpr (MODE == kGemmRsNorm) {
+    if (!aborted) rs_reducer_role<T, THREADS>(ctx, a, sc);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+
+// 2-D tensor map over a row-major [rows, cols] 16-bit matrix; box = box_rows x 64 elements, 128-byte swizzle.
+typedef bool (*TmapFn)(CUtensorMap* out, const void* p, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows);
+
+inline int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+// `emu_table_dev`: device memory for 3 * kMaxRanks tensor maps (emulation only; may be null otherwise).
+template <typename T, int MODE>
+cudaError_t launch_mode(const CommCtx& ctx, const GemmArgs& a, cudaStream_t stream, TmapFn make_tmap,
+                        CUtensorMap* emu_table_dev) {
+  constexpr int THREADS = MODE == kGemmPlain ? kThreadsPlain : kThreadsFused;
+  auto kernel = gemm_kernel<T, MODE>;
+  static uint64_t attr_set_mask = 0;  // per device (one bit each)
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!(attr_set_mask >> (dev & 63) & 1)) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set_mask |= uint64_t(1) << (dev & 63);
+  }
+  const bool emu = ctx.emu_table != nullptr;
+  const int world = ctx.world;
+  const int tiles = ((a.M + kTileM - 1) / kTileM) * ((a.N + kTileN - 1) / kTileN);
+  const int splits = (MODE == kGemmPlain && a.splits > 1) ? a.splits : 1;
+  int budget = a.max_ctas > 0 ? a.max_ctas : sm_count();
+  if (emu) budget = budget / world;
+  int comm = MODE == kGemmPlain ? 0 : (a.comm_ctas > 0 ? a.comm_ctas : 16);
+  if (comm > budget / 2) comm = budget / 2;
+  if (MODE != kGemmPlain && comm < 1) return cudaErrorInvalidValue;
+  int gemm_ctas = budget - comm;
+  if (gemm_ctas > tiles * splits) gemm_ctas = tiles * splits;
+  if (gemm_ctas < 1) return cudaErrorInvalidValue;
+
+  const int shard_rows = a.M / world;
+  CUtensorMap ta, tb, tal;
+  EmuMaps em{nullptr};
+  if (!emu) {
+    const void* a_ptr = MODE == kGemmAg ? a.a_full.p[ctx.rank] : a.A;
+    const uint64_t a_ld = MODE == kGemmAg ? uint64_t(a.K) : uint64_t(a.lda);
+    if (!make_tmap(&ta, a_ptr, a.M, a.K, a_ld, kTileM)) return cudaErrorInvalidValue;
+    if (!make_tmap(&tb, a.B, a.N, a.K, a.ldb, kTileN)) return cudaErrorInvalidValue;
+    if (MODE == kGemmAg) {
+      if (!make_tmap(&tal, a.A, shard_rows, a.K, a.lda, kTileM)) return cudaErrorInvalidValue;
+    } else {
+      tal = ta;
+    }
+  } else {
+    if (emu_table_dev == nullptr) return cudaErrorInvalidValue;
+    CUtensorMap host[3 * kMaxRanks];
+    for (int r = 0; r < world; ++r) {
+      const char* A_r = static_cast<const char*>(a.A) + a.a_emu_stride * r;
+      const char* B_r = static_cast<const char*>(a.B) + a.b_emu_stride * r;
+      const void* a_ptr = MODE == kGemmAg ? a.a_full.p[r] : static_cast<const void*>(A_r);
+      const uint64_t a_ld = MODE == kGemmAg ? uint64_t(a.K) : uint64_t(a.lda);
+      if (!make_tmap(&host[3 * r + 0], a_ptr, a.M, a.K, a_ld, kTileM)) return cudaErrorInvalidValue;
+      if (!make_tmap(&host[3 * r + 1], B_r, a.N, a.K, a.ldb, kTileN)) return cudaErrorInvalidValue;
+      if (MODE == kGemmAg) {
+        if (!make_tmap(&host[3 * r + 2], A_r, shard_rows, a.K, a.lda, kTileM)) return cudaErrorInvalidValue;
+      } else {
+        host[3 * r + 2] = host[3 * r + 0];
+      }
+    }
+    // Synchronous on purpose: the emulation path is a test harness.
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return e;
+    e = cudaMemcpy(emu_table_dev, host, sizeof(CUtensorMap) * 3 * world, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return e;
+    em.table = emu_table_dev;
+    ta = tb = tal = host[0];
+  }
+
+  const int grid_x = gemm_ctas + comm;
+  if (emu) {
+    dim3 grid(grid_x, world);
+    CommCtx c = ctx;
+    GemmArgs aa = a;
+    int g = gemm_ctas;
+    void* argv[] = {(void*)&ta, (void*)&tb, (void*)&tal, (void*)&em, (void*)&c, (void*)&aa, (void*)&g};
+    return cudaLaunchCooperativeKernel((const void*)kernel, grid, dim3(THREADS), argv, kSmemBytes, stream);
+  }
+  kernel<<<dim3(grid_x, 1), THREADS, kSmemBytes, stream>>>(ta, tb, tal, em, ctx, a, gemm_ctas);
+  return cudaGetLastError();
+}
+
+// Bytes of split-K workspace for a problem: the counter block plus the fp32 partial tiles.
+inline size_t splitk_workspace_bytes(int M, int N, int splits) {
+  const size_t tiles = size_t((M + kTileM - 1) / kTileM) * ((N + kTileN - 1) / kTileN);
+  return kSplitkCounterBytes + tiles * splits * (size_t(kTileM) * kTileN * 4);
+}
+
+// Number of K splits that leaves no split empty (each split gets ceil(num_kb / splits) K blocks).
+inline int normalize_splits(int K, int want) {
+  const int num_kb = (K + kTileK - 1) / kTileK;
+  if (want < 1) want = 1;
+  if (want > num_kb) want = num_kb;
+  const int per = (num_kb + want - 1) / want;
+  return (num_kb + per - 1) / per;
+}
+
+}  // namespace gemm_detail
+}  // namespace oob

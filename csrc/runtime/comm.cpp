@@ -918,6 +918,9 @@ int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream) {
   g.c_emu_stride = emu ? a->c_emu_stride : 0;
   g.comm_ctas = a->comm_ctas;
   g.max_ctas = a->max_ctas;
+  g.use_nvls = a->use_nvls;
+  g.splits = a->splits;
+  g.splitk_ws = nullptr;
   g.counter_base = a->counter_base;
   g.residual = a->residual;
   g.weight = a->weight;

@@ -67,7 +67,8 @@ class GemmArgs(Structure):
                 ("comm_ctas", c_int), ("max_ctas", c_int), ("partial_reg", c_int), ("partial_off", c_uint64),
                 ("c_reg", c_int), ("c_off", c_uint64), ("counter_base", c_int), ("residual", c_void_p),
                 ("weight", c_void_p), ("eps", c_float), ("y_local", c_void_p), ("res_out_local", c_void_p),
-                ("rs_emu_stride", c_uint64), ("a_full_reg", c_int), ("a_full_off", c_uint64)]
+                ("rs_emu_stride", c_uint64), ("a_full_reg", c_int), ("a_full_off", c_uint64), ("use_nvls", c_int),
+                ("splits", c_int)]
 
 
 _lock = threading.Lock()

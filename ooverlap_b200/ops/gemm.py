@@ -35,8 +35,13 @@ def fill_gemm_args(args: _lib.GemmArgs, a: torch.Tensor, b: torch.Tensor) -> Non
     args.B, args.ldb = b.data_ptr(), b.stride(0)
 
 
-def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, max_ctas: int = 0) -> torch.Tensor:
-    """``out = a @ b.T`` with fp32 accumulation in TMEM."""
+def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, max_ctas: int = 0,
+         splits: int = 0) -> torch.Tensor:
+    """``out = a @ b.T`` with fp32 accumulation in TMEM.
+
+    ``splits`` > 1 splits K over that many CTAs per output tile (fp32 partials in the library's workspace,
+    summed in split order); 0 picks a split from the shape (small-M problems that would otherwise leave most
+    SMs idle), 1 turns it off."""
     _check_operands(a, b)
     M, N = a.shape[0], b.shape[0]
     if out is None:
@@ -48,5 +53,6 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     fill_gemm_args(args, a, b)
     args.C, args.ldc = out.data_ptr(), out.stride(0)
     args.max_ctas = max_ctas
+    args.splits = splits
     _lib.check(_lib.lib().oob_gemm(None, ctypes.byref(args), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return out

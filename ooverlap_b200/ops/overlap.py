@@ -37,6 +37,16 @@ def _emulated(comm) -> bool:
     return bool(getattr(comm, "emulated", False))
 
 
+def _use_nvls(comm, choice: Optional[bool]) -> int:
+    """NVLS (in-switch reduction / broadcast) pays off from four ranks on; between two GPUs plain peer
+    loads and stores are faster.  ``choice`` overrides the default."""
+    if not getattr(comm, "nvls", False):
+        return 0
+    if choice is None:
+        return 1 if comm.world >= 4 else 0
+    return 1 if choice else 0
+
+
 def _operands(comm, a: torch.Tensor, b: torch.Tensor):
     """In emulation ``a`` and ``b`` are stacked ``[world, ...]``; returns (a0, b0, a_stride, b_stride)."""
     if _emulated(comm):
@@ -47,7 +57,9 @@ def _operands(comm, a: torch.Tensor, b: torch.Tensor):
 
 
 class GemmAllReduce:
-    def __init__(self, comm, M: int, N: int, dtype: torch.dtype, *, comm_ctas: int = 20, max_ctas: int = 0):
+    def __init__(self, comm, M: int, N: int, dtype: torch.dtype, *, comm_ctas: int = 20, max_ctas: int = 0,
+                 use_nvls: Optional[bool] = None):
+        self.use_nvls = use_nvls
         self.comm, self.M, self.N, self.dtype = comm, M, N, dtype
         self.comm_ctas, self.max_ctas = comm_ctas, max_ctas
         self.fused = comm.world > 1
@@ -76,6 +88,7 @@ class GemmAllReduce:
         fill_gemm_args(args, a0, b0)
         args.a_emu_stride, args.b_emu_stride = sa, sb
         args.comm_ctas, args.max_ctas = self.comm_ctas, self.max_ctas
+        args.use_nvls = _use_nvls(self.comm, self.use_nvls)
         args.partial_reg, args.partial_off = 0, self.partial_off
         args.c_reg, args.c_off = 0, self.c_off
         args.counter_base = self.counter_base
@@ -87,12 +100,14 @@ class GemmReduceScatterNorm:
     """``weight=None`` gives the plain GEMM->reduce-scatter (+ optional residual add)."""
 
     def __init__(self, comm, M: int, N: int, dtype: torch.dtype, *, eps: float = 1e-6, comm_ctas: int = 16,
+                 use_nvls: Optional[bool] = None,
                  max_ctas: int = 0):
         if comm.world < 2:
             raise ValueError("needs at least two ranks")
         if M % comm.world or (M // comm.world) % TILE_M:
             raise ValueError(f"M / world must be a multiple of {TILE_M}")
         self.comm, self.M, self.N, self.dtype, self.eps = comm, M, N, dtype, eps
+        self.use_nvls = use_nvls
         self.comm_ctas, self.max_ctas = comm_ctas, max_ctas
         lib = _lib.lib()
         self.partial_off = comm.alloc(int(lib.oob_gemm_partial_bytes(M, N)))
@@ -116,6 +131,7 @@ class GemmReduceScatterNorm:
         fill_gemm_args(args, a0, b0)
         args.a_emu_stride, args.b_emu_stride = sa, sb
         args.comm_ctas, args.max_ctas = self.comm_ctas, self.max_ctas
+        args.use_nvls = _use_nvls(self.comm, self.use_nvls)
         args.partial_reg, args.partial_off = 0, self.partial_off
         args.counter_base = self.counter_base
         args.residual = residual.data_ptr() if residual is not None else None
@@ -129,7 +145,9 @@ class GemmReduceScatterNorm:
 
 
 class AllGatherGemm:
-    def __init__(self, comm, M: int, K: int, dtype: torch.dtype, *, comm_ctas: int = 16, max_ctas: int = 0):
+    def __init__(self, comm, M: int, K: int, dtype: torch.dtype, *, comm_ctas: int = 16, max_ctas: int = 0,
+                 use_nvls: Optional[bool] = None):
+        self.use_nvls = use_nvls
         if comm.world < 2:
             raise ValueError("needs at least two ranks")
         if M % comm.world or (M // comm.world) % TILE_M:
@@ -163,6 +181,7 @@ class AllGatherGemm:
         args.a_emu_stride, args.b_emu_stride = sa, sb
         args.c_emu_stride = self.M * N * 2 if emu else 0
         args.comm_ctas, args.max_ctas = self.comm_ctas, self.max_ctas
+        args.use_nvls = _use_nvls(self.comm, self.use_nvls)
         args.a_full_reg, args.a_full_off = 0, self.a_full_off
         args.counter_base = self.counter_base
         _lib.check(_lib.lib().oob_gemm(self.comm._h, ctypes.byref(args), _stream()))

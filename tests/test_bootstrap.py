@@ -33,15 +33,14 @@ def _rank_allgather_and_fds(rank, world, key, tmpdir):
     assert lib.oob_bootstrap_exchange_fds(h, fd, fds) == 0, lib.oob_last_error()
     texts = []
     for r in range(world):
-        os.lseek(fds[r], 0, os.SEEK_SET)
-        texts.append(os.read(fds[r], 64).decode())
+        # positional read: a passed descriptor shares its file offset with the sender and the other receivers
+        texts.append(os.pread(fds[r], 64, 0).decode())
         os.close(fds[r])
     os.close(fd)
     # broadcast of one descriptor from rank 1
     bfd = ctypes.c_int(os.open(path, os.O_RDONLY) if rank == 1 else -1)
     assert lib.oob_bootstrap_broadcast_fd(h, 1, ctypes.byref(bfd)) == 0
-    os.lseek(bfd.value, 0, os.SEEK_SET)
-    btext = os.read(bfd.value, 64).decode()
+    btext = os.pread(bfd.value, 64, 0).decode()
     os.close(bfd.value)
     assert lib.oob_bootstrap_barrier(h) == 0
     lib.oob_bootstrap_destroy(h)

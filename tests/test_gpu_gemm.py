@@ -59,10 +59,33 @@ def test_cta_budget():
     from ooverlap_b200.ops import gemm
     a = torch.randn(1024, 512, device="cuda").bfloat16()
     b = torch.randn(1024, 512, device="cuda").bfloat16()
-    c_full = gemm(a, b)
-    c_few = gemm(a, b, max_ctas=7)
+    c_full = gemm(a, b, splits=1)  # same K order in both runs, so the bits must agree
+    c_few = gemm(a, b, max_ctas=7, splits=1)
     torch.cuda.synchronize()
     assert torch.equal(c_full, c_few)
+
+
+@pytest.mark.parametrize("shape", [(16, 8192, 1024), (128, 2048, 4096), (200, 520, 1032), (1, 256, 512)])
+@pytest.mark.parametrize("splits", [0, 2, 4, 8])
+def test_split_k(shape, splits):
+    """K split over several CTAs per tile (fp32 partials in the library workspace, summed in split order)."""
+    from ooverlap_b200.ops import gemm
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(K + splits)
+    a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    b = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    ref = _ref(a, b)
+    c1 = gemm(a, b, splits=splits)
+    c2 = gemm(a, b, splits=splits)  # counters re-armed by the first call
+    torch.cuda.synchronize()
+    assert (c1.float() - ref).abs().max().item() <= 1e-2 * max(1.0, ref.abs().max().item())
+    assert torch.equal(c1, c2)
+    # shapes of different size share (and regrow) the workspace
+    a2 = torch.randn(64, 2048, device="cuda", generator=g).half()
+    b2 = (torch.randn(4096, 2048, device="cuda", generator=g) / 45).half()
+    c3 = gemm(a2, b2, splits=4)
+    torch.cuda.synchronize()
+    assert (c3.float() - _ref(a2, b2)).abs().max().item() <= 2e-2
 
 
 def test_rejects_bad_operands():

@@ -145,8 +145,11 @@ def _rank_fused(rank, world, key):
         s = (torch.stack([t.float() for t in xs]).sum(0) + res.float()).to(dt).float()
         want = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + eps) * w.float()
         out.append((f"ar_norm {rows}", (y.float().cpu() - want).abs().max().item(), 6e-2))
-        # through NVLS the switch rounds the sum once before the residual is added: two roundings
-        out.append((f"ar_norm_res {rows}", ((ro.float().cpu() - s).abs() - s.abs() * 2 ** -6).max().item(), 1e-2))
+        # through NVLS the switch rounds the sum of the partials once before the residual is added, so the
+        # error scales with the operands (which may cancel), not with the result
+        sx = torch.stack([t.float() for t in xs]).sum(0)
+        allow = (sx.abs() + res.float().abs()) * 2 ** -7
+        out.append((f"ar_norm_res {rows}", ((ro.float().cpu() - s).abs() - allow).max().item(), 1e-3))
         # sequence-parallel form
         b, e = rows * rank // world, rows * (rank + 1) // world
         if rows % world == 0:
