@@ -155,6 +155,7 @@ typedef struct {
   uint64_t a_full_off;
   int use_nvls; /* fused modes: 0 = peer loads/stores only, non-zero = NVLS multimem when the heap has it */
   int splits;   /* plain mode: K splits per tile; 0 = chosen from the shape, 1 = off */
+  int no_join;  /* fused AR / RS: 1 = only the dedicated communication CTAs reduce */
 } oob_gemm_args_t;
 /* c may be NULL for OOB_GEMM_PLAIN. */
 int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream);

@@ -38,6 +38,7 @@ struct GemmArgs {
   int comm_ctas;  // CTAs reserved for the communication role (fused modes)
   int max_ctas;   // 0 = one CTA per SM
   int use_nvls;   // fused modes: 0 = peer loads/stores even when a multicast alias exists
+  int no_join;    // fused AR / RS: 1 = only the comm_ctas CTAs reduce (GEMM CTAs exit when out of tiles)
 
   // Plain mode: K split over `splits` CTAs per tile (0 = choose from the shape, 1 = off).  The fp32 partials
   // and their arrival counters live in splitk_ws (nullptr = the library's own workspace, grown on demand).

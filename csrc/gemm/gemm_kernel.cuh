@@ -193,11 +193,11 @@ __device__ __forceinline__ void reduce_pack_any(bool use_mc, const PeerPtrs& buf
 
 // Draws the next ticket of this launch.  The counter is re-armed by whoever draws the last ticket that can ever
 // be drawn: `total` in-range tickets plus one out-of-range ticket per CTA of the launch.
-__device__ __forceinline__ int draw_ticket(uint32_t* ticket, int total, int* s_slot) {
+__device__ __forceinline__ int draw_ticket(uint32_t* ticket, int total, int* s_slot, int drawers) {
   __syncthreads();
   if (threadIdx.x == 0) {
     const uint32_t t = atomicAdd(ticket, 1u);
-    if (t == uint32_t(total) + gridDim.x - 1) {
+    if (t == uint32_t(total + drawers - 1)) {
       *ticket = 0;
       __threadfence();
     }
@@ -207,6 +207,89 @@ __device__ __forceinline__ int draw_ticket(uint32_t* ticket, int total, int* s_s
   return *s_slot;
 }
 
+// Raw 16-byte pack of every rank (NR > 0: all loads issued back to back, no arithmetic in between, so that
+// many packs of many ranks are in flight per thread), or the in-switch sum (MC: one multimem load).
+template <typename T, int NR, bool MC>
+struct RawPack {
+  static constexpr int kSlots = MC ? 1 : (NR > 0 ? NR : 1);
+  uint4 v[kSlots];
+  __device__ __forceinline__ void load(const PeerPtrs& buf, size_t off, int world) {
+    if constexpr (MC) {
+      v[0] = reduce_pack_mc<T, kSum>(static_cast<const char*>(buf.mc) + off);
+    } else if constexpr (NR > 0) {
+#pragma unroll
+      for (int r = 0; r < NR; ++r) v[r] = ptx::ld_nc_v4(static_cast<const char*>(buf.p[r]) + off);
+    } else {
+      // Generic world size: reduced right away (sequential loads; fallback path only).
+      float acc[8];
+      reduce_pack_p2p_f32<T, kSum, 0>(buf, off, world, acc);
+      v[0] = make_uint4(0, 0, 0, 0);
+      generic_[0] = acc[0], generic_[1] = acc[1], generic_[2] = acc[2], generic_[3] = acc[3];
+      generic_[4] = acc[4], generic_[5] = acc[5], generic_[6] = acc[6], generic_[7] = acc[7];
+    }
+  }
+  __device__ __forceinline__ void sum(float (&acc)[8]) const {
+    using PT = PackTraits<T>;
+    if constexpr (MC) {
+      PT::unpack(v[0], acc);
+    } else if constexpr (NR > 0) {
+      PT::unpack(v[0], acc);
+#pragma unroll
+      for (int r = 1; r < NR; ++r) {
+        float f[8];
+        PT::unpack(v[r], f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = generic_[i];
+    }
+  }
+  float generic_[(!MC && NR == 0) ? 8 : 1];
+};
+
+// Packs per thread and batch for the reducer loops: bounded by registers (NR raw packs each).
+template <int NR, bool MC>
+constexpr int kReduceBatch = MC ? 8 : (NR == 0 ? 1 : (NR >= 8 ? 2 : 4));
+
+// All-reduce of one 128x256 tile: pull from every rank's tile-packed partial buffer, push into every rank's C.
+template <typename T, int THREADS, int NR, bool MC>
+__device__ __forceinline__ void ar_reduce_tile(const GemmArgs& a, int world, int rank, size_t tile_off, size_t c_off0,
+                                               size_t row_bytes, int rows_valid, int packs_valid_row) {
+  constexpr int U = kReduceBatch<NR, MC>;
+  for (int base = 0; base < kPacksPerTile; base += THREADS * U) {
+    RawPack<T, NR, MC> raw[U];
+    bool live[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int p = base + u * THREADS + threadIdx.x;
+      const int row = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
+      live[u] = p < kPacksPerTile && row < rows_valid && cp < packs_valid_row;
+      // Dead lanes load pack 0 of the tile (always mapped) instead of branching around the load.
+      raw[u].load(a.partial, tile_off + size_t(live[u] ? p : 0) * 16, world);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!live[u]) continue;
+      const int p = base + u * THREADS + threadIdx.x;
+      const int row = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
+      float acc[8];
+      raw[u].sum(acc);
+      const uint4 v = PackTraits<T>::pack(acc);
+      const size_t coff = c_off0 + size_t(row) * row_bytes + size_t(cp) * 16;
+      if constexpr (MC) {
+        ptx::multimem_st_v4(static_cast<char*>(a.c_sym.mc) + coff, v);
+      } else if constexpr (NR > 0) {
+#pragma unroll
+        for (int r = 0; r < NR; ++r) ptx::st_v4(static_cast<char*>(a.c_sym.p[(rank + r) % NR]) + coff, v);
+      } else {
+        for (int r = 0; r < world; ++r) ptx::st_v4(static_cast<char*>(a.c_sym.p[(rank + r) % world]) + coff, v);
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Communication roles
 // ---------------------------------------------------------------------------
@@ -214,7 +297,7 @@ __device__ __forceinline__ int draw_ticket(uint32_t* ticket, int total, int* s_s
 // GEMM->AR: owned tiles are those at schedule positions seq with seq % world == rank; ticket k is the k-th of them.
 // Counter layout from counter_base: [owned] arrivals per owned tile, then the ticket counter.
 template <typename T, int THREADS>
-__device__ void ar_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sched& sc) {
+__device__ void ar_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sched& sc, int drawers) {
   __shared__ int s_ok;
   __shared__ int s_ticket;
   const int world = ctx.world, rank = ctx.rank;
@@ -225,7 +308,7 @@ __device__ void ar_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
   uint32_t* ticket = counter_ptr(ctx, rank, a.counter_base + owned_max);
   bool ok = true;
   while (true) {
-    const int k = draw_ticket(ticket, owned, &s_ticket);
+    const int k = draw_ticket(ticket, owned, &s_ticket, drawers);
     if (k >= owned) break;
     const int seq = k * world + rank;
     if (threadIdx.x == 0) {
@@ -241,33 +324,17 @@ __device__ void ar_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
     const size_t tile_off = size_t(m_blk * sc.tiles_n + n_blk) * kTileBytes;
     const int rows_valid = min(kTileM, a.M - m_blk * kTileM);
     const int packs_valid_row = min(kPacksPerTileRow, (a.N - n_blk * kTileN) / 8);
-    constexpr int U = 4;
-    for (int base = 0; base < kPacksPerTile; base += THREADS * U) {
-      uint4 v[U];
-      bool live[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int p = base + u * THREADS + threadIdx.x;
-        const int row = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
-        live[u] = p < kPacksPerTile && row < rows_valid && cp < packs_valid_row;
-        if (live[u]) {
-          float acc[8];
-          reduce_pack_any<T>(use_mc, a.partial, tile_off + size_t(p) * 16, world, acc);
-          v[u] = PackTraits<T>::pack(acc);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (!live[u]) continue;
-        const int p = base + u * THREADS + threadIdx.x;
-        const int row = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
-        const size_t coff = size_t(m_blk * kTileM + row) * row_bytes + size_t(n_blk * kTileN + cp * 8) * 2;
-        if (use_mc) {
-          ptx::multimem_st_v4(static_cast<char*>(a.c_sym.mc) + coff, v[u]);
-        } else {
-          for (int r = 0; r < world; ++r) ptx::st_v4(static_cast<char*>(a.c_sym.p[(rank + r) % world]) + coff, v[u]);
-        }
-      }
+    const size_t c_off0 = size_t(m_blk * kTileM) * row_bytes + size_t(n_blk * kTileN) * 2;
+    if (use_mc) {
+      ar_reduce_tile<T, THREADS, 1, true>(a, world, rank, tile_off, c_off0, row_bytes, rows_valid, packs_valid_row);
+    } else if (world == 2) {
+      ar_reduce_tile<T, THREADS, 2, false>(a, world, rank, tile_off, c_off0, row_bytes, rows_valid, packs_valid_row);
+    } else if (world == 4) {
+      ar_reduce_tile<T, THREADS, 4, false>(a, world, rank, tile_off, c_off0, row_bytes, rows_valid, packs_valid_row);
+    } else if (world == 8) {
+      ar_reduce_tile<T, THREADS, 8, false>(a, world, rank, tile_off, c_off0, row_bytes, rows_valid, packs_valid_row);
+    } else {
+      ar_reduce_tile<T, THREADS, 0, false>(a, world, rank, tile_off, c_off0, row_bytes, rows_valid, packs_valid_row);
     }
   }
   // Block b of every rank is past its last tile: together (all blocks) this means every push into this rank's C
@@ -275,20 +342,117 @@ __device__ void ar_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
   if (ok) rank_barrier(ctx, blockIdx.x, 51);
 }
 
+// One ticket of the GEMM->RS tail: rows [r_begin, r_end) of an owned 128-row block.
+struct RsRowCtx {
+  size_t row_base0;  // byte offset of the block's first tile in the partial buffers
+  int lrow0;         // rank-local index of the block's first row
+  int r_begin, r_end;
+  const char* res;
+  char* y;
+  char* ro;
+  const char* wgt;
+  float* s_part;
+  float* s_total;
+};
+
+// PPT = packs per thread and row (N <= PPT * THREADS * 8).  For each row: all raw packs of all ranks are loaded
+// first (in batches bounded by registers), then summed, the residual is added, the row's mean square is reduced
+// over the CTA, and the normalised row is written.
+template <typename T, int THREADS, int NR, bool MC, int PPT>
+__device__ __forceinline__ void rs_process_rows(const GemmArgs& a, int world, const RsRowCtx& rc) {
+  using PT = PackTraits<T>;
+  constexpr int QB = MC ? PPT : (NR == 0 ? 1 : (NR >= 8 ? 1 : (NR == 4 ? 2 : PPT)));
+  const int packs_per_row = a.N / 8;
+  const size_t row_bytes = size_t(a.N) * 2;
+  for (int r_in = rc.r_begin; r_in < rc.r_end; ++r_in) {
+    const size_t lrow_off = size_t(rc.lrow0 + r_in) * row_bytes;
+    const size_t row_base = rc.row_base0 + size_t(r_in) * (kTileN * 2);
+    float v[PPT][8];
+#pragma unroll
+    for (int q0 = 0; q0 < PPT; q0 += QB) {
+      RawPack<T, NR, MC> raw[QB];
+#pragma unroll
+      for (int i = 0; i < QB; ++i) {
+        if (q0 + i < PPT) {
+          const int p = threadIdx.x + (q0 + i) * THREADS;
+          const int pc = p < packs_per_row ? p : 0;  // dead lanes reload pack 0 instead of branching
+          raw[i].load(a.partial, row_base + size_t(pc / kPacksPerTileRow) * kTileBytes + size_t(pc % kPacksPerTileRow) * 16,
+                      world);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < QB; ++i)
+        if (q0 + i < PPT) raw[i].sum(v[q0 + i]);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int q = 0; q < PPT; ++q) {
+      const int p = threadIdx.x + q * THREADS;
+      if (p < packs_per_row) {
+        if (rc.res != nullptr) {
+          const uint4 rv = ptx::ld_nc_v4(rc.res + lrow_off + size_t(p) * 16);
+          float rf[8];
+          PT::unpack(rv, rf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[q][i] += rf[i];
+          const uint4 rounded = PT::pack(v[q]);
+          PT::unpack(rounded, v[q]);
+        }
+        if (rc.ro != nullptr) ptx::st_v4(rc.ro + lrow_off + size_t(p) * 16, PT::pack(v[q]));
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += v[q][i] * v[q][i];
+      }
+    }
+    float scale = 1.f;
+    if (rc.wgt != nullptr) {
+      const float total_ss = cta_sum<THREADS>(ss, rc.s_part, rc.s_total);
+      scale = rsqrtf(total_ss / float(a.N) + a.eps);
+    }
+#pragma unroll
+    for (int q = 0; q < PPT; ++q) {
+      const int p = threadIdx.x + q * THREADS;
+      if (p < packs_per_row) {
+        float o[8];
+        if (rc.wgt != nullptr) {
+          const uint4 wv = *reinterpret_cast<const uint4*>(rc.wgt + size_t(p) * 16);
+          float wf[8];
+          PT::unpack(wv, wf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = v[q][i] * scale * wf[i];
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] = v[q][i];
+        }
+        ptx::st_v4(rc.y + lrow_off + size_t(p) * 16, PT::pack(o));
+      }
+    }
+  }
+}
+
+template <typename T, int THREADS, int PPT>
+__device__ __forceinline__ void rs_rows_dispatch(const GemmArgs& a, int world, bool use_mc, const RsRowCtx& rc) {
+  if (use_mc)
+    rs_process_rows<T, THREADS, 1, true, PPT>(a, world, rc);
+  else if (world == 2)
+    rs_process_rows<T, THREADS, 2, false, PPT>(a, world, rc);
+  else if (world == 4)
+    rs_process_rows<T, THREADS, 4, false, PPT>(a, world, rc);
+  else if (world == 8)
+    rs_process_rows<T, THREADS, 8, false, PPT>(a, world, rc);
+  else
+    rs_process_rows<T, THREADS, 0, false, PPT>(a, world, rc);
+}
+
 // GEMM->RS + residual + RMSNorm.  Ticket t = (owned row block t / kRsItemsPerBlock, row group t % kRsItemsPerBlock).
 // Counter layout from counter_base: [bps] tile arrivals per row block, [bps] finished items per row block, ticket.
 template <typename T, int THREADS>
-__device__ void rs_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sched& sc) {
+__device__ void rs_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sched& sc, int drawers) {
   __shared__ int s_ok;
   __shared__ int s_ticket;
   __shared__ float s_part[THREADS / 32];
   __shared__ float s_total;
-  using PT = PackTraits<T>;
-  constexpr int PPT = 6;  // N <= 6 * 384 * 8 = 18432
   const int world = ctx.world, rank = ctx.rank;
   const bool use_mc = a.partial.mc != nullptr && a.use_nvls != 0;
-  const int packs_per_row = a.N / 8;
-  const size_t row_bytes = size_t(a.N) * 2;
   const char* res = a.residual ? static_cast<const char*>(a.residual) + a.rs_emu_stride * blockIdx.y : nullptr;
   char* y = static_cast<char*>(a.y_local) + a.rs_emu_stride * blockIdx.y;
   char* ro = a.res_out_local ? static_cast<char*>(a.res_out_local) + a.rs_emu_stride * blockIdx.y : nullptr;
@@ -297,7 +461,7 @@ __device__ void rs_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
   uint32_t* ticket = counter_ptr(ctx, rank, a.counter_base + 2 * sc.bps);
   bool ok = true;
   while (true) {
-    const int t = draw_ticket(ticket, total, &s_ticket);
+    const int t = draw_ticket(ticket, total, &s_ticket, drawers);
     if (t >= total) break;
     const int lb = t / kRsItemsPerBlock, grp = t % kRsItemsPerBlock;
     uint32_t* cnt = counter_ptr(ctx, rank, a.counter_base + lb);
@@ -307,57 +471,24 @@ __device__ void rs_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
     __syncthreads();
     if (s_ok == 0) ok = false;
     if (ok) {
-      const int m_blk = rank * sc.bps + lb;
-      for (int r_in = grp * kRsRowsPerItem; r_in < (grp + 1) * kRsRowsPerItem; ++r_in) {
-        const size_t lrow_off = size_t(lb * kTileM + r_in) * row_bytes;
-        float v[PPT][8];
-        float ss = 0.f;
-#pragma unroll
-        for (int q = 0; q < PPT; ++q) {
-          const int p = threadIdx.x + q * THREADS;
-          if (p < packs_per_row) {
-            const int n_blk = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
-            const size_t off =
-                size_t(m_blk * sc.tiles_n + n_blk) * kTileBytes + size_t(r_in) * (kTileN * 2) + size_t(cp) * 16;
-            reduce_pack_any<T>(use_mc, a.partial, off, world, v[q]);
-            if (res != nullptr) {
-              const uint4 rv = ptx::ld_nc_v4(res + lrow_off + size_t(p) * 16);
-              float rf[8];
-              PT::unpack(rv, rf);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) v[q][i] += rf[i];
-              const uint4 rounded = PT::pack(v[q]);
-              PT::unpack(rounded, v[q]);
-            }
-            if (ro != nullptr) ptx::st_v4(ro + lrow_off + size_t(p) * 16, PT::pack(v[q]));
-#pragma unroll
-            for (int i = 0; i < 8; ++i) ss += v[q][i] * v[q][i];
-          }
-        }
-        float scale = 1.f;
-        if (wgt != nullptr) {
-          const float total_ss = cta_sum<THREADS>(ss, s_part, &s_total);
-          scale = rsqrtf(total_ss / float(a.N) + a.eps);
-        }
-#pragma unroll
-        for (int q = 0; q < PPT; ++q) {
-          const int p = threadIdx.x + q * THREADS;
-          if (p < packs_per_row) {
-            float o[8];
-            if (wgt != nullptr) {
-              const uint4 wv = *reinterpret_cast<const uint4*>(wgt + size_t(p) * 16);
-              float wf[8];
-              PT::unpack(wv, wf);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) o[i] = v[q][i] * scale * wf[i];
-            } else {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) o[i] = v[q][i];
-            }
-            ptx::st_v4(y + lrow_off + size_t(p) * 16, PT::pack(o));
-          }
-        }
-      }
+      RsRowCtx rc;
+      rc.row_base0 = size_t((rank * sc.bps + lb) * sc.tiles_n) * kTileBytes;
+      rc.lrow0 = lb * kTileM;
+      rc.r_begin = grp * kRsRowsPerItem;
+      rc.r_end = (grp + 1) * kRsRowsPerItem;
+      rc.res = res;
+      rc.y = y;
+      rc.ro = ro;
+      rc.wgt = wgt;
+      rc.s_part = s_part;
+      rc.s_total = &s_total;
+      const int ppt = (a.N / 8 + THREADS - 1) / THREADS;
+      if (ppt <= 2)
+        rs_rows_dispatch<T, THREADS, 2>(a, world, use_mc, rc);
+      else if (ppt <= 3)
+        rs_rows_dispatch<T, THREADS, 3>(a, world, use_mc, rc);
+      else
+        rs_rows_dispatch<T, THREADS, 6>(a, world, use_mc, rc);
     }
     // Whoever finishes the last row group of a block re-arms the block's counters for the next call.
     __syncthreads();
@@ -388,14 +519,26 @@ __device__ void ag_pusher_role(const CommCtx& ctx, const GemmArgs& a, const Sche
     const int row0 = c * kTileM;
     const int rows = min(kTileM, shard_rows - row0);
     const int total = rows * packs_per_row;
-    for (int p = j * THREADS + threadIdx.x; p < total; p += R * THREADS) {
-      const int row = row0 + p / packs_per_row, cp = p % packs_per_row;
-      const uint4 v = ptx::ld_nc_v4(src + size_t(row) * src_row_bytes + size_t(cp) * 16);
-      const size_t doff = size_t(rank * shard_rows + row) * row_bytes + size_t(cp) * 16;
-      if (use_mc) {
-        ptx::multimem_st_v4(static_cast<char*>(a.a_full.mc) + doff, v);
-      } else {
-        for (int r = 1; r < world; ++r) ptx::st_v4(static_cast<char*>(a.a_full.p[(rank + r) % world]) + doff, v);
+    constexpr int U = 8;
+    for (int pb = j * THREADS + threadIdx.x; pb < total; pb += R * THREADS * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int p = pb + u * R * THREADS;
+        const int pc = p < total ? p : pb;
+        v[u] = ptx::ld_nc_v4(src + size_t(row0 + pc / packs_per_row) * src_row_bytes + size_t(pc % packs_per_row) * 16);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int p = pb + u * R * THREADS;
+        if (p >= total) continue;
+        const int row = row0 + p / packs_per_row, cp = p % packs_per_row;
+        const size_t doff = size_t(rank * shard_rows + row) * row_bytes + size_t(cp) * 16;
+        if (use_mc) {
+          ptx::multimem_st_v4(static_cast<char*>(a.a_full.mc) + doff, v[u]);
+        } else {
+          for (int r = 1; r < world; ++r) ptx::st_v4(static_cast<char*>(a.a_full.p[(rank + r) % world]) + doff, v[u]);
+        }
       }
     }
     __syncthreads();
@@ -449,8 +592,9 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
   if constexpr (MODE != kGemmPlain) {
     if (static_cast<int>(blockIdx.x) >= gemm_ctas) {
       const int j = blockIdx.x - gemm_ctas, R = gridDim.x - gemm_ctas;
-      if constexpr (MODE == kGemmAr) ar_reducer_role<T, THREADS>(ctx, a, sc);
-      if constexpr (MODE == kGemmRsNorm) rs_reducer_role<T, THREADS>(ctx, a, sc);
+      const int drawers = a.no_join ? R : int(gridDim.x);
+      if constexpr (MODE == kGemmAr) ar_reducer_role<T, THREADS>(ctx, a, sc, drawers);
+      if constexpr (MODE == kGemmRsNorm) rs_reducer_role<T, THREADS>(ctx, a, sc, drawers);
       if constexpr (MODE == kGemmAg) ag_pusher_role<THREADS>(ctx, a, sc, j, R);
       return;
     }
@@ -742,10 +886,10 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
   }
   // GEMM CTAs that are done computing help with the reduction of what is still in flight.
   if constexpr (MODE == kGemmAr) {
-    if (!aborted) ar_reducer_role<T, THREADS>(ctx, a, sc);
+    if (!aborted && !a.no_join) ar_reducer_role<T, THREADS>(ctx, a, sc, int(gridDim.x));
   }
   if constexpr (MODE == kGemmRsNorm) {
-    if (!aborted) rs_reducer_role<T, THREADS>(ctx, a, sc);
+    if (!aborted && !a.no_join) rs_reducer_role<T, THREADS>(ctx, a, sc, int(gridDim.x));
   }
 }
 

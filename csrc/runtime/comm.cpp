@@ -920,6 +920,7 @@ int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream) {
   g.max_ctas = a->max_ctas;
   g.use_nvls = a->use_nvls;
   g.splits = a->splits;
+  g.no_join = a->no_join;
   g.splitk_ws = nullptr;
   g.counter_base = a->counter_base;
   g.residual = a->residual;

@@ -1,0 +1,223 @@
+"""GEMM + collective overlap benchmark: fused kernels of this library against cuBLAS + NCCL.
+
+Launch with one process per GPU::
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        -m ooverlap_b200.bench.overlap_bench --ops gemm_ar,gemm_rs_norm,ag_gemm --out overlap.jsonl
+
+Ops and shapes (tp = number of ranks):
+
+* ``gemm_ar``       fp16 ``A[M, 8192/tp] @ B[8192, 8192/tp]^T`` summed over ranks, M in {512, 2048, 8192}
+* ``gemm_rs_norm``  bf16 M = 4096 tokens, hidden 8192, K = 28672/tp, + residual + RMSNorm (eps 1e-6) on the rank's rows
+* ``ag_gemm``       bf16 all-gather of A[4096/tp, 8192] then ``@ B[28672/tp, 8192]^T``
+
+For each it times (CUDA-graph replay, CUDA events, max over ranks): the fused kernel over a few
+communication-CTA budgets and with/without NVLS, this library's unfused GEMM + collective, and
+torch.matmul (cuBLAS) + NCCL (+ a PyTorch RMSNorm for the tail).  Every line carries the roofline: the slower
+of FLOPs at the measured GEMM peak and bytes over NVLink at the measured link bandwidth.
+
+Capability parity: test/test.py:509-1043 (perf_overlap / baselines / speed-up summary) and
+tool/evaluate_sm90.py of the reference.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+from .. import Communicator
+from ..ops import AllGatherGemm, GemmAllReduce, GemmReduceScatterNorm, gemm, rmsnorm_reference
+
+GEMM_PEAK_TFLOPS = 1629.9   # measured cuBLAS bf16 burst on this machine class
+LINK_GBS = 770.0            # measured peer copy, per direction per GPU
+PER_GRAPH = 5
+
+
+def timed(fn, iters, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    graph = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(PER_GRAPH):
+                fn()
+        graph.replay()
+    except Exception:
+        graph = None
+    torch.cuda.synchronize()
+
+    def once(reps):
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            if graph is not None:
+                graph.replay()
+            else:
+                for _ in range(PER_GRAPH):
+                    fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / (reps * PER_GRAPH)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) * 1e3  # microseconds per call, max over ranks
+
+    # The ranks never start a measurement at exactly the same instant; the skew (tens of microseconds of host
+    # jitter) is paid once per measurement, so each measurement runs for at least ~30 ms of device time.
+    pilot = once(max(1, iters // PER_GRAPH))
+    reps = int(min(400, max(iters // PER_GRAPH, 30000.0 / max(pilot * PER_GRAPH, 1.0))))
+    trials = sorted(once(reps) for _ in range(3))
+    return trials[1]
+
+
+def main() -> int:
+    p = argparse.ArgumentParser()
+    p.add_argument("--ops", default="gemm_ar,gemm_rs_norm,ag_gemm")
+    p.add_argument("--iters", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--comm-ctas", default="8,20,32")
+    p.add_argument("--nvls", default="auto", help="auto | on | off | both")
+    p.add_argument("--join", default="on", help="on | off | both: GEMM CTAs join the reduction when out of tiles")
+    p.add_argument("--ms", default="512,2048,8192")
+    p.add_argument("--out", default="")
+    args = p.parse_args()
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    comm = Communicator(list(range(world)), rank, heap_bytes=3 << 30)
+    ctas = [int(c) for c in args.comm_ctas.split(",")]
+    nvls_opts = {"auto": [None], "on": [True], "off": [False], "both": [True, False]}[args.nvls]
+    join_opts = {"on": [True], "off": [False], "both": [True, False]}[args.join]
+    lines = []
+    gen = torch.Generator(device="cuda").manual_seed(100 + rank)
+
+    def emit(rec):
+        lines.append(rec)
+        if rank == 0:
+            print(json.dumps(rec), flush=True)
+
+    def roofline_us(flops_per_rank, link_bytes):
+        return max(flops_per_rank / (GEMM_PEAK_TFLOPS * 1e12), link_bytes / (LINK_GBS * 1e9)) * 1e6
+
+    if "gemm_ar" in args.ops:
+        N = K = 8192
+        k_local = K // world
+        dt = torch.float16
+        for M in [int(m) for m in args.ms.split(",")]:
+            a = torch.randn(M, k_local, device="cuda", generator=gen).to(dt)
+            b = (torch.randn(N, k_local, device="cuda", generator=gen) / K ** 0.5).to(dt)
+            msg = M * N * 2
+            roof = roofline_us(2.0 * M * N * k_local, 2.0 * (world - 1) / world * msg)
+            roof_nvls = roofline_us(2.0 * M * N * k_local, float(msg))
+            base = dict(op="gemm_ar", M=M, N=N, K=K, tp=world, dtype="fp16", roofline_p2p_us=round(roof, 1),
+                        roofline_nvls_us=round(roof_nvls, 1))
+            out = torch.empty(M, N, dtype=dt, device="cuda")
+
+            def cublas_nccl():
+                torch.matmul(a, b.t(), out=out)
+                dist.all_reduce(out)
+            us = timed(cublas_nccl, args.iters, args.warmup)
+            emit({**base, "impl": "cublas+nccl", "us": round(us, 1)})
+            us_gemm = timed(lambda: torch.matmul(a, b.t(), out=out), args.iters, args.warmup)
+            emit({**base, "impl": "cublas_gemm_only", "us": round(us_gemm, 1)})
+            sym = comm.empty((M, N), dt)
+
+            def ours_unfused():
+                gemm(a, b, out=sym, splits=1)
+                comm.all_reduce(sym)
+            emit({**base, "impl": "ours_unfused", "us": round(timed(ours_unfused, args.iters, args.warmup), 1)})
+            emit({**base, "impl": "ours_gemm_only", "us": round(timed(lambda: gemm(a, b, out=sym, splits=1), args.iters, args.warmup), 1)})
+            for c in ctas:
+                for nv in nvls_opts:
+                    for jn in join_opts:
+                        op = GemmAllReduce(comm, M, N, dt, comm_ctas=c, use_nvls=nv)
+                        op.join = jn
+                        us = timed(lambda: op(a, b), args.iters, args.warmup)
+                        emit({**base, "impl": "ours_fused", "comm_ctas": c, "nvls": nv, "join": jn, "us": round(us, 1),
+                              "roofline_frac": round((roof_nvls if comm.nvls and nv is not False else roof) / us, 3)})
+                        comm.free(op.partial_off)
+                        comm.free(op.c_off)
+                        comm.release_counters(op.counter_base)
+            torch.cuda.synchronize()
+            comm.check_status()
+
+    if "gemm_rs_norm" in args.ops and 4096 % (128 * world) == 0:
+        M, H, K = 4096, 8192, 28672 // world
+        dt = torch.bfloat16
+        a = torch.randn(M, K, device="cuda", generator=gen).to(dt)
+        b = (torch.randn(H, K, device="cuda", generator=gen) / 28672 ** 0.5).to(dt)
+        rows = M // world
+        res = torch.randn(rows, H, device="cuda", generator=gen).to(dt)
+        w = (1 + 0.02 * torch.randn(H, device="cuda", generator=gen)).to(dt)
+        roof = roofline_us(2.0 * M * H * K, (world - 1) / world * M * H * 2)
+        base = dict(op="gemm_rs_norm", M=M, N=H, K=K * world, tp=world, dtype="bf16", roofline_us=round(roof, 1))
+        full = torch.empty(M, H, dtype=dt, device="cuda")
+        shard = torch.empty(rows, H, dtype=dt, device="cuda")
+
+        def cublas_nccl_rs():
+            torch.matmul(a, b.t(), out=full)
+            dist.reduce_scatter_tensor(shard, full)
+            return rmsnorm_reference(shard, w, 1e-6, res)
+        emit({**base, "impl": "cublas+nccl_rs+torch_norm", "us": round(timed(cublas_nccl_rs, args.iters, args.warmup), 1)})
+        emit({**base, "impl": "cublas_gemm_only", "us": round(timed(lambda: torch.matmul(a, b.t(), out=full), args.iters, args.warmup), 1)})
+        for c in ctas:
+            for nv in nvls_opts:
+                op = GemmReduceScatterNorm(comm, M, H, dt, eps=1e-6, comm_ctas=c, use_nvls=nv)
+                y = torch.empty(rows, H, dtype=dt, device="cuda")
+                ro = torch.empty(rows, H, dtype=dt, device="cuda")
+                us = timed(lambda: op(a, b, w, res, y=y, residual_out=ro), args.iters, args.warmup)
+                emit({**base, "impl": "ours_fused", "comm_ctas": c, "nvls": nv, "us": round(us, 1),
+                      "roofline_frac": round(roof / us, 3)})
+                comm.free(op.partial_off)
+                comm.release_counters(op.counter_base)
+        torch.cuda.synchronize()
+        comm.check_status()
+
+    if "ag_gemm" in args.ops and 4096 % (128 * world) == 0 and world > 1:
+        M, K, N = 4096, 8192, 28672 // world
+        dt = torch.bfloat16
+        rows = M // world
+        a_shard = torch.randn(rows, K, device="cuda", generator=gen).to(dt)
+        b = (torch.randn(N, K, device="cuda", generator=gen) / K ** 0.5).to(dt)
+        roof = roofline_us(2.0 * M * N * K, (world - 1) / world * M * K * 2)
+        base = dict(op="ag_gemm", M=M, N=N * world, K=K, tp=world, dtype="bf16", roofline_us=round(roof, 1))
+        a_full = torch.empty(M, K, dtype=dt, device="cuda")
+        out = torch.empty(M, N, dtype=dt, device="cuda")
+
+        def nccl_ag_cublas():
+            dist.all_gather_into_tensor(a_full, a_shard)
+            torch.matmul(a_full, b.t(), out=out)
+        emit({**base, "impl": "nccl_ag+cublas", "us": round(timed(nccl_ag_cublas, args.iters, args.warmup), 1)})
+        emit({**base, "impl": "cublas_gemm_only", "us": round(timed(lambda: torch.matmul(a_full, b.t(), out=out), args.iters, args.warmup), 1)})
+        for c in ctas:
+            for nv in nvls_opts:
+                op = AllGatherGemm(comm, M, K, dt, comm_ctas=c, use_nvls=nv)
+                us = timed(lambda: op(a_shard, b, out=out), args.iters, args.warmup)
+                emit({**base, "impl": "ours_fused", "comm_ctas": c, "nvls": nv, "us": round(us, 1),
+                      "roofline_frac": round(roof / us, 3)})
+                comm.free(op.a_full_off)
+                comm.release_counters(op.counter_base)
+        torch.cuda.synchronize()
+        comm.check_status()
+
+    if rank == 0 and args.out:
+        with open(args.out, "w") as f:
+            for rec in lines:
+                f.write(json.dumps(rec) + "\n")
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -78,6 +78,7 @@ class Communicator:
         self._h = None
         self._cpu_group = cpu_group
         self._scratch = {}
+        self._view_cache = {}
         self._ipc_cache = {}
         self._ar_pool: Optional[SlotPool] = None
         self._ag_pool: Optional[SlotPool] = None
@@ -226,6 +227,12 @@ class Communicator:
         self._counter_next += n
         return base
 
+    def release_counters(self, base: int) -> None:
+        """Gives back every counter reserved at or after ``base`` (stack discipline; counters are zero
+        between calls because their consumers re-arm them)."""
+        if 0 <= base < self._counter_next:
+            self._counter_next = base
+
     # ------------------------------------------------------------- host sync
     def barrier(self) -> None:
         if self._h is None:
@@ -257,6 +264,20 @@ class Communicator:
         off = self.alloc(max(nbytes, 16))
         self._scratch[key] = (off, nbytes)
         return off
+
+    def scratch_view(self, key, shape, dtype: torch.dtype) -> torch.Tensor:
+        """A cached registered scratch tensor for ``key`` (same call order on every rank)."""
+        shape = tuple(int(s) for s in shape)
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        off = self._scratch_for(key, nbytes)
+        ck = (off, shape, dtype)
+        hit = self._view_cache.get(ck)
+        if hit is None:
+            hit = self._view_cache[ck] = self.view(off, shape, dtype)
+        return hit
 
     # ------------------------------------------------------------ all-reduce
     def all_reduce(self, x: torch.Tensor, op: str = "sum", *, algo: int = _lib.ALGO_AUTO, max_ctas: int = 0) -> torch.Tensor:
@@ -414,7 +435,14 @@ class Communicator:
         nbytes = n * torch.empty((), dtype=pool.dtype).element_size()
         if nbytes > pool.capacity_bytes:
             raise ValueError(f"{nbytes} bytes do not fit a {pool.capacity_bytes}-byte slot")
-        return self.view(pool.offsets[pool.next_index], shape, pool.dtype)
+        # Views are cached per (slot, shape): the hot path (and CUDA-graph capture) then creates no tensors.
+        key = (pool.offsets[pool.next_index], tuple(int(s) for s in shape), pool.dtype)
+        hit = self._view_cache.get(key)
+        if hit is None:
+            if len(self._view_cache) > 4096:
+                self._view_cache.clear()
+            hit = self._view_cache[key] = self.view(key[0], key[1], pool.dtype)
+        return hit
 
     def acquire_all_reduce_slot(self, shape) -> torch.Tensor:
         """View of the NEXT slot; a producer (e.g. a GEMM) writes its output straight into it."""

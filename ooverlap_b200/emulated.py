@@ -82,6 +82,10 @@ class EmulatedGroup:
         self._counter_next += n
         return base
 
+    def release_counters(self, base: int) -> None:
+        if 0 <= base < self._counter_next:
+            self._counter_next = base
+
     def check_status(self) -> None:
         torch.cuda.synchronize(self.device)
         _lib.check(_lib.lib().oob_comm_status(self._h, None))

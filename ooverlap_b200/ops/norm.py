@@ -86,10 +86,10 @@ def fused_allreduce_rmsnorm(comm, x: torch.Tensor, weight: torch.Tensor, eps: fl
         ro = residual_out if residual_out is not None else torch.empty_like(x)
         a.y_local, a.res_out_local = y.data_ptr(), ro.data_ptr()
     else:
-        y = out if out is not None and comm.heap_offset(out) is not None else comm.view(
-            comm._scratch_for(("norm_y", x.dtype, tuple(x.shape)), x.numel() * x.element_size()), x.shape, x.dtype)
-        ro = residual_out if residual_out is not None and comm.heap_offset(residual_out) is not None else comm.view(
-            comm._scratch_for(("norm_r", x.dtype, tuple(x.shape)), x.numel() * x.element_size()), x.shape, x.dtype)
+        y = out if out is not None and comm.heap_offset(out) is not None else comm.scratch_view(
+            ("norm_y", x.dtype, tuple(x.shape)), x.shape, x.dtype)
+        ro = residual_out if residual_out is not None and comm.heap_offset(residual_out) is not None else (
+            comm.scratch_view(("norm_r", x.dtype, tuple(x.shape)), x.shape, x.dtype))
         a.y_reg, a.y_off = 0, comm.heap_offset(y)
         a.res_out_reg, a.res_out_off = 0, comm.heap_offset(ro)
     _lib.check(_lib.lib().oob_fused_norm(comm._h, algo, ctypes.byref(a), max_ctas or 32, _stream()))

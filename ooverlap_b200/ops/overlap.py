@@ -89,6 +89,7 @@ class GemmAllReduce:
         args.a_emu_stride, args.b_emu_stride = sa, sb
         args.comm_ctas, args.max_ctas = self.comm_ctas, self.max_ctas
         args.use_nvls = _use_nvls(self.comm, self.use_nvls)
+        args.no_join = 0 if getattr(self, "join", True) else 1
         args.partial_reg, args.partial_off = 0, self.partial_off
         args.c_reg, args.c_off = 0, self.c_off
         args.counter_base = self.counter_base
@@ -132,6 +133,7 @@ class GemmReduceScatterNorm:
         args.a_emu_stride, args.b_emu_stride = sa, sb
         args.comm_ctas, args.max_ctas = self.comm_ctas, self.max_ctas
         args.use_nvls = _use_nvls(self.comm, self.use_nvls)
+        args.no_join = 0 if getattr(self, "join", True) else 1
         args.partial_reg, args.partial_off = 0, self.partial_off
         args.counter_base = self.counter_base
         args.residual = residual.data_ptr() if residual is not None else None
@@ -182,6 +184,7 @@ class AllGatherGemm:
         args.c_emu_stride = self.M * N * 2 if emu else 0
         args.comm_ctas, args.max_ctas = self.comm_ctas, self.max_ctas
         args.use_nvls = _use_nvls(self.comm, self.use_nvls)
+        args.no_join = 0 if getattr(self, "join", True) else 1
         args.a_full_reg, args.a_full_off = 0, self.a_full_off
         args.counter_base = self.counter_base
         _lib.check(_lib.lib().oob_gemm(self.comm._h, ctypes.byref(args), _stream()))

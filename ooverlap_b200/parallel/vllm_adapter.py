@@ -1,0 +1,262 @@
+"""vLLM tensor-parallel backend hook.
+
+``OoverlapAllReduce`` is a drop-in for vLLM's ``CustomAllreduce`` (the object
+``CudaCommunicator.ca_comm`` of vLLM 0.22: ``disabled``, ``should_custom_ar``,
+``custom_all_reduce``, ``capture``, ``close``) whose all-reduces run on this
+library's kernels, plus the extras of the reference adapter: ``all_gather``
+along any dimension, a direct-slot row-parallel linear (the GEMM writes straight
+into the registered slot that is then reduced in place), and ``destroy``.
+
+``install()`` wires it into vLLM without touching vLLM's files: it wraps
+``CudaCommunicator.__init__`` so that, when ``VLLM_FORCE_ALLREDUCE_BACKEND``
+is ``ooverlap``, ``ca_comm`` is an ``OoverlapAllReduce`` and the other
+fast paths (quick all-reduce, FlashInfer, torch symmetric memory) are turned
+off; failing to build the communicator raises instead of silently falling back,
+as the reference's forced-backend switch does.
+
+Environment (names follow the reference's ``VLLM_OOVERLAP_*`` family):
+
+  VLLM_FORCE_ALLREDUCE_BACKEND   auto | ooverlap | custom | pynccl  (``auto`` / unset: leave vLLM alone)
+  VLLM_OOVERLAP_RR_SLOTS         all-reduce ring slots (default 32)
+  VLLM_OOVERLAP_RR_CAPACITY_BYTES  bytes per slot (default 8 MiB)
+  VLLM_OOVERLAP_RR_DTYPE         bf16 | fp16 | fp32 (default bf16)
+  VLLM_OOVERLAP_AG_SLOTS / _AG_CAPACITY_BYTES / _AG_DTYPE   all-gather pool (4 x 64 MiB, bf16)
+  VLLM_OOVERLAP_BROKER_KEY       fixed rendezvous key (default: a UUID broadcast over the CPU group)
+  VLLM_OOVERLAP_DEBUG            verbose logging
+
+Capability parity: patches/vllm/v0.25.0/vllm/distributed/device_communicators/ooverlap_all_reduce.py:44-704
+(adapter), cuda_communicator.py:52-60,99-107,160-169,311-343,451-472 (forced backend), and
+model_executor/models/qwen2.py:84-120 (direct-slot row-parallel) of the reference.  The reference overwrites vLLM
+0.25.0 source files guarded by git-blob hashes; the vLLM installed here is 0.22, so the hook is a run-time patch.
+"""
+from __future__ import annotations
+
+import contextlib
+import os
+import uuid
+from typing import Optional
+
+import torch
+
+from ..comm import Communicator
+from ..utils.logging import logger
+
+_DTYPES = {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "fp16": torch.float16, "float16": torch.float16,
+           "half": torch.float16, "fp32": torch.float32, "float32": torch.float32}
+
+
+def _env_int(name: str, default: int) -> int:
+    v = os.environ.get(name)
+    return int(v) if v not in (None, "") else default
+
+
+def _env_dtype(name: str, default: str) -> torch.dtype:
+    v = os.environ.get(name, default).lower()
+    if v not in _DTYPES:
+        raise ValueError(f"{name}={v!r}: expected one of {sorted(_DTYPES)}")
+    return _DTYPES[v]
+
+
+def forced_backend() -> str:
+    v = os.environ.get("VLLM_FORCE_ALLREDUCE_BACKEND", "auto").strip().lower()
+    if v not in ("auto", "ooverlap", "custom", "pynccl", "nccl_symm"):
+        raise ValueError(f"VLLM_FORCE_ALLREDUCE_BACKEND={v!r} is not one of auto, ooverlap, custom, pynccl, nccl_symm")
+    return v
+
+
+def short_broker_key(seed: str) -> str:
+    """A rendezvous key short enough for a socket name (the reference keeps its prefix under 90 characters)."""
+    clean = "".join(c if c.isalnum() else "_" for c in seed)
+    return ("vllm_" + clean)[:48]
+
+
+class OoverlapAllReduce:
+    """All-reduce / all-gather backend for one tensor-parallel group (one process per GPU)."""
+
+    def __init__(self, group=None, device: Optional[torch.device | int | str] = None, *,
+                 communicator: Optional[Communicator] = None, max_size: Optional[int] = None):
+        self.disabled = True
+        self._IS_CAPTURING = False
+        self.comm: Optional[Communicator] = None
+        self.group = group
+        self.debug = os.environ.get("VLLM_OOVERLAP_DEBUG", "0") not in ("", "0")
+        self.rr_dtype = _env_dtype("VLLM_OOVERLAP_RR_DTYPE", "bf16")
+        self.rr_slots = _env_int("VLLM_OOVERLAP_RR_SLOTS", 32)
+        self.rr_capacity = _env_int("VLLM_OOVERLAP_RR_CAPACITY_BYTES", 8 << 20)
+        self.ag_dtype = _env_dtype("VLLM_OOVERLAP_AG_DTYPE", "bf16")
+        self.ag_slots = _env_int("VLLM_OOVERLAP_AG_SLOTS", 4)
+        self.ag_capacity = _env_int("VLLM_OOVERLAP_AG_CAPACITY_BYTES", 64 << 20)
+        self.max_size = max_size if max_size is not None else self.rr_capacity
+        if communicator is None:
+            communicator = self._build_communicator(group, device)
+        self.comm = communicator
+        self.rank, self.world_size = communicator.rank, communicator.world
+        self.device = torch.device("cuda", communicator.device)
+        if self.world_size == 1:
+            return  # nothing to reduce: stay disabled, callers fall through
+        communicator.init_round_robin_slots(self.rr_dtype, self.rr_capacity, self.rr_slots)
+        communicator.init_all_gather_slots(self.ag_dtype, self.ag_capacity, self.ag_slots)
+        self.disabled = False
+        logger.info("ooverlap backend ready: rank %d/%d on %s, %d x %d MiB all-reduce slots (%s), NVLS %s", self.rank,
+                    self.world_size, self.device, self.rr_slots, self.rr_capacity >> 20, self.rr_dtype, communicator.nvls)
+
+    # ------------------------------------------------------------------ setup
+    def _build_communicator(self, group, device) -> Communicator:
+        import torch.distributed as dist
+        if group is None:
+            group = dist.group.WORLD
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        if device is None:
+            device = torch.cuda.current_device()
+        index = torch.device(device).index if not isinstance(device, int) else device
+        if index is None:
+            index = torch.cuda.current_device()
+        # Every rank learns every rank's device index through the (CPU) group.
+        devices = [None] * world
+        dist.all_gather_object(devices, int(index), group=group)
+        key = os.environ.get("VLLM_OOVERLAP_BROKER_KEY")
+        if key is None:
+            box = [uuid.uuid4().hex if rank == 0 else None]
+            dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0), group=group)
+            key = box[0]
+        heap = (self.rr_slots * self.rr_capacity + self.ag_slots * self.ag_capacity + (256 << 20))
+        return Communicator(devices, rank, short_broker_key(key), heap_bytes=heap)
+
+    # ---------------------------------------------------- vLLM CustomAllreduce
+    def should_custom_ar(self, inp: torch.Tensor) -> bool:
+        if self.disabled or not inp.is_cuda or inp.device != self.device:
+            return False
+        if inp.dtype != self.rr_dtype or not inp.is_contiguous():
+            return False
+        nbytes = inp.numel() * inp.element_size()
+        return 0 < nbytes <= self.max_size and nbytes % 16 == 0
+
+    should_ooverlap_ar = should_custom_ar
+
+    def all_reduce(self, inp: torch.Tensor) -> Optional[torch.Tensor]:
+        """Copy into the next ring slot, reduce in place, return the slot view (it aliases pool memory and
+        stays valid until the ring wraps: ``VLLM_OOVERLAP_RR_SLOTS`` later all-reduces)."""
+        if not self.should_custom_ar(inp):
+            return None
+        return self.comm.all_reduce_round_robin(inp)
+
+    def custom_all_reduce(self, inp: torch.Tensor) -> Optional[torch.Tensor]:
+        out = self.all_reduce(inp)
+        if self.debug and out is not None:
+            logger.debug("all_reduce %s %s capturing=%s", tuple(inp.shape), inp.dtype, self._IS_CAPTURING)
+        return out
+
+    @contextlib.contextmanager
+    def capture(self):
+        """vLLM wraps CUDA-graph capture in this.  Slots have fixed addresses and the epoch counters of the
+        kernels live on the device, so nothing needs registering afterwards."""
+        self._IS_CAPTURING = True
+        try:
+            yield
+        finally:
+            self._IS_CAPTURING = False
+
+    def close(self) -> None:
+        if self.comm is not None:
+            self.comm.close()
+            self.comm = None
+        self.disabled = True
+
+    destroy = close
+
+    # ----------------------------------------------------------- all-gather
+    def should_all_gather(self, inp: torch.Tensor) -> bool:
+        if self.disabled or not inp.is_cuda or inp.dtype != self.ag_dtype:
+            return False
+        return inp.numel() * inp.element_size() * self.world_size <= self.ag_capacity
+
+    def all_gather(self, inp: torch.Tensor, dim: int = -1) -> Optional[torch.Tensor]:
+        """Gather along ``dim``: rank-major gather through the slot pool, then a ``movedim``/``reshape`` to put the
+        gathered axis in place (same data flow as the reference adapter)."""
+        if not self.should_all_gather(inp):
+            return None
+        if dim < 0:
+            dim += inp.dim()
+        x = inp.contiguous()
+        lead = x.reshape(1, -1) if x.dim() == 0 else x.reshape(x.shape[0], -1) if x.dim() > 1 else x.reshape(-1, 1)
+        gathered = self.comm.all_gather_round_robin(lead)           # [world * d0, rest]
+        gathered = gathered.reshape((self.world_size,) + tuple(x.shape))
+        gathered = gathered.movedim(0, dim)                          # [..., world, d_dim, ...]
+        shape = list(x.shape)
+        shape[dim] *= self.world_size
+        return gathered.reshape(shape)
+
+    # ------------------------------------------------ direct-slot row-parallel
+    def row_parallel(self, x: torch.Tensor, weight: torch.Tensor) -> Optional[torch.Tensor]:
+        """``all_reduce(x @ weight.T)`` for a bias-free, unquantised row-parallel layer: the GEMM (this library's
+        tcgen05 kernel) writes straight into the next registered slot, which is then reduced in place."""
+        from ..ops import gemm
+        if self.disabled or x.dtype != self.rr_dtype or weight.dtype != self.rr_dtype:
+            return None
+        x2 = x.reshape(-1, x.shape[-1])
+        out_shape = (x2.shape[0], weight.shape[0])
+        nbytes = out_shape[0] * out_shape[1] * x.element_size()
+        if nbytes > self.rr_capacity or x2.shape[1] % 8 or not x2.is_contiguous() or x2.shape[0] == 0:
+            return None
+        slot = self.comm.acquire_all_reduce_slot(out_shape)
+        gemm(x2, weight, out=slot)
+        out = self.comm.all_reduce_preloaded_slot(slot)
+        return out.reshape(tuple(x.shape[:-1]) + (weight.shape[0],))
+
+    qwen_row_parallel = row_parallel
+
+
+_installed = False
+
+
+def install() -> bool:
+    """Patches vLLM's ``CudaCommunicator`` in this process.  Returns True when the ``ooverlap`` backend is forced
+    and the patch is in place.  Call before vLLM builds its distributed groups (e.g. from a ``sitecustomize`` or at
+    the top of the serving script of every worker)."""
+    global _installed
+    mode = forced_backend()
+    if mode != "ooverlap":
+        return False
+    if _installed:
+        return True
+    from vllm.distributed.device_communicators import cuda_communicator as cc
+
+    original_init = cc.CudaCommunicator.__init__
+    original_all_gather = cc.CudaCommunicator.all_gather
+    original_destroy = cc.CudaCommunicator.destroy
+
+    def patched_init(self, *args, **kwargs):
+        original_init(self, *args, **kwargs)
+        if getattr(self, "world_size", 1) <= 1:
+            return
+        # Forced: no silent fallback.  Any failure to build the backend propagates.
+        self.ca_comm = OoverlapAllReduce(group=self.cpu_group, device=self.device)
+        for name in ("qr_comm", "fi_ar_comm", "symm_mem_comm"):
+            other = getattr(self, name, None)
+            if other is not None and hasattr(other, "destroy"):
+                try:
+                    other.destroy()
+                except Exception:  # noqa: BLE001
+                    pass
+            setattr(self, name, None)
+        logger.info("vLLM all-reduce backend forced to ooverlap")
+
+    def patched_all_gather(self, input_, dim: int = -1):
+        ca = getattr(self, "ca_comm", None)
+        if isinstance(ca, OoverlapAllReduce):
+            out = ca.all_gather(input_, dim)
+            if out is not None:
+                return out
+        return original_all_gather(self, input_, dim)
+
+    def patched_destroy(self):
+        ca = getattr(self, "ca_comm", None)
+        if isinstance(ca, OoverlapAllReduce):
+            ca.close()
+        return original_destroy(self)
+
+    cc.CudaCommunicator.__init__ = patched_init
+    cc.CudaCommunicator.all_gather = patched_all_gather
+    cc.CudaCommunicator.destroy = patched_destroy
+    _installed = True
+    return True

