@@ -48,7 +48,10 @@ constexpr int kPadEpochOffset = kPadInboxWords;
 constexpr int kPadCounterOffset = kPadEpochOffset + kMaxCommBlocks;
 constexpr int kPadCallEpochOffset = kPadCounterOffset + kNumCounters;  // 64 per-op call counters
 constexpr int kNumCallEpochs = 64;
-constexpr int kPadWords = kPadCallEpochOffset + kNumCallEpochs;
+// One word that mirrors "this rank has recorded an error" in DEVICE memory: waiters poll it instead of the
+// host-mapped status block (a poll loop must never read over PCIe).
+constexpr int kPadErrorFlagOffset = kPadCallEpochOffset + kNumCallEpochs;
+constexpr int kPadWords = kPadErrorFlagOffset + 16;
 constexpr uint64_t kPadBytes = ((uint64_t(kPadWords) * 4 + 4095) / 4096) * 4096;
 
 // Passed by value to every communicating kernel.

@@ -17,6 +17,7 @@ namespace oob {
 __device__ __forceinline__ void report_error(const CommCtx& ctx, int code, int peer, unsigned expected,
                                              unsigned observed, int where) {
   DeviceStatus* s = ctx.status;
+  if (ctx.pad[ctx.rank] != nullptr) atomicExch(ctx.pad[ctx.rank] + kPadErrorFlagOffset, static_cast<uint32_t>(code));
   if (s == nullptr) return;
   if (atomicCAS(&s->code, 0, code) == 0) {
     s->rank = ctx.rank;
@@ -40,14 +41,17 @@ __device__ __forceinline__ bool wait_word_ge(const CommCtx& ctx, const uint32_t*
   while (true) {
     v = ptx::ld_acquire_sys(p);
     if (static_cast<int32_t>(v - want) >= 0) return true;
-    if (++spins > 32) __nanosleep(spins > 2048 ? 200 : 20);
-    if ((spins & 63) == 0) {
+    if (++spins > 64) __nanosleep(spins > 4096 ? 100 : 20);
+    if ((spins & 255) == 0) {
       if (ptx::globaltimer_ns() - t0 > ctx.timeout_ns) {
         report_error(ctx, code, peer, want, v, where);
         return false;
       }
-      // Somebody on this rank already failed: do not wait out a second budget.
-      if (ctx.status != nullptr && *reinterpret_cast<volatile int*>(&ctx.status->code) != 0) return false;
+      // Somebody on this rank already failed: do not wait out a second budget.  (Device-memory mirror of the
+      // status code; the status block itself lives in host memory.)
+      if (ctx.pad[ctx.rank] != nullptr &&
+          *reinterpret_cast<volatile uint32_t*>(ctx.pad[ctx.rank] + kPadErrorFlagOffset) != 0)
+        return false;
     }
   }
 }

@@ -51,7 +51,9 @@ constexpr int kBBytes = kTileN * kTileK * 2;  // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kAccStages = 2;
 constexpr int kTmemCols = 512;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kEpiWarpBytes = 32 * 256;  // epilogue staging per warp: 32 rows x 128 16-bit columns
+constexpr int kEpiBytes = 4 * kEpiWarpBytes;
+constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int kThreadsPlain = 192;
 constexpr int kThreadsFused = 384;
 constexpr int kPacksPerTile = kTileBytes / 16;  // 4096
@@ -74,7 +76,7 @@ struct SmemCtl {
   uint64_t tmem_empty[kAccStages];
   uint32_t tmem_base;
   int abort;
-  uint32_t epi_count[kAccStages];  // epilogue warps that have stored their rows of the tile in this TMEM stage
+  uint32_t epi_count[4];  // epilogue warps that have stored their rows of a tile (slot = tile iteration & 3)
 };
 
 struct Sched {
@@ -174,23 +176,6 @@ __device__ __forceinline__ float cta_sum(float v, float* s_part, float* s_total)
   return *s_total;
 }
 
-// Sum of one 16-byte pack over all ranks, fp32 result, through the switch or by peer loads.
-template <typename T>
-__device__ __forceinline__ void reduce_pack_any(bool use_mc, const PeerPtrs& buf, size_t off, int world,
-                                                float (&acc)[8]) {
-  if (use_mc) {
-    PackTraits<T>::unpack(reduce_pack_mc<T, kSum>(static_cast<const char*>(buf.mc) + off), acc);
-  } else if (world == 2) {
-    reduce_pack_p2p_f32<T, kSum, 2>(buf, off, world, acc);
-  } else if (world == 4) {
-    reduce_pack_p2p_f32<T, kSum, 4>(buf, off, world, acc);
-  } else if (world == 8) {
-    reduce_pack_p2p_f32<T, kSum, 8>(buf, off, world, acc);
-  } else {
-    reduce_pack_p2p_f32<T, kSum, 0>(buf, off, world, acc);
-  }
-}
-
 // Draws the next ticket of this launch.  The counter is re-armed by whoever draws the last ticket that can ever
 // be drawn: `total` in-range tickets plus one out-of-range ticket per CTA of the launch.
 __device__ __forceinline__ int draw_ticket(uint32_t* ticket, int total, int* s_slot, int drawers) {
@@ -207,32 +192,36 @@ __device__ __forceinline__ int draw_ticket(uint32_t* ticket, int total, int* s_s
   return *s_slot;
 }
 
-// Raw 16-byte pack of every rank (NR > 0: all loads issued back to back, no arithmetic in between, so that
-// many packs of many ranks are in flight per thread), or the in-switch sum (MC: one multimem load).
-template <typename T, int NR, bool MC>
-struct RawPack {
-  static constexpr int kSlots = MC ? 1 : (NR > 0 ? NR : 1);
+// The partial products of all ranks for one tile sit side by side in the OWNER's memory (every rank's epilogue
+// pushed its slice there), kTileBytes apart.  Slices<> holds the raw 16-byte pack of every slice: all loads are
+// issued back to back, with no arithmetic in between, so that many local loads are in flight per thread.
+template <typename T, int NR>
+struct Slices {
+  static constexpr int kSlots = NR > 0 ? NR : 1;
   uint4 v[kSlots];
-  __device__ __forceinline__ void load(const PeerPtrs& buf, size_t off, int world) {
-    if constexpr (MC) {
-      v[0] = reduce_pack_mc<T, kSum>(static_cast<const char*>(buf.mc) + off);
-    } else if constexpr (NR > 0) {
+  float generic_[NR == 0 ? 8 : 1];
+  __device__ __forceinline__ void load(const char* base, int world) {
+    if constexpr (NR > 0) {
 #pragma unroll
-      for (int r = 0; r < NR; ++r) v[r] = ptx::ld_nc_v4(static_cast<const char*>(buf.p[r]) + off);
+      for (int r = 0; r < NR; ++r) v[r] = ptx::ld_nc_v4(base + size_t(r) * kTileBytes);
     } else {
-      // Generic world size: reduced right away (sequential loads; fallback path only).
+      // Generic world size: summed right away (fallback path).
+      using PT = PackTraits<T>;
       float acc[8];
-      reduce_pack_p2p_f32<T, kSum, 0>(buf, off, world, acc);
-      v[0] = make_uint4(0, 0, 0, 0);
-      generic_[0] = acc[0], generic_[1] = acc[1], generic_[2] = acc[2], generic_[3] = acc[3];
-      generic_[4] = acc[4], generic_[5] = acc[5], generic_[6] = acc[6], generic_[7] = acc[7];
+      PT::unpack(ptx::ld_nc_v4(base), acc);
+      for (int r = 1; r < world; ++r) {
+        float f[8];
+        PT::unpack(ptx::ld_nc_v4(base + size_t(r) * kTileBytes), f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) generic_[i] = acc[i];
     }
   }
   __device__ __forceinline__ void sum(float (&acc)[8]) const {
     using PT = PackTraits<T>;
-    if constexpr (MC) {
-      PT::unpack(v[0], acc);
-    } else if constexpr (NR > 0) {
+    if constexpr (NR > 0) {
       PT::unpack(v[0], acc);
 #pragma unroll
       for (int r = 1; r < NR; ++r) {
@@ -246,20 +235,20 @@ struct RawPack {
       for (int i = 0; i < 8; ++i) acc[i] = generic_[i];
     }
   }
-  float generic_[(!MC && NR == 0) ? 8 : 1];
 };
 
 // Packs per thread and batch for the reducer loops: bounded by registers (NR raw packs each).
-template <int NR, bool MC>
-constexpr int kReduceBatch = MC ? 8 : (NR == 0 ? 1 : (NR >= 8 ? 2 : 4));
+template <int NR>
+constexpr int kReduceBatch = NR == 0 ? 1 : (NR >= 8 ? 3 : (NR == 4 ? 6 : 8));
 
-// All-reduce of one 128x256 tile: pull from every rank's tile-packed partial buffer, push into every rank's C.
+// All-reduce of one 128x256 tile: sum the `world` local slices (fp32, rank order) and push the result into every
+// rank's C, through the switch (multimem.st) or with peer stores.
 template <typename T, int THREADS, int NR, bool MC>
-__device__ __forceinline__ void ar_reduce_tile(const GemmArgs& a, int world, int rank, size_t tile_off, size_t c_off0,
-                                               size_t row_bytes, int rows_valid, int packs_valid_row) {
-  constexpr int U = kReduceBatch<NR, MC>;
+__device__ __forceinline__ void ar_reduce_tile(const GemmArgs& a, int world, int rank, const char* slices,
+                                               size_t c_off0, size_t row_bytes, int rows_valid, int packs_valid_row) {
+  constexpr int U = kReduceBatch<NR>;
   for (int base = 0; base < kPacksPerTile; base += THREADS * U) {
-    RawPack<T, NR, MC> raw[U];
+    Slices<T, NR> raw[U];
     bool live[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -267,7 +256,7 @@ __device__ __forceinline__ void ar_reduce_tile(const GemmArgs& a, int world, int
       const int row = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
       live[u] = p < kPacksPerTile && row < rows_valid && cp < packs_valid_row;
       // Dead lanes load pack 0 of the tile (always mapped) instead of branching around the load.
-      raw[u].load(a.partial, tile_off + size_t(live[u] ? p : 0) * 16, world);
+      raw[u].load(slices + size_t(live[u] ? p : 0) * 16, world);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -290,19 +279,35 @@ __device__ __forceinline__ void ar_reduce_tile(const GemmArgs& a, int world, int
   }
 }
 
+template <typename T, int THREADS, bool MC>
+__device__ __forceinline__ void ar_reduce_tile_dispatch(const GemmArgs& a, int world, int rank, const char* slices,
+                                                        size_t c_off0, size_t row_bytes, int rows_valid,
+                                                        int packs_valid_row) {
+  if (world == 2)
+    ar_reduce_tile<T, THREADS, 2, MC>(a, world, rank, slices, c_off0, row_bytes, rows_valid, packs_valid_row);
+  else if (world == 4)
+    ar_reduce_tile<T, THREADS, 4, MC>(a, world, rank, slices, c_off0, row_bytes, rows_valid, packs_valid_row);
+  else if (world == 8)
+    ar_reduce_tile<T, THREADS, 8, MC>(a, world, rank, slices, c_off0, row_bytes, rows_valid, packs_valid_row);
+  else
+    ar_reduce_tile<T, THREADS, 0, MC>(a, world, rank, slices, c_off0, row_bytes, rows_valid, packs_valid_row);
+}
+
 // ---------------------------------------------------------------------------
 // Communication roles
 // ---------------------------------------------------------------------------
 
 // GEMM->AR: owned tiles are those at schedule positions seq with seq % world == rank; ticket k is the k-th of them.
+// Staging layout in the owner's partial buffer: [k][source rank][128][256].
 // Counter layout from counter_base: [owned] arrivals per owned tile, then the ticket counter.
 template <typename T, int THREADS>
 __device__ void ar_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sched& sc, int drawers) {
   __shared__ int s_ok;
   __shared__ int s_ticket;
   const int world = ctx.world, rank = ctx.rank;
-  const bool use_mc = a.partial.mc != nullptr && a.c_sym.mc != nullptr && a.use_nvls != 0;
+  const bool use_mc = a.c_sym.mc != nullptr && a.use_nvls != 0;  // broadcast of the result through the switch
   const size_t row_bytes = size_t(a.N) * 2;
+  const char* staged = static_cast<const char*>(a.partial.p[rank]);
   const int owned = (sc.tiles - rank + world - 1) / world;  // tickets that map to a tile
   const int owned_max = (sc.tiles + world - 1) / world;
   uint32_t* ticket = counter_ptr(ctx, rank, a.counter_base + owned_max);
@@ -321,21 +326,14 @@ __device__ void ar_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
     if (!ok) continue;  // keep drawing so that the ticket counter still gets re-armed
     int m_blk, n_blk;
     sc.coord(seq, m_blk, n_blk);
-    const size_t tile_off = size_t(m_blk * sc.tiles_n + n_blk) * kTileBytes;
+    const char* slices = staged + size_t(k) * world * kTileBytes;  // [world][128][256] pushed by the epilogues
     const int rows_valid = min(kTileM, a.M - m_blk * kTileM);
     const int packs_valid_row = min(kPacksPerTileRow, (a.N - n_blk * kTileN) / 8);
     const size_t c_off0 = size_t(m_blk * kTileM) * row_bytes + size_t(n_blk * kTileN) * 2;
-    if (use_mc) {
-      ar_reduce_tile<T, THREADS, 1, true>(a, world, rank, tile_off, c_off0, row_bytes, rows_valid, packs_valid_row);
-    } else if (world == 2) {
-      ar_reduce_tile<T, THREADS, 2, false>(a, world, rank, tile_off, c_off0, row_bytes, rows_valid, packs_valid_row);
-    } else if (world == 4) {
-      ar_reduce_tile<T, THREADS, 4, false>(a, world, rank, tile_off, c_off0, row_bytes, rows_valid, packs_valid_row);
-    } else if (world == 8) {
-      ar_reduce_tile<T, THREADS, 8, false>(a, world, rank, tile_off, c_off0, row_bytes, rows_valid, packs_valid_row);
-    } else {
-      ar_reduce_tile<T, THREADS, 0, false>(a, world, rank, tile_off, c_off0, row_bytes, rows_valid, packs_valid_row);
-    }
+    if (use_mc)
+      ar_reduce_tile_dispatch<T, THREADS, true>(a, world, rank, slices, c_off0, row_bytes, rows_valid, packs_valid_row);
+    else
+      ar_reduce_tile_dispatch<T, THREADS, false>(a, world, rank, slices, c_off0, row_bytes, rows_valid, packs_valid_row);
   }
   // Block b of every rank is past its last tile: together (all blocks) this means every push into this rank's C
   // has been issued and released, and nobody reads this rank's partial buffer any more.
@@ -344,7 +342,7 @@ __device__ void ar_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
 
 // One ticket of the GEMM->RS tail: rows [r_begin, r_end) of an owned 128-row block.
 struct RsRowCtx {
-  size_t row_base0;  // byte offset of the block's first tile in the partial buffers
+  const char* row_base0;  // the block's first staged tile: layout [n_blk][source rank][128][256]
   int lrow0;         // rank-local index of the block's first row
   int r_begin, r_end;
   const char* res;
@@ -358,25 +356,25 @@ struct RsRowCtx {
 // PPT = packs per thread and row (N <= PPT * THREADS * 8).  For each row: all raw packs of all ranks are loaded
 // first (in batches bounded by registers), then summed, the residual is added, the row's mean square is reduced
 // over the CTA, and the normalised row is written.
-template <typename T, int THREADS, int NR, bool MC, int PPT>
+template <typename T, int THREADS, int NR, int PPT>
 __device__ __forceinline__ void rs_process_rows(const GemmArgs& a, int world, const RsRowCtx& rc) {
   using PT = PackTraits<T>;
-  constexpr int QB = MC ? PPT : (NR == 0 ? 1 : (NR >= 8 ? 1 : (NR == 4 ? 2 : PPT)));
+  constexpr int QB = NR == 0 ? 1 : (NR >= 8 ? (PPT < 3 ? PPT : 3) : PPT);
   const int packs_per_row = a.N / 8;
   const size_t row_bytes = size_t(a.N) * 2;
   for (int r_in = rc.r_begin; r_in < rc.r_end; ++r_in) {
     const size_t lrow_off = size_t(rc.lrow0 + r_in) * row_bytes;
-    const size_t row_base = rc.row_base0 + size_t(r_in) * (kTileN * 2);
+    const char* row_base = rc.row_base0 + size_t(r_in) * (kTileN * 2);
     float v[PPT][8];
 #pragma unroll
     for (int q0 = 0; q0 < PPT; q0 += QB) {
-      RawPack<T, NR, MC> raw[QB];
+      Slices<T, NR> raw[QB];
 #pragma unroll
       for (int i = 0; i < QB; ++i) {
         if (q0 + i < PPT) {
           const int p = threadIdx.x + (q0 + i) * THREADS;
           const int pc = p < packs_per_row ? p : 0;  // dead lanes reload pack 0 instead of branching
-          raw[i].load(a.partial, row_base + size_t(pc / kPacksPerTileRow) * kTileBytes + size_t(pc % kPacksPerTileRow) * 16,
+          raw[i].load(row_base + size_t(pc / kPacksPerTileRow) * world * kTileBytes + size_t(pc % kPacksPerTileRow) * 16,
                       world);
         }
       }
@@ -430,21 +428,20 @@ __device__ __forceinline__ void rs_process_rows(const GemmArgs& a, int world, co
 }
 
 template <typename T, int THREADS, int PPT>
-__device__ __forceinline__ void rs_rows_dispatch(const GemmArgs& a, int world, bool use_mc, const RsRowCtx& rc) {
-  if (use_mc)
-    rs_process_rows<T, THREADS, 1, true, PPT>(a, world, rc);
-  else if (world == 2)
-    rs_process_rows<T, THREADS, 2, false, PPT>(a, world, rc);
+__device__ __forceinline__ void rs_rows_dispatch(const GemmArgs& a, int world, const RsRowCtx& rc) {
+  if (world == 2)
+    rs_process_rows<T, THREADS, 2, PPT>(a, world, rc);
   else if (world == 4)
-    rs_process_rows<T, THREADS, 4, false, PPT>(a, world, rc);
+    rs_process_rows<T, THREADS, 4, PPT>(a, world, rc);
   else if (world == 8)
-    rs_process_rows<T, THREADS, 8, false, PPT>(a, world, rc);
+    rs_process_rows<T, THREADS, 8, PPT>(a, world, rc);
   else
-    rs_process_rows<T, THREADS, 0, false, PPT>(a, world, rc);
+    rs_process_rows<T, THREADS, 0, PPT>(a, world, rc);
 }
 
 // GEMM->RS + residual + RMSNorm.  Ticket t = (owned row block t / kRsItemsPerBlock, row group t % kRsItemsPerBlock).
 // Counter layout from counter_base: [bps] tile arrivals per row block, [bps] finished items per row block, ticket.
+// Staging layout in the owner's partial buffer: [owned row block][n_blk][source rank][128][256].
 template <typename T, int THREADS>
 __device__ void rs_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sched& sc, int drawers) {
   __shared__ int s_ok;
@@ -452,7 +449,6 @@ __device__ void rs_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
   __shared__ float s_part[THREADS / 32];
   __shared__ float s_total;
   const int world = ctx.world, rank = ctx.rank;
-  const bool use_mc = a.partial.mc != nullptr && a.use_nvls != 0;
   const char* res = a.residual ? static_cast<const char*>(a.residual) + a.rs_emu_stride * blockIdx.y : nullptr;
   char* y = static_cast<char*>(a.y_local) + a.rs_emu_stride * blockIdx.y;
   char* ro = a.res_out_local ? static_cast<char*>(a.res_out_local) + a.rs_emu_stride * blockIdx.y : nullptr;
@@ -472,7 +468,7 @@ __device__ void rs_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
     if (s_ok == 0) ok = false;
     if (ok) {
       RsRowCtx rc;
-      rc.row_base0 = size_t((rank * sc.bps + lb) * sc.tiles_n) * kTileBytes;
+      rc.row_base0 = static_cast<const char*>(a.partial.p[rank]) + size_t(lb) * sc.tiles_n * world * kTileBytes;
       rc.lrow0 = lb * kTileM;
       rc.r_begin = grp * kRsRowsPerItem;
       rc.r_end = (grp + 1) * kRsRowsPerItem;
@@ -484,11 +480,11 @@ __device__ void rs_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
       rc.s_total = &s_total;
       const int ppt = (a.N / 8 + THREADS - 1) / THREADS;
       if (ppt <= 2)
-        rs_rows_dispatch<T, THREADS, 2>(a, world, use_mc, rc);
+        rs_rows_dispatch<T, THREADS, 2>(a, world, rc);
       else if (ppt <= 3)
-        rs_rows_dispatch<T, THREADS, 3>(a, world, use_mc, rc);
+        rs_rows_dispatch<T, THREADS, 3>(a, world, rc);
       else
-        rs_rows_dispatch<T, THREADS, 6>(a, world, use_mc, rc);
+        rs_rows_dispatch<T, THREADS, 6>(a, world, rc);
     }
     // Whoever finishes the last row group of a block re-arms the block's counters for the next call.
     __syncthreads();
@@ -570,7 +566,7 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
   constexpr int FMT = PackTraits<T>::kDType == kBF16 ? 1 : 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem + kStages * kStageBytes);
+  SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem + kStages * kStageBytes + kEpiBytes);
 
   const CommCtx ctx = resolve_ctx(ctx_param);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -613,8 +609,8 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
     for (int s = 0; s < kAccStages; ++s) {
       ptx::mbar_init(&ctl->tmem_full[s], 1);
       ptx::mbar_init(&ctl->tmem_empty[s], 4);  // one arrival per epilogue warp
-      ctl->epi_count[s] = 0;
     }
+    for (int s = 0; s < 4; ++s) ctl->epi_count[s] = 0;
     ctl->abort = 0;
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(ta);
@@ -724,21 +720,25 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
     }
   } else if (warp < 6) {
     // --------------------------- epilogue -----------------------------
+    // Each epilogue warp owns the 32 accumulator rows of its TMEM lane quadrant.  A row is read from TMEM by one
+    // thread (tcgen05.ld 32x32b), converted, and staged in shared memory (XOR-swizzled 16-byte units, conflict
+    // free both ways); the warp then writes 256-byte row segments with all lanes, so that stores -- to local
+    // memory or to the owner rank's memory over NVLink -- are whole lines, not 16-byte fragments.
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    uint8_t* stage_buf = smem + kStages * kStageBytes + (warp - 2) * kEpiWarpBytes;
+    const uint32_t stage_u32 = ptx::smem_u32(stage_buf);
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t iter = 0;
     char* c_base = nullptr;
     if constexpr (MODE == kGemmPlain || MODE == kGemmAg) c_base = static_cast<char*>(a.C) + a.c_emu_stride * blockIdx.y;
-    char* p_base = nullptr;
-    if constexpr (MODE == kGemmAr || MODE == kGemmRsNorm) p_base = static_cast<char*>(a.partial.p[ctx.rank]);
-    for (int item = blockIdx.x; item < sc.items; item += G) {
+    for (int item = blockIdx.x; item < sc.items; item += G, ++iter) {
       const int seq = item / sc.splits, split = item - seq * sc.splits;
       int m_blk, n_blk;
       sc.coord(seq, m_blk, n_blk);
       if (!ptx::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort)) break;
       ptx::tc_fence_after_sync();
       const int r_in = q * 32 + lane;
-      const int row = m_blk * kTileM + r_in;
       const uint32_t t_addr = tmem_base + (uint32_t(q * 32) << 16) + acc * kTileN;
       const int tile_id = m_blk * sc.tiles_n + n_blk;
       float* ws_tile = nullptr;
@@ -746,108 +746,172 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
         if (sc.splits > 1)
           ws_tile = splitk_partials(a.splitk_ws) + (size_t(tile_id) * sc.splits + split) * (kTileM * kTileN);
       }
+      if (ws_tile != nullptr) {
+        // split-K: fp32 partial accumulator, tile-packed [128][256]; rows past M are never read back
+        const bool row_live = m_blk * kTileM + r_in < a.M;
 #pragma unroll 2
-      for (int c = 0; c < kTileN / 32; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32b_x32(t_addr + c * 32, r);
-        ptx::tmem_ld_wait();
-        const int col = n_blk * kTileN + c * 32;
-        if constexpr (MODE == kGemmPlain || MODE == kGemmAg) {
-          if (ws_tile != nullptr) {
-            // split-K: fp32 partial accumulator, tile-packed [128][256]
+        for (int c = 0; c < kTileN / 32; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32b_x32(t_addr + c * 32, r);
+          ptx::tmem_ld_wait();
+          if (row_live) {
             float4* dst = reinterpret_cast<float4*>(ws_tile + size_t(r_in) * kTileN + c * 32);
 #pragma unroll
             for (int i = 0; i < 8; ++i)
               dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
                                    __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-          } else if (row < a.M && col < a.N) {
-            const int valid = min(32, a.N - col);
-            cvt_store_32<T>(c_base + (size_t(row) * a.ldc + col) * 2, r, valid == 32 && (a.ldc % 8) == 0, valid);
           }
-        } else {
-          // Tile-packed partial buffer: the whole (padded) tile is written so that reducers can stream it.
-          cvt_store_32<T>(p_base + size_t(tile_id) * kTileBytes + size_t(r_in) * (kTileN * 2) + c * 64, r, true, 32);
         }
-      }
-      if constexpr (MODE == kGemmPlain) {
-        if (ws_tile != nullptr) {
-          // The last CTA to deliver this 32-row quadrant sums the splits in split order and writes C.
-          uint32_t* qcnt = static_cast<uint32_t*>(a.splitk_ws) + tile_id * 4 + q;
-          __syncwarp();
-          uint32_t prev = 0;
-          if (lane == 0) {
-            __threadfence();
-            prev = atomicAdd(qcnt, 1u);
-          }
-          prev = __shfl_sync(0xffffffffu, prev, 0);
-          if (prev == uint32_t(sc.splits - 1)) {
-            __threadfence();
-            if (lane == 0) *qcnt = 0;  // re-arm for the next call
-            const float* base = splitk_partials(a.splitk_ws) + size_t(tile_id) * sc.splits * (kTileM * kTileN);
-            for (int rr = 0; rr < 32; ++rr) {
-              const int grow = m_blk * kTileM + q * 32 + rr;
-              if (grow >= a.M) break;
+        // Accumulator drained: hand the TMEM stage back to the MMA warp.
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
+        // The last CTA to deliver this 32-row quadrant sums the splits in split order and writes C.
+        uint32_t* qcnt = static_cast<uint32_t*>(a.splitk_ws) + tile_id * 4 + q;
+        __threadfence();
+        __syncwarp();
+        uint32_t prev = 0;
+        if (lane == 0) prev = atomicAdd(qcnt, 1u);
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        if (prev == uint32_t(sc.splits - 1)) {
+          __threadfence();
+          if (lane == 0) *qcnt = 0;  // re-arm for the next call
+          const float* base = splitk_partials(a.splitk_ws) + size_t(tile_id) * sc.splits * (kTileM * kTileN);
+          for (int rr = 0; rr < 32; ++rr) {
+            const int grow = m_blk * kTileM + q * 32 + rr;
+            if (grow >= a.M) break;
 #pragma unroll
-              for (int half = 0; half < 2; ++half) {
-                const int cc = half * 128 + lane * 4;
-                float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int sp = 0; sp < sc.splits; ++sp) {
-                  const float4 v = __ldcg(reinterpret_cast<const float4*>(
-                      base + size_t(sp) * (kTileM * kTileN) + size_t(q * 32 + rr) * kTileN + cc));
-                  s.x += v.x;
-                  s.y += v.y;
-                  s.z += v.z;
-                  s.w += v.w;
-                }
-                const int gcol = n_blk * kTileN + cc;
-                if (gcol < a.N) {
-                  const float f[4] = {s.x, s.y, s.z, s.w};
-                  char* dst = c_base + (size_t(grow) * a.ldc + gcol) * 2;
-                  if (gcol + 4 <= a.N && (a.ldc % 4) == 0) {
-                    uint2 o;
-                    if constexpr (PackTraits<T>::kDType == kBF16) {
-                      __nv_bfloat162 h0 = __floats2bfloat162_rn(f[0], f[1]), h1 = __floats2bfloat162_rn(f[2], f[3]);
-                      o.x = *reinterpret_cast<uint32_t*>(&h0);
-                      o.y = *reinterpret_cast<uint32_t*>(&h1);
-                    } else {
-                      __half2 h0 = __floats2half2_rn(f[0], f[1]), h1 = __floats2half2_rn(f[2], f[3]);
-                      o.x = *reinterpret_cast<uint32_t*>(&h0);
-                      o.y = *reinterpret_cast<uint32_t*>(&h1);
-                    }
-                    *reinterpret_cast<uint2*>(dst) = o;
+            for (int half = 0; half < 2; ++half) {
+              const int cc = half * 128 + lane * 4;
+              float4 sacc = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int sp = 0; sp < sc.splits; ++sp) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(
+                    base + size_t(sp) * (kTileM * kTileN) + size_t(q * 32 + rr) * kTileN + cc));
+                sacc.x += v.x;
+                sacc.y += v.y;
+                sacc.z += v.z;
+                sacc.w += v.w;
+              }
+              const int gcol = n_blk * kTileN + cc;
+              if (gcol < a.N) {
+                const float f[4] = {sacc.x, sacc.y, sacc.z, sacc.w};
+                char* dst = c_base + (size_t(grow) * a.ldc + gcol) * 2;
+                if (gcol + 4 <= a.N && (a.ldc % 4) == 0) {
+                  uint2 o;
+                  if constexpr (PackTraits<T>::kDType == kBF16) {
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(f[0], f[1]), h1 = __floats2bfloat162_rn(f[2], f[3]);
+                    o.x = *reinterpret_cast<uint32_t*>(&h0);
+                    o.y = *reinterpret_cast<uint32_t*>(&h1);
                   } else {
-                    for (int i = 0; i < 4 && gcol + i < a.N; ++i)
-                      reinterpret_cast<T*>(dst)[i] = PackTraits<T>::from_float(f[i]);
+                    __half2 h0 = __floats2half2_rn(f[0], f[1]), h1 = __floats2half2_rn(f[2], f[3]);
+                    o.x = *reinterpret_cast<uint32_t*>(&h0);
+                    o.y = *reinterpret_cast<uint32_t*>(&h1);
                   }
+                  *reinterpret_cast<uint2*>(dst) = o;
+                } else {
+                  for (int i = 0; i < 4 && gcol + i < a.N; ++i)
+                    reinterpret_cast<T*>(dst)[i] = PackTraits<T>::from_float(f[i]);
                 }
               }
             }
           }
         }
-      }
-      if constexpr (MODE == kGemmAr || MODE == kGemmRsNorm) {
-        // The last of the four epilogue warps to finish its rows publishes one arrival for the tile.  The
-        // count is taken BEFORE the TMEM stage is handed back, so arrivals of the next tile that uses the
-        // same stage cannot mix with this tile's.
-        __syncwarp();
-        if (lane == 0) {
-          __threadfence();
-          if ((atomicAdd(&ctl->epi_count[acc], 1u) & 3u) == 3u) {
-            ptx::fence_acq_rel_sys();
-            if constexpr (MODE == kGemmAr) {
-              const int owner = seq % ctx.world;
-              ptx::red_release_sys_add(counter_ptr(ctx, owner, a.counter_base + seq / ctx.world), 1u);
-            } else {
-              const int owner = m_blk / sc.bps;
-              ptx::red_release_sys_add(counter_ptr(ctx, owner, a.counter_base + (m_blk - owner * sc.bps)), 1u);
+      } else {
+        // Destination of this warp's 32 rows: local C, or this rank's slice of the tile in the OWNER's buffer.
+        char* dst_rows;        // address of (row q*32, column 0 of the tile)
+        size_t dst_row_bytes;  // distance between rows
+        int owner = 0, owner_counter = 0;
+        if constexpr (MODE == kGemmPlain || MODE == kGemmAg) {
+          dst_row_bytes = size_t(a.ldc) * 2;
+          dst_rows = c_base + (size_t(m_blk * kTileM + q * 32) * a.ldc + size_t(n_blk) * kTileN) * 2;
+        } else {
+          size_t slice;
+          if constexpr (MODE == kGemmAr) {
+            owner = seq % ctx.world;
+            owner_counter = a.counter_base + seq / ctx.world;
+            slice = size_t(seq / ctx.world) * ctx.world + ctx.rank;
+          } else {
+            owner = m_blk / sc.bps;
+            const int lb = m_blk - owner * sc.bps;
+            owner_counter = a.counter_base + lb;
+            slice = (size_t(lb) * sc.tiles_n + n_blk) * ctx.world + ctx.rank;
+          }
+          dst_row_bytes = kTileN * 2;
+          dst_rows = static_cast<char*>(a.partial.p[owner]) + slice * kTileBytes + size_t(q * 32) * (kTileN * 2);
+        }
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            ptx::tmem_ld_32x32b_x32(t_addr + h * 128 + c * 32, r);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t w[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float lo = __uint_as_float(r[8 * j + 2 * i]), hi = __uint_as_float(r[8 * j + 2 * i + 1]);
+                if constexpr (PackTraits<T>::kDType == kBF16) {
+                  __nv_bfloat162 hh = __floats2bfloat162_rn(lo, hi);
+                  w[i] = *reinterpret_cast<uint32_t*>(&hh);
+                } else {
+                  __half2 hh = __floats2half2_rn(lo, hi);
+                  w[i] = *reinterpret_cast<uint32_t*>(&hh);
+                }
+              }
+              const int u = c * 4 + j;  // 16-byte unit of the 256-byte staged row
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage_u32 + lane * 256 + ((u ^ (lane & 7)) << 4)),
+                           "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                           : "memory");
             }
+          }
+          if (h == 1) {
+            // Everything has left TMEM: hand the accumulator stage back before the last copy-out.
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
+          }
+          __syncwarp();
+#pragma unroll 4
+          for (int i = 0; i < 16; ++i) {
+            const int rr = 2 * i + (lane >> 4), u = lane & 15;
+            uint4 v;
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                         : "r"(stage_u32 + rr * 256 + ((u ^ (rr & 7)) << 4))
+                         : "memory");
+            char* dst = dst_rows + size_t(rr) * dst_row_bytes + h * 256 + u * 16;
+            if constexpr (MODE == kGemmPlain || MODE == kGemmAg) {
+              const int grow = m_blk * kTileM + q * 32 + rr;
+              const int gcol = n_blk * kTileN + h * 128 + u * 8;
+              if (grow < a.M && gcol < a.N) {
+                if (gcol + 8 <= a.N && (a.ldc % 8) == 0) {
+                  ptx::st_v4(dst, v);
+                } else {
+                  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                  for (int e = 0; e < 8 && gcol + e < a.N; ++e)
+                    reinterpret_cast<unsigned short*>(dst)[e] =
+                        static_cast<unsigned short>((e & 1) ? (w[e >> 1] >> 16) : (w[e >> 1] & 0xffff));
+                }
+              }
+            } else {
+              ptx::st_v4(dst, v);  // the whole padded tile is pushed so that the owner can stream it
+            }
+          }
+          __syncwarp();
+        }
+        if constexpr (MODE == kGemmAr || MODE == kGemmRsNorm) {
+          // Every lane makes its (possibly remote) stores visible system-wide; the last of the four epilogue
+          // warps to get here publishes one arrival for the tile on the owner rank.
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) {
+            if ((atomicAdd(&ctl->epi_count[iter & 3], 1u) & 3u) == 3u)
+              ptx::red_release_sys_add(counter_ptr(ctx, owner, owner_counter), 1u);
           }
         }
       }
-      // Accumulator drained: hand the TMEM stage back to the MMA warp.
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
       if (++acc == kAccStages) {
         acc = 0;
         acc_phase ^= 1;

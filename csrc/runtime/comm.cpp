@@ -949,8 +949,9 @@ int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream) {
 int oob_gemm_counters_needed(int mode, int M, int N, int world) { return gemm_counters_needed(mode, M, N, world); }
 
 uint64_t oob_gemm_partial_bytes(int M, int N) {
+  // One slice per (tile, source rank) in the owner's buffer: tiles rounded up to a whole number per rank.
   const uint64_t tm = (M + kTileM - 1) / kTileM, tn = (N + kTileN - 1) / kTileN;
-  return tm * tn * kTileBytes;
+  return (tm * tn + kMaxRanks) * kTileBytes;
 }
 
 }  // extern "C"

@@ -75,7 +75,7 @@ def timed(fn, iters, warmup, world):
 
     # The start skew between ranks is paid once per measurement: run long enough (>= ~5 ms) to amortise it.
     pilot = once(max(1, iters // PER_GRAPH))
-    reps = int(min(200, max(iters // PER_GRAPH, 5e-3 / max(pilot * PER_GRAPH, 1e-7))))
+    reps = max(1, int(min(200, max(iters // PER_GRAPH, 5e-3 / max(pilot * PER_GRAPH, 1e-7)))))
     return min(once(reps), once(reps))
 
 

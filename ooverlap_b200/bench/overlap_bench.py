@@ -72,7 +72,7 @@ def timed(fn, iters, warmup):
     # The ranks never start a measurement at exactly the same instant; the skew (tens of microseconds of host
     # jitter) is paid once per measurement, so each measurement runs for at least ~30 ms of device time.
     pilot = once(max(1, iters // PER_GRAPH))
-    reps = int(min(400, max(iters // PER_GRAPH, 30000.0 / max(pilot * PER_GRAPH, 1.0))))
+    reps = max(1, int(min(400, max(iters // PER_GRAPH, 30000.0 / max(pilot * PER_GRAPH, 1.0)))))
     trials = sorted(once(reps) for _ in range(3))
     return trials[1]
 

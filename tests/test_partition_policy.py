@@ -87,8 +87,8 @@ def test_policy_rejects_malformed(lib, tmp_path):
 
 
 def test_gemm_bookkeeping_helpers(lib):
-    assert lib.oob_gemm_partial_bytes(8192, 8192) == 64 * 32 * 128 * 256 * 2
-    assert lib.oob_gemm_partial_bytes(100, 100) == 128 * 256 * 2
-    assert lib.oob_gemm_counters_needed(_lib.GEMM_AR, 8192, 8192, 8) == 256
-    assert lib.oob_gemm_counters_needed(_lib.GEMM_RS_NORM, 4096, 8192, 8) == 8
+    assert lib.oob_gemm_partial_bytes(8192, 8192) == (64 * 32 + 16) * 128 * 256 * 2
+    assert lib.oob_gemm_partial_bytes(100, 100) == (1 + 16) * 128 * 256 * 2
+    assert lib.oob_gemm_counters_needed(_lib.GEMM_AR, 8192, 8192, 8) == 257
+    assert lib.oob_gemm_counters_needed(_lib.GEMM_RS_NORM, 4096, 8192, 8) == 9
     assert lib.oob_gemm_counters_needed(_lib.GEMM_AG, 4096, 3584, 8) == 33
