@@ -227,7 +227,10 @@ cudaError_t launch_fused_norm(const CommCtx& ctx, int algo, const NormArgs& a, i
   int rows = a.rows;
   if (algo >= kNormArTwoShot) rows = (a.rows + ctx.world - 1) / ctx.world;
   int ctas = max_ctas < 1 ? 1 : max_ctas;
-  if (ctas > kMaxCommBlocks) ctas = kMaxCommBlocks;
+  // Communicating launches are bounded by the barrier slots of the pad; the local one may fill the GPU
+  // (one row per CTA at a time, eight resident CTAs per SM hide the three dependent passes over a row).
+  const int cap = algo == kNormLocal ? 148 * 8 : kMaxCommBlocks;
+  if (ctas > cap) ctas = cap;
   if (ctas > rows) ctas = rows < 1 ? 1 : rows;
   if (a.dtype == kF16) return dispatch_ppt<__half>(algo, ctx, ctas, a, stream);
   return dispatch_ppt<__nv_bfloat16>(algo, ctx, ctas, a, stream);

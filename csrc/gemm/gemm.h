@@ -20,6 +20,19 @@ constexpr int kTileN = 256;
 constexpr int kTileK = 64;
 constexpr int kTileBytes = kTileM * kTileN * 2;  // one 16-bit output tile
 
+// Layout of one CTA's trace record (GemmArgs::trace).
+enum TraceSlot : int {
+  kTraceStart = 0,       // kernel entry
+  kTraceGemmDone = 1,    // GEMM CTAs: all tiles computed and stored / pushed
+  kTraceFirstReady = 2,  // communication role: first work item became ready
+  kTraceCommDone = 3,    // communication role: last work item finished (before the final rank barrier)
+  kTraceEnd = 4,         // after the final rank barrier
+  kTraceItems = 5,       // communication work items this CTA processed
+  kTraceWaitNs = 6,      // total time this CTA spent waiting for arrival counters
+  kTraceRole = 7,        // 0 = GEMM CTA, 1 = dedicated communication CTA
+  kTraceWords = 8
+};
+
 // All matrices are 16-bit (fp16 or bf16), A is [M, K] row-major with leading
 // dimension lda, B is [N, K] row-major (the layout of a torch Linear weight)
 // with leading dimension ldb, C is [M, N] row-major.
@@ -39,6 +52,9 @@ struct GemmArgs {
   int max_ctas;   // 0 = one CTA per SM
   int use_nvls;   // fused modes: 0 = peer loads/stores even when a multicast alias exists
   int no_join;    // fused AR / RS: 1 = only the comm_ctas CTAs reduce (GEMM CTAs exit when out of tiles)
+  // Optional device-side trace: kTraceWords 64-bit words per CTA (globaltimer nanoseconds at fixed points of
+  // the kernel and a few counts), written when non-null.  See TraceSlot.
+  unsigned long long* trace;
 
   // Plain mode: K split over `splits` CTAs per tile (0 = choose from the shape, 1 = off).  The fp32 partials
   // and their arrival counters live in splitk_ws (nullptr = the library's own workspace, grown on demand).

@@ -76,7 +76,7 @@ struct SmemCtl {
   uint64_t tmem_empty[kAccStages];
   uint32_t tmem_base;
   int abort;
-  uint32_t epi_count[4];  // epilogue warps that have stored their rows of a tile (slot = tile iteration & 3)
+  uint32_t epi_count[8];  // epilogue warps that have issued their rows of a tile (slot = tile iteration & 7; never reset)
 };
 
 struct Sched {
@@ -174,6 +174,12 @@ __device__ __forceinline__ float cta_sum(float v, float* s_part, float* s_total)
   }
   __syncthreads();
   return *s_total;
+}
+
+// Device-side trace (GemmArgs::trace): thread 0 of each CTA records globaltimer stamps and counts.
+__device__ __forceinline__ void trace_put(const GemmArgs& a, int slot, unsigned long long v) {
+  if (a.trace != nullptr && threadIdx.x == 0)
+    a.trace[(size_t(blockIdx.y) * gridDim.x + blockIdx.x) * kTraceWords + slot] = v;
 }
 
 // Draws the next ticket of this launch.  The counter is re-armed by whoever draws the last ticket that can ever
@@ -312,14 +318,22 @@ __device__ void ar_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
   const int owned_max = (sc.tiles + world - 1) / world;
   uint32_t* ticket = counter_ptr(ctx, rank, a.counter_base + owned_max);
   bool ok = true;
+  unsigned long long t_wait = 0, n_items = 0;
   while (true) {
     const int k = draw_ticket(ticket, owned, &s_ticket, drawers);
     if (k >= owned) break;
     const int seq = k * world + rank;
     if (threadIdx.x == 0) {
       uint32_t* cnt = counter_ptr(ctx, rank, a.counter_base + k);
+      const unsigned long long tw = a.trace ? ptx::globaltimer_ns() : 0;
       s_ok = wait_word_ge(ctx, cnt, world, kDevTimeoutCounter, -1, 50) ? 1 : 0;
       *cnt = 0;  // single consumer: re-arm now (next call's arrivals cannot come before this launch ends everywhere)
+      if (a.trace) {
+        const unsigned long long now = ptx::globaltimer_ns();
+        t_wait += now - tw;
+        if (n_items == 0) trace_put(a, kTraceFirstReady, now);
+        ++n_items;
+      }
     }
     __syncthreads();
     if (s_ok == 0) ok = false;
@@ -335,9 +349,15 @@ __device__ void ar_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
     else
       ar_reduce_tile_dispatch<T, THREADS, false>(a, world, rank, slices, c_off0, row_bytes, rows_valid, packs_valid_row);
   }
+  if (a.trace) {
+    trace_put(a, kTraceCommDone, ptx::globaltimer_ns());
+    trace_put(a, kTraceItems, n_items);
+    trace_put(a, kTraceWaitNs, t_wait);
+  }
   // Block b of every rank is past its last tile: together (all blocks) this means every push into this rank's C
   // has been issued and released, and nobody reads this rank's partial buffer any more.
   if (ok) rank_barrier(ctx, blockIdx.x, 51);
+  if (a.trace) trace_put(a, kTraceEnd, ptx::globaltimer_ns());
 }
 
 // One ticket of the GEMM->RS tail: rows [r_begin, r_end) of an owned 128-row block.
@@ -456,14 +476,23 @@ __device__ void rs_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
   const int total = sc.bps * kRsItemsPerBlock;
   uint32_t* ticket = counter_ptr(ctx, rank, a.counter_base + 2 * sc.bps);
   bool ok = true;
+  unsigned long long t_wait = 0, n_items = 0;
   while (true) {
     const int t = draw_ticket(ticket, total, &s_ticket, drawers);
     if (t >= total) break;
     const int lb = t / kRsItemsPerBlock, grp = t % kRsItemsPerBlock;
     uint32_t* cnt = counter_ptr(ctx, rank, a.counter_base + lb);
     uint32_t* done = counter_ptr(ctx, rank, a.counter_base + sc.bps + lb);
-    if (threadIdx.x == 0)
+    if (threadIdx.x == 0) {
+      const unsigned long long tw = a.trace ? ptx::globaltimer_ns() : 0;
       s_ok = wait_word_ge(ctx, cnt, uint32_t(world) * sc.tiles_n, kDevTimeoutCounter, -1, 60) ? 1 : 0;
+      if (a.trace) {
+        const unsigned long long now = ptx::globaltimer_ns();
+        t_wait += now - tw;
+        if (n_items == 0) trace_put(a, kTraceFirstReady, now);
+        ++n_items;
+      }
+    }
     __syncthreads();
     if (s_ok == 0) ok = false;
     if (ok) {
@@ -496,7 +525,13 @@ __device__ void rs_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
       }
     }
   }
+  if (a.trace) {
+    trace_put(a, kTraceCommDone, ptx::globaltimer_ns());
+    trace_put(a, kTraceItems, n_items);
+    trace_put(a, kTraceWaitNs, t_wait);
+  }
   if (ok) rank_barrier(ctx, blockIdx.x, 61);
+  if (a.trace) trace_put(a, kTraceEnd, ptx::globaltimer_ns());
 }
 
 // AG->GEMM pusher: broadcasts this rank's shard, one 128-row chunk at a time.
@@ -571,6 +606,10 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
   const CommCtx ctx = resolve_ctx(ctx_param);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (a.K + kTileK - 1) / kTileK;
+  if (a.trace) {
+    trace_put(a, kTraceStart, ptx::globaltimer_ns());
+    trace_put(a, kTraceRole, static_cast<int>(blockIdx.x) >= gemm_ctas ? 1 : 0);
+  }
 
   Sched sc;
   sc.tiles_m = (a.M + kTileM - 1) / kTileM;
@@ -610,7 +649,7 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
       ptx::mbar_init(&ctl->tmem_full[s], 1);
       ptx::mbar_init(&ctl->tmem_empty[s], 4);  // one arrival per epilogue warp
     }
-    for (int s = 0; s < 4; ++s) ctl->epi_count[s] = 0;
+    for (int s = 0; s < 8; ++s) ctl->epi_count[s] = 0;
     ctl->abort = 0;
     ptx::mbar_fence_init();
     ptx::prefetch_tmap(ta);
@@ -777,21 +816,42 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
           __threadfence();
           if (lane == 0) *qcnt = 0;  // re-arm for the next call
           const float* base = splitk_partials(a.splitk_ws) + size_t(tile_id) * sc.splits * (kTileM * kTileN);
-          for (int rr = 0; rr < 32; ++rr) {
-            const int grow = m_blk * kTileM + q * 32 + rr;
-            if (grow >= a.M) break;
+          // Eight rows x two 128-column halves per step: sixteen independent loads per lane are in flight for
+          // every split, instead of one dependent chain per row.
+          const int rows_live = min(32, a.M - (m_blk * kTileM + q * 32));
+          for (int rr0 = 0; rr0 < rows_live; rr0 += 8) {
+            float4 sacc8[8][2];
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-              const int cc = half * 128 + lane * 4;
-              float4 sacc = make_float4(0.f, 0.f, 0.f, 0.f);
-              for (int sp = 0; sp < sc.splits; ++sp) {
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(
-                    base + size_t(sp) * (kTileM * kTileN) + size_t(q * 32 + rr) * kTileN + cc));
-                sacc.x += v.x;
-                sacc.y += v.y;
-                sacc.z += v.z;
-                sacc.w += v.w;
+            for (int i = 0; i < 8; ++i) sacc8[i][0] = sacc8[i][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+            for (int sp = 0; sp < sc.splits; ++sp) {
+              const float* sbase = base + size_t(sp) * (kTileM * kTileN) + size_t(q * 32 + rr0) * kTileN + lane * 4;
+              float4 v[8][2];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                // rows past the live range re-read the first row instead of branching (result unused)
+                const int ro = rr0 + i < rows_live ? i : 0;
+                v[i][0] = __ldcg(reinterpret_cast<const float4*>(sbase + size_t(ro) * kTileN));
+                v[i][1] = __ldcg(reinterpret_cast<const float4*>(sbase + size_t(ro) * kTileN + 128));
               }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                  sacc8[i][hh].x += v[i][hh].x;
+                  sacc8[i][hh].y += v[i][hh].y;
+                  sacc8[i][hh].z += v[i][hh].z;
+                  sacc8[i][hh].w += v[i][hh].w;
+                }
+              }
+            }
+#pragma unroll
+            for (int idx = 0; idx < 16; ++idx) {
+              const int rr = rr0 + (idx >> 1), half = idx & 1;
+              if (rr >= rows_live) continue;
+              const int grow = m_blk * kTileM + q * 32 + rr;
+              const float4 sacc = sacc8[idx >> 1][half];
+              const int cc = half * 128 + lane * 4;
               const int gcol = n_blk * kTileN + cc;
               if (gcol < a.N) {
                 const float f[4] = {sacc.x, sacc.y, sacc.z, sacc.w};
@@ -902,13 +962,14 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
           __syncwarp();
         }
         if constexpr (MODE == kGemmAr || MODE == kGemmRsNorm) {
-          // Every lane makes its (possibly remote) stores visible system-wide; the last of the four epilogue
-          // warps to get here publishes one arrival for the tile on the owner rank.
-          __threadfence_system();
+          // This warp's rows of the tile have been issued.  It does NOT wait for the (remote) stores to land:
+          // it only tells the signal warp, which takes the wait, and moves on to the next tile.
+          (void)owner;
+          (void)owner_counter;
           __syncwarp();
           if (lane == 0) {
-            if ((atomicAdd(&ctl->epi_count[iter & 3], 1u) & 3u) == 3u)
-              ptx::red_release_sys_add(counter_ptr(ctx, owner, owner_counter), 1u);
+            __threadfence_block();
+            atomicAdd(&ctl->epi_count[iter & 7], 1u);
           }
         }
       }
@@ -917,10 +978,50 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
         acc_phase ^= 1;
       }
     }
+  } else if (warp == 6) {
+    // --------------------------- signal warp (fused AR / RS) -----------------------------
+    // One thread follows the CTA's tiles in order.  When all four epilogue warps have issued their rows of a
+    // tile it orders those stores system-wide (the fence is cumulative over what it observed through the
+    // CTA-scope counter) and publishes one arrival on the owner rank.  The epilogue warps never stall on NVLink.
+    if constexpr (MODE == kGemmAr || MODE == kGemmRsNorm) {
+      if (lane == 0) {
+        uint32_t iter = 0;
+        for (int item = blockIdx.x; item < sc.items; item += G, ++iter) {
+          const uint32_t expected = 4u * (iter / 8u + 1u);
+          volatile uint32_t* cnt = &ctl->epi_count[iter & 7];
+          uint32_t polls = 0;
+          bool ok = true;
+          while (*cnt < expected) {
+            if (*abort || ++polls > (1u << 26)) {
+              ok = false;
+              break;
+            }
+            __nanosleep(40);
+          }
+          if (!ok) {
+            *abort = 1;
+            break;
+          }
+          int m_blk, n_blk;
+          sc.coord(item, m_blk, n_blk);
+          int owner, idx;
+          if constexpr (MODE == kGemmAr) {
+            owner = item % ctx.world;
+            idx = a.counter_base + item / ctx.world;
+          } else {
+            owner = m_blk / sc.bps;
+            idx = a.counter_base + (m_blk - owner * sc.bps);
+          }
+          ptx::fence_acq_rel_sys();
+          ptx::red_release_sys_add(counter_ptr(ctx, owner, idx), 1u);
+        }
+      }
+    }
   }
 
   // ---- teardown -----------------------------------------------------------
   __syncthreads();
+  if (a.trace) trace_put(a, kTraceGemmDone, ptx::globaltimer_ns());
   const bool aborted = *abort != 0;
   if (aborted) {
     // Give copies that may still be in flight time to land before shared memory is released.

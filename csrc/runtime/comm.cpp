@@ -848,7 +848,7 @@ int oob_fused_norm(oob_comm* c, int algo, const oob_norm_args_t* a, int max_ctas
     CommCtx ctx{};
     ctx.world = 1;
     ctx.rank = 0;
-    if (max_ctas <= 0) max_ctas = 148;
+    if (max_ctas <= 0) max_ctas = 148 * 8;
     cudaError_t e = launch_fused_norm(ctx, algo, n, max_ctas, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(e, "rmsnorm launch");
     return OOB_OK;
@@ -921,6 +921,7 @@ int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream) {
   g.use_nvls = a->use_nvls;
   g.splits = a->splits;
   g.no_join = a->no_join;
+  g.trace = static_cast<unsigned long long*>(a->trace);
   g.splitk_ws = nullptr;
   g.counter_base = a->counter_base;
   g.residual = a->residual;

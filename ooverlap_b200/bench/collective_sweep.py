@@ -114,9 +114,13 @@ def main() -> int:
                "nvls": int(comm.nvls)}
         lines.append(rec)
         if impl == "ours":
-            key = (coll, nbytes)
-            if key not in best or sec < best[key][0]:
-                best[key] = (sec, algo, ctas, int("nvls" in algo_name))
+            # Two policies: for communicators with an NVLS alias (any algorithm may win) and without one.
+            for has_nvls in ((1, 0) if "nvls" not in algo_name else (1,)):
+                if has_nvls and not comm.nvls:
+                    continue
+                key = (coll, nbytes, has_nvls)
+                if key not in best or sec < best[key][0]:
+                    best[key] = (sec, algo, ctas)
         if rank == 0:
             print(json.dumps(rec), flush=True)
 
@@ -132,7 +136,7 @@ def main() -> int:
                 algos += [_lib.AR_ONESHOT_P2P] + ([_lib.AR_ONESHOT_NVLS] if comm.nvls else [])
             for algo in algos:
                 for ctas in cta_list:
-                    if ctas * 512 * 16 > max(size, 8192) * 4:
+                    if ctas != cta_list[0] and ctas * 512 * 16 > max(size, 8192) * 4:
                         continue  # more CTAs than work
                     if algo in (_lib.AR_ONESHOT_P2P, _lib.AR_ONESHOT_NVLS):
                         fn = lambda: comm.all_reduce_out(sym_in[:n], sym_out[:n], algo=algo, max_ctas=ctas)  # noqa: E731
@@ -148,7 +152,7 @@ def main() -> int:
             out = nccl_out[: e - b]
             for algo in [_lib.RS_P2P] + ([_lib.RS_NVLS] if comm.nvls else []):
                 for ctas in cta_list:
-                    if ctas * 512 * 16 > max(size, 8192) * 4:
+                    if ctas != cta_list[0] and ctas * 512 * 16 > max(size, 8192) * 4:
                         continue
                     fn = lambda: comm.reduce_scatter(sym_in[:n], out=out, algo=algo, max_ctas=ctas)  # noqa: E731
                     record("reduce_scatter", size, "ours", RS_NAMES[algo], algo, ctas, timed(fn, iters, args.warmup, world))
@@ -159,7 +163,7 @@ def main() -> int:
             record("all_gather", size, "nccl", "nccl", -1, 0, sec)
             for algo in [_lib.AG_PUSH_P2P] + ([_lib.AG_PUSH_NVLS] if comm.nvls else []):
                 for ctas in cta_list:
-                    if ctas * 512 * 16 > max(size, 8192) * 4:
+                    if ctas != cta_list[0] and ctas * 512 * 16 > max(size, 8192) * 4:
                         continue
                     fn = lambda: comm.all_gather(src[:shard], out=sym_out[: shard * world], algo=algo, max_ctas=ctas)  # noqa: E731
                     record("all_gather", size, "ours", AG_NAMES[algo], algo, ctas, timed(fn, iters, args.warmup, world))
@@ -174,7 +178,7 @@ def main() -> int:
                     f.write(json.dumps(rec) + "\n")
         if args.policy:
             pts = [{"world": world, "collective": coll, "nvls": nv, "bytes": nbytes, "algo": algo, "ctas": ctas}
-                   for (coll, nbytes), (_, algo, ctas, nv) in sorted(best.items())]
+                   for (coll, nbytes, nv), (_, algo, ctas) in sorted(best.items())]
             with open(args.policy, "w") as f:
                 json.dump({"points": pts}, f, indent=1)
     dist.barrier()

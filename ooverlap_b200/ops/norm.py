@@ -31,7 +31,7 @@ def rmsnorm_reference(x: torch.Tensor, weight: torch.Tensor, eps: float,
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, residual: Optional[torch.Tensor] = None,
-            *, out: Optional[torch.Tensor] = None, residual_out: Optional[torch.Tensor] = None, max_ctas: int = 148):
+            *, out: Optional[torch.Tensor] = None, residual_out: Optional[torch.Tensor] = None, max_ctas: int = 0):
     """Local ``y = rmsnorm(x + residual) * weight`` (no communication).  Returns ``y`` or ``(y, residual_out)``."""
     if x.dim() != 2 or not x.is_contiguous():
         raise ValueError("x must be a contiguous [rows, hidden] tensor")

@@ -90,6 +90,8 @@ class GemmAllReduce:
         args.comm_ctas, args.max_ctas = self.comm_ctas, self.max_ctas
         args.use_nvls = _use_nvls(self.comm, self.use_nvls)
         args.no_join = 0 if getattr(self, "join", True) else 1
+        trace = getattr(self, "trace_buffer", None)  # [ctas, 8] int64 device tensor: per-CTA phase stamps
+        args.trace = trace.data_ptr() if trace is not None else None
         args.partial_reg, args.partial_off = 0, self.partial_off
         args.c_reg, args.c_off = 0, self.c_off
         args.counter_base = self.counter_base
@@ -134,6 +136,8 @@ class GemmReduceScatterNorm:
         args.comm_ctas, args.max_ctas = self.comm_ctas, self.max_ctas
         args.use_nvls = _use_nvls(self.comm, self.use_nvls)
         args.no_join = 0 if getattr(self, "join", True) else 1
+        trace = getattr(self, "trace_buffer", None)  # [ctas, 8] int64 device tensor: per-CTA phase stamps
+        args.trace = trace.data_ptr() if trace is not None else None
         args.partial_reg, args.partial_off = 0, self.partial_off
         args.counter_base = self.counter_base
         args.residual = residual.data_ptr() if residual is not None else None
@@ -185,6 +189,8 @@ class AllGatherGemm:
         args.comm_ctas, args.max_ctas = self.comm_ctas, self.max_ctas
         args.use_nvls = _use_nvls(self.comm, self.use_nvls)
         args.no_join = 0 if getattr(self, "join", True) else 1
+        trace = getattr(self, "trace_buffer", None)  # [ctas, 8] int64 device tensor: per-CTA phase stamps
+        args.trace = trace.data_ptr() if trace is not None else None
         args.a_full_reg, args.a_full_off = 0, self.a_full_off
         args.counter_base = self.counter_base
         _lib.check(_lib.lib().oob_gemm(self.comm._h, ctypes.byref(args), _stream()))
