@@ -35,10 +35,12 @@ REFERENCE_UNAVAILABLE = (
 def parse_args():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
-    p.add_argument("--steps", type=int, default=20)
-    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--steps", type=int, default=200)
+    p.add_argument("--warmup", type=int, default=10)
     p.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl_cublas"])
-    p.add_argument("--comm-ctas", type=int, default=int(os.environ.get("OOB_BENCH_COMM_CTAS", "20")))
+    p.add_argument("--comm-ctas", type=int, default=int(os.environ.get("OOB_BENCH_COMM_CTAS", "0")),
+                   help="communication CTAs of the fused kernel (0 = the library's choice per shape)")
+    p.add_argument("--strategy", default="auto", choices=["auto", "fused", "unfused"])
     return p.parse_args()
 
 
@@ -85,8 +87,8 @@ def main() -> int:
             heap = sum(2 * m * N_DIM * 2 for m in MS) + (64 << 20)
             comm = Communicator(list(range(world)), rank, heap_bytes=heap)
             for m in MS:
-                ops[m] = GemmAllReduce(comm, m, N_DIM, dtype, comm_ctas=args.comm_ctas)
-        launches_per_step = len(MS)
+                ops[m] = GemmAllReduce(comm, m, N_DIM, dtype, comm_ctas=args.comm_ctas or None, strategy=args.strategy)
+        launches_per_step = sum(2 if (m in ops and ops[m].strategy == "unfused") else 1 for m in MS)
 
     outs = {m: torch.empty(m, N_DIM, dtype=dtype, device=dev) for m in MS}
 
@@ -215,7 +217,8 @@ def main() -> int:
             "config": {"model": "row-parallel TP linear GEMM->AllReduce", "M": list(MS), "N": N_DIM, "K": K_DIM,
                        "global_batch": sum(MS), "seq_len": 1, "parallelism": f"tp{world}",
                        "l2": f"{ROTATE} operand sets rotated between steps; per-step working set exceeds the 126 MB L2",
-                       "comm_ctas": args.comm_ctas if world > 1 else 0},
+                       "strategy": {str(m): (ops[m].strategy if m in ops else "gemm") for m in MS},
+                       "comm_ctas": {str(m): (ops[m].comm_ctas if m in ops and ops[m].strategy == "fused" else 0) for m in MS}},
             "per_shape_us": {str(m): round(v, 2) for m, v in per_shape.items()},
             "tflops_aggregate": round(flops / (ms_per_step * 1e-3) / 1e12, 1),
             "clocks": clocks,

@@ -83,6 +83,54 @@ cudaError_t ensure_splitk(int dev, size_t need, cudaStream_t stream, void** out)
   return cudaSuccess;
 }
 
+// Tensor maps over every rank's staging buffer (for the epilogue's bulk tensor stores), kept on the device and
+// cached by the buffer they describe.
+struct PushKey {
+  const void* p[kMaxRanks];  // every rank's buffer as mapped here: a map is only valid for exactly these addresses
+  uint64_t rows;
+  int world;
+  bool operator==(const PushKey& o) const {
+    if (rows != o.rows || world != o.world) return false;
+    for (int r = 0; r < world; ++r)
+      if (p[r] != o.p[r]) return false;
+    return true;
+  }
+};
+struct PushKeyHash {
+  size_t operator()(const PushKey& k) const {
+    size_t h = k.rows * 1000003u ^ size_t(k.world);
+    for (int r = 0; r < k.world; ++r) h = h * 1000003u ^ reinterpret_cast<size_t>(k.p[r]);
+    return h;
+  }
+};
+std::unordered_map<PushKey, CUtensorMap*, PushKeyHash> g_push_maps;
+
+cudaError_t ensure_push_maps(const CommCtx& ctx, const GemmArgs& a, const void** out) {
+  const uint64_t tiles = uint64_t((a.M + kTileM - 1) / kTileM) * ((a.N + kTileN - 1) / kTileN);
+  const uint64_t rows = (tiles + kMaxRanks) * kTileM;  // capacity promised by oob_gemm_partial_bytes
+  PushKey key{};
+  for (int r = 0; r < ctx.world; ++r) key.p[r] = a.partial.p[r];
+  key.rows = rows;
+  key.world = ctx.world;
+  std::lock_guard<std::mutex> g(g_scratch_mu);
+  auto it = g_push_maps.find(key);
+  if (it != g_push_maps.end()) {
+    *out = it->second;
+    return cudaSuccess;
+  }
+  CUtensorMap host[kMaxRanks];
+  for (int r = 0; r < ctx.world; ++r)
+    if (!encode_tmap_2d(&host[r], a.partial.p[r], rows, kTileN, kTileN, 32)) return cudaErrorInvalidValue;
+  CUtensorMap* dev_maps = nullptr;
+  cudaError_t e = cudaMalloc(&dev_maps, sizeof(CUtensorMap) * kMaxRanks);
+  if (e != cudaSuccess) return e;
+  e = cudaMemcpy(dev_maps, host, sizeof(CUtensorMap) * ctx.world, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return e;
+  g_push_maps.emplace(key, dev_maps);
+  *out = dev_maps;
+  return cudaSuccess;
+}
+
 cudaError_t ensure_emu_maps(int dev, CUtensorMap** out) {
   std::lock_guard<std::mutex> g(g_scratch_mu);
   DeviceScratch& s = g_scratch[dev & 63];
@@ -187,6 +235,10 @@ cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& args, cudaStream_t s
     }
   } else {
     a.splits = 1;
+  }
+  if (a.mode == kGemmAr || a.mode == kGemmRsNorm) {
+    e = ensure_push_maps(ctx, a, &a.push_maps);
+    if (e != cudaSuccess) return e;
   }
   CUtensorMap* emu_maps = nullptr;
   if (ctx.emu_table != nullptr) {

@@ -62,7 +62,9 @@ struct GemmArgs {
   void* splitk_ws;
 
   // Fused modes
-  PeerPtrs partial;     // AR / RS: tile-packed partial products, registered; >= tiles * kTileBytes
+  PeerPtrs partial;     // AR / RS: per-owner staging of partial tiles, registered; see oob_gemm_partial_bytes
+  const void* push_maps; // AR / RS: device array of `world` tensor maps, one over each rank's staging buffer
+                        // seen as [slices * 128, 256]; filled in by launch_gemm
   PeerPtrs c_sym;       // AR: output [M, N] in every rank's registered memory
   int counter_base;     // first general counter of the pad used by this op
   // RS + norm tail (rows of this rank only; M / world must be a multiple of 128)

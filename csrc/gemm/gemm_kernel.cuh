@@ -285,6 +285,32 @@ __device__ __forceinline__ void ar_reduce_tile(const GemmArgs& a, int world, int
   }
 }
 
+// Pull variant (use_nvls == 2): every rank keeps its partial tile in its OWN buffer at the same offset; the owner
+// reads the sum of all ranks with one in-switch multimem.ld_reduce per pack and broadcasts it with multimem.st.
+// Per direction this moves the message once (the push variants move it 1.75 times).
+template <typename T, int THREADS>
+__device__ __forceinline__ void ar_reduce_tile_pull(const GemmArgs& a, size_t tile_off, size_t c_off0, size_t row_bytes,
+                                                    int rows_valid, int packs_valid_row) {
+  constexpr int U = (kPacksPerTile + THREADS - 1) / THREADS;  // the whole tile in one batch of loads
+  uint4 v[U];
+  bool live[U];
+  const char* src = static_cast<const char*>(a.partial.mc) + tile_off;
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int p = u * THREADS + threadIdx.x;
+    const int row = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
+    live[u] = p < kPacksPerTile && row < rows_valid && cp < packs_valid_row;
+    v[u] = reduce_pack_mc<T, kSum>(src + size_t(live[u] ? p : 0) * 16);
+  }
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    if (!live[u]) continue;
+    const int p = u * THREADS + threadIdx.x;
+    const int row = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
+    ptx::multimem_st_v4(static_cast<char*>(a.c_sym.mc) + c_off0 + size_t(row) * row_bytes + size_t(cp) * 16, v[u]);
+  }
+}
+
 template <typename T, int THREADS, bool MC>
 __device__ __forceinline__ void ar_reduce_tile_dispatch(const GemmArgs& a, int world, int rank, const char* slices,
                                                         size_t c_off0, size_t row_bytes, int rows_valid,
@@ -344,7 +370,10 @@ __device__ void ar_reducer_role(const CommCtx& ctx, const GemmArgs& a, const Sch
     const int rows_valid = min(kTileM, a.M - m_blk * kTileM);
     const int packs_valid_row = min(kPacksPerTileRow, (a.N - n_blk * kTileN) / 8);
     const size_t c_off0 = size_t(m_blk * kTileM) * row_bytes + size_t(n_blk * kTileN) * 2;
-    if (use_mc)
+    if (a.use_nvls == 2 && a.partial.mc != nullptr && use_mc)
+      ar_reduce_tile_pull<T, THREADS>(a, size_t(m_blk * sc.tiles_n + n_blk) * kTileBytes, c_off0, row_bytes, rows_valid,
+                                      packs_valid_row);
+    else if (use_mc)
       ar_reduce_tile_dispatch<T, THREADS, true>(a, world, rank, slices, c_off0, row_bytes, rows_valid, packs_valid_row);
     else
       ar_reduce_tile_dispatch<T, THREADS, false>(a, world, rank, slices, c_off0, row_bytes, rows_valid, packs_valid_row);
@@ -768,7 +797,8 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
     const uint32_t stage_u32 = ptx::smem_u32(stage_buf);
     int acc = 0;
     uint32_t acc_phase = 0;
-    uint32_t iter = 0;
+    uint32_t iter = 0, prev_iter = 0;
+    bool have_prev = false;
     char* c_base = nullptr;
     if constexpr (MODE == kGemmPlain || MODE == kGemmAg) c_base = static_cast<char*>(a.C) + a.c_emu_stride * blockIdx.y;
     for (int item = blockIdx.x; item < sc.items; item += G, ++iter) {
@@ -881,6 +911,7 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
         char* dst_rows;        // address of (row q*32, column 0 of the tile)
         size_t dst_row_bytes;  // distance between rows
         int owner = 0, owner_counter = 0;
+        size_t push_row0 = 0;
         if constexpr (MODE == kGemmPlain || MODE == kGemmAg) {
           dst_row_bytes = size_t(a.ldc) * 2;
           dst_rows = c_base + (size_t(m_blk * kTileM + q * 32) * a.ldc + size_t(n_blk) * kTileN) * 2;
@@ -890,6 +921,10 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
             owner = seq % ctx.world;
             owner_counter = a.counter_base + seq / ctx.world;
             slice = size_t(seq / ctx.world) * ctx.world + ctx.rank;
+            if (a.use_nvls == 2 && a.partial.mc != nullptr && a.c_sym.mc != nullptr) {
+              owner = ctx.rank;  // pull variant: the tile stays here, at the offset every rank uses for it
+              slice = size_t(tile_id);
+            }
           } else {
             owner = m_blk / sc.bps;
             const int lb = m_blk - owner * sc.bps;
@@ -898,7 +933,10 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
           }
           dst_row_bytes = kTileN * 2;
           dst_rows = static_cast<char*>(a.partial.p[owner]) + slice * kTileBytes + size_t(q * 32) * (kTileN * 2);
+          push_row0 = slice * kTileM + size_t(q * 32);  // row of the owner's buffer seen as [slices * 128, 256]
         }
+        (void)dst_rows;
+        (void)dst_row_bytes;
 #pragma unroll 1
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
@@ -921,8 +959,15 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
                 }
               }
               const int u = c * 4 + j;  // 16-byte unit of the 256-byte staged row
-              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(stage_u32 + lane * 256 + ((u ^ (lane & 7)) << 4)),
-                           "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+              uint32_t saddr;
+              if constexpr (MODE == kGemmAr || MODE == kGemmRsNorm) {
+                // Two [32 rows][128 B] sub-tiles in the 128-byte-swizzle layout of the TMA store below.
+                saddr = stage_u32 + (u >> 3) * 4096 + lane * 128 + (((u & 7) ^ (lane & 7)) << 4);
+              } else {
+                saddr = stage_u32 + lane * 256 + ((u ^ (lane & 7)) << 4);
+              }
+              asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                           "r"(w[3])
                            : "memory");
             }
           }
@@ -931,6 +976,37 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
+          }
+          if constexpr (MODE == kGemmAr || MODE == kGemmRsNorm) {
+            // Push this half (32 rows x 128 columns) into the owner's buffer with two bulk tensor stores issued
+            // by one lane: the copy engine moves the data, no warp waits on NVLink.
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              const CUtensorMap* pm = static_cast<const CUtensorMap*>(a.push_maps) + owner;
+              const int y = static_cast<int>(push_row0);
+              ptx::tma_store_2d(pm, stage_buf, h * 128, y);
+              ptx::tma_store_2d(pm, stage_buf + 4096, h * 128 + 64, y);
+              ptx::bulk_commit_group();
+              if (h == 0) {
+                ptx::bulk_wait_group_read<0>();  // staging buffer is reused by the second half
+              } else {
+                // Tile i-1 of this warp is complete once only this tile's two groups may still be pending.
+                ptx::bulk_wait_group<2>();
+                if (have_prev) {
+                  ptx::fence_proxy_async_all();
+                  __threadfence_block();
+                  atomicAdd(&ctl->epi_count[prev_iter & 7], 1u);
+                }
+                ptx::bulk_wait_group_read<0>();
+              }
+            }
+            __syncwarp();
+            if (h == 1) {
+              have_prev = true;
+              prev_iter = iter;
+            }
+            continue;
           }
           __syncwarp();
 #pragma unroll 4
@@ -964,18 +1040,21 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
         if constexpr (MODE == kGemmAr || MODE == kGemmRsNorm) {
           // This warp's rows of the tile have been issued.  It does NOT wait for the (remote) stores to land:
           // it only tells the signal warp, which takes the wait, and moves on to the next tile.
-          (void)owner;
           (void)owner_counter;
-          __syncwarp();
-          if (lane == 0) {
-            __threadfence_block();
-            atomicAdd(&ctl->epi_count[iter & 7], 1u);
-          }
         }
       }
       if (++acc == kAccStages) {
         acc = 0;
         acc_phase ^= 1;
+      }
+    }
+    if constexpr (MODE == kGemmAr || MODE == kGemmRsNorm) {
+      // Last tile of this warp: wait for its bulk stores, then tell the signal warp.
+      if (lane == 0 && have_prev) {
+        ptx::bulk_wait_group<0>();
+        ptx::fence_proxy_async_all();
+        __threadfence_block();
+        atomicAdd(&ctl->epi_count[prev_iter & 7], 1u);
       }
     }
   } else if (warp == 6) {

@@ -95,7 +95,7 @@ def main() -> int:
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     comm = Communicator(list(range(world)), rank, heap_bytes=3 << 30)
     ctas = [int(c) for c in args.comm_ctas.split(",")]
-    nvls_opts = {"auto": [None], "on": [True], "off": [False], "both": [True, False]}[args.nvls]
+    nvls_opts = {"auto": [None], "on": [True], "off": [False], "pull": [2], "both": [True, False], "all": [2, True, False]}[args.nvls]
     join_opts = {"on": [True], "off": [False], "both": [True, False]}[args.join]
     lines = []
     gen = torch.Generator(device="cuda").manual_seed(100 + rank)
@@ -139,14 +139,15 @@ def main() -> int:
             for c in ctas:
                 for nv in nvls_opts:
                     for jn in join_opts:
-                        op = GemmAllReduce(comm, M, N, dt, comm_ctas=c, use_nvls=nv)
+                        op = GemmAllReduce(comm, M, N, dt, comm_ctas=c, use_nvls=nv, strategy="fused")
                         op.join = jn
                         us = timed(lambda: op(a, b), args.iters, args.warmup)
                         emit({**base, "impl": "ours_fused", "comm_ctas": c, "nvls": nv, "join": jn, "us": round(us, 1),
                               "roofline_frac": round((roof_nvls if comm.nvls and nv is not False else roof) / us, 3)})
-                        comm.free(op.partial_off)
-                        comm.free(op.c_off)
-                        comm.release_counters(op.counter_base)
+                        op.release()
+            op = GemmAllReduce(comm, M, N, dt)  # the library's own choice for this shape
+            emit({**base, "impl": "ours_auto", "strategy": op.strategy, "us": round(timed(lambda: op(a, b), args.iters, args.warmup), 1)})
+            op.release()
             torch.cuda.synchronize()
             comm.check_status()
 

@@ -43,7 +43,7 @@ def main() -> int:
     p.add_argument("--N", dest="n", type=int, default=8192)
     p.add_argument("--K", dest="k", type=int, default=8192, help="global K (split over ranks)")
     p.add_argument("--comm-ctas", type=int, default=16)
-    p.add_argument("--nvls", default="auto", choices=["auto", "on", "off"])
+    p.add_argument("--nvls", default="auto", choices=["auto", "on", "off", "pull"])
     p.add_argument("--no-join", action="store_true")
     args = p.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -51,13 +51,13 @@ def main() -> int:
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     comm = Communicator(list(range(world)), rank, heap_bytes=1 << 30)
-    nv = {"auto": None, "on": True, "off": False}[args.nvls]
+    nv = {"auto": None, "on": True, "off": False, "pull": 2}[args.nvls]
     dt = torch.float16 if args.op == "gemm_ar" else torch.bfloat16
     kl = args.k // world
     a = torch.randn(args.m, kl, device="cuda").to(dt)
     b = (torch.randn(args.n, kl, device="cuda") / args.k ** 0.5).to(dt)
     if args.op == "gemm_ar":
-        op = GemmAllReduce(comm, args.m, args.n, dt, comm_ctas=args.comm_ctas, use_nvls=nv)
+        op = GemmAllReduce(comm, args.m, args.n, dt, comm_ctas=args.comm_ctas, use_nvls=nv, strategy="fused")
         run = lambda: op(a, b)  # noqa: E731
     else:
         op = GemmReduceScatterNorm(comm, args.m, args.n, dt, comm_ctas=args.comm_ctas, use_nvls=nv)

@@ -107,8 +107,14 @@ class Communicator:
         if self.config.legacy_ipc:
             flags |= _lib.FLAG_LEGACY_IPC
         lib = _lib.lib()
-        if self.config.tuning_policy:
-            _lib.check(lib.oob_policy_load(self.config.tuning_policy.encode()))
+        # OOB_TUNING_POLICY names a policy file; without it the policy measured on B200 / NVSwitch that ships
+        # with the package is used ("builtin" selects the compiled-in size rule instead).
+        policy = self.config.tuning_policy
+        if not policy:
+            packaged = os.path.join(os.path.dirname(os.path.abspath(__file__)), "policy", "b200_nvswitch.json")
+            policy = packaged if os.path.exists(packaged) else ""
+        if policy and policy != "builtin":
+            _lib.check(lib.oob_policy_load(policy.encode()))
         handle = ctypes.c_void_p()
         _lib.check(lib.oob_comm_create(self.rank, self.world, self.device, broker_key.encode(),
                                        heap_bytes or self.config.heap_bytes, flags, self.config.timeout_ms,

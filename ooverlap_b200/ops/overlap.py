@@ -37,14 +37,18 @@ def _emulated(comm) -> bool:
     return bool(getattr(comm, "emulated", False))
 
 
-def _use_nvls(comm, choice: Optional[bool]) -> int:
+def _use_nvls(comm, choice) -> int:
     """NVLS (in-switch reduction / broadcast) pays off from four ranks on; between two GPUs plain peer
-    loads and stores are faster.  ``choice`` overrides the default."""
+    stores are faster.  ``choice`` overrides the default: False / 0 = peer pushes only, True / 1 = peer pushes of the
+    partial tiles + multimem.st of the result, 2 = partial tiles stay local and the owner reduces them inside the
+    switch (multimem.ld_reduce), which moves the message once per direction instead of 1.75 times."""
     if not getattr(comm, "nvls", False):
         return 0
     if choice is None:
-        return 1 if comm.world >= 4 else 0
-    return 1 if choice else 0
+        return 2 if comm.world >= 4 else 0
+    if choice is True:
+        return 1
+    return int(choice)  # 0 = peer pushes only, 1 = push + multimem.st, 2 = in-switch reduce (pull) + multimem.st
 
 
 def _operands(comm, a: torch.Tensor, b: torch.Tensor):
@@ -57,18 +61,45 @@ def _operands(comm, a: torch.Tensor, b: torch.Tensor):
 
 
 class GemmAllReduce:
-    def __init__(self, comm, M: int, N: int, dtype: torch.dtype, *, comm_ctas: int = 20, max_ctas: int = 0,
-                 use_nvls: Optional[bool] = None):
-        self.use_nvls = use_nvls
+    """Row-parallel linear: ``C = sum_ranks(A_r @ B_r^T)`` in every rank's registered memory.
+
+    ``strategy``:
+      * ``"fused"``   one kernel: the epilogue pushes partial tiles to their owner rank, communication CTAs (and GEMM
+                      CTAs that ran out of tiles) reduce and broadcast them while later tiles still compute;
+      * ``"unfused"`` this library's GEMM writes into the registered output, then its all-reduce kernel runs on it
+                      (the policy picks one-shot / two-shot / NVLS and the CTA budget);
+      * ``"auto"``    (default) what measured best on B200 / NVSwitch: between two ranks the fused kernel; from four
+                      ranks on the unfused pair for messages up to 64 MiB (a single wave or few waves of tiles leave
+                      nothing to overlap and the NVLS all-reduce moves the message once per direction) and the fused
+                      kernel with peer pushes above.
+    """
+
+    def __init__(self, comm, M: int, N: int, dtype: torch.dtype, *, comm_ctas: Optional[int] = None, max_ctas: int = 0,
+                 use_nvls=None, strategy: str = "auto"):
+        if strategy not in ("auto", "fused", "unfused"):
+            raise ValueError(strategy)
         self.comm, self.M, self.N, self.dtype = comm, M, N, dtype
-        self.comm_ctas, self.max_ctas = comm_ctas, max_ctas
-        self.fused = comm.world > 1
-        if self.fused:
+        self.max_ctas = max_ctas
+        self.multi = comm.world > 1
+        if strategy == "auto":
+            big = M * N * 2 > (64 << 20)
+            strategy = "fused" if (comm.world < 4 or big or _emulated(comm)) else "unfused"
+            if use_nvls is None and comm.world >= 4:
+                use_nvls = 0  # measured: peer pushes beat both NVLS variants inside the fused kernel
+        self.strategy = strategy
+        self.use_nvls = use_nvls
+        self.comm_ctas = comm_ctas if comm_ctas is not None else (20 if comm.world < 4 else 16)
+        if self.multi:
             lib = _lib.lib()
-            self.partial_off = comm.alloc(int(lib.oob_gemm_partial_bytes(M, N)))
             self.c_off = comm.alloc(M * N * 2)
-            self.counter_base = comm.reserve_counters(lib.oob_gemm_counters_needed(_lib.GEMM_AR, M, N, comm.world))
             self._out = None if _emulated(comm) else comm.view(self.c_off, (M, N), dtype)
+            if self.strategy == "fused":
+                self.partial_off = comm.alloc(int(lib.oob_gemm_partial_bytes(M, N)))
+                self.counter_base = comm.reserve_counters(lib.oob_gemm_counters_needed(_lib.GEMM_AR, M, N, comm.world))
+
+    @property
+    def fused(self) -> bool:
+        return self.multi and self.strategy == "fused"
 
     def output(self, rank: Optional[int] = None) -> torch.Tensor:
         """The [M, N] result buffer in registered memory (of ``rank`` in emulation)."""
@@ -76,9 +107,22 @@ class GemmAllReduce:
             return self.comm.view(self.c_off, (self.M, self.N), self.dtype, rank or 0)
         return self._out
 
+    def release(self) -> None:
+        """Gives the op's registered buffers and counters back (collective by convention)."""
+        if not self.multi:
+            return
+        if self.strategy == "fused":
+            self.comm.free(self.partial_off)
+            self.comm.release_counters(self.counter_base)
+        self.comm.free(self.c_off)
+        self.multi = False
+
     def __call__(self, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-        if not self.fused:
+        if not self.multi:
             return gemm(a, b, max_ctas=self.max_ctas)
+        if self.strategy == "unfused":
+            gemm(a, b, out=self._out, max_ctas=self.max_ctas, splits=1)
+            return self.comm.all_reduce(self._out)
         a0, b0, sa, sb = _operands(self.comm, a, b)
         _check_operands(a0, b0)
         if a0.shape[0] != self.M or b0.shape[0] != self.N:

@@ -161,11 +161,22 @@ def _rank_fused(rank, world, key):
     a = [gen((M, K), 200 + r) for r in range(world)]
     bw = [gen((N, K), 300 + r, (K * world) ** -0.5) for r in range(world)]
     want = sum(a[r].float() @ bw[r].float().t() for r in range(world))
-    op = GemmAllReduce(comm, M, N, dt, comm_ctas=8)
-    for it in range(3):
+    # every data path of the fused all-reduce: peer pushes, pushes + multicast result, in-switch reduction
+    for variant in ([0, 1, 2] if comm.nvls else [0]):
+        op = GemmAllReduce(comm, M, N, dt, comm_ctas=8, use_nvls=variant, strategy="fused")
+        for it in range(3):
+            c = op(a[rank].cuda(), bw[rank].cuda())
+            torch.cuda.synchronize()
+            out.append((f"gemm_ar nvls{variant} {it}", (c.float().cpu() - want).abs().max().item(),
+                        3e-2 * max(1, want.abs().max().item())))
+            c.zero_()
+        op.release()
+    for strat in ("auto", "unfused"):
+        op = GemmAllReduce(comm, M, N, dt, strategy=strat)
         c = op(a[rank].cuda(), bw[rank].cuda())
         torch.cuda.synchronize()
-        out.append((f"gemm_ar {it}", (c.float().cpu() - want).abs().max().item(), 3e-2 * max(1, want.abs().max().item())))
+        out.append((f"gemm_ar {strat}", (c.float().cpu() - want).abs().max().item(), 3e-2 * max(1, want.abs().max().item())))
+        op.release()
     rs = GemmReduceScatterNorm(comm, M, N, dt, eps=eps, comm_ctas=8)
     wn = (1 + 0.02 * torch.randn(N, generator=torch.Generator().manual_seed(6))).to(dt)
     res = gen((M, N), 400)
