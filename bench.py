@@ -123,10 +123,12 @@ def main() -> int:
         return 1
 
     # ---- device-timed arm ---------------------------------------------------
+    # The clock sampler runs from the warm-up on (nvidia-smi needs a moment to start) and is stopped right
+    # after the timed loop, so its samples are taken under this load.
+    sampler = ClockSampler(local_rank, period_ms=50).start() if rank == 0 else None
     for i in range(max(3, args.warmup)):
         step(i)
     fence()
-    sampler = ClockSampler(local_rank).start() if rank == 0 else None
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     per_shape = {m: 0.0 for m in MS}
     start.record()

@@ -13,16 +13,21 @@
 // sums the splits in a fixed order and writes C.
 // Fused modes add a communication role.  `comm_ctas` CTAs run it from the start and every GEMM CTA joins when it
 // has finished its tiles, drawing work from a ticket counter:
-//   GEMM->AR      the epilogue writes the partial tile to a registered buffer and bumps an arrival counter on the
-//                 tile's owner rank; the owner pulls the tile from all ranks (multimem.ld_reduce in the switch, or
-//                 P2P loads, fp32 accumulate) and broadcasts the sum into every rank's C (multimem.st / P2P stores)
-//                 while later tiles still compute.
-//   GEMM->RS+norm counters are per 128-row block on the rank that owns the rows; reducers sum the rows, add the
-//                 residual, apply RMSNorm and write the rank's rows.
+//   GEMM->AR      every tile has an owner rank.  The epilogue stages its 32-row strips in shared memory and PUSHES
+//                 them into the owner's registered buffer with bulk tensor stores (cp.async.bulk.tensor, smem ->
+//                 peer global memory); a signal warp waits for those stores, orders them system-wide and bumps the
+//                 tile's arrival counter on the owner, so the epilogue warps never stall on NVLink.  The owner sums
+//                 the `world` slices from its LOCAL memory (fp32, rank order) and broadcasts the result into every
+//                 rank's C (multimem.st through the switch, or peer stores) while later tiles still compute.
+//                 use_nvls == 2 selects the pull variant: tiles stay in the producer's buffer and the owner reads
+//                 their in-switch sum with multimem.ld_reduce.
+//   GEMM->RS+norm same push, counters per 128-row block on the rank that owns the rows; reducers sum the rows, add
+//                 the residual, apply RMSNorm and write the rank's rows.
 //   AG->GEMM      pusher CTAs broadcast this rank's A shard chunk by chunk into every rank's gathered buffer and bump
 //                 per-chunk flags; the TMA producer waits for the flag of the chunk it is about to load from LOCAL
 //                 memory.
-// All cross-GPU traffic is plain ld/st/red or multimem.*; TMA only ever touches local memory.
+// Cross-GPU traffic is ld/st/red, multimem.* and bulk tensor STORES into peer memory.  TMA LOADS only ever read
+// this GPU's own memory, and nothing here uses cluster multicast.
 //
 // Capability parity with the reference: signalling GEMM + reorder epilogue + wait kernel + per-segment all-reduce
 // (src/gemm/gemm_with_signal_sm90.h:102-513, src/epilogue/reorder_epilogue.h:324-595, src/wait.cuh:5-9,

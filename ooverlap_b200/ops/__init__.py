@@ -1,4 +1,5 @@
 """Hot ops: hand-written sm_100a kernels behind small Python entry points."""
+from . import solutions  # noqa: F401
 from .gemm import gemm  # noqa: F401
 from .norm import (fused_allreduce_rmsnorm, fused_reduce_scatter_rmsnorm, rmsnorm,  # noqa: F401
                    rmsnorm_reference)

@@ -82,6 +82,16 @@ class GemmAllReduce:
         self.max_ctas = max_ctas
         self.multi = comm.world > 1
         if strategy == "auto":
+            # A tuned solution for this shape (OOB_OVERLAP_SOLUTIONS, written by bench.tune_overlap) wins.
+            from . import solutions
+            sol = solutions.lookup("gemm_ar", M, N, 0, comm.world, "bf16" if dtype == torch.bfloat16 else "fp16")
+            if sol is not None and not _emulated(comm):
+                strategy = sol.get("strategy", "auto")
+                if comm_ctas is None and sol.get("comm_ctas"):
+                    comm_ctas = int(sol["comm_ctas"])
+                if use_nvls is None and "use_nvls" in sol:
+                    use_nvls = int(sol["use_nvls"])
+        if strategy == "auto":
             big = M * N * 2 > (64 << 20)
             strategy = "fused" if (comm.world < 4 or big or _emulated(comm)) else "unfused"
             if use_nvls is None and comm.world >= 4:

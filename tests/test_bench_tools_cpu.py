@@ -1,0 +1,63 @@
+"""Host-only tooling: result aggregation over backend orders, plot series, tuning solutions."""
+import json
+
+from ooverlap_b200.bench import aggregate, plot
+from ooverlap_b200.ops import solutions
+
+
+def _write(path, rows):
+    path.write_text("\n".join(json.dumps(r) for r in rows) + "\nnot json\n")
+    return str(path)
+
+
+def test_aggregate_over_orders(tmp_path):
+    f1 = _write(tmp_path / "a.jsonl", [
+        {"model": "m", "tp": 8, "batch": 1, "backend": "nccl", "output_tok_s": 10.0},
+        {"model": "m", "tp": 8, "batch": 1, "backend": "ours", "output_tok_s": 20.0},
+        {"model": "m", "tp": 8, "batch": 64, "backend": "nccl", "output_tok_s": 100.0}])
+    f2 = _write(tmp_path / "b.jsonl", [
+        {"model": "m", "tp": 8, "batch": 1, "backend": "ours", "output_tok_s": 24.0},
+        {"model": "m", "tp": 8, "batch": 1, "backend": "nccl", "output_tok_s": 12.0},
+        {"model": "m", "tp": 8, "batch": 1, "backend": "nccl"}])  # row without the metric is ignored
+    out = aggregate.aggregate(aggregate.read_lines([f1, f2]), "output_tok_s", ["model", "tp", "batch"], "backend", "nccl")
+    assert len(out) == 2
+    b1 = out[0]
+    assert b1["batch"] == 1 and b1["stats"]["nccl"]["n"] == 2 and b1["stats"]["nccl"]["median"] == 11.0
+    assert b1["stats"]["ours"]["mean"] == 22.0
+    assert abs(b1["speedup_vs_nccl"]["ours"] - 2.0) < 1e-9
+    assert "ours" not in out[1]["stats"]
+    # latency-like metrics: lower is better
+    lat = aggregate.aggregate([{"g": 1, "impl": "a", "us": 10.0}, {"g": 1, "impl": "b", "us": 5.0}], "us", ["g"], "impl", "a",
+                              higher_is_better=False)
+    assert lat[0]["speedup_vs_a"]["b"] == 2.0
+    assert aggregate.main([f1, "--metric", "output_tok_s"]) == 0
+
+
+def test_plot_series(tmp_path, capsys):
+    sweep = [{"collective": "all_reduce", "impl": "nccl", "algo": "nccl", "bytes": 1024, "bus_gbs": 1.0, "ctas": 0},
+             {"collective": "all_reduce", "impl": "ours", "algo": "twoshot_nvls", "bytes": 1024, "bus_gbs": 2.0, "ctas": 8},
+             {"collective": "all_reduce", "impl": "ours", "algo": "twoshot_nvls", "bytes": 1024, "bus_gbs": 3.0, "ctas": 32}]
+    s = plot.sweep_series(sweep)
+    assert s["all_reduce"]["twoshot_nvls"] == [(1024, 3.0)] and s["all_reduce"]["nccl"] == [(1024, 1.0)]
+    ov = plot.overlap_series([{"op": "gemm_ar", "M": 512, "impl": "ours_fused", "nvls": 2, "us": 50.0},
+                              {"op": "gemm_ar", "M": 512, "impl": "ours_fused", "nvls": 2, "us": 40.0},
+                              {"op": "gemm_ar", "M": 512, "impl": "cublas+nccl", "us": 80.0}])
+    assert ov[("gemm_ar", 512)] == {"ours_fused(nvls=2)": 40.0, "cublas+nccl": 80.0}
+    f = _write(tmp_path / "s.jsonl", sweep)
+    assert plot.main([f, "--kind", "sweep"]) == 0
+    assert "twoshot_nvls" in capsys.readouterr().out
+
+
+def test_solutions_roundtrip(tmp_path, monkeypatch):
+    path = str(tmp_path / "sol.json")
+    k = solutions.key("gemm_ar", 8192, 8192, 8192, 8, "fp16")
+    assert k == "gemm_ar:8192x8192x8192:tp8:fp16"
+    solutions.save(path, {k: {"strategy": "fused", "comm_ctas": 16, "use_nvls": 0, "us": 417.0}})
+    assert solutions.lookup("gemm_ar", 8192, 8192, 8192, 8, "fp16", path)["comm_ctas"] == 16
+    assert solutions.lookup("gemm_ar", 8192, 8192, 0, 8, "fp16", path)["strategy"] == "fused"  # any K
+    assert solutions.lookup("gemm_ar", 512, 8192, 8192, 8, "fp16", path) is None
+    monkeypatch.setenv("OOB_OVERLAP_SOLUTIONS", path)
+    assert solutions.lookup("gemm_ar", 8192, 8192, 8192, 8, "fp16")["us"] == 417.0
+    monkeypatch.delenv("OOB_OVERLAP_SOLUTIONS")
+    assert solutions.lookup("gemm_ar", 8192, 8192, 8192, 8, "fp16") is None
+    assert solutions.load(str(tmp_path / "missing.json")) == {}
