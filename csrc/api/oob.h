@@ -157,6 +157,7 @@ typedef struct {
   int splits;   /* plain mode: K splits per tile; 0 = chosen from the shape, 1 = off */
   int no_join;  /* fused AR / RS: 1 = only the dedicated communication CTAs reduce */
   void* trace;  /* optional device buffer, 8 x uint64 per CTA: globaltimer stamps of the kernel's phases */
+  int pair;     /* plain mode: 0 = two-SM kernel when the shape suits it, 1 = whenever possible, -1 = never */
 } oob_gemm_args_t;
 /* c may be NULL for OOB_GEMM_PLAIN. */
 int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream);

@@ -1,5 +1,6 @@
 // Host entry of the tcgen05 GEMM family: argument checks, tensor-map cache, the library-owned split-K
 // workspace, and dispatch to the kernels of gemm_kernel.cuh.
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -7,6 +8,10 @@
 #include "gemm_kernel.cuh"
 
 namespace oob {
+
+// gemm_pair.cu
+cudaError_t launch_gemm_pair(const GemmArgs& a, DeviceStatus* status, cudaStream_t stream, gemm_detail::TmapFn make_tmap);
+
 namespace {
 
 using namespace gemm_detail;
@@ -232,6 +237,18 @@ cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& args, cudaStream_t s
     if (splits > 1 && a.splitk_ws == nullptr) {
       e = ensure_splitk(dev, splitk_workspace_bytes(a.M, a.N, splits), stream, &a.splitk_ws);
       if (e != cudaSuccess) return e;
+    }
+    // Large problems go to the two-SM kernel: same tile count per SM, two thirds of the operand traffic.
+    const bool pair_ok = splits == 1 && ctx.emu_table == nullptr && a.c_emu_stride == 0 && (a.max_ctas == 0 || a.max_ctas >= 2);
+    static const bool pair_env_off = [] {
+      const char* v = getenv("OOB_GEMM_PAIR");
+      return v != nullptr && v[0] == '0';
+    }();
+    const bool pair_auto = a.M > kTileM && !pair_env_off;
+    if (pair_ok && (a.pair > 0 || (a.pair == 0 && pair_auto))) {
+      e = launch_gemm_pair(a, ctx.status, stream, make_tmap_cached);
+      if (e != cudaErrorNotSupported) return e;
+      cudaGetLastError();
     }
   } else {
     a.splits = 1;

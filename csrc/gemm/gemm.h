@@ -60,6 +60,9 @@ struct GemmArgs {
   // and their arrival counters live in splitk_ws (nullptr = the library's own workspace, grown on demand).
   int splits;
   void* splitk_ws;
+  // Plain mode: 0 = the two-SM kernel (256x256 tiles on CTA pairs) when the shape suits it, 1 = always when
+  // possible, -1 = never.
+  int pair;
 
   // Fused modes
   PeerPtrs partial;     // AR / RS: per-owner staging of partial tiles, registered; see oob_gemm_partial_bytes

@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import ctypes
 import threading
-from ctypes import (POINTER, Structure, byref, c_char_p, c_float, c_int, c_uint, c_uint64, c_void_p)
+from ctypes import (POINTER, Structure, byref, c_char_p, c_float, c_int, c_int64, c_uint, c_uint64, c_void_p)
 
 from . import _build
 
@@ -68,7 +68,21 @@ class GemmArgs(Structure):
                 ("c_reg", c_int), ("c_off", c_uint64), ("counter_base", c_int), ("residual", c_void_p),
                 ("weight", c_void_p), ("eps", c_float), ("y_local", c_void_p), ("res_out_local", c_void_p),
                 ("rs_emu_stride", c_uint64), ("a_full_reg", c_int), ("a_full_off", c_uint64), ("use_nvls", c_int),
-                ("splits", c_int), ("no_join", c_int), ("trace", c_void_p)]
+                ("splits", c_int), ("no_join", c_int), ("trace", c_void_p), ("pair", c_int)]
+
+
+class RopeArgs(Structure):
+    _fields_ = [("dtype", c_int), ("B", c_int), ("T", c_int), ("H", c_int), ("KV", c_int), ("hd", c_int),
+                ("qkv", c_void_p), ("q_out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
+                ("cache_batch_stride", c_int64), ("max_len", c_int), ("batch0", c_int), ("cos_table", c_void_p),
+                ("sin_table", c_void_p), ("pos_dev", c_void_p), ("pos0", c_int)]
+
+
+class AttnDecodeArgs(Structure):
+    _fields_ = [("dtype", c_int), ("B", c_int), ("H", c_int), ("KV", c_int), ("q", c_void_p), ("k_cache", c_void_p),
+                ("v_cache", c_void_p), ("cache_batch_stride", c_int64), ("max_len", c_int), ("batch0", c_int),
+                ("out", c_void_p), ("pos_dev", c_void_p), ("len", c_int), ("scale", c_float), ("splits", c_int),
+                ("len_bound", c_int), ("workspace", c_void_p)]
 
 
 _lock = threading.Lock()
@@ -103,6 +117,12 @@ def _declare(lib) -> None:
     lib.oob_gemm_counters_needed.argtypes = [c_int, c_int, c_int, c_int]
     lib.oob_gemm_partial_bytes.argtypes = [c_int, c_int]
     lib.oob_gemm_partial_bytes.restype = c_uint64
+    lib.oob_rope_kv_write.argtypes = [POINTER(RopeArgs), P]
+    lib.oob_silu_mul.argtypes = [c_int, P, c_int64, P, c_int, c_int, P]
+    lib.oob_attn_decode.argtypes = [POINTER(AttnDecodeArgs), P]
+    lib.oob_attn_decode_auto_splits.argtypes = [c_int, c_int, c_int]
+    lib.oob_attn_decode_workspace_bytes.argtypes = [c_int, c_int, c_int]
+    lib.oob_attn_decode_workspace_bytes.restype = c_uint64
     lib.oob_policy_load.argtypes = [c_char_p]
     lib.oob_policy_select.argtypes = [c_int, c_int, c_uint64, c_int, POINTER(c_int), POINTER(c_int)]
     lib.oob_topology_json.argtypes = [c_char_p, c_uint64, c_int]

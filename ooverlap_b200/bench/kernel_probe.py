@@ -7,6 +7,10 @@ Small enough to sit under a profiler::
     python -m ooverlap_b200.bench.kernel_probe --op rmsnorm --m 16384 --n 8192
     python -m ooverlap_b200.bench.kernel_probe --op allreduce --world 8 --bytes 67108864     (emulated ranks)
     python -m ooverlap_b200.bench.kernel_probe --op gemm_ar --world 2 --m 2048 --n 2048 --k 1024  (emulated ranks)
+    python -m ooverlap_b200.bench.kernel_probe --op attn_decode --m 64 --heads 8 --kv-heads 1 --ctx 1088
+    python -m ooverlap_b200.bench.kernel_probe --specs '[{"op": "gemm", "m": 2048, "pair": 1}, {"op": "cublas", "m": 2048}]'
+
+``--specs`` runs several probes in one process (each entry overrides the command-line values).
 
 Each run prints a JSON line with the time per call, the achieved TFLOP/s or GB/s and the fraction of the
 measured peak (``MEASURED_PEAKS.json`` beside the repository root when present, else 1629.9 TFLOP/s and
@@ -52,9 +56,12 @@ def timed(fn, iters, warmup, flush):
     return ms[len(ms) // 2]
 
 
+OPS = ["gemm", "gemm_splitk", "cublas", "rmsnorm", "allreduce", "gemm_ar", "attn_decode", "sdpa_decode", "silu_mul", "rope"]
+
+
 def main() -> int:
     p = argparse.ArgumentParser()
-    p.add_argument("--op", default="gemm", choices=["gemm", "gemm_splitk", "cublas", "rmsnorm", "allreduce", "gemm_ar"])
+    p.add_argument("--op", default="gemm", choices=OPS)
     p.add_argument("--m", type=int, default=8192)
     p.add_argument("--n", type=int, default=8192)
     p.add_argument("--k", type=int, default=8192)
@@ -64,15 +71,36 @@ def main() -> int:
     p.add_argument("--world", type=int, default=8)
     p.add_argument("--bytes", type=int, default=64 << 20)
     p.add_argument("--splits", type=int, default=0)
+    p.add_argument("--pair", type=int, default=0, help="plain GEMM: 1 = two-SM kernel, -1 = one-SM kernel, 0 = auto")
+    p.add_argument("--heads", type=int, default=8)
+    p.add_argument("--kv-heads", type=int, default=1)
+    p.add_argument("--ctx", type=int, default=1088, help="attention: context length (keys attended)")
     p.add_argument("--no-flush", action="store_true")
+    p.add_argument("--specs", default="", help="JSON list of probes; each entry overrides these options")
     args = p.parse_args()
-
-    from .. import EmulatedGroup, _lib
-    from ..ops import GemmAllReduce, gemm, rmsnorm
     torch.cuda.set_device(0)
+    flush = None if args.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    if not args.specs:
+        print(json.dumps(probe(args, flush)))
+        return 0
+    for spec in json.loads(args.specs):
+        one = argparse.Namespace(**vars(args))
+        for k, v in spec.items():
+            if not hasattr(one, k.replace("-", "_")):
+                raise SystemExit(f"unknown probe option {k!r}")
+            setattr(one, k.replace("-", "_"), v)
+        if one.op not in OPS:
+            raise SystemExit(f"unknown op {one.op!r}")
+        print(json.dumps(probe(one, flush)), flush=True)
+        torch.cuda.empty_cache()
+    return 0
+
+
+def probe(args, flush) -> dict:
+    from .. import EmulatedGroup, _lib
+    from ..ops import GemmAllReduce, attn_decode, gemm, rmsnorm, rope_kv_write, rope_tables, silu_mul
     dt = torch.bfloat16 if args.dtype == "bf16" else torch.float16
     tf_peak, bw_peak, src = peaks()
-    flush = None if args.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     rec = {"op": args.op, "dtype": args.dtype, "peaks": src}
     if args.op in ("gemm", "gemm_splitk", "cublas"):
         a = torch.randn(args.m, args.k, device="cuda").to(dt)
@@ -82,7 +110,8 @@ def main() -> int:
             fn = lambda: torch.matmul(a, b.t(), out=out)  # noqa: E731
         else:
             splits = args.splits if args.op == "gemm_splitk" else 1
-            fn = lambda: gemm(a, b, out=out, splits=splits)  # noqa: E731
+            rec["pair"] = args.pair
+            fn = lambda: gemm(a, b, out=out, splits=splits, pair=args.pair)  # noqa: E731
         ms = timed(fn, args.iters, args.warmup, flush)
         tflops = 2.0 * args.m * args.n * args.k / (ms * 1e-3) / 1e12
         gbs = (args.m * args.k + args.n * args.k + args.m * args.n) * 2 / (ms * 1e-3) / 1e9
@@ -97,6 +126,42 @@ def main() -> int:
         ms = timed(lambda: rmsnorm(x, w, 1e-6, r, out=y, residual_out=ro), args.iters, args.warmup, flush)
         gbs = 4.0 * x.numel() * 2 / (ms * 1e-3) / 1e9
         rec.update(rows=args.m, hidden=args.n, us=round(ms * 1e3, 2), gbs=round(gbs, 1), frac_of_peak_hbm=round(gbs / bw_peak, 3))
+    elif args.op in ("attn_decode", "sdpa_decode"):
+        # args.m sequences, one new token each, against `ctx` cached keys per sequence.
+        B, H, KV, L = args.m, args.heads, args.kv_heads, args.ctx
+        max_len = (L + 127) // 128 * 128
+        q = torch.randn(B, H, 128, device="cuda").to(dt)
+        kc = torch.randn(B, KV, max_len, 128, device="cuda").to(dt)
+        vc = torch.randn(B, KV, max_len, 128, device="cuda").to(dt)
+        pos = torch.full((1,), L - 1, dtype=torch.long, device="cuda")
+        if args.op == "attn_decode":
+            out = torch.empty(B, H * 128, device="cuda", dtype=dt)
+            fn = lambda: attn_decode(q, kc, vc, pos, out=out, splits=args.splits)  # noqa: E731
+        else:
+            mask = torch.full((1, 1, 1, max_len), float("-inf"), device="cuda", dtype=dt)
+            mask[..., :L] = 0
+            fn = lambda: torch.nn.functional.scaled_dot_product_attention(  # noqa: E731
+                q.view(B, H, 1, 128), kc, vc, attn_mask=mask, enable_gqa=True)
+        ms = timed(fn, args.iters, args.warmup, flush)
+        gbs = 2.0 * B * KV * L * 128 * 2 / (ms * 1e-3) / 1e9
+        rec.update(B=B, heads=H, kv_heads=KV, ctx=L, us=round(ms * 1e3, 2), kv_gbs=round(gbs, 1),
+                   frac_of_peak_hbm=round(gbs / bw_peak, 3))
+    elif args.op == "silu_mul":
+        gu = torch.randn(args.m, 2 * args.n, device="cuda").to(dt)
+        out = torch.empty(args.m, args.n, device="cuda", dtype=dt)
+        ms = timed(lambda: silu_mul(gu, out), args.iters, args.warmup, flush)
+        gbs = 3.0 * args.m * args.n * 2 / (ms * 1e-3) / 1e9
+        rec.update(rows=args.m, F=args.n, us=round(ms * 1e3, 2), gbs=round(gbs, 1), frac_of_peak_hbm=round(gbs / bw_peak, 3))
+    elif args.op == "rope":
+        B, H, KV = args.m, args.heads, args.kv_heads
+        qkv = torch.randn(B, (H + 2 * KV) * 128, device="cuda").to(dt)
+        kc = torch.zeros(B, KV, 256, 128, device="cuda", dtype=dt)
+        vc = torch.zeros_like(kc)
+        cos, sin = rope_tables(256, 128, 500000.0, qkv.device)
+        pos = torch.full((1,), 100, dtype=torch.long, device="cuda")
+        qo = torch.empty(B, H * 128, device="cuda", dtype=dt)
+        ms = timed(lambda: rope_kv_write(qkv, B, 1, H, KV, kc, vc, cos, sin, pos, q_out=qo), args.iters, args.warmup, flush)
+        rec.update(B=B, heads=H, kv_heads=KV, us=round(ms * 1e3, 2))
     elif args.op == "allreduce":
         g = EmulatedGroup(args.world, heap_bytes=args.bytes + (32 << 20))
         n = args.bytes // 2
@@ -121,8 +186,7 @@ def main() -> int:
         tflops = 2.0 * args.world * args.m * args.n * args.k / (ms * 1e-3) / 1e12
         rec.update(world=args.world, M=args.m, N=args.n, K=args.k, us=round(ms * 1e3, 2), tflops_all_ranks=round(tflops, 1))
         g.close()
-    print(json.dumps(rec))
-    return 0
+    return rec
 
 
 if __name__ == "__main__":

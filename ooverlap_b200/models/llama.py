@@ -2,10 +2,12 @@
 
 Every linear layer is this library's tcgen05 GEMM; each transformer layer has two row-parallel projections
 (``o_proj`` and ``down_proj``) whose all-reduce is fused with the residual add and the following RMSNorm, i.e. 160
-all-reduces per token step for the 80-layer 70B configuration.  Attention itself uses PyTorch's
-``scaled_dot_product_attention`` (the reference has no attention kernels either; it only replaces the
-tensor-parallel communication of a served model).  The decode step has static shapes (position and mask are
-device tensors) and is replayed from one CUDA graph.
+all-reduces per token step for the 80-layer 70B configuration.  A decode step of a layer is nine kernels of this
+library: QKV GEMM, RoPE + KV-cache write, grouped-query decode attention over the static cache (head size 128),
+output GEMM, all-reduce + residual + RMSNorm, gate/up GEMM, SwiGLU, down GEMM, all-reduce + residual + RMSNorm.
+Prefill attention uses PyTorch's causal ``scaled_dot_product_attention`` (the reference has no attention kernels;
+it only replaces the tensor-parallel communication of a served model).  The decode step has static shapes (the
+position is a device tensor) and is replayed from one CUDA graph.
 
 ``backend="nccl"`` runs the same model with ``torch.mm`` (cuBLAS) + ``torch.distributed.all_reduce`` (NCCL) +
 PyTorch RMSNorm: the comparison arm of the serving benchmark.
@@ -21,7 +23,7 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
-from ..ops import fused_allreduce_rmsnorm, gemm, rmsnorm
+from ..ops import attn_decode, fused_allreduce_rmsnorm, gemm, rmsnorm, rope_kv_write, rope_tables, silu_mul
 
 
 @dataclass
@@ -34,15 +36,25 @@ class LlamaConfig:
     vocab: int = 128256
     eps: float = 1e-5
     rope_theta: float = 500000.0
+    head_size: int = 0  # 0 = hidden / heads
 
     @property
     def head_dim(self) -> int:
-        return self.hidden // self.heads
+        return self.head_size or self.hidden // self.heads
+
+    def shard(self, world: int, layers: int = 0) -> "LlamaConfig":
+        """The configuration one rank of a ``world``-way tensor-parallel group computes (heads, KV heads, FFN and
+        vocabulary divided, head size kept): lets one GPU run a rank's kernels at their real shapes, without the
+        communication."""
+        return LlamaConfig(layers=layers or self.layers, hidden=self.hidden, heads=self.heads // world,
+                           kv_heads=max(1, self.kv_heads // world), ffn=self.ffn // world, vocab=self.vocab // world,
+                           eps=self.eps, rope_theta=self.rope_theta, head_size=self.head_dim)
 
 
 LLAMA3_70B = LlamaConfig()
 LLAMA3_8B = LlamaConfig(layers=32, hidden=4096, heads=32, kv_heads=8, ffn=14336)
 TINY = LlamaConfig(layers=2, hidden=512, heads=8, kv_heads=2, ffn=1024, vocab=1024)
+TINY128 = LlamaConfig(layers=2, hidden=1024, heads=8, kv_heads=2, ffn=2048, vocab=1024)  # head size 128
 
 
 def _apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
@@ -94,6 +106,8 @@ class LlamaTP:
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, hd, 2, device=self.device, dtype=torch.float32) / hd))
         ang = torch.arange(max_len, device=self.device, dtype=torch.float32).unsqueeze(-1) * inv
         self.rope_cos, self.rope_sin = ang.cos().to(dtype), ang.sin().to(dtype)  # [max_len, hd/2]
+        if backend == "ours":
+            self.rope_cos32, self.rope_sin32 = rope_tables(max_len, hd, cfg.rope_theta, self.device)
 
     # ------------------------------------------------------------ primitives
     def _mm(self, x, wt):
@@ -135,32 +149,55 @@ class LlamaTP:
         cfg, hd = self.cfg, self.cfg.head_dim
         B, T = tokens.shape
         decode = isinstance(pos, torch.Tensor)
-        if decode:
-            cos, sin = self.rope_cos.index_select(0, pos), self.rope_sin.index_select(0, pos)
-        else:
-            cos, sin = self.rope_cos[pos:pos + T], self.rope_sin[pos:pos + T]
+        ours = self.backend == "ours"
+        if not ours:
+            if decode:
+                cos, sin = self.rope_cos.index_select(0, pos), self.rope_sin.index_select(0, pos)
+            else:
+                cos, sin = self.rope_cos[pos:pos + T], self.rope_sin[pos:pos + T]
         h = self.embed[tokens.reshape(-1)]  # [B*T, hidden]  residual stream
         x = self._norm(h, self.layers[0]["norm1"])
         sl = slice(batch0, batch0 + B)
         for li, layer in enumerate(self.layers):
-            qkv = self._mm(x, layer["wqkv"]).view(B, T, self.h_local + 2 * self.kv_local, hd)
-            q = _apply_rope(qkv[:, :, : self.h_local], cos, sin).transpose(1, 2)
-            k = _apply_rope(qkv[:, :, self.h_local: self.h_local + self.kv_local], cos, sin).transpose(1, 2)
-            v = qkv[:, :, self.h_local + self.kv_local:].transpose(1, 2)
-            if decode:
-                self.k_cache[li, sl].index_copy_(2, pos, k)
-                self.v_cache[li, sl].index_copy_(2, pos, v)
-                att = F.scaled_dot_product_attention(q, self.k_cache[li, sl], self.v_cache[li, sl], attn_mask=attn_mask,
-                                                     enable_gqa=True)
+            qkv = self._mm(x, layer["wqkv"])
+            if ours:
+                # One kernel rotates q and k and writes k, v into the cache.
+                kc, vc = self.k_cache[li], self.v_cache[li]
+                q = rope_kv_write(qkv, B, T, self.h_local, self.kv_local, kc, vc, self.rope_cos32, self.rope_sin32,
+                                  pos, batch0=batch0)
+                if decode and hd == 128:
+                    att = attn_decode(q.view(B, self.h_local, hd), kc, vc, pos, batch0=batch0)
+                elif decode:
+                    att = F.scaled_dot_product_attention(q.view(B, 1, self.h_local, hd).transpose(1, 2), kc[sl], vc[sl],
+                                                         attn_mask=attn_mask, enable_gqa=True)
+                    att = att.transpose(1, 2).reshape(B * T, self.h_local * hd)
+                else:
+                    att = F.scaled_dot_product_attention(q.view(B, T, self.h_local, hd).transpose(1, 2),
+                                                         kc[sl, :, pos:pos + T], vc[sl, :, pos:pos + T],
+                                                         is_causal=True, enable_gqa=True)
+                    att = att.transpose(1, 2).reshape(B * T, self.h_local * hd)
             else:
-                self.k_cache[li, sl, :, pos:pos + T] = k
-                self.v_cache[li, sl, :, pos:pos + T] = v
-                att = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
-            att = att.transpose(1, 2).reshape(B * T, self.h_local * hd)
+                qkv = qkv.view(B, T, self.h_local + 2 * self.kv_local, hd)
+                q = _apply_rope(qkv[:, :, : self.h_local], cos, sin).transpose(1, 2)
+                k = _apply_rope(qkv[:, :, self.h_local: self.h_local + self.kv_local], cos, sin).transpose(1, 2)
+                v = qkv[:, :, self.h_local + self.kv_local:].transpose(1, 2)
+                if decode:
+                    self.k_cache[li, sl].index_copy_(2, pos, k)
+                    self.v_cache[li, sl].index_copy_(2, pos, v)
+                    att = F.scaled_dot_product_attention(q, self.k_cache[li, sl], self.v_cache[li, sl],
+                                                         attn_mask=attn_mask, enable_gqa=True)
+                else:
+                    self.k_cache[li, sl, :, pos:pos + T] = k
+                    self.v_cache[li, sl, :, pos:pos + T] = v
+                    att = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+                att = att.transpose(1, 2).reshape(B * T, self.h_local * hd)
             x, h = self._row_parallel_norm(att, layer["wo"], h, layer["norm2"])
             gu = self._mm(x, layer["wgu"])
-            half = gu.shape[1] // 2
-            act = F.silu(gu[:, :half]) * gu[:, half:]
+            if ours:
+                act = silu_mul(gu)
+            else:
+                half = gu.shape[1] // 2
+                act = F.silu(gu[:, :half]) * gu[:, half:]
             next_norm = self.layers[li + 1]["norm1"] if li + 1 < len(self.layers) else self.final_norm
             x, h = self._row_parallel_norm(act, layer["wd"], h, next_norm)
         return x

@@ -1,5 +1,6 @@
 """Hot ops: hand-written sm_100a kernels behind small Python entry points."""
 from . import solutions  # noqa: F401
+from .decode import attn_decode, attn_decode_reference, rope_kv_write, rope_tables, silu_mul  # noqa: F401
 from .gemm import gemm  # noqa: F401
 from .norm import (fused_allreduce_rmsnorm, fused_reduce_scatter_rmsnorm, rmsnorm,  # noqa: F401
                    rmsnorm_reference)

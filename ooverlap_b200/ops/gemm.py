@@ -36,12 +36,16 @@ def fill_gemm_args(args: _lib.GemmArgs, a: torch.Tensor, b: torch.Tensor) -> Non
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, max_ctas: int = 0,
-         splits: int = 0) -> torch.Tensor:
+         splits: int = 0, pair: int = 0) -> torch.Tensor:
     """``out = a @ b.T`` with fp32 accumulation in TMEM.
 
     ``splits`` > 1 splits K over that many CTAs per output tile (fp32 partials in the library's workspace,
     summed in split order); 0 picks a split from the shape (small-M problems that would otherwise leave most
-    SMs idle), 1 turns it off."""
+    SMs idle), 1 turns it off.
+
+    ``pair`` selects the two-SM kernel (256x256 tiles computed by CTA pairs with ``tcgen05.mma.cta_group::2``; each
+    CTA stages half of the B block): 0 uses it for unsplit problems with more than 128 rows, 1 whenever the problem
+    is unsplit, -1 never."""
     _check_operands(a, b)
     M, N = a.shape[0], b.shape[0]
     if out is None:
@@ -54,5 +58,6 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     args.C, args.ldc = out.data_ptr(), out.stride(0)
     args.max_ctas = max_ctas
     args.splits = splits
+    args.pair = pair
     _lib.check(_lib.lib().oob_gemm(None, ctypes.byref(args), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return out

@@ -1,0 +1,102 @@
+"""Decode-path kernels (RoPE + KV-cache write, SwiGLU, grouped-query decode attention) against plain PyTorch fp32
+references of the same ops."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rope_ref(x, cos, sin):
+    # x: [..., hd] fp32, rotation pairs (2i, 2i+1); cos/sin: broadcastable [..., hd/2]
+    x1, x2 = x[..., 0::2], x[..., 1::2]
+    return torch.stack((x1 * cos - x2 * sin, x1 * sin + x2 * cos), dim=-1).flatten(-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,T,H,KV,hd,pos,dev_pos", [(2, 1, 8, 1, 128, 37, True), (3, 16, 4, 2, 64, 5, False),
+                                                      (1, 1, 8, 2, 128, 0, True), (2, 40, 8, 1, 128, 0, False)])
+def test_rope_kv_write(B, T, H, KV, hd, pos, dev_pos, dtype):
+    from ooverlap_b200.ops import rope_kv_write, rope_tables
+    max_len, max_batch, batch0 = 96, B + 2, 1
+    g = torch.Generator(device="cuda").manual_seed(B * 100 + T)
+    qkv = torch.randn(B * T, (H + 2 * KV) * hd, device="cuda", generator=g).to(dtype)
+    kc = torch.full((max_batch, KV, max_len, hd), 7.0, device="cuda", dtype=dtype)
+    vc = torch.full_like(kc, -3.0)
+    cos, sin = rope_tables(max_len, hd, 10000.0, qkv.device)
+    p = torch.full((1,), pos, dtype=torch.long, device="cuda") if dev_pos else pos
+    q = rope_kv_write(qkv, B, T, H, KV, kc, vc, cos, sin, p, batch0=batch0)
+    torch.cuda.synchronize()
+    x = qkv.float().view(B, T, H + 2 * KV, hd)
+    c, s = cos[pos:pos + T][None, :, None, :], sin[pos:pos + T][None, :, None, :]
+    q_ref = _rope_ref(x[:, :, :H], c, s).reshape(B * T, H * hd)
+    k_ref = _rope_ref(x[:, :, H:H + KV], c, s).transpose(1, 2)  # [B, KV, T, hd]
+    v_ref = x[:, :, H + KV:].transpose(1, 2)
+    tol = 2e-2 if dtype == torch.bfloat16 else 3e-3
+    assert (q.float() - q_ref).abs().max().item() <= tol * max(1.0, q_ref.abs().max().item())
+    got_k = kc[batch0:batch0 + B, :, pos:pos + T].float()
+    assert (got_k - k_ref).abs().max().item() <= tol * max(1.0, k_ref.abs().max().item())
+    assert torch.equal(vc[batch0:batch0 + B, :, pos:pos + T].float(), v_ref)
+    # nothing else in the cache was touched
+    untouched = torch.ones_like(kc, dtype=torch.bool)
+    untouched[batch0:batch0 + B, :, pos:pos + T] = False
+    assert (kc[untouched] == 7.0).all() and (vc[untouched] == -3.0).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,F", [(1, 3584), (7, 64), (300, 1024)])
+def test_silu_mul(rows, F, dtype):
+    from ooverlap_b200.ops import silu_mul
+    gu = (torch.randn(rows, 2 * F, device="cuda") * 2).to(dtype)
+    out = silu_mul(gu)
+    torch.cuda.synchronize()
+    ref = torch.nn.functional.silu(gu[:, :F].float()) * gu[:, F:].float()
+    tol = 1e-2 if dtype == torch.bfloat16 else 2e-3
+    assert (out.float() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,KV,L,splits", [(1, 8, 1, 1, 1), (2, 8, 1, 31, 1), (2, 8, 2, 33, 1), (3, 8, 1, 128, 0),
+                                            (1, 8, 1, 700, 0), (2, 16, 2, 700, 3), (4, 8, 8, 257, 2), (1, 32, 2, 400, 0),
+                                            (5, 8, 1, 1100, 0)])
+def test_attn_decode(B, H, KV, L, splits, dtype):
+    from ooverlap_b200.ops import attn_decode, attn_decode_reference
+    max_len, max_batch, batch0 = 1152, B + 1, 1
+    g = torch.Generator(device="cuda").manual_seed(L * 7 + B)
+    q = torch.randn(B, H, 128, device="cuda", generator=g).to(dtype)
+    kc = torch.randn(max_batch, KV, max_len, 128, device="cuda", generator=g).to(dtype)
+    vc = torch.randn(max_batch, KV, max_len, 128, device="cuda", generator=g).to(dtype)
+    # Poison everything past the context: the kernel must neither read it into the result nor be upset by it.
+    kc[:, :, L:] = float("nan")
+    vc[:, :, L:] = float("nan")
+    pos_dev = torch.full((1,), L - 1, dtype=torch.long, device="cuda")
+    out_int = attn_decode(q, kc, vc, L - 1, batch0=batch0, splits=splits)
+    out_dev = attn_decode(q, kc, vc, pos_dev, batch0=batch0, splits=splits)
+    torch.cuda.synchronize()
+    ref = attn_decode_reference(q, kc, vc, L - 1, batch0=batch0)
+    tol = 2e-2 if dtype == torch.bfloat16 else 4e-3
+    err = (out_int.float() - ref).abs().max().item()
+    assert err <= tol * max(1.0, ref.abs().max().item()), (B, H, KV, L, splits, err)
+    assert torch.equal(out_int, out_dev)
+
+
+def test_attn_decode_follows_device_position_under_graph_replay():
+    from ooverlap_b200.ops import attn_decode, attn_decode_reference
+    B, H, KV, max_len = 2, 8, 1, 512
+    q = torch.randn(B, H, 128, device="cuda").bfloat16()
+    kc = torch.randn(B, KV, max_len, 128, device="cuda").bfloat16()
+    vc = torch.randn(B, KV, max_len, 128, device="cuda").bfloat16()
+    pos = torch.full((1,), 99, dtype=torch.long, device="cuda")
+    out = torch.empty(B, H * 128, device="cuda", dtype=torch.bfloat16)
+    attn_decode(q, kc, vc, pos, out=out)  # warm-up outside the capture (workspace, kernel attributes)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        attn_decode(q, kc, vc, pos, out=out)
+    for p in (99, 300, 511):
+        pos.fill_(p)
+        graph.replay()
+        torch.cuda.synchronize()
+        ref = attn_decode_reference(q, kc, vc, p)
+        assert (out.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item()), p

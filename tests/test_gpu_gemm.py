@@ -97,3 +97,39 @@ def test_rejects_bad_operands():
         gemm(a, b)
     with pytest.raises(TypeError):
         gemm(a.float(), b.float())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(256, 256, 64), (256, 512, 1024), (384, 512, 256), (129, 264, 136), (1000, 200, 72),
+                                   (2048, 2048, 2048), (4096, 4096, 1024)])
+def test_two_sm_kernel(shape, dtype):
+    """256x256 tiles on CTA pairs (tcgen05.mma.cta_group::2) against fp32, and bit-equal to the one-SM kernel: both
+    accumulate the K blocks of a tile in the same order in fp32."""
+    from ooverlap_b200.ops import gemm
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g).to(dtype)
+    b = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).to(dtype)
+    c_pair = gemm(a, b, splits=1, pair=1)
+    c_pair2 = gemm(a, b, splits=1, pair=1)
+    c_one = gemm(a, b, splits=1, pair=-1)
+    torch.cuda.synchronize()
+    ref = _ref(a, b)
+    err = (c_pair.float() - ref).abs().max().item()
+    assert err <= 1e-2 * max(1.0, ref.abs().max().item()), (shape, dtype, err)
+    assert torch.equal(c_pair, c_pair2)
+    assert torch.equal(c_pair, c_one)
+
+
+def test_two_sm_kernel_cta_budget_and_padded_output():
+    from ooverlap_b200.ops import gemm
+    a = torch.randn(1024, 512, device="cuda").bfloat16()
+    b = torch.randn(1024, 512, device="cuda").bfloat16()
+    c_full = gemm(a, b, splits=1, pair=1)
+    c_few = gemm(a, b, splits=1, pair=1, max_ctas=6)
+    big = torch.zeros(1024, 1280, device="cuda", dtype=torch.bfloat16)
+    gemm(a, b, out=big[:, :1024], splits=1, pair=1)
+    torch.cuda.synchronize()
+    assert torch.equal(c_full, c_few)
+    assert torch.equal(big[:, :1024], c_full)
+    assert big[:, 1024:].abs().max().item() == 0
