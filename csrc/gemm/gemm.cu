@@ -11,6 +11,9 @@ namespace oob {
 
 // gemm_pair.cu
 cudaError_t launch_gemm_pair(const GemmArgs& a, DeviceStatus* status, cudaStream_t stream, gemm_detail::TmapFn make_tmap);
+// gemm_skinny.cu
+bool gemm_skinny_supported(const GemmArgs& a);
+cudaError_t launch_gemm_skinny(const GemmArgs& a, DeviceStatus* status, cudaStream_t stream, gemm_detail::TmapFn make_tmap);
 
 namespace {
 
@@ -164,6 +167,12 @@ cudaError_t launch_fmt(const CommCtx& ctx, const GemmArgs& a, cudaStream_t strea
 
 }  // namespace
 
+cudaError_t gemm_library_workspace(size_t bytes, void** out) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return ensure_splitk(dev, bytes, nullptr, out);
+}
+
 bool encode_tmap_2d(CUtensorMap* out, const void* p, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
   const DriverApi* drv = driver_api();
   if (drv == nullptr || drv->cuTensorMapEncodeTiled == nullptr) return false;
@@ -228,6 +237,16 @@ cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& args, cudaStream_t s
   int dev = 0;
   cudaGetDevice(&dev);
   if (a.mode == kGemmPlain) {
+    // A handful of rows: the weight-streaming kernel (stream-K over 128-row weight tiles).  Measured on B200 it
+    // equals the split-K path at M <= 16 and falls behind it from M = 32 on (every CTA re-reads its share of the
+    // activations, which then rivals the weight traffic), so larger M keeps the 128x256 tiles.
+    static const bool skinny_env_off = [] {
+      const char* v = getenv("OOB_GEMM_SKINNY");
+      return v != nullptr && v[0] == '0';
+    }();
+    if (gemm_skinny_supported(a) && ctx.emu_table == nullptr && a.c_emu_stride == 0 && a.splitk_ws == nullptr &&
+        (a.skinny > 0 || (a.skinny == 0 && a.splits == 0 && a.M <= 16 && !skinny_env_off)))
+      return launch_gemm_skinny(a, ctx.status, stream, make_tmap_cached);
     int splits = a.splits;
     if (splits == 0) splits = gemm_auto_splits(a.M, a.N, a.K, a.max_ctas > 0 ? a.max_ctas : sm_count());
     splits = normalize_splits(a.K, splits);

@@ -63,6 +63,9 @@ struct GemmArgs {
   // Plain mode: 0 = the two-SM kernel (256x256 tiles on CTA pairs) when the shape suits it, 1 = always when
   // possible, -1 = never.
   int pair;
+  // Plain mode, M <= 128: 0 = the weight-streaming kernel (gemm_skinny.cu) for M <= 16 unless the caller fixed
+  // `splits`, 1 = always, -1 = never.
+  int skinny;
 
   // Fused modes
   PeerPtrs partial;     // AR / RS: per-owner staging of partial tiles, registered; see oob_gemm_partial_bytes

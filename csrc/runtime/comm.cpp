@@ -923,6 +923,7 @@ int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream) {
   g.no_join = a->no_join;
   g.trace = static_cast<unsigned long long*>(a->trace);
   g.pair = a->pair;
+  g.skinny = a->skinny;
   g.splitk_ws = nullptr;
   g.counter_base = a->counter_base;
   g.residual = a->residual;

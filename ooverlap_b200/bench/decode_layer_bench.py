@@ -33,6 +33,9 @@ def main() -> int:
     p.add_argument("--ctx", type=int, default=1088, help="keys attended per sequence")
     p.add_argument("--steps", type=int, default=20)
     p.add_argument("--backends", default="ours,nccl")
+    p.add_argument("--kernels", action="store_true",
+                   help="also list the kernels of one replayed step with their device time (CUPTI activity records "
+                        "through torch.profiler: for shares and gaps, not for reported numbers)")
     args = p.parse_args()
 
     from ..models import LLAMA3_8B, LLAMA3_70B, LlamaTP
@@ -78,6 +81,27 @@ def main() -> int:
                               "peaks": src,
                               "l2": "weights of the layers (%.0f MB) exceed the 126 MB L2" % (w_bytes * cfg.layers / 1e6)}),
                   flush=True)
+            if args.kernels:
+                from torch.profiler import ProfilerActivity, profile
+                with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                    for _ in range(3):
+                        graph.replay()
+                    torch.cuda.synchronize()
+                evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                             key=lambda e: e.time_range.start)
+                n = len(evs) // 3
+                step = evs[2 * n:]  # the last of the three replays
+                per = {}
+                for e in step:
+                    d = per.setdefault(e.name[:60], [0, 0.0])
+                    d[0] += 1
+                    d[1] += e.time_range.end - e.time_range.start
+                busy = sum(v[1] for v in per.values())
+                span = step[-1].time_range.end - step[0].time_range.start if step else 0.0
+                print(json.dumps({"bench": "decode_step_kernels", "backend": backend, "batch": B, "kernels_per_step": len(step),
+                                  "busy_us": round(busy, 1), "span_us": round(span, 1),
+                                  "by_kernel_us": {k: [v[0], round(v[1], 1)] for k, v in
+                                                   sorted(per.items(), key=lambda kv: -kv[1][1])}}), flush=True)
             del m, graph
             torch.cuda.empty_cache()
     return 0

@@ -36,7 +36,7 @@ def fill_gemm_args(args: _lib.GemmArgs, a: torch.Tensor, b: torch.Tensor) -> Non
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, max_ctas: int = 0,
-         splits: int = 0, pair: int = 0) -> torch.Tensor:
+         splits: int = 0, pair: int = 0, skinny: int = 0) -> torch.Tensor:
     """``out = a @ b.T`` with fp32 accumulation in TMEM.
 
     ``splits`` > 1 splits K over that many CTAs per output tile (fp32 partials in the library's workspace,
@@ -45,7 +45,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
 
     ``pair`` selects the two-SM kernel (256x256 tiles computed by CTA pairs with ``tcgen05.mma.cta_group::2``; each
     CTA stages half of the B block): 0 uses it for unsplit problems with more than 128 rows, 1 whenever the problem
-    is unsplit, -1 never."""
+    is unsplit, -1 never.
+
+    ``skinny`` selects the weight-streaming kernel for ``M <= 128`` (the weight rows fill the tensor-core
+    instruction's 128-row dimension, the tokens are its narrow dimension; stream-K split, deterministic): 0 uses it
+    for ``M <= 16`` unless ``splits`` is given, 1 always, -1 never."""
     _check_operands(a, b)
     M, N = a.shape[0], b.shape[0]
     if out is None:
@@ -59,5 +63,6 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     args.max_ctas = max_ctas
     args.splits = splits
     args.pair = pair
+    args.skinny = skinny
     _lib.check(_lib.lib().oob_gemm(None, ctypes.byref(args), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return out

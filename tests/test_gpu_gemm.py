@@ -133,3 +133,52 @@ def test_two_sm_kernel_cta_budget_and_padded_output():
     assert torch.equal(c_full, c_few)
     assert torch.equal(big[:, :1024], c_full)
     assert big[:, 1024:].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(1, 256, 64), (1, 1280, 8192), (7, 7168, 8192), (16, 8192, 1024), (64, 8192, 3584),
+                                   (100, 200, 72), (128, 2048, 4096), (33, 1000, 1096), (17, 16032, 2048)])
+def test_weight_streaming_kernel(shape, dtype):
+    """M <= 128: weight rows on the instruction's 128-row dimension, stream-K split, fp32 partials summed in CTA
+    order -- against fp32, and bit-identical from call to call and for any CTA budget that splits K the same way."""
+    from ooverlap_b200.ops import gemm
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g).to(dtype)
+    b = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).to(dtype)
+    c1 = gemm(a, b, skinny=1)
+    c2 = gemm(a, b, skinny=1)
+    c_auto = gemm(a, b)  # the default route: this kernel for M <= 16, split-K tiles above
+    torch.cuda.synchronize()
+    ref = _ref(a, b)
+    err = (c1.float() - ref).abs().max().item()
+    assert err <= 1e-2 * max(1.0, ref.abs().max().item()), (shape, dtype, err)
+    assert torch.equal(c1, c2)
+    if M <= 16:
+        assert torch.equal(c1, c_auto)
+    else:
+        assert (c_auto.float() - ref).abs().max().item() <= 1e-2 * max(1.0, ref.abs().max().item())
+    # a small CTA budget changes the split, not the result beyond rounding of the partial sums
+    c_few = gemm(a, b, skinny=1, max_ctas=5)
+    torch.cuda.synchronize()
+    assert (c_few.float() - ref).abs().max().item() <= 1e-2 * max(1.0, ref.abs().max().item())
+
+
+def test_weight_streaming_kernel_strided_output_and_graph_replay():
+    from ooverlap_b200.ops import gemm
+    a = torch.randn(5, 512, device="cuda").bfloat16()
+    b = torch.randn(264, 512, device="cuda").bfloat16()
+    big = torch.zeros(5, 300, device="cuda", dtype=torch.bfloat16)
+    gemm(a, b, out=big[:, :264], skinny=1)
+    torch.cuda.synchronize()
+    assert (big[:, :264].float() - _ref(a, b)).abs().max().item() < 0.5
+    assert big[:, 264:].abs().max().item() == 0
+    out = torch.empty(5, 264, device="cuda", dtype=torch.bfloat16)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        gemm(a, b, out=out, skinny=1)
+    for _ in range(3):
+        a.normal_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert (out.float() - _ref(a, b)).abs().max().item() < 0.5

@@ -266,11 +266,12 @@ def test_absent_peer_is_detected_and_recovered():
             assert detected is not None and f"peer {world - 1}" in detected
 
 
-def _rank_llama(rank, world, key, port):
+def _rank_llama(rank, world, key, port, cfg_name="TINY"):
     import os
     import torch.distributed as dist
-    from ooverlap_b200 import Communicator
-    from ooverlap_b200.models import TINY, LlamaTP
+    from ooverlap_b200 import Communicator, models
+    from ooverlap_b200.models import LlamaTP
+    TINY = getattr(models, cfg_name)
     torch.cuda.set_device(rank)
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
@@ -298,10 +299,11 @@ def _rank_llama(rank, world, key, port):
 
 
 @needs_multi
-def test_llama_tensor_parallel_matches_nccl_backend():
+@pytest.mark.parametrize("cfg_name", ["TINY", "TINY128"])  # head size 64 (SDPA decode) and 128 (decode-attention kernel)
+def test_llama_tensor_parallel_matches_nccl_backend(cfg_name):
     from mp_util import free_port
     world = 2
-    res = run_ranks(_rank_llama, world, ("ml_" + uuid.uuid4().hex[:10], free_port()), timeout=600)
+    res = run_ranks(_rank_llama, world, ("ml_" + uuid.uuid4().hex[:10], free_port(), cfg_name), timeout=600)
     assert len(res) == world, res
     for r in range(world):
         kind, val = res[r]
