@@ -158,7 +158,8 @@ typedef struct {
   int no_join;  /* fused AR / RS: 1 = only the dedicated communication CTAs reduce */
   void* trace;  /* optional device buffer, 8 x uint64 per CTA: globaltimer stamps of the kernel's phases */
   int pair;     /* plain mode: 0 = two-SM kernel when the shape suits it, 1 = whenever possible, -1 = never */
-  int skinny;   /* plain mode, M <= 128: 0 = weight-streaming kernel for M <= 16 unless `splits` is set, 1 = always, -1 = never */
+  int splitk_reduce; /* split-K: 0 / 1 = separate reduction kernel, -1 = sum inside the GEMM kernel */
+  int skinny;   /* plain mode, M <= 128: 1 = weight-streaming stream-K kernel; 0 / -1 = tiled kernels */
 } oob_gemm_args_t;
 /* c may be NULL for OOB_GEMM_PLAIN. */
 int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream);

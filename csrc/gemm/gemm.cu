@@ -237,15 +237,16 @@ cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& args, cudaStream_t s
   int dev = 0;
   cudaGetDevice(&dev);
   if (a.mode == kGemmPlain) {
-    // A handful of rows: the weight-streaming kernel (stream-K over 128-row weight tiles).  Measured on B200 it
-    // equals the split-K path at M <= 16 and falls behind it from M = 32 on (every CTA re-reads its share of the
-    // activations, which then rivals the weight traffic), so larger M keeps the 128x256 tiles.
-    static const bool skinny_env_off = [] {
+    // The weight-streaming kernel (stream-K over 128-row weight tiles) is opt-in: measured on B200, inside a replayed
+    // decode step it is 2 - 12 % slower at M <= 16 than the 128x256 split-K tiles followed by the reduction kernel,
+    // and far slower from M = 32 on (every CTA re-reads its share of the activations, which then rivals the weight
+    // traffic).  OOB_GEMM_SKINNY=1 makes it the default for M <= 16.
+    static const bool skinny_env_on = [] {
       const char* v = getenv("OOB_GEMM_SKINNY");
-      return v != nullptr && v[0] == '0';
+      return v != nullptr && v[0] == '1';
     }();
     if (gemm_skinny_supported(a) && ctx.emu_table == nullptr && a.c_emu_stride == 0 && a.splitk_ws == nullptr &&
-        (a.skinny > 0 || (a.skinny == 0 && a.splits == 0 && a.M <= 16 && !skinny_env_off)))
+        (a.skinny > 0 || (a.skinny == 0 && a.splits == 0 && a.M <= 16 && skinny_env_on)))
       return launch_gemm_skinny(a, ctx.status, stream, make_tmap_cached);
     int splits = a.splits;
     if (splits == 0) splits = gemm_auto_splits(a.M, a.N, a.K, a.max_ctas > 0 ? a.max_ctas : sm_count());
@@ -257,6 +258,19 @@ cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& args, cudaStream_t s
       e = ensure_splitk(dev, splitk_workspace_bytes(a.M, a.N, splits), stream, &a.splitk_ws);
       if (e != cudaSuccess) return e;
     }
+    // The sum over the splits is left to a second, grid-wide kernel.  In the GEMM kernel that sum is done by the
+    // one warp that arrives last for a 32-row quadrant, a chain of (rows / 8) x splits L2 round trips behind a
+    // fence and an atomic; measured inside a replayed decode step the second kernel wins at every M (batch 1: 92.6
+    // -> 86.0 us per layer, batch 16: 113.8 -> 91.1, batch 64: 160.6 -> 109.8).  OOB_SPLITK_REDUCE_MIN_M raises the
+    // row count from which it is used.  Both paths add the splits in the same order: bit-identical results.
+    static const int splitk_reduce_min_rows = [] {
+      const char* v = getenv("OOB_SPLITK_REDUCE_MIN_M");
+      return v != nullptr && atoi(v) > 0 ? atoi(v) : 1;
+    }();
+    a.splitk_defer = 0;
+    if (splits > 1 && ctx.emu_table == nullptr && a.c_emu_stride == 0 &&
+        (a.splitk_reduce > 0 || (a.splitk_reduce == 0 && a.M >= splitk_reduce_min_rows)))
+      a.splitk_defer = 1;
     // Large problems go to the two-SM kernel: same tile count per SM, two thirds of the operand traffic.
     const bool pair_ok = splits == 1 && ctx.emu_table == nullptr && a.c_emu_stride == 0 && (a.max_ctas == 0 || a.max_ctas >= 2);
     static const bool pair_env_off = [] {
@@ -281,7 +295,9 @@ cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& args, cudaStream_t s
     e = ensure_emu_maps(dev, &emu_maps);
     if (e != cudaSuccess) return e;
   }
-  return a.fmt == 1 ? launch_fmt<__nv_bfloat16>(ctx, a, stream, emu_maps) : launch_fmt<__half>(ctx, a, stream, emu_maps);
+  e = a.fmt == 1 ? launch_fmt<__nv_bfloat16>(ctx, a, stream, emu_maps) : launch_fmt<__half>(ctx, a, stream, emu_maps);
+  if (e != cudaSuccess || a.mode != kGemmPlain || !a.splitk_defer) return e;
+  return a.fmt == 1 ? launch_splitk_reduce<__nv_bfloat16>(a, stream) : launch_splitk_reduce<__half>(a, stream);
 }
 
 }  // namespace oob

@@ -60,11 +60,15 @@ struct GemmArgs {
   // and their arrival counters live in splitk_ws (nullptr = the library's own workspace, grown on demand).
   int splits;
   void* splitk_ws;
+  // Split-K: 1 = the kernel only writes its partial tiles and a reduction kernel launched right after sums them
+  // (set by launch_gemm; callers ask through splitk_reduce: 0 / 1 = second kernel, -1 = sum inside the GEMM kernel).
+  int splitk_defer;
+  int splitk_reduce;
   // Plain mode: 0 = the two-SM kernel (256x256 tiles on CTA pairs) when the shape suits it, 1 = always when
   // possible, -1 = never.
   int pair;
-  // Plain mode, M <= 128: 0 = the weight-streaming kernel (gemm_skinny.cu) for M <= 16 unless the caller fixed
-  // `splits`, 1 = always, -1 = never.
+  // Plain mode, M <= 128: 1 = the weight-streaming kernel (gemm_skinny.cu), 0 / -1 = the tiled kernels (0 follows
+  // OOB_GEMM_SKINNY=1 for M <= 16).
   int skinny;
 
   // Fused modes

@@ -840,13 +840,17 @@ __global__ void __launch_bounds__(MODE == kGemmPlain ? kThreadsPlain : kThreadsF
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
-        // The last CTA to deliver this 32-row quadrant sums the splits in split order and writes C.
+        // The last CTA to deliver this 32-row quadrant sums the splits in split order and writes C -- unless the
+        // host asked for the sum to be left to the reduction kernel that follows this launch (many live rows: one
+        // warp summing them is a chain of L2 round trips, a whole grid is not).
         uint32_t* qcnt = static_cast<uint32_t*>(a.splitk_ws) + tile_id * 4 + q;
-        __threadfence();
-        __syncwarp();
-        uint32_t prev = 0;
-        if (lane == 0) prev = atomicAdd(qcnt, 1u);
-        prev = __shfl_sync(0xffffffffu, prev, 0);
+        uint32_t prev = 0xffffffffu;
+        if (!a.splitk_defer) {
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) prev = atomicAdd(qcnt, 1u);
+          prev = __shfl_sync(0xffffffffu, prev, 0);
+        }
         if (prev == uint32_t(sc.splits - 1)) {
           __threadfence();
           if (lane == 0) *qcnt = 0;  // re-arm for the next call
@@ -1235,6 +1239,60 @@ cudaError_t launch_mode(const CommCtx& ctx, const GemmArgs& a, cudaStream_t stre
     return cudaLaunchCooperativeKernel((const void*)kernel, grid, dim3(THREADS), argv, kSmemBytes, stream);
   }
   kernel<<<dim3(grid_x, 1), THREADS, kSmemBytes, stream>>>(ta, tb, tal, em, ctx, a, gemm_ctas);
+  return cudaGetLastError();
+}
+
+// Sums the split-K partial tiles [tile][split][128][256] in split order and writes C: the second kernel of a
+// split-K GEMM whose launch asked for a deferred reduction.  One thread per row and 8 columns.
+template <typename T>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partials, T* C, int M, int N, int ldc, int tiles_n,
+                                     int splits) {
+  const int n8 = (N + 7) / 8;
+  const long long total = static_cast<long long>(M) * n8;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int m = static_cast<int>(i / n8), n = static_cast<int>(i % n8) * 8;
+    const int tile_id = (m / kTileM) * tiles_n + n / kTileN;
+    const float* src = partials + static_cast<size_t>(tile_id) * splits * (kTileM * kTileN) + static_cast<size_t>(m % kTileM) * kTileN +
+                       (n % kTileN);
+    float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+#pragma unroll 8
+    for (int sp = 0; sp < splits; ++sp) {
+      const float4 a0 = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(sp) * (kTileM * kTileN)));
+      const float4 a1 = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(sp) * (kTileM * kTileN) + 4));
+      lo.x += a0.x; lo.y += a0.y; lo.z += a0.z; lo.w += a0.w;
+      hi.x += a1.x; hi.y += a1.y; hi.z += a1.z; hi.w += a1.w;
+    }
+    const float f[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    T* dst = C + static_cast<size_t>(m) * ldc + n;
+    if (n + 8 <= N && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) {
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if constexpr (PackTraits<T>::kDType == kBF16) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+          w[j] = *reinterpret_cast<uint32_t*>(&h);
+        } else {
+          __half2 h = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+          w[j] = *reinterpret_cast<uint32_t*>(&h);
+        }
+      }
+      *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      for (int j = 0; j < 8 && n + j < N; ++j) dst[j] = PackTraits<T>::from_float(f[j]);
+    }
+  }
+}
+
+template <typename T>
+cudaError_t launch_splitk_reduce(const GemmArgs& a, cudaStream_t stream) {
+  const int tiles_n = (a.N + kTileN - 1) / kTileN;
+  const long long total = static_cast<long long>(a.M) * ((a.N + 7) / 8);
+  const int threads = 256;
+  long long blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  splitk_reduce_kernel<T><<<static_cast<int>(blocks), threads, 0, stream>>>(
+      splitk_partials(a.splitk_ws), static_cast<T*>(a.C), a.M, a.N, a.ldc, tiles_n, a.splits);
   return cudaGetLastError();
 }
 

@@ -924,6 +924,7 @@ int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream) {
   g.trace = static_cast<unsigned long long*>(a->trace);
   g.pair = a->pair;
   g.skinny = a->skinny;
+  g.splitk_reduce = a->splitk_reduce;
   g.splitk_ws = nullptr;
   g.counter_base = a->counter_base;
   g.residual = a->residual;

@@ -36,7 +36,7 @@ def fill_gemm_args(args: _lib.GemmArgs, a: torch.Tensor, b: torch.Tensor) -> Non
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, max_ctas: int = 0,
-         splits: int = 0, pair: int = 0, skinny: int = 0) -> torch.Tensor:
+         splits: int = 0, pair: int = 0, skinny: int = 0, splitk_reduce: int = 0) -> torch.Tensor:
     """``out = a @ b.T`` with fp32 accumulation in TMEM.
 
     ``splits`` > 1 splits K over that many CTAs per output tile (fp32 partials in the library's workspace,
@@ -48,8 +48,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     is unsplit, -1 never.
 
     ``skinny`` selects the weight-streaming kernel for ``M <= 128`` (the weight rows fill the tensor-core
-    instruction's 128-row dimension, the tokens are its narrow dimension; stream-K split, deterministic): 0 uses it
-    for ``M <= 16`` unless ``splits`` is given, 1 always, -1 never."""
+    instruction's 128-row dimension, the tokens are its narrow dimension; stream-K split, deterministic) with 1.
+    It is opt-in: measured inside a decode step the tiled split-K path is a little faster at every ``M``.
+
+    ``splitk_reduce`` says where a split-K sum is taken: -1 inside the GEMM kernel (the warp that delivers the last
+    partial of a 32-row quadrant), 0 or 1 in a second kernel launched right after it (faster at every ``M``).
+    The order of summation, and so the result, is the same."""
     _check_operands(a, b)
     M, N = a.shape[0], b.shape[0]
     if out is None:
@@ -64,5 +68,6 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     args.splits = splits
     args.pair = pair
     args.skinny = skinny
+    args.splitk_reduce = splitk_reduce
     _lib.check(_lib.lib().oob_gemm(None, ctypes.byref(args), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return out
