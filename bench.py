@@ -27,7 +27,7 @@ K_DIM = 8192
 ROTATE = 4  # operand sets cycled between steps so that no step finds its inputs in L2
 
 REFERENCE_UNAVAILABLE = (
-    "reference cannot be installed offline: pip reports /root/reference has neither setup.py nor pyproject.toml, "
+    "reference cannot be installed offline: pip reports that the reference tree has neither setup.py nor pyproject.toml, "
     "its CMake build needs the empty submodules src/third-party/{cutlass,nccl,nlohmann_json}, and its device code "
     "is compute_90a only (WGMMA GEMMs do not run on sm_100)")
 
