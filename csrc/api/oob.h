@@ -160,7 +160,18 @@ typedef struct {
   int pair;     /* plain mode: 0 = two-SM kernel when the shape suits it, 1 = whenever possible, -1 = never */
   int splitk_reduce; /* split-K: 0 / 1 = separate reduction kernel, -1 = sum inside the GEMM kernel */
   int skinny;   /* plain mode, M <= 128: 1 = weight-streaming stream-K kernel; 0 / -1 = tiled kernels */
+  int epilogue; /* plain mode, split problems only (oob_gemm_plan_splits > 1): OOB_EPILOGUE_* applied by the kernel
+                   that sums the K splits */
+  const void* epilogue_args; /* host pointer: oob_gemm_epilogue_swiglu_t or oob_rope_args_t (oob_model.h) */
 } oob_gemm_args_t;
+#define OOB_EPILOGUE_NONE 0
+#define OOB_EPILOGUE_SWIGLU 1  /* N = 2F columns [gate | up]; C is [M, F] = silu(gate) * up */
+#define OOB_EPILOGUE_ROPE_KV 2 /* columns = (H + 2 KV) heads of hd: rotate q and k, q -> q_out, k and v -> cache; C unused */
+typedef struct {
+  int F;
+} oob_gemm_epilogue_swiglu_t;
+/* Number of K splits oob_gemm uses for a plain GEMM of this shape (`splits` as in oob_gemm_args_t, 0 = by shape). */
+int oob_gemm_plan_splits(int M, int N, int K, int max_ctas, int splits);
 /* c may be NULL for OOB_GEMM_PLAIN. */
 int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream);
 int oob_gemm_counters_needed(int mode, int M, int N, int world);

@@ -6,6 +6,7 @@
 
 #include "../runtime/driver_api.h"
 #include "gemm_kernel.cuh"
+#include "splitk_epilogues.cuh"
 
 namespace oob {
 
@@ -210,6 +211,14 @@ int gemm_auto_splits(int M, int N, int K, int sms) {
   return gemm_detail::normalize_splits(K, s);
 }
 
+int gemm_plan_splits(int M, int N, int K, int max_ctas, int splits) {
+  if (splits == 0) splits = gemm_auto_splits(M, N, K, max_ctas > 0 ? max_ctas : gemm_detail::sm_count());
+  splits = gemm_detail::normalize_splits(K, splits);
+  const size_t tiles = size_t((M + kTileM - 1) / kTileM) * ((N + kTileN - 1) / kTileN);
+  if (tiles > gemm_detail::kSplitkMaxTiles) splits = 1;
+  return splits;
+}
+
 cudaError_t validate_gemm(const CommCtx& ctx, const GemmArgs& a) {
   if (a.M <= 0 || a.N <= 0 || a.K <= 0) return cudaErrorInvalidValue;
   if (a.K % 8 != 0 || a.lda % 8 != 0 || a.ldb % 8 != 0) return cudaErrorInvalidValue;
@@ -245,15 +254,16 @@ cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& args, cudaStream_t s
       const char* v = getenv("OOB_GEMM_SKINNY");
       return v != nullptr && v[0] == '1';
     }();
-    if (gemm_skinny_supported(a) && ctx.emu_table == nullptr && a.c_emu_stride == 0 && a.splitk_ws == nullptr &&
+    if (a.epilogue == 0 && gemm_skinny_supported(a) && ctx.emu_table == nullptr && a.c_emu_stride == 0 && a.splitk_ws == nullptr &&
         (a.skinny > 0 || (a.skinny == 0 && a.splits == 0 && a.M <= 16 && skinny_env_on)))
       return launch_gemm_skinny(a, ctx.status, stream, make_tmap_cached);
-    int splits = a.splits;
-    if (splits == 0) splits = gemm_auto_splits(a.M, a.N, a.K, a.max_ctas > 0 ? a.max_ctas : sm_count());
-    splits = normalize_splits(a.K, splits);
-    const size_t tiles = size_t((a.M + kTileM - 1) / kTileM) * ((a.N + kTileN - 1) / kTileN);
-    if (tiles > kSplitkMaxTiles) splits = 1;
+    const int splits = gemm_plan_splits(a.M, a.N, a.K, a.max_ctas, a.splits);
     a.splits = splits;
+    if (a.epilogue != 0) {
+      // The epilogue lives in the kernel that sums the splits: the problem has to be one that is split.
+      if (splits <= 1 || ctx.emu_table != nullptr || a.c_emu_stride != 0 || a.epilogue_args == nullptr || a.epilogue > 2)
+        return cudaErrorInvalidValue;
+    }
     if (splits > 1 && a.splitk_ws == nullptr) {
       e = ensure_splitk(dev, splitk_workspace_bytes(a.M, a.N, splits), stream, &a.splitk_ws);
       if (e != cudaSuccess) return e;
@@ -269,7 +279,7 @@ cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& args, cudaStream_t s
     }();
     a.splitk_defer = 0;
     if (splits > 1 && ctx.emu_table == nullptr && a.c_emu_stride == 0 &&
-        (a.splitk_reduce > 0 || (a.splitk_reduce == 0 && a.M >= splitk_reduce_min_rows)))
+        (a.epilogue != 0 || a.splitk_reduce > 0 || (a.splitk_reduce == 0 && a.M >= splitk_reduce_min_rows)))
       a.splitk_defer = 1;
     // Large problems go to the two-SM kernel: same tile count per SM, two thirds of the operand traffic.
     const bool pair_ok = splits == 1 && ctx.emu_table == nullptr && a.c_emu_stride == 0 && (a.max_ctas == 0 || a.max_ctas >= 2);
@@ -297,6 +307,14 @@ cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& args, cudaStream_t s
   }
   e = a.fmt == 1 ? launch_fmt<__nv_bfloat16>(ctx, a, stream, emu_maps) : launch_fmt<__half>(ctx, a, stream, emu_maps);
   if (e != cudaSuccess || a.mode != kGemmPlain || !a.splitk_defer) return e;
+  if (a.epilogue == 1) {
+    const int F = static_cast<const oob_gemm_epilogue_swiglu_t*>(a.epilogue_args)->F;
+    return a.fmt == 1 ? launch_splitk_reduce_swiglu<__nv_bfloat16>(a, F, stream) : launch_splitk_reduce_swiglu<__half>(a, F, stream);
+  }
+  if (a.epilogue == 2) {
+    const oob_rope_args_t& r = *static_cast<const oob_rope_args_t*>(a.epilogue_args);
+    return a.fmt == 1 ? launch_splitk_reduce_rope_kv<__nv_bfloat16>(a, r, stream) : launch_splitk_reduce_rope_kv<__half>(a, r, stream);
+  }
   return a.fmt == 1 ? launch_splitk_reduce<__nv_bfloat16>(a, stream) : launch_splitk_reduce<__half>(a, stream);
 }
 

@@ -64,6 +64,10 @@ struct GemmArgs {
   // (set by launch_gemm; callers ask through splitk_reduce: 0 / 1 = second kernel, -1 = sum inside the GEMM kernel).
   int splitk_defer;
   int splitk_reduce;
+  // Plain mode, split problems only: an elementwise op applied by the kernel that sums the splits (see
+  // splitk_epilogues.cuh).  epilogue_args is a HOST pointer to the op's argument block.
+  int epilogue;               // 0 = none, 1 = SwiGLU (oob_gemm_epilogue_swiglu_t), 2 = RoPE + KV write (oob_rope_args_t)
+  const void* epilogue_args;
   // Plain mode: 0 = the two-SM kernel (256x256 tiles on CTA pairs) when the shape suits it, 1 = always when
   // possible, -1 = never.
   int pair;
@@ -100,5 +104,8 @@ int gemm_counters_needed(int mode, int M, int N, int world);
 
 // Split count the plain GEMM picks for a shape on `sms` SMs (1 = no split).
 int gemm_auto_splits(int M, int N, int K, int sms);
+
+// Split count launch_gemm uses for a plain GEMM given the caller's `splits` (0 = by shape) and CTA budget.
+int gemm_plan_splits(int M, int N, int K, int max_ctas, int splits);
 
 }  // namespace oob

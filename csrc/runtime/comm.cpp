@@ -7,6 +7,7 @@
 #include <cstring>
 
 #include "../api/oob.h"
+#include "../api/oob_model.h"
 #include "../collectives/collectives.h"
 #include "../gemm/gemm.h"
 #include "driver_api.h"
@@ -925,6 +926,38 @@ int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream) {
   g.pair = a->pair;
   g.skinny = a->skinny;
   g.splitk_reduce = a->splitk_reduce;
+  g.epilogue = a->epilogue;
+  g.epilogue_args = a->epilogue_args;
+  if (a->epilogue != OOB_EPILOGUE_NONE) {
+    if (a->mode != OOB_GEMM_PLAIN || emu) return set_error(OOB_ERR_INVALID, "epilogues apply to the plain GEMM only");
+    if (a->epilogue_args == nullptr) return set_error(OOB_ERR_INVALID, "null epilogue arguments");
+    if (gemm_plan_splits(a->M, a->N, a->K, a->max_ctas, a->splits) <= 1)
+      return set_error(OOB_ERR_UNSUPPORTED, "the epilogue runs in the split-K sum, and this problem is not split "
+                                            "(see oob_gemm_plan_splits)");
+    if (a->epilogue == OOB_EPILOGUE_SWIGLU) {
+      const int F = static_cast<const oob_gemm_epilogue_swiglu_t*>(a->epilogue_args)->F;
+      if (F <= 0 || F % 8 != 0 || a->N != 2 * F || a->ldc < F || a->ldc % 8 != 0 || a->C == nullptr)
+        return set_error(OOB_ERR_INVALID, "SwiGLU epilogue: N must be 2F, F and ldc multiples of 8, ldc >= F");
+    } else if (a->epilogue == OOB_EPILOGUE_ROPE_KV) {
+      const oob_rope_args_t* r = static_cast<const oob_rope_args_t*>(a->epilogue_args);
+      if (r->B <= 0 || r->T <= 0 || r->H <= 0 || r->KV <= 0 || r->hd <= 0 || r->hd % 8 != 0 ||
+          static_cast<long long>(r->B) * r->T != a->M || (r->H + 2 * r->KV) * r->hd != a->N)
+        return set_error(OOB_ERR_INVALID, "RoPE epilogue: M must be B*T and N (H + 2 KV) * hd");
+      if (r->q_out == nullptr || r->k_cache == nullptr || r->v_cache == nullptr || r->cos_table == nullptr ||
+          r->sin_table == nullptr)
+        return set_error(OOB_ERR_INVALID, "RoPE epilogue: null pointer");
+      const uintptr_t align = reinterpret_cast<uintptr_t>(r->q_out) | reinterpret_cast<uintptr_t>(r->k_cache) |
+                              reinterpret_cast<uintptr_t>(r->v_cache) | reinterpret_cast<uintptr_t>(r->cos_table) |
+                              reinterpret_cast<uintptr_t>(r->sin_table);
+      if ((align & 15) || r->cache_batch_stride % 8 != 0 || r->max_len <= 0 || r->batch0 < 0 ||
+          r->cache_batch_stride < static_cast<int64_t>(r->KV) * r->max_len * r->hd)
+        return set_error(OOB_ERR_INVALID, "RoPE epilogue: bad cache geometry or alignment");
+      if (r->pos_dev == nullptr && (r->pos0 < 0 || r->pos0 + r->T > r->max_len))
+        return set_error(OOB_ERR_INVALID, "RoPE epilogue: positions outside the cache");
+    } else {
+      return set_error(OOB_ERR_INVALID, "unknown epilogue");
+    }
+  }
   g.splitk_ws = nullptr;
   g.counter_base = a->counter_base;
   g.residual = a->residual;
@@ -948,6 +981,11 @@ int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream) {
   cudaError_t e = launch_gemm(ctx, g, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "GEMM launch");
   return OOB_OK;
+}
+
+int oob_gemm_plan_splits(int M, int N, int K, int max_ctas, int splits) {
+  if (M <= 0 || N <= 0 || K <= 0) return 1;
+  return gemm_plan_splits(M, N, K, max_ctas, splits);
 }
 
 int oob_gemm_counters_needed(int mode, int M, int N, int world) { return gemm_counters_needed(mode, M, N, world); }

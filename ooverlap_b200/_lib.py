@@ -28,6 +28,7 @@ RS_P2P, RS_NVLS = 0, 1
 AG_PUSH_P2P, AG_PUSH_NVLS, AG_PULL_P2P = 0, 1, 2
 NORM_LOCAL, NORM_AR_ONESHOT, NORM_AR_TWOSHOT, NORM_AR_TWOSHOT_NVLS, NORM_RS, NORM_RS_NVLS = range(6)
 GEMM_PLAIN, GEMM_AR, GEMM_RS_NORM, GEMM_AG = range(4)
+EPILOGUE_NONE, EPILOGUE_SWIGLU, EPILOGUE_ROPE_KV = range(3)
 FLAG_NO_NVLS, FLAG_LEGACY_IPC = 1, 2
 
 
@@ -68,7 +69,12 @@ class GemmArgs(Structure):
                 ("c_reg", c_int), ("c_off", c_uint64), ("counter_base", c_int), ("residual", c_void_p),
                 ("weight", c_void_p), ("eps", c_float), ("y_local", c_void_p), ("res_out_local", c_void_p),
                 ("rs_emu_stride", c_uint64), ("a_full_reg", c_int), ("a_full_off", c_uint64), ("use_nvls", c_int),
-                ("splits", c_int), ("no_join", c_int), ("trace", c_void_p), ("pair", c_int), ("splitk_reduce", c_int), ("skinny", c_int)]
+                ("splits", c_int), ("no_join", c_int), ("trace", c_void_p), ("pair", c_int), ("splitk_reduce", c_int), ("skinny", c_int), ("epilogue", c_int),
+                ("epilogue_args", c_void_p)]
+
+
+class SwigluEpilogue(Structure):
+    _fields_ = [("F", c_int)]
 
 
 class RopeArgs(Structure):
@@ -114,6 +120,7 @@ def _declare(lib) -> None:
     lib.oob_all_gather.argtypes = [P, c_int, c_int, c_int, c_uint64, P, P, c_uint64, c_int, P]
     lib.oob_fused_norm.argtypes = [P, c_int, POINTER(NormArgs), c_int, P]
     lib.oob_gemm.argtypes = [P, POINTER(GemmArgs), P]
+    lib.oob_gemm_plan_splits.argtypes = [c_int, c_int, c_int, c_int, c_int]
     lib.oob_gemm_counters_needed.argtypes = [c_int, c_int, c_int, c_int]
     lib.oob_gemm_partial_bytes.argtypes = [c_int, c_int]
     lib.oob_gemm_partial_bytes.restype = c_uint64

@@ -23,7 +23,9 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
-from ..ops import attn_decode, fused_allreduce_rmsnorm, gemm, rmsnorm, rope_kv_write, rope_tables, silu_mul
+from ..ops import (attn_decode, fused_allreduce_rmsnorm, gemm, gemm_rope_kv_write, gemm_swiglu, rmsnorm, rope_kv_write,
+                   rope_tables, silu_mul)
+from ..utils.config import env_flag
 
 
 @dataclass
@@ -108,6 +110,9 @@ class LlamaTP:
         self.rope_cos, self.rope_sin = ang.cos().to(dtype), ang.sin().to(dtype)  # [max_len, hd/2]
         if backend == "ours":
             self.rope_cos32, self.rope_sin32 = rope_tables(max_len, hd, cfg.rope_theta, self.device)
+        # RoPE + cache write and SwiGLU applied by the kernel that sums the K splits of the preceding GEMM (two
+        # launches fewer per layer in a decode step).  Off unless OOB_FUSED_EPILOGUES=1.
+        self.fused_epilogues = backend == "ours" and env_flag("OOB_FUSED_EPILOGUES", False)
 
     # ------------------------------------------------------------ primitives
     def _mm(self, x, wt):
@@ -159,12 +164,18 @@ class LlamaTP:
         x = self._norm(h, self.layers[0]["norm1"])
         sl = slice(batch0, batch0 + B)
         for li, layer in enumerate(self.layers):
-            qkv = self._mm(x, layer["wqkv"])
+            if ours and self.fused_epilogues:
+                kc, vc = self.k_cache[li], self.v_cache[li]
+                q = gemm_rope_kv_write(x, layer["wqkv"], B, T, self.h_local, self.kv_local, kc, vc, self.rope_cos32,
+                                       self.rope_sin32, pos, batch0=batch0)
+            else:
+                qkv = self._mm(x, layer["wqkv"])
             if ours:
                 # One kernel rotates q and k and writes k, v into the cache.
-                kc, vc = self.k_cache[li], self.v_cache[li]
-                q = rope_kv_write(qkv, B, T, self.h_local, self.kv_local, kc, vc, self.rope_cos32, self.rope_sin32,
-                                  pos, batch0=batch0)
+                if not self.fused_epilogues:
+                    kc, vc = self.k_cache[li], self.v_cache[li]
+                    q = rope_kv_write(qkv, B, T, self.h_local, self.kv_local, kc, vc, self.rope_cos32, self.rope_sin32,
+                                      pos, batch0=batch0)
                 if decode and hd == 128:
                     att = attn_decode(q.view(B, self.h_local, hd), kc, vc, pos, batch0=batch0)
                 elif decode:
@@ -192,10 +203,12 @@ class LlamaTP:
                     att = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
                 att = att.transpose(1, 2).reshape(B * T, self.h_local * hd)
             x, h = self._row_parallel_norm(att, layer["wo"], h, layer["norm2"])
-            gu = self._mm(x, layer["wgu"])
-            if ours:
-                act = silu_mul(gu)
+            if ours and self.fused_epilogues:
+                act = gemm_swiglu(x, layer["wgu"])
+            elif ours:
+                act = silu_mul(self._mm(x, layer["wgu"]))
             else:
+                gu = self._mm(x, layer["wgu"])
                 half = gu.shape[1] // 2
                 act = F.silu(gu[:, :half]) * gu[:, half:]
             next_norm = self.layers[li + 1]["norm1"] if li + 1 < len(self.layers) else self.final_norm

@@ -28,6 +28,33 @@ def rope_tables(max_len: int, head_dim: int, theta: float, device) -> tuple[torc
     return ang.cos().contiguous(), ang.sin().contiguous()
 
 
+def _rope_args(dtype, B: int, T: int, heads: int, kv_heads: int, hd: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+               cos: torch.Tensor, sin: torch.Tensor, pos, batch0: int, q_out: torch.Tensor) -> "_lib.RopeArgs":
+    if k_cache.shape[-1] != hd or k_cache.shape != v_cache.shape:
+        raise ValueError("head geometry does not match the cache")
+    if k_cache.dim() != 4 or k_cache.shape[1] != kv_heads or k_cache.stride(3) != 1 or k_cache.stride(2) != hd \
+            or k_cache.stride(1) != k_cache.shape[2] * hd or v_cache.stride() != k_cache.stride():
+        raise ValueError("cache must be [batch, kv_heads, max_len, hd] with contiguous (kv_heads, max_len, hd)")
+    if batch0 + B > k_cache.shape[0]:
+        raise ValueError("sequences outside the cache")
+    max_len = k_cache.shape[2]
+    if cos.dtype != torch.float32 or cos.shape != (max_len, hd // 2) or not cos.is_contiguous() or sin.shape != cos.shape:
+        raise ValueError("cos / sin must be contiguous fp32 [max_len, hd/2] tables")
+    a = _lib.RopeArgs()
+    a.dtype, a.B, a.T, a.H, a.KV, a.hd = dtype_code(dtype), B, T, heads, kv_heads, hd
+    a.qkv, a.q_out = None, q_out.data_ptr()
+    a.k_cache, a.v_cache = k_cache.data_ptr(), v_cache.data_ptr()
+    a.cache_batch_stride, a.max_len, a.batch0 = k_cache.stride(0), max_len, batch0
+    a.cos_table, a.sin_table = cos.data_ptr(), sin.data_ptr()
+    if isinstance(pos, torch.Tensor):
+        if pos.dtype != torch.int64 or pos.numel() != 1 or not pos.is_cuda:
+            raise ValueError("pos must be a one-element int64 CUDA tensor")
+        a.pos_dev, a.pos0 = pos.data_ptr(), 0
+    else:
+        a.pos_dev, a.pos0 = None, int(pos)
+    return a
+
+
 def rope_kv_write(qkv: torch.Tensor, B: int, T: int, heads: int, kv_heads: int, k_cache: torch.Tensor,
                   v_cache: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos, *, batch0: int = 0,
                   q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -38,31 +65,51 @@ def rope_kv_write(qkv: torch.Tensor, B: int, T: int, heads: int, kv_heads: int, 
     if qkv.dim() != 2 or not qkv.is_contiguous() or qkv.shape[0] != B * T:
         raise ValueError("qkv must be a contiguous [B*T, (heads + 2*kv_heads) * hd] tensor")
     hd = qkv.shape[1] // (heads + 2 * kv_heads)
-    if hd * (heads + 2 * kv_heads) != qkv.shape[1] or k_cache.shape[-1] != hd or k_cache.shape != v_cache.shape:
-        raise ValueError("head geometry does not match the cache")
-    if k_cache.dim() != 4 or k_cache.shape[1] != kv_heads or k_cache.stride(3) != 1 or k_cache.stride(2) != hd \
-            or k_cache.stride(1) != k_cache.shape[2] * hd or v_cache.stride() != k_cache.stride():
-        raise ValueError("cache must be [batch, kv_heads, max_len, hd] with contiguous (kv_heads, max_len, hd)")
-    if batch0 + B > k_cache.shape[0]:
-        raise ValueError("sequences outside the cache")
-    max_len = k_cache.shape[2]
-    if cos.dtype != torch.float32 or cos.shape != (max_len, hd // 2) or not cos.is_contiguous() or sin.shape != cos.shape:
-        raise ValueError("cos / sin must be contiguous fp32 [max_len, hd/2] tables")
+    if hd * (heads + 2 * kv_heads) != qkv.shape[1]:
+        raise ValueError("head geometry does not match qkv")
     if q_out is None:
         q_out = torch.empty((B * T, heads * hd), dtype=qkv.dtype, device=qkv.device)
-    a = _lib.RopeArgs()
-    a.dtype, a.B, a.T, a.H, a.KV, a.hd = dtype_code(qkv.dtype), B, T, heads, kv_heads, hd
-    a.qkv, a.q_out = qkv.data_ptr(), q_out.data_ptr()
-    a.k_cache, a.v_cache = k_cache.data_ptr(), v_cache.data_ptr()
-    a.cache_batch_stride, a.max_len, a.batch0 = k_cache.stride(0), max_len, batch0
-    a.cos_table, a.sin_table = cos.data_ptr(), sin.data_ptr()
-    if isinstance(pos, torch.Tensor):
-        if pos.dtype != torch.int64 or pos.numel() != 1 or not pos.is_cuda:
-            raise ValueError("pos must be a one-element int64 CUDA tensor")
-        a.pos_dev, a.pos0 = pos.data_ptr(), 0
-    else:
-        a.pos_dev, a.pos0 = None, int(pos)
+    a = _rope_args(qkv.dtype, B, T, heads, kv_heads, hd, k_cache, v_cache, cos, sin, pos, batch0, q_out)
+    a.qkv = qkv.data_ptr()
     _lib.check(_lib.lib().oob_rope_kv_write(ctypes.byref(a), _stream()))
+    return q_out
+
+
+def gemm_rope_kv_write(x: torch.Tensor, wqkv: torch.Tensor, B: int, T: int, heads: int, kv_heads: int,
+                       k_cache: torch.Tensor, v_cache: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos, *,
+                       batch0: int = 0, q_out: Optional[torch.Tensor] = None, fused: Optional[bool] = None) -> torch.Tensor:
+    """``rope_kv_write(x @ wqkv.T, ...)``: the QKV projection followed by the rotation and the cache write.
+
+    When the GEMM is one that is split over K (every decode-step shape), rotation and cache write are done by the
+    kernel that sums the splits, from the fp32 sums; otherwise (or with ``fused=False``) the GEMM is followed by
+    :func:`rope_kv_write`.  Returns the rotated queries, [B*T, heads * hd]."""
+    from .gemm import _check_operands, fill_gemm_args, gemm, gemm_plan_splits
+    _check_operands(x, wqkv)
+    M, N, K = x.shape[0], wqkv.shape[0], x.shape[1]
+    if M != B * T:
+        raise ValueError("x must have B*T rows")
+    hd = N // (heads + 2 * kv_heads)
+    if hd * (heads + 2 * kv_heads) != N or hd % 8 != 0:
+        raise ValueError("head geometry does not match the QKV weight")
+    can_fuse = gemm_plan_splits(M, N, K) > 1
+    if fused is None:
+        fused = can_fuse
+    if fused and not can_fuse:
+        raise ValueError("this problem is not split over K, so the epilogue has no kernel to run in")
+    if not fused:
+        return rope_kv_write(gemm(x, wqkv), B, T, heads, kv_heads, k_cache, v_cache, cos, sin, pos, batch0=batch0,
+                             q_out=q_out)
+    if q_out is None:
+        q_out = torch.empty((M, heads * hd), dtype=x.dtype, device=x.device)
+    r = _rope_args(x.dtype, B, T, heads, kv_heads, hd, k_cache, v_cache, cos, sin, pos, batch0, q_out)
+    args = _lib.GemmArgs()
+    args.mode = _lib.GEMM_PLAIN
+    fill_gemm_args(args, x, wqkv)
+    args.C, args.ldc = q_out.data_ptr(), N  # C itself is not written; a valid aligned pointer keeps the checks uniform
+    args.skinny = -1
+    args.epilogue = _lib.EPILOGUE_ROPE_KV
+    args.epilogue_args = ctypes.cast(ctypes.pointer(r), ctypes.c_void_p)
+    _lib.check(_lib.lib().oob_gemm(None, ctypes.byref(args), _stream()))
     return q_out
 
 

@@ -71,3 +71,46 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     args.splitk_reduce = splitk_reduce
     _lib.check(_lib.lib().oob_gemm(None, ctypes.byref(args), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return out
+
+
+def gemm_plan_splits(M: int, N: int, K: int, *, max_ctas: int = 0, splits: int = 0) -> int:
+    """Number of K splits :func:`gemm` uses for this shape (1 = the problem is not split)."""
+    return int(_lib.lib().oob_gemm_plan_splits(M, N, K, max_ctas, splits))
+
+
+def gemm_swiglu(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, max_ctas: int = 0,
+                fused: Optional[bool] = None) -> torch.Tensor:
+    """``silu(a @ b[:F].T) * (a @ b[F:].T)`` for a gate/up weight ``b`` of shape [2F, K]; returns [M, F].
+
+    When the GEMM is one that is split over K (every decode-step shape), the activation is applied by the kernel
+    that sums the splits: no separate launch and no 16-bit round trip of the [M, 2F] intermediate.  Otherwise, or
+    with ``fused=False``, the GEMM is followed by the stand-alone SwiGLU kernel."""
+    from .decode import silu_mul
+    _check_operands(a, b)
+    M, N = a.shape[0], b.shape[0]
+    if N % 16 != 0:
+        raise ValueError("the gate/up weight must have 2F rows with F a multiple of 8")
+    F = N // 2
+    if out is None:
+        out = torch.empty((M, F), dtype=a.dtype, device=a.device)
+    elif out.shape != (M, F) or out.dtype != a.dtype or out.stride(1) != 1 or out.stride(0) % 8 != 0:
+        raise ValueError("bad output tensor")
+    can_fuse = gemm_plan_splits(M, N, a.shape[1], max_ctas=max_ctas) > 1
+    if fused is None:
+        fused = can_fuse
+    if fused and not can_fuse:
+        raise ValueError("this problem is not split over K, so the epilogue has no kernel to run in")
+    if not fused:
+        return silu_mul(gemm(a, b, max_ctas=max_ctas), out)
+    epi = _lib.SwigluEpilogue()
+    epi.F = F
+    args = _lib.GemmArgs()
+    args.mode = _lib.GEMM_PLAIN
+    fill_gemm_args(args, a, b)
+    args.C, args.ldc = out.data_ptr(), out.stride(0)
+    args.max_ctas = max_ctas
+    args.skinny = -1
+    args.epilogue = _lib.EPILOGUE_SWIGLU
+    args.epilogue_args = ctypes.cast(ctypes.pointer(epi), ctypes.c_void_p)
+    _lib.check(_lib.lib().oob_gemm(None, ctypes.byref(args), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return out

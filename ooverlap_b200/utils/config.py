@@ -29,6 +29,19 @@ def _flag(name: str, default: bool = False) -> bool:
     return v.strip().lower() not in ("", "0", "false", "no", "off")
 
 
+def env_flag(name: str, default: bool = False) -> bool:
+    """Boolean environment variable ("", 0, false, no, off are false)."""
+    return _flag(name, default)
+
+
+# Names read directly by the native library (csrc/gemm/gemm.cu) or by single call sites:
+#   OOB_GEMM_PAIR=0            plain GEMM: never use the two-SM kernel
+#   OOB_GEMM_SKINNY=1          plain GEMM: weight-streaming kernel for M <= 16
+#   OOB_SPLITK_REDUCE_MIN_M=n  split-K: sum inside the GEMM kernel below n rows (default 1: always the second kernel)
+#   OOB_FUSED_EPILOGUES=1      model runner: RoPE + cache write and SwiGLU in the split-K sum of the preceding GEMM
+#   OOB_RUN_UNVALIDATED=1      tests: also run the GPU tests of paths that have not been run on hardware yet
+
+
 @dataclass
 class Config:
     heap_bytes: int            # OOB_HEAP_BYTES: symmetric heap per rank
