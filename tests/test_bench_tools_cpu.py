@@ -1,5 +1,6 @@
 """Host-only tooling: result aggregation over backend orders, plot series, tuning solutions."""
 import json
+import os
 
 from ooverlap_b200.bench import aggregate, plot
 from ooverlap_b200.ops import solutions
@@ -61,3 +62,45 @@ def test_solutions_roundtrip(tmp_path, monkeypatch):
     monkeypatch.delenv("OOB_OVERLAP_SOLUTIONS")
     assert solutions.lookup("gemm_ar", 8192, 8192, 8192, 8, "fp16") is None
     assert solutions.load(str(tmp_path / "missing.json")) == {}
+
+
+def test_vllm_bench_model_dir_env_and_commands(tmp_path):
+    import json
+    import subprocess
+    import sys
+    from ooverlap_b200.bench import vllm_bench
+    d = vllm_bench.write_model_dir(str(tmp_path / "m"), "llama3-70b", layers=4, max_len=1200)
+    cfg = json.load(open(os.path.join(d, "config.json")))
+    assert cfg["num_hidden_layers"] == 4 and cfg["hidden_size"] == 8192 and cfg["num_key_value_heads"] == 8
+    from transformers import AutoConfig
+    hf = AutoConfig.from_pretrained(d)
+    assert hf.model_type == "llama" and hf.intermediate_size == 28672 and hf.vocab_size == 128256
+    env = vllm_bench.child_env("ooverlap", "/some/repo", base={"PYTHONPATH": "/x"})
+    assert env["VLLM_FORCE_ALLREDUCE_BACKEND"] == "ooverlap" and env["PYTHONPATH"].split(os.pathsep) == ["/some/repo", "/x"]
+    env2 = vllm_bench.child_env("pynccl", "/some/repo", base={"VLLM_FORCE_ALLREDUCE_BACKEND": "ooverlap"})
+    assert "VLLM_FORCE_ALLREDUCE_BACKEND" not in env2 and env2["MASTER_ADDR"] == "127.0.0.1"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-m", "ooverlap_b200.bench.vllm_bench", "--dry-run", "--model", "tiny", "--tp", "2",
+                          "--batches", "1,4", "--backends", "pynccl,ooverlap", "--orders", "all"], cwd=root,
+                         capture_output=True, text=True, check=True).stdout
+    recs = [json.loads(ln) for ln in out.splitlines()]
+    assert len(recs) == 2 * 2 * 2  # orders x batches x backends
+    assert {r["backend"] for r in recs} == {"pynccl", "ooverlap"}
+    assert all("--worker" in r["cmd"] and "--model-dir" in r["cmd"] for r in recs)
+
+
+def test_vllm_plugin_entry_point_is_discoverable_from_the_repository_root():
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = ("from importlib.metadata import entry_points\n"
+            "eps = [e for e in entry_points(group='vllm.general_plugins') if e.name == 'ooverlap_b200']\n"
+            "assert len(eps) == 1, eps\n"
+            "f = eps[0].load()\n"
+            "import os\n"
+            "os.environ.pop('VLLM_FORCE_ALLREDUCE_BACKEND', None)\n"
+            "assert f() is False  # not forced: the hook leaves vLLM alone\n"
+            "print('ok')\n")
+    env = dict(os.environ, PYTHONPATH=root)
+    out = subprocess.run([sys.executable, "-c", code], cwd="/", env=env, capture_output=True, text=True)
+    assert out.returncode == 0 and "ok" in out.stdout, out.stderr[-800:]
