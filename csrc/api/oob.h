@@ -163,6 +163,7 @@ typedef struct {
   int epilogue; /* plain mode, split problems only (oob_gemm_plan_splits > 1): OOB_EPILOGUE_* applied by the kernel
                    that sums the K splits */
   const void* epilogue_args; /* host pointer: oob_gemm_epilogue_swiglu_t or oob_rope_args_t (oob_model.h) */
+  int gemv;     /* plain mode, M <= 4: 1 = CUDA-core streaming kernel, 0 = only with OOB_GEMM_GEMV=1, -1 = never */
 } oob_gemm_args_t;
 #define OOB_EPILOGUE_NONE 0
 #define OOB_EPILOGUE_SWIGLU 1  /* N = 2F columns [gate | up]; C is [M, F] = silu(gate) * up */

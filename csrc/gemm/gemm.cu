@@ -12,6 +12,9 @@ namespace oob {
 
 // gemm_pair.cu
 cudaError_t launch_gemm_pair(const GemmArgs& a, DeviceStatus* status, cudaStream_t stream, gemm_detail::TmapFn make_tmap);
+// gemv.cu
+bool gemv_supported(const GemmArgs& a);
+cudaError_t launch_gemv(const GemmArgs& a, int sms, cudaStream_t stream);
 // gemm_skinny.cu
 bool gemm_skinny_supported(const GemmArgs& a);
 cudaError_t launch_gemm_skinny(const GemmArgs& a, DeviceStatus* status, cudaStream_t stream, gemm_detail::TmapFn make_tmap);
@@ -246,6 +249,15 @@ cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& args, cudaStream_t s
   int dev = 0;
   cudaGetDevice(&dev);
   if (a.mode == kGemmPlain) {
+    // One to four rows: the CUDA-core streaming kernel.  Opt-in (argument, or OOB_GEMM_GEMV=1 for every call that
+    // leaves the choice open) until it has been measured against the split-K path.
+    static const bool gemv_env_on = [] {
+      const char* v = getenv("OOB_GEMM_GEMV");
+      return v != nullptr && v[0] == '1';
+    }();
+    if (a.epilogue == 0 && gemv_supported(a) && ctx.emu_table == nullptr && a.c_emu_stride == 0 && a.splitk_ws == nullptr &&
+        (a.gemv > 0 || (a.gemv == 0 && a.splits == 0 && a.skinny <= 0 && gemv_env_on)))
+      return launch_gemv(a, a.max_ctas > 0 ? a.max_ctas : sm_count(), stream);
     // The weight-streaming kernel (stream-K over 128-row weight tiles) is opt-in: measured on B200, inside a replayed
     // decode step it is 2 - 12 % slower at M <= 16 than the 128x256 split-K tiles followed by the reduction kernel,
     // and far slower from M = 32 on (every CTA re-reads its share of the activations, which then rivals the weight

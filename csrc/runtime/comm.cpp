@@ -926,6 +926,7 @@ int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream) {
   g.pair = a->pair;
   g.skinny = a->skinny;
   g.splitk_reduce = a->splitk_reduce;
+  g.gemv = a->gemv;
   g.epilogue = a->epilogue;
   g.epilogue_args = a->epilogue_args;
   if (a->epilogue != OOB_EPILOGUE_NONE) {

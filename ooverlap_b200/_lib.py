@@ -70,7 +70,7 @@ class GemmArgs(Structure):
                 ("weight", c_void_p), ("eps", c_float), ("y_local", c_void_p), ("res_out_local", c_void_p),
                 ("rs_emu_stride", c_uint64), ("a_full_reg", c_int), ("a_full_off", c_uint64), ("use_nvls", c_int),
                 ("splits", c_int), ("no_join", c_int), ("trace", c_void_p), ("pair", c_int), ("splitk_reduce", c_int), ("skinny", c_int), ("epilogue", c_int),
-                ("epilogue_args", c_void_p)]
+                ("epilogue_args", c_void_p), ("gemv", c_int)]
 
 
 class SwigluEpilogue(Structure):

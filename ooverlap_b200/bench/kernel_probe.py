@@ -74,6 +74,7 @@ def main() -> int:
     p.add_argument("--pair", type=int, default=0, help="plain GEMM: 1 = two-SM kernel, -1 = one-SM kernel, 0 = auto")
     p.add_argument("--skinny", type=int, default=0, help="plain GEMM, M <= 128: 1 = weight-streaming kernel, -1 = never")
     p.add_argument("--splitk-reduce", type=int, default=0, help="split-K sum: 1 = second kernel, -1 = inside the GEMM kernel")
+    p.add_argument("--gemv", type=int, default=0, help="plain GEMM, M <= 4: 1 = CUDA-core streaming kernel")
     p.add_argument("--heads", type=int, default=8)
     p.add_argument("--kv-heads", type=int, default=1)
     p.add_argument("--ctx", type=int, default=1088, help="attention: context length (keys attended)")
@@ -112,9 +113,9 @@ def probe(args, flush) -> dict:
             fn = lambda: torch.matmul(a, b.t(), out=out)  # noqa: E731
         else:
             splits = args.splits if args.op == "gemm_splitk" else 1
-            rec["pair"], rec["skinny"], rec["splitk_reduce"] = args.pair, args.skinny, args.splitk_reduce
+            rec["pair"], rec["skinny"], rec["splitk_reduce"], rec["gemv"] = args.pair, args.skinny, args.splitk_reduce, args.gemv
             fn = lambda: gemm(a, b, out=out, splits=splits, pair=args.pair, skinny=args.skinny,  # noqa: E731
-                              splitk_reduce=args.splitk_reduce)
+                              splitk_reduce=args.splitk_reduce, gemv=args.gemv)
         ms = timed(fn, args.iters, args.warmup, flush)
         tflops = 2.0 * args.m * args.n * args.k / (ms * 1e-3) / 1e12
         gbs = (args.m * args.k + args.n * args.k + args.m * args.n) * 2 / (ms * 1e-3) / 1e9

@@ -36,7 +36,8 @@ def fill_gemm_args(args: _lib.GemmArgs, a: torch.Tensor, b: torch.Tensor) -> Non
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, max_ctas: int = 0,
-         splits: int = 0, pair: int = 0, skinny: int = 0, splitk_reduce: int = 0) -> torch.Tensor:
+         splits: int = 0, pair: int = 0, skinny: int = 0, splitk_reduce: int = 0,
+         gemv: int = 0) -> torch.Tensor:
     """``out = a @ b.T`` with fp32 accumulation in TMEM.
 
     ``splits`` > 1 splits K over that many CTAs per output tile (fp32 partials in the library's workspace,
@@ -53,7 +54,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
 
     ``splitk_reduce`` says where a split-K sum is taken: -1 inside the GEMM kernel (the warp that delivers the last
     partial of a 32-row quadrant), 0 or 1 in a second kernel launched right after it (faster at every ``M``).
-    The order of summation, and so the result, is the same."""
+    The order of summation, and so the result, is the same.
+
+    ``gemv`` = 1 uses the CUDA-core streaming kernel for ``M <= 4`` (a warp per weight row, no tensor cores, no
+    split-K hand-off); 0 uses it only when ``OOB_GEMM_GEMV=1``."""
     _check_operands(a, b)
     M, N = a.shape[0], b.shape[0]
     if out is None:
@@ -69,6 +73,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     args.pair = pair
     args.skinny = skinny
     args.splitk_reduce = splitk_reduce
+    args.gemv = gemv
     _lib.check(_lib.lib().oob_gemm(None, ctypes.byref(args), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return out
 
