@@ -17,6 +17,7 @@
 
 #include <cmath>
 #include <cstdint>
+#include <cstdlib>
 #include <type_traits>
 
 #include "../api/oob.h"
@@ -130,9 +131,11 @@ constexpr int kAttnWarps = 4;
 constexpr int kAttnThreads = kAttnWarps * 32;
 constexpr int kRowBytes = kHD * 2;                 // 256
 constexpr int kKvTileBytes = kTileKeys * kRowBytes;  // 8 KiB
-constexpr int kAttnStages = 2;
-constexpr int kWarpBufBytes = kAttnStages * 2 * kKvTileBytes;  // K and V, two stages: 32 KiB
-constexpr int kAttnSmem = kAttnWarps * kWarpBufBytes;           // 128 KiB; reused for the cross-warp merge
+// Pipeline depth per warp (tiles of K and V in flight or in use): 2 by default (128 KiB per CTA), 3 with
+// OOB_ATTN_STAGES=3 (192 KiB: two tiles in flight while one is consumed).  The buffers are reused for the
+// cross-warp merge.
+__host__ __device__ constexpr int attn_warp_buf_bytes(int stages) { return stages * 2 * kKvTileBytes; }
+__host__ __device__ constexpr int attn_smem_bytes(int stages) { return kAttnWarps * attn_warp_buf_bytes(stages); }
 constexpr int kPartialStride = kHD + 2;            // fp32 words of one partial result: 128 values, max, sum
 
 template <typename T>
@@ -188,8 +191,9 @@ struct AttnParams {
   float scale_log2;
 };
 
-template <typename T>
+template <typename T, int STAGES>
 __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(AttnParams p) {
+  constexpr int kWarpBufBytes = attn_warp_buf_bytes(STAGES);
   extern __shared__ __align__(128) uint8_t attn_smem[];
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -253,13 +257,18 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attn_decode_kernel(AttnParams
   for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-  if (my_tiles > 0) issue_tile(0, 0);
-  cp_async_commit();
-  for (int i = 0; i < my_tiles; ++i) {
-    const int stage = i & 1;
-    if (i + 1 < my_tiles) issue_tile(i + 1, stage ^ 1);
+  // One commit group per tile slot, empty when there is no tile: the group count is then the same for every warp
+  // and wait<STAGES - 1> always means "tile i has landed".
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < my_tiles) issue_tile(s, s);
     cp_async_commit();
-    cp_async_wait<1>();
+  }
+  for (int i = 0; i < my_tiles; ++i) {
+    const int stage = i % STAGES;
+    if (i + STAGES - 1 < my_tiles) issue_tile(i + STAGES - 1, (i + STAGES - 1) % STAGES);
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();
     __syncwarp();
     const int key0 = start + (warp + i * kAttnWarps) * kTileKeys;
     const uint32_t ks = wbuf_u32 + stage * 2 * kKvTileBytes, vs = ks + kKvTileBytes;
@@ -431,18 +440,28 @@ int sm_count_model() {
   return n;
 }
 
-template <typename T>
-cudaError_t launch_attn(const AttnParams& p, cudaStream_t stream) {
+template <typename T, int STAGES>
+cudaError_t launch_attn_stages(const AttnParams& p, cudaStream_t stream) {
   static bool attr_done[64];
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_done[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<T, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         attn_smem_bytes(STAGES));
     if (e != cudaSuccess) return e;
     attr_done[dev & 63] = true;
   }
-  attn_decode_kernel<T><<<dim3(p.splits, p.KV, p.B), kAttnThreads, kAttnSmem, stream>>>(p);
-  cudaError_t e = cudaGetLastError();
+  attn_decode_kernel<T, STAGES><<<dim3(p.splits, p.KV, p.B), kAttnThreads, attn_smem_bytes(STAGES), stream>>>(p);
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_attn(const AttnParams& p, cudaStream_t stream) {
+  static const bool three_stages = [] {
+    const char* v = getenv("OOB_ATTN_STAGES");
+    return v != nullptr && v[0] == '3';
+  }();
+  cudaError_t e = three_stages ? launch_attn_stages<T, 3>(p, stream) : launch_attn_stages<T, 2>(p, stream);
   if (e != cudaSuccess) return e;
   if (p.splits > 1) {
     attn_combine_kernel<T><<<p.B * p.H, kHD, 0, stream>>>(p.ws, p.out, p.splits);

@@ -100,3 +100,31 @@ def test_attn_decode_follows_device_position_under_graph_replay():
         torch.cuda.synchronize()
         ref = attn_decode_reference(q, kc, vc, p)
         assert (out.float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item()), p
+
+
+@pytest.mark.skipif(__import__("os").environ.get("OOB_RUN_UNVALIDATED", "0") in ("", "0"),
+                    reason="three-stage pipeline not yet run on hardware; set OOB_RUN_UNVALIDATED=1")
+def test_attn_decode_three_stage_pipeline_in_a_fresh_process():
+    """OOB_ATTN_STAGES=3 is read once per process, so the deeper pipeline is checked in a child."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import torch\n"
+        "from ooverlap_b200.ops import attn_decode, attn_decode_reference\n"
+        "for B, H, KV, L, splits in [(1, 8, 1, 1, 1), (2, 8, 2, 33, 1), (3, 8, 1, 700, 0), (2, 16, 2, 1100, 3), (64, 8, 1, 1088, 0)]:\n"
+        "    g = torch.Generator(device='cuda').manual_seed(L)\n"
+        "    q = torch.randn(B, H, 128, device='cuda', generator=g).bfloat16()\n"
+        "    kc = torch.randn(B, KV, 1152, 128, device='cuda', generator=g).bfloat16()\n"
+        "    vc = torch.randn(B, KV, 1152, 128, device='cuda', generator=g).bfloat16()\n"
+        "    kc[:, :, L:] = float('nan'); vc[:, :, L:] = float('nan')\n"
+        "    out = attn_decode(q, kc, vc, L - 1, splits=splits)\n"
+        "    torch.cuda.synchronize()\n"
+        "    ref = attn_decode_reference(q, kc, vc, L - 1)\n"
+        "    err = (out.float() - ref).abs().max().item()\n"
+        "    assert err <= 2e-2 * max(1.0, ref.abs().max().item()), (B, H, KV, L, splits, err)\n"
+        "print('ok')\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, OOB_ATTN_STAGES="3", PYTHONPATH=root)
+    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and "ok" in res.stdout, res.stderr[-1500:]
