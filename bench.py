@@ -47,7 +47,8 @@ def parse_args():
 def main() -> int:
     args = parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        if int(os.environ.get("RANK", "0")) == 0:  # one line per job, also when launched as several ranks
+            print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
 
     import torch
