@@ -40,7 +40,7 @@ def parse_args():
     p.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl_cublas"])
     p.add_argument("--comm-ctas", type=int, default=int(os.environ.get("OOB_BENCH_COMM_CTAS", "0")),
                    help="communication CTAs of the fused kernel (0 = the library's choice per shape)")
-    p.add_argument("--strategy", default="auto", choices=["auto", "fused", "unfused"])
+    p.add_argument("--strategy", default="auto", choices=["auto", "fused", "unfused", "chunked"])
     return p.parse_args()
 
 
@@ -89,7 +89,8 @@ def main() -> int:
             comm = Communicator(list(range(world)), rank, heap_bytes=heap)
             for m in MS:
                 ops[m] = GemmAllReduce(comm, m, N_DIM, dtype, comm_ctas=args.comm_ctas or None, strategy=args.strategy)
-        launches_per_step = sum(2 if (m in ops and ops[m].strategy == "unfused") else 1 for m in MS)
+        per_op = {"unfused": lambda op: 2, "chunked": lambda op: 2 * op.chunks}
+        launches_per_step = sum(per_op.get(ops[m].strategy, lambda op: 1)(ops[m]) if m in ops else 1 for m in MS)
 
     outs = {m: torch.empty(m, N_DIM, dtype=dtype, device=dev) for m in MS}
 

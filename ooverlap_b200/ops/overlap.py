@@ -68,6 +68,11 @@ class GemmAllReduce:
                       CTAs that ran out of tiles) reduce and broadcast them while later tiles still compute;
       * ``"unfused"`` this library's GEMM writes into the registered output, then its all-reduce kernel runs on it
                       (the policy picks one-shot / two-shot / NVLS and the CTA budget);
+      * ``"chunked"`` the rows are cut into ``chunks`` slabs; slab i is computed by this library's GEMM on the
+                      caller's stream and all-reduced (in-switch two-shot, a handful of CTAs) on a side stream while
+                      the GEMM of slab i + 1 runs on the other SMs: the all-reduce moves each byte once per direction
+                      through the switch, which the fused kernel's peer pushes cannot, and only the first GEMM slab
+                      is exposed.  For large M from four ranks on;
       * ``"auto"``    (default) what measured best on B200 / NVSwitch: between two ranks the fused kernel; from four
                       ranks on the unfused pair for messages up to 64 MiB (a single wave or few waves of tiles leave
                       nothing to overlap and the NVLS all-reduce moves the message once per direction) and the fused
@@ -75,9 +80,12 @@ class GemmAllReduce:
     """
 
     def __init__(self, comm, M: int, N: int, dtype: torch.dtype, *, comm_ctas: Optional[int] = None, max_ctas: int = 0,
-                 use_nvls=None, strategy: str = "auto"):
-        if strategy not in ("auto", "fused", "unfused"):
+                 use_nvls=None, strategy: str = "auto", chunks: int = 4):
+        if strategy not in ("auto", "fused", "unfused", "chunked"):
             raise ValueError(strategy)
+        if strategy == "chunked" and (chunks < 1 or M % chunks):
+            raise ValueError("M must be a multiple of the number of chunks")
+        self.chunks = chunks
         self.comm, self.M, self.N, self.dtype = comm, M, N, dtype
         self.max_ctas = max_ctas
         self.multi = comm.world > 1
@@ -96,6 +104,10 @@ class GemmAllReduce:
             strategy = "fused" if (comm.world < 4 or big or _emulated(comm)) else "unfused"
             if use_nvls is None and comm.world >= 4:
                 use_nvls = 0  # measured: peer pushes beat both NVLS variants inside the fused kernel
+        if strategy == "chunked" and (comm.world < 2 or _emulated(comm)):
+            strategy = "fused" if _emulated(comm) else "unfused"  # nothing to pipeline against
+        if strategy == "chunked" and M // chunks < 1024 and M >= 1024:
+            strategy = "unfused"  # slabs below ~1k rows are single-wave GEMMs: the pipeline has nothing to hide
         self.strategy = strategy
         self.use_nvls = use_nvls
         self.comm_ctas = comm_ctas if comm_ctas is not None else (20 if comm.world < 4 else 16)
@@ -106,6 +118,10 @@ class GemmAllReduce:
             if self.strategy == "fused":
                 self.partial_off = comm.alloc(int(lib.oob_gemm_partial_bytes(M, N)))
                 self.counter_base = comm.reserve_counters(lib.oob_gemm_counters_needed(_lib.GEMM_AR, M, N, comm.world))
+            if self.strategy == "chunked":
+                self._side = torch.cuda.Stream()
+                self._slab_done = [torch.cuda.Event() for _ in range(self.chunks)]
+                self._joined = torch.cuda.Event()
 
     @property
     def fused(self) -> bool:
@@ -133,6 +149,21 @@ class GemmAllReduce:
         if self.strategy == "unfused":
             gemm(a, b, out=self._out, max_ctas=self.max_ctas, splits=1)
             return self.comm.all_reduce(self._out)
+        if self.strategy == "chunked":
+            # Every collective of this op is issued on the side stream, in slab order, on every rank; the caller's
+            # stream only computes, and joins the side stream at the end.
+            main = torch.cuda.current_stream()
+            rows = self.M // self.chunks
+            for i in range(self.chunks):
+                sl = slice(i * rows, (i + 1) * rows)
+                gemm(a[sl], b, out=self._out[sl], max_ctas=self.max_ctas, splits=1)
+                self._slab_done[i].record(main)
+                self._side.wait_event(self._slab_done[i])
+                with torch.cuda.stream(self._side):
+                    self.comm.all_reduce(self._out[sl])
+            self._joined.record(self._side)
+            main.wait_event(self._joined)
+            return self._out
         a0, b0, sa, sb = _operands(self.comm, a, b)
         _check_operands(a0, b0)
         if a0.shape[0] != self.M or b0.shape[0] != self.N:

@@ -1,5 +1,6 @@
 """One process per GPU with the real ``Communicator`` (symmetric heap over VMM file descriptors, NVLS multicast
 where the driver grants it).  Needs at least two GPUs; skipped otherwise.  Oracle: PyTorch fp32 on the host."""
+import os
 import uuid
 
 import pytest
@@ -176,6 +177,17 @@ def _rank_fused(rank, world, key):
         c = op(a[rank].cuda(), bw[rank].cuda())
         torch.cuda.synchronize()
         out.append((f"gemm_ar {strat}", (c.float().cpu() - want).abs().max().item(), 3e-2 * max(1, want.abs().max().item())))
+        op.release()
+    if os.environ.get("OOB_RUN_UNVALIDATED", "0") not in ("", "0"):
+        # slabs of rows: GEMM on the caller's stream, all-reduce of each slab on a side stream (not yet run on hardware)
+        op = GemmAllReduce(comm, M, N, dt, strategy="chunked", chunks=2)
+        for it in range(3):
+            c = op(a[rank].cuda(), bw[rank].cuda())
+            torch.cuda.synchronize()
+            out.append((f"gemm_ar chunked {it}", (c.float().cpu() - want).abs().max().item(),
+                        3e-2 * max(1, want.abs().max().item())))
+            c.zero_()
+            torch.cuda.synchronize()
         op.release()
     rs = GemmReduceScatterNorm(comm, M, N, dt, eps=eps, comm_ctas=8)
     wn = (1 + 0.02 * torch.randn(N, generator=torch.Generator().manual_seed(6))).to(dt)
