@@ -68,7 +68,7 @@ class GemmAllReduce:
                       CTAs that ran out of tiles) reduce and broadcast them while later tiles still compute;
       * ``"unfused"`` this library's GEMM writes into the registered output, then its all-reduce kernel runs on it
                       (the policy picks one-shot / two-shot / NVLS and the CTA budget);
-      * ``"chunked"`` the rows are cut into ``chunks`` slabs; slab i is computed by this library's GEMM on the
+      * ``"chunked"`` the rows are cut into ``chunks`` slabs (default: slabs of 2048 rows; a single slab means unfused); slab i is computed by this library's GEMM on the
                       caller's stream and all-reduced (in-switch two-shot, a handful of CTAs) on a side stream while
                       the GEMM of slab i + 1 runs on the other SMs: the all-reduce moves each byte once per direction
                       through the switch, which the fused kernel's peer pushes cannot, and only the first GEMM slab
@@ -80,12 +80,17 @@ class GemmAllReduce:
     """
 
     def __init__(self, comm, M: int, N: int, dtype: torch.dtype, *, comm_ctas: Optional[int] = None, max_ctas: int = 0,
-                 use_nvls=None, strategy: str = "auto", chunks: int = 4):
+                 use_nvls=None, strategy: str = "auto", chunks: Optional[int] = None):
         if strategy not in ("auto", "fused", "unfused", "chunked"):
             raise ValueError(strategy)
-        if strategy == "chunked" and (chunks < 1 or M % chunks):
-            raise ValueError("M must be a multiple of the number of chunks")
-        self.chunks = chunks
+        if strategy == "chunked":
+            if chunks is None:
+                chunks = M // 2048 if M % 2048 == 0 else 1  # slabs of 2048 rows: several waves of tiles each
+            if chunks < 1 or M % chunks:
+                raise ValueError("M must be a multiple of the number of chunks")
+            if chunks == 1:
+                strategy = "unfused"  # a single slab has nothing to pipeline against
+        self.chunks = chunks or 1
         self.comm, self.M, self.N, self.dtype = comm, M, N, dtype
         self.max_ctas = max_ctas
         self.multi = comm.world > 1
@@ -106,8 +111,6 @@ class GemmAllReduce:
                 use_nvls = 0  # measured: peer pushes beat both NVLS variants inside the fused kernel
         if strategy == "chunked" and (comm.world < 2 or _emulated(comm)):
             strategy = "fused" if _emulated(comm) else "unfused"  # nothing to pipeline against
-        if strategy == "chunked" and M // chunks < 1024 and M >= 1024:
-            strategy = "unfused"  # slabs below ~1k rows are single-wave GEMMs: the pipeline has nothing to hide
         self.strategy = strategy
         self.use_nvls = use_nvls
         self.comm_ctas = comm_ctas if comm_ctas is not None else (20 if comm.world < 4 else 16)
