@@ -22,6 +22,8 @@ Environment (names follow the reference's ``VLLM_OOVERLAP_*`` family):
   VLLM_OOVERLAP_RR_DTYPE         bf16 | fp16 | fp32 (default bf16)
   VLLM_OOVERLAP_AG_SLOTS / _AG_CAPACITY_BYTES / _AG_DTYPE   all-gather pool (4 x 64 MiB, bf16)
   VLLM_OOVERLAP_BROKER_KEY       fixed rendezvous key (default: a UUID broadcast over the CPU group)
+  VLLM_OOVERLAP_ROW_PARALLEL     1: bias-free, unquantised ``RowParallelLinear`` layers (o_proj, down_proj) run as
+                                 this library's GEMM into a registered slot + in-place all-reduce (default 0)
   VLLM_OOVERLAP_DEBUG            verbose logging
 
 Capability parity: patches/vllm/v0.25.0/vllm/distributed/device_communicators/ooverlap_all_reduce.py:44-704
@@ -206,6 +208,74 @@ class OoverlapAllReduce:
     qwen_row_parallel = row_parallel
 
 
+# --------------------------------------------------------------------------------------------------------------------
+# Direct-slot row-parallel linear as a torch custom op, so that a compiled vLLM model can call it.
+# --------------------------------------------------------------------------------------------------------------------
+_row_parallel_backend: Optional["OoverlapAllReduce"] = None  # the tensor-parallel group's backend in this process
+
+
+@torch.library.custom_op("ooverlap_b200::row_parallel_linear", mutates_args=())
+def row_parallel_linear_op(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``all_reduce(x @ weight.T)`` over the tensor-parallel group through the registered backend.  The result lives
+    in a slot of the backend's ring: it must be consumed before the ring wraps (32 slots by default)."""
+    backend = _row_parallel_backend
+    out = backend.row_parallel(x, weight) if backend is not None else None
+    if out is None:
+        raise RuntimeError("row_parallel_linear: no backend, or the operands do not fit a slot (check the caller's "
+                           "eligibility test)")
+    return out
+
+
+@row_parallel_linear_op.register_fake
+def _row_parallel_linear_fake(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    return x.new_empty(tuple(x.shape[:-1]) + (weight.shape[0],))
+
+
+def row_parallel_eligible(layer, x: torch.Tensor, backend) -> bool:
+    """True when a vLLM ``RowParallelLinear`` call can take the direct-slot path: the reference restricts it to
+    bias-free, unquantised layers whose result is reduced (model_executor/models/qwen2.py:84-120)."""
+    if not isinstance(backend, OoverlapAllReduce) or backend.disabled:
+        return False
+    if not getattr(layer, "reduce_results", False) or getattr(layer, "tp_size", 1) <= 1:
+        return False
+    if not getattr(layer, "input_is_parallel", False) or getattr(layer, "bias", None) is not None:
+        return False
+    if type(getattr(layer, "quant_method", None)).__name__ != "UnquantizedLinearMethod":
+        return False
+    w = getattr(layer, "weight", None)
+    if w is None or w.dtype != backend.rr_dtype or x.dtype != backend.rr_dtype or not x.is_cuda:
+        return False
+    rows = x.numel() // max(1, x.shape[-1])
+    if rows == 0 or x.shape[-1] % 8 or not x.is_contiguous():
+        return False
+    return rows * w.shape[0] * x.element_size() <= backend.rr_capacity
+
+
+def _patch_row_parallel_linear() -> bool:
+    """Routes eligible ``RowParallelLinear.forward`` calls through :func:`row_parallel_linear_op`."""
+    from vllm.distributed.parallel_state import get_tp_group
+    from vllm.model_executor.layers import linear as vl
+
+    original_forward = vl.RowParallelLinear.forward
+
+    def patched_forward(self, input_):
+        try:
+            backend = getattr(get_tp_group().device_communicator, "ca_comm", None)
+        except Exception:  # noqa: BLE001  (group not built yet)
+            backend = None
+        if row_parallel_eligible(self, input_, backend):
+            global _row_parallel_backend
+            _row_parallel_backend = backend
+            out = torch.ops.ooverlap_b200.row_parallel_linear(input_, self.weight)
+            if not self.return_bias:
+                return out
+            return out, None
+        return original_forward(self, input_)
+
+    vl.RowParallelLinear.forward = patched_forward
+    return True
+
+
 _installed = False
 
 
@@ -258,5 +328,8 @@ def install() -> bool:
     cc.CudaCommunicator.__init__ = patched_init
     cc.CudaCommunicator.all_gather = patched_all_gather
     cc.CudaCommunicator.destroy = patched_destroy
+    if _env_int("VLLM_OOVERLAP_ROW_PARALLEL", 0):
+        _patch_row_parallel_linear()
+        logger.info("vLLM RowParallelLinear routed through the direct-slot GEMM + all-reduce")
     _installed = True
     return True

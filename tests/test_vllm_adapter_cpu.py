@@ -141,3 +141,89 @@ def test_install_patches_vllm_communicator(monkeypatch):
     finally:
         cc.CudaCommunicator.__init__, cc.CudaCommunicator.all_gather, cc.CudaCommunicator.destroy = orig_init, orig_ag, orig_destroy
         va._installed = False
+
+
+def test_row_parallel_eligibility_and_custom_op():
+    """The direct-slot row-parallel path is taken only for bias-free, unquantised, reduced layers whose result fits
+    a slot; the torch custom op dispatches to the registered backend and has a shape-only (fake) implementation."""
+
+    class UnquantizedLinearMethod:  # same class NAME as vLLM's; the check is by name
+        pass
+
+    class Layer:
+        reduce_results, tp_size, input_is_parallel, bias, return_bias = True, 2, True, None, False
+        quant_method = UnquantizedLinearMethod()
+        weight = torch.zeros(16, 8, dtype=torch.bfloat16)
+
+    class Backend(va.OoverlapAllReduce):
+        def __init__(self):
+            self.disabled, self.rr_dtype, self.rr_capacity = False, torch.bfloat16, 1 << 20
+            self.calls = 0
+
+        def row_parallel(self, x, weight):
+            self.calls += 1
+            return (x.float() @ weight.float().t()).to(x.dtype) * 2  # stand-in for GEMM + 2-rank all-reduce
+
+    b = Backend()
+    x = torch.ones(4, 8, dtype=torch.bfloat16)
+    # CPU tensors are never eligible (the kernels need CUDA memory) ...
+    assert not va.row_parallel_eligible(Layer(), x, b)
+    # ... every other condition is checked on a meta-free stand-in that claims to be on the GPU
+    class CudaLike:
+        def __init__(self, t):
+            self._t = t
+            self.dtype, self.shape, self.is_cuda = t.dtype, t.shape, True
+
+        def numel(self):
+            return self._t.numel()
+
+        def is_contiguous(self):
+            return True
+
+        def element_size(self):
+            return self._t.element_size()
+
+    xc = CudaLike(x)
+    assert va.row_parallel_eligible(Layer(), xc, b)
+    for attr, val in (("reduce_results", False), ("tp_size", 1), ("input_is_parallel", False), ("bias", torch.zeros(16))):
+        layer = Layer()
+        setattr(layer, attr, val)
+        assert not va.row_parallel_eligible(layer, xc, b), attr
+    quant = Layer()
+    quant.quant_method = object()
+    assert not va.row_parallel_eligible(quant, xc, b)
+    small = Backend()
+    small.rr_capacity = 16
+    assert not va.row_parallel_eligible(Layer(), xc, small)
+    assert not va.row_parallel_eligible(Layer(), xc, "vllm-ca")
+    # the custom op: real dispatch and fake (meta) shape inference
+    va._row_parallel_backend = b
+    try:
+        out = torch.ops.ooverlap_b200.row_parallel_linear(x, Layer.weight)
+        assert out.shape == (4, 16) and b.calls == 1
+        meta = torch.ops.ooverlap_b200.row_parallel_linear(x.to("meta"), Layer.weight.to("meta"))
+        assert meta.shape == (4, 16) and meta.device.type == "meta"
+        va._row_parallel_backend = None
+        with pytest.raises(RuntimeError):
+            torch.ops.ooverlap_b200.row_parallel_linear(x, Layer.weight)
+    finally:
+        va._row_parallel_backend = None
+
+
+def test_row_parallel_patch_falls_back_to_vllm(monkeypatch):
+    """With VLLM_OOVERLAP_ROW_PARALLEL the patched RowParallelLinear.forward defers to vLLM's own forward for any
+    call that is not eligible (here: no tensor-parallel group exists)."""
+    vl = pytest.importorskip("vllm.model_executor.layers.linear")
+    orig = vl.RowParallelLinear.forward
+    seen = {}
+    monkeypatch.setattr(vl.RowParallelLinear, "forward", lambda self, x: seen.setdefault("orig", x))
+    try:
+        assert va._patch_row_parallel_linear()
+
+        class L:
+            reduce_results, tp_size, input_is_parallel, bias, return_bias = True, 2, True, None, False
+
+        out = vl.RowParallelLinear.forward(L(), torch.ones(2, 8))
+        assert out is seen["orig"]
+    finally:
+        vl.RowParallelLinear.forward = orig
