@@ -60,6 +60,42 @@ def _operands(comm, a: torch.Tensor, b: torch.Tensor):
     return a, b, 0, 0
 
 
+def plan_gemm_all_reduce(world: int, M: int, N: int, emulated: bool, strategy: str = "auto", chunks: Optional[int] = None,
+                         use_nvls=None, comm_ctas: Optional[int] = None, solution: Optional[dict] = None):
+    """Resolves what :class:`GemmAllReduce` will run: ``(strategy, chunks, use_nvls, comm_ctas)`` with ``strategy``
+    one of fused / unfused / chunked.  Pure function of its arguments (``solution`` is a tuned entry for the shape,
+    or None), so that the rule can be read and tested without a GPU."""
+    if strategy not in ("auto", "fused", "unfused", "chunked"):
+        raise ValueError(strategy)
+    if strategy == "auto" and solution is not None and not emulated:
+        strategy = solution.get("strategy", "auto")
+        if strategy not in ("auto", "fused", "unfused", "chunked"):
+            raise ValueError(f"solution names an unknown strategy {strategy!r}")
+        if comm_ctas is None and solution.get("comm_ctas"):
+            comm_ctas = int(solution["comm_ctas"])
+        if use_nvls is None and "use_nvls" in solution:
+            use_nvls = int(solution["use_nvls"])
+        if chunks is None and solution.get("chunks"):
+            chunks = int(solution["chunks"])
+    if strategy == "auto":
+        big = M * N * 2 > (64 << 20)
+        strategy = "fused" if (world < 4 or big or emulated) else "unfused"
+        if use_nvls is None and world >= 4:
+            use_nvls = 0  # measured: peer pushes beat both NVLS variants inside the fused kernel
+    if strategy == "chunked":
+        if chunks is None:
+            chunks = M // 2048 if M % 2048 == 0 else 1  # slabs of 2048 rows: several waves of tiles each
+        if chunks < 1 or M % chunks:
+            raise ValueError("M must be a multiple of the number of chunks")
+        if emulated:
+            strategy = "fused"  # one launch per op in emulation
+        elif world < 2 or chunks == 1:
+            strategy = "unfused"  # nothing to pipeline against
+    if strategy != "chunked":
+        chunks = 1
+    return strategy, chunks, use_nvls, comm_ctas
+
+
 class GemmAllReduce:
     """Row-parallel linear: ``C = sum_ranks(A_r @ B_r^T)`` in every rank's registered memory.
 
@@ -81,36 +117,17 @@ class GemmAllReduce:
 
     def __init__(self, comm, M: int, N: int, dtype: torch.dtype, *, comm_ctas: Optional[int] = None, max_ctas: int = 0,
                  use_nvls=None, strategy: str = "auto", chunks: Optional[int] = None):
-        if strategy not in ("auto", "fused", "unfused", "chunked"):
-            raise ValueError(strategy)
-        if strategy == "chunked":
-            if chunks is None:
-                chunks = M // 2048 if M % 2048 == 0 else 1  # slabs of 2048 rows: several waves of tiles each
-            if chunks < 1 or M % chunks:
-                raise ValueError("M must be a multiple of the number of chunks")
-            if chunks == 1:
-                strategy = "unfused"  # a single slab has nothing to pipeline against
-        self.chunks = chunks or 1
         self.comm, self.M, self.N, self.dtype = comm, M, N, dtype
         self.max_ctas = max_ctas
         self.multi = comm.world > 1
-        if strategy == "auto":
+        sol = None
+        if strategy == "auto" and not _emulated(comm):
             # A tuned solution for this shape (OOB_OVERLAP_SOLUTIONS, written by bench.tune_overlap) wins.
             from . import solutions
             sol = solutions.lookup("gemm_ar", M, N, 0, comm.world, "bf16" if dtype == torch.bfloat16 else "fp16")
-            if sol is not None and not _emulated(comm):
-                strategy = sol.get("strategy", "auto")
-                if comm_ctas is None and sol.get("comm_ctas"):
-                    comm_ctas = int(sol["comm_ctas"])
-                if use_nvls is None and "use_nvls" in sol:
-                    use_nvls = int(sol["use_nvls"])
-        if strategy == "auto":
-            big = M * N * 2 > (64 << 20)
-            strategy = "fused" if (comm.world < 4 or big or _emulated(comm)) else "unfused"
-            if use_nvls is None and comm.world >= 4:
-                use_nvls = 0  # measured: peer pushes beat both NVLS variants inside the fused kernel
-        if strategy == "chunked" and (comm.world < 2 or _emulated(comm)):
-            strategy = "fused" if _emulated(comm) else "unfused"  # nothing to pipeline against
+        strategy, chunks, use_nvls, comm_ctas = plan_gemm_all_reduce(comm.world, M, N, _emulated(comm), strategy, chunks,
+                                                                     use_nvls, comm_ctas, sol)
+        self.chunks = chunks
         self.strategy = strategy
         self.use_nvls = use_nvls
         self.comm_ctas = comm_ctas if comm_ctas is not None else (20 if comm.world < 4 else 16)

@@ -1,0 +1,42 @@
+"""The strategy rule of GemmAllReduce is a pure function: the choices that were measured on 8 x B200 are pinned here."""
+import pytest
+
+from ooverlap_b200.ops.overlap import plan_gemm_all_reduce as plan
+
+
+def test_measured_choices_on_nvswitch():
+    # tp8, N = 8192: single-wave / few-wave shapes run the GEMM and the in-switch all-reduce back to back ...
+    assert plan(8, 512, 8192, False)[0] == "unfused"
+    assert plan(8, 2048, 8192, False)[0] == "unfused"
+    # ... above 64 MiB the fused kernel with peer pushes wins (use_nvls 0)
+    assert plan(8, 8192, 8192, False)[:3] == ("fused", 1, 0)
+    assert plan(4, 2048, 8192, False)[0] == "unfused" and plan(4, 8192, 8192, False)[0] == "fused"
+    # two ranks: always the fused kernel, and the NVLS choice is left to the op's default
+    assert plan(2, 512, 8192, False)[0] == "fused" and plan(2, 8192, 8192, False)[2] is None
+    # emulation runs one launch per op
+    assert plan(8, 512, 8192, True)[0] == "fused"
+
+
+def test_chunked_strategy_resolution():
+    assert plan(8, 8192, 8192, False, "chunked")[:2] == ("chunked", 4)          # slabs of 2048 rows
+    assert plan(8, 512, 8192, False, "chunked")[0] == "unfused"                 # a single slab: nothing to pipeline
+    assert plan(8, 512, 8192, False, "chunked", 2)[:2] == ("chunked", 2)        # explicit slab count
+    assert plan(1, 8192, 8192, False, "chunked")[0] == "unfused"
+    assert plan(8, 8192, 8192, True, "chunked")[0] == "fused"
+    with pytest.raises(ValueError):
+        plan(8, 1000, 8192, False, "chunked", 3)
+    with pytest.raises(ValueError):
+        plan(8, 512, 8192, False, "pipelined")
+
+
+def test_tuned_solution_overrides_the_rule():
+    sol = {"strategy": "fused", "comm_ctas": 24, "use_nvls": 2}
+    assert plan(8, 512, 8192, False, "auto", None, None, None, sol) == ("fused", 1, 2, 24)
+    # explicit arguments win over the solution's
+    assert plan(8, 512, 8192, False, "auto", None, 0, 8, sol) == ("fused", 1, 0, 8)
+    assert plan(8, 8192, 8192, False, "auto", None, None, None, {"strategy": "chunked", "chunks": 8})[:2] == ("chunked", 8)
+    # a solution is ignored in emulation and when the caller named a strategy
+    assert plan(8, 512, 8192, True, "auto", None, None, None, sol)[0] == "fused"
+    assert plan(8, 512, 8192, False, "unfused", None, None, None, sol)[0] == "unfused"
+    with pytest.raises(ValueError):
+        plan(8, 512, 8192, False, "auto", None, None, None, {"strategy": "bogus"})
