@@ -26,6 +26,7 @@ import torch.nn.functional as F
 from ..ops import (attn_decode, fused_allreduce_rmsnorm, gemm, gemm_rope_kv_write, gemm_swiglu, rmsnorm, rope_kv_write,
                    rope_tables, silu_mul)
 from ..utils.config import env_flag
+from ..utils.tracing import nvtx_range
 
 
 @dataclass
@@ -164,55 +165,56 @@ class LlamaTP:
         x = self._norm(h, self.layers[0]["norm1"])
         sl = slice(batch0, batch0 + B)
         for li, layer in enumerate(self.layers):
-            if ours and self.fused_epilogues:
-                kc, vc = self.k_cache[li], self.v_cache[li]
-                q = gemm_rope_kv_write(x, layer["wqkv"], B, T, self.h_local, self.kv_local, kc, vc, self.rope_cos32,
-                                       self.rope_sin32, pos, batch0=batch0)
-            else:
-                qkv = self._mm(x, layer["wqkv"])
-            if ours:
-                # One kernel rotates q and k and writes k, v into the cache.
-                if not self.fused_epilogues:
+            with nvtx_range("layer"):
+                if ours and self.fused_epilogues:
                     kc, vc = self.k_cache[li], self.v_cache[li]
-                    q = rope_kv_write(qkv, B, T, self.h_local, self.kv_local, kc, vc, self.rope_cos32, self.rope_sin32,
-                                      pos, batch0=batch0)
-                if decode and hd == 128:
-                    att = attn_decode(q.view(B, self.h_local, hd), kc, vc, pos, batch0=batch0)
-                elif decode:
-                    att = F.scaled_dot_product_attention(q.view(B, 1, self.h_local, hd).transpose(1, 2), kc[sl], vc[sl],
-                                                         attn_mask=attn_mask, enable_gqa=True)
-                    att = att.transpose(1, 2).reshape(B * T, self.h_local * hd)
+                    q = gemm_rope_kv_write(x, layer["wqkv"], B, T, self.h_local, self.kv_local, kc, vc, self.rope_cos32,
+                                           self.rope_sin32, pos, batch0=batch0)
                 else:
-                    att = F.scaled_dot_product_attention(q.view(B, T, self.h_local, hd).transpose(1, 2),
-                                                         kc[sl, :, pos:pos + T], vc[sl, :, pos:pos + T],
-                                                         is_causal=True, enable_gqa=True)
-                    att = att.transpose(1, 2).reshape(B * T, self.h_local * hd)
-            else:
-                qkv = qkv.view(B, T, self.h_local + 2 * self.kv_local, hd)
-                q = _apply_rope(qkv[:, :, : self.h_local], cos, sin).transpose(1, 2)
-                k = _apply_rope(qkv[:, :, self.h_local: self.h_local + self.kv_local], cos, sin).transpose(1, 2)
-                v = qkv[:, :, self.h_local + self.kv_local:].transpose(1, 2)
-                if decode:
-                    self.k_cache[li, sl].index_copy_(2, pos, k)
-                    self.v_cache[li, sl].index_copy_(2, pos, v)
-                    att = F.scaled_dot_product_attention(q, self.k_cache[li, sl], self.v_cache[li, sl],
-                                                         attn_mask=attn_mask, enable_gqa=True)
+                    qkv = self._mm(x, layer["wqkv"])
+                if ours:
+                    # One kernel rotates q and k and writes k, v into the cache.
+                    if not self.fused_epilogues:
+                        kc, vc = self.k_cache[li], self.v_cache[li]
+                        q = rope_kv_write(qkv, B, T, self.h_local, self.kv_local, kc, vc, self.rope_cos32, self.rope_sin32,
+                                          pos, batch0=batch0)
+                    if decode and hd == 128:
+                        att = attn_decode(q.view(B, self.h_local, hd), kc, vc, pos, batch0=batch0)
+                    elif decode:
+                        att = F.scaled_dot_product_attention(q.view(B, 1, self.h_local, hd).transpose(1, 2), kc[sl], vc[sl],
+                                                             attn_mask=attn_mask, enable_gqa=True)
+                        att = att.transpose(1, 2).reshape(B * T, self.h_local * hd)
+                    else:
+                        att = F.scaled_dot_product_attention(q.view(B, T, self.h_local, hd).transpose(1, 2),
+                                                             kc[sl, :, pos:pos + T], vc[sl, :, pos:pos + T],
+                                                             is_causal=True, enable_gqa=True)
+                        att = att.transpose(1, 2).reshape(B * T, self.h_local * hd)
                 else:
-                    self.k_cache[li, sl, :, pos:pos + T] = k
-                    self.v_cache[li, sl, :, pos:pos + T] = v
-                    att = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
-                att = att.transpose(1, 2).reshape(B * T, self.h_local * hd)
-            x, h = self._row_parallel_norm(att, layer["wo"], h, layer["norm2"])
-            if ours and self.fused_epilogues:
-                act = gemm_swiglu(x, layer["wgu"])
-            elif ours:
-                act = silu_mul(self._mm(x, layer["wgu"]))
-            else:
-                gu = self._mm(x, layer["wgu"])
-                half = gu.shape[1] // 2
-                act = F.silu(gu[:, :half]) * gu[:, half:]
-            next_norm = self.layers[li + 1]["norm1"] if li + 1 < len(self.layers) else self.final_norm
-            x, h = self._row_parallel_norm(act, layer["wd"], h, next_norm)
+                    qkv = qkv.view(B, T, self.h_local + 2 * self.kv_local, hd)
+                    q = _apply_rope(qkv[:, :, : self.h_local], cos, sin).transpose(1, 2)
+                    k = _apply_rope(qkv[:, :, self.h_local: self.h_local + self.kv_local], cos, sin).transpose(1, 2)
+                    v = qkv[:, :, self.h_local + self.kv_local:].transpose(1, 2)
+                    if decode:
+                        self.k_cache[li, sl].index_copy_(2, pos, k)
+                        self.v_cache[li, sl].index_copy_(2, pos, v)
+                        att = F.scaled_dot_product_attention(q, self.k_cache[li, sl], self.v_cache[li, sl],
+                                                             attn_mask=attn_mask, enable_gqa=True)
+                    else:
+                        self.k_cache[li, sl, :, pos:pos + T] = k
+                        self.v_cache[li, sl, :, pos:pos + T] = v
+                        att = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+                    att = att.transpose(1, 2).reshape(B * T, self.h_local * hd)
+                x, h = self._row_parallel_norm(att, layer["wo"], h, layer["norm2"])
+                if ours and self.fused_epilogues:
+                    act = gemm_swiglu(x, layer["wgu"])
+                elif ours:
+                    act = silu_mul(self._mm(x, layer["wgu"]))
+                else:
+                    gu = self._mm(x, layer["wgu"])
+                    half = gu.shape[1] // 2
+                    act = F.silu(gu[:, :half]) * gu[:, half:]
+                next_norm = self.layers[li + 1]["norm1"] if li + 1 < len(self.layers) else self.final_norm
+                x, h = self._row_parallel_norm(act, layer["wd"], h, next_norm)
         return x
 
     def greedy_token(self, hidden_last: torch.Tensor) -> torch.Tensor:

@@ -41,6 +41,7 @@ def env_flag(name: str, default: bool = False) -> bool:
 #   OOB_SPLITK_REDUCE_MIN_M=n  split-K: sum inside the GEMM kernel below n rows (default 1: always the second kernel)
 #   OOB_ATTN_STAGES=3          decode attention: three pipeline stages per warp (192 KiB of shared memory per CTA)
 #   OOB_FUSED_EPILOGUES=1      model runner: RoPE + cache write and SwiGLU in the split-K sum of the preceding GEMM
+#   OOB_NVTX=1                 NVTX ranges around the model runner's layers (utils/tracing.py)
 #   OOB_RUN_UNVALIDATED=1      tests: also run the GPU tests of paths that have not been run on hardware yet
 
 
