@@ -1,0 +1,257 @@
+"""Randomised interleaving simulation of the device-side synchronisation protocols.
+
+compute-sanitizer's racecheck is not available where this library is developed, so the protocols that carry the
+cross-CTA and cross-GPU ordering are restated here as small state machines (one Python generator per CTA or thread
+role; every ``yield`` is a point where any other role may run) and executed under thousands of random schedules:
+
+* ``rank_barrier``            epoch inboxes in every rank's signal pad (csrc/device/sync.cuh)
+* ticket + arrival counters   fused GEMM -> all-reduce: producers bump the owner's per-tile counter, reducer CTAs draw
+                              tickets, wait for ``world`` arrivals, re-arm the counter; the ticket counter is re-armed
+                              by whoever draws the last ticket (csrc/gemm/gemm_kernel.cuh: draw_ticket, ar_reducer_role)
+* last-arriver split-K sum    per-quadrant arrival counter re-armed by the CTA that completes it
+                              (csrc/gemm/gemm_kernel.cuh, csrc/gemm/gemm_skinny.cu)
+
+What is checked: no role waits forever, every unit of work is done exactly once and only after its inputs were
+complete, and every counter is back at its initial value when a launch ends, so the next launch (run here back to
+back on the same memory) starts from the state it expects.  The memory model is sequential consistency: these
+tests find protocol errors (lost updates, double consumption, stale re-arms), not missing fences.
+"""
+import random
+
+import pytest
+
+
+def run_schedule(roles, rng, max_steps=200000):
+    """Runs generator roles to completion under a random schedule; a role that yields "blocked" made no progress."""
+    live = list(roles)
+    idle_rounds = 0
+    steps = 0
+    while live:
+        steps += 1
+        assert steps < max_steps, "schedule did not terminate"
+        g = rng.choice(live)
+        try:
+            state = next(g)
+        except StopIteration:
+            live.remove(g)
+            idle_rounds = 0
+            continue
+        if state == "blocked":
+            idle_rounds += 1
+            # every live role blocked many times in a row: nobody can make progress any more
+            assert idle_rounds < 50 * len(live) + 1000, "deadlock: every remaining role is waiting"
+        else:
+            idle_rounds = 0
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# rank_barrier
+# ---------------------------------------------------------------------------------------------------------------------
+class Pads:
+    def __init__(self, world, slots):
+        self.epoch = [[0] * slots for _ in range(world)]                      # per rank, per slot (own memory)
+        self.inbox = [[[0] * world for _ in range(slots)] for _ in range(world)]  # [rank][slot][peer]
+
+
+def barrier_block(pads, world, rank, slot, rounds, log):
+    """Block `slot` of `rank`: `rounds` barriers with a little "work" in between (an entry in the log)."""
+    for r in range(rounds):
+        log.append(("enter", rank, slot, r))
+        yield
+        pads.epoch[rank][slot] += 1          # thread 0: s_epoch = *ep + 1; *ep = s_epoch
+        e = pads.epoch[rank][slot]
+        yield
+        for peer in range(world):            # threads 0..world-1 run concurrently on the device; any order is one of them
+            pads.inbox[peer][slot][rank] = e  # st.release.sys to the peer's inbox
+            yield
+        for peer in range(world):
+            while pads.inbox[rank][slot][peer] - e < 0:  # wait_word_ge: (int)(v - want) >= 0
+                yield "blocked"
+            yield
+        log.append(("leave", rank, slot, r))
+        yield
+
+
+@pytest.mark.parametrize("world,slots,rounds", [(2, 1, 4), (3, 2, 3), (4, 2, 3), (8, 1, 2)])
+def test_rank_barrier_orders_every_round(world, slots, rounds):
+    for seed in range(300):
+        rng = random.Random(seed * 7919 + world)
+        pads, log = Pads(world, slots), []
+        roles = [barrier_block(pads, world, r, s, rounds, log) for r in range(world) for s in range(slots)]
+        run_schedule(roles, rng)
+        # nobody leaves round r of a slot before everybody has entered it
+        for s in range(slots):
+            for r in range(rounds):
+                first_leave = min(i for i, ev in enumerate(log) if ev == ("leave", ev[1], s, r) and ev[0] == "leave")
+                last_enter = max(i for i, ev in enumerate(log) if ev[0] == "enter" and ev[2] == s and ev[3] == r)
+                assert last_enter < first_leave, (seed, s, r)
+        assert all(pads.epoch[r][s] == rounds for r in range(world) for s in range(slots))
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# fused GEMM -> all-reduce: arrival counters, tickets, re-arming, two launches back to back
+# ---------------------------------------------------------------------------------------------------------------------
+class ArState:
+    def __init__(self, world, tiles):
+        self.world, self.tiles = world, tiles
+        self.owned_max = (tiles + world - 1) // world
+        self.counter = [[0] * self.owned_max for _ in range(world)]  # arrivals per owned tile, in the owner's pad
+        self.ticket = [0] * world
+        self.pushed = [[set() for _ in range(self.owned_max)] for _ in range(world)]  # which source ranks have pushed
+        self.reduced = [[0] * self.owned_max for _ in range(world)]
+
+
+def gemm_cta(st, rank, my_tiles, launch, pads, slot, reducer_ctas_total):
+    """A GEMM CTA of `rank`: computes its tiles, pushes each to the owner, signals; then joins the reducers."""
+    for seq in my_tiles:
+        owner, k = seq % st.world, seq // st.world
+        yield
+        st.pushed[owner][k].add((launch, rank))   # bulk tensor stores into the owner's staging buffer
+        yield
+        st.counter[owner][k] += 1                 # signal warp: red.release.sys on the owner's counter
+        yield
+    yield from reducer_cta(st, rank, launch, pads, slot, reducer_ctas_total)
+
+
+def reducer_cta(st, rank, launch, pads, slot, drawers):
+    owned = (st.tiles - rank + st.world - 1) // st.world
+    while True:
+        t = st.ticket[rank]                       # atomicAdd(ticket, 1)
+        st.ticket[rank] += 1
+        if t == owned + drawers - 1:
+            st.ticket[rank] = 0                   # the last ticket that can ever be drawn re-arms the counter
+        yield
+        if t >= owned:
+            break
+        k = t
+        while st.counter[rank][k] < st.world:     # wait_word_ge(cnt, world)
+            yield "blocked"
+        st.counter[rank][k] = 0                   # single consumer: re-arm now
+        yield
+        # every rank's slice of THIS launch must be in place when the tile is summed
+        assert st.pushed[rank][k] == {(launch, r) for r in range(st.world)}, (rank, k, st.pushed[rank][k])
+        st.pushed[rank][k] = set()
+        st.reduced[rank][k] += 1
+        yield
+    # final barrier between block `slot` of every rank (rank_barrier)
+    yield from barrier_block(pads, st.world, rank, slot, 1, [])
+
+
+@pytest.mark.parametrize("world,tiles,gemm_ctas,comm_ctas", [(2, 5, 2, 1), (2, 8, 3, 2), (4, 9, 2, 1), (3, 4, 1, 2)])
+def test_fused_all_reduce_counters_and_tickets(world, tiles, gemm_ctas, comm_ctas):
+    ctas = gemm_ctas + comm_ctas
+    for seed in range(150):
+        rng = random.Random(seed * 104729 + tiles)
+        st, pads = ArState(world, tiles), Pads(world, ctas)
+        for launch in range(2):  # the second launch runs on the memory the first one left behind
+            roles = []
+            for rank in range(world):
+                for c in range(gemm_ctas):
+                    roles.append(gemm_cta(st, rank, list(range(c, tiles, gemm_ctas)), launch, pads, c, ctas))
+                for c in range(comm_ctas):
+                    roles.append(reducer_cta(st, rank, launch, pads, gemm_ctas + c, ctas))
+            run_schedule(roles, rng)
+            for rank in range(world):
+                owned = (tiles - rank + world - 1) // world
+                assert st.reduced[rank][:owned] == [launch + 1] * owned, (seed, launch, rank, st.reduced[rank])
+                assert st.ticket[rank] == 0 and all(c == 0 for c in st.counter[rank]), (seed, launch, rank)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# split-K: last arriver sums and re-arms
+# ---------------------------------------------------------------------------------------------------------------------
+def splitk_cta(state, tile, split, splits, launch):
+    yield
+    state["partial"][tile][split] = launch          # fp32 partial tile written to the workspace
+    yield                                           # __threadfence
+    prev = state["count"][tile]                     # atomicAdd(qcnt, 1)
+    state["count"][tile] += 1
+    yield
+    if prev == splits - 1:
+        state["count"][tile] = 0                    # re-arm for the next call
+        yield
+        assert state["partial"][tile] == [launch] * splits, (tile, state["partial"][tile])
+        state["summed"][tile] += 1
+
+
+@pytest.mark.parametrize("tiles,splits", [(1, 2), (3, 5), (4, 8)])
+def test_split_k_last_arriver(tiles, splits):
+    for seed in range(200):
+        rng = random.Random(seed * 31 + splits)
+        state = {"partial": [[None] * splits for _ in range(tiles)], "count": [0] * tiles, "summed": [0] * tiles}
+        for launch in range(3):
+            roles = [splitk_cta(state, t, s, splits, launch) for t in range(tiles) for s in range(splits)]
+            run_schedule(roles, rng)
+            assert state["summed"] == [launch + 1] * tiles and state["count"] == [0] * tiles
+
+
+def test_the_simulator_finds_a_planted_bug():
+    """Sanity of the method: a reducer that re-arms the counter AFTER summing (instead of before any later arrival can
+    happen) is harmless, but one that draws tickets without the re-arm rule leaves the ticket counter dirty."""
+    world, tiles = 2, 4
+    st, pads = ArState(world, tiles), Pads(world, 2)
+
+    def broken_reducer(rank):
+        owned = (tiles - rank + world - 1) // world
+        while True:
+            t = st.ticket[rank]
+            st.ticket[rank] += 1  # never re-armed
+            yield
+            if t >= owned:
+                break
+            while st.counter[rank][t] < world:
+                yield "blocked"
+            st.counter[rank][t] = 0
+            yield
+
+    roles = [gemm_cta(st, r, list(range(tiles)), 0, pads, 0, 2) for r in range(world)]
+    roles += [broken_reducer(r) for r in range(world)]
+    with pytest.raises(AssertionError):
+        run_schedule(roles, random.Random(0))
+        assert all(t == 0 for t in st.ticket)
+
+
+def test_the_simulator_catches_a_counter_that_is_not_re_armed():
+    """Without the re-arm (``*cnt = 0``) the second launch finds the first launch's arrivals still counted and sums a
+    tile before this launch's slices are in place: some schedule must trip the reducer's input check."""
+    world, tiles, ctas = 2, 2, 2
+
+    def reducer_without_rearm(st, rank, launch, pads, slot):
+        owned = (st.tiles - rank + st.world - 1) // st.world
+        while True:
+            t = st.ticket[rank]
+            st.ticket[rank] += 1
+            if t == owned + 1 - 1:  # one drawer per rank in this set-up
+                st.ticket[rank] = 0
+            yield
+            if t >= owned:
+                break
+            while st.counter[rank][t] < st.world * 1:  # stale arrivals of the previous launch satisfy this at once
+                yield "blocked"
+            yield
+            assert st.pushed[rank][t] == {(launch, r) for r in range(st.world)}, "summed before the inputs were complete"
+            st.pushed[rank][t] = set()
+            yield
+        yield from barrier_block(pads, st.world, rank, slot, 1, [])
+
+    def producer(st, rank, launch, pads, slot):
+        for seq in range(st.tiles):
+            owner, k = seq % st.world, seq // st.world
+            yield
+            st.pushed[owner][k].add((launch, rank))
+            yield
+            st.counter[owner][k] += 1
+            yield
+        yield from barrier_block(pads, st.world, rank, slot, 1, [])
+
+    tripped = 0
+    for seed in range(60):
+        st, pads = ArState(world, tiles), Pads(world, ctas)
+        try:
+            for launch in range(2):
+                roles = [producer(st, r, launch, pads, 0) for r in range(world)]
+                roles += [reducer_without_rearm(st, r, launch, pads, 1) for r in range(world)]
+                run_schedule(roles, random.Random(seed))
+        except AssertionError:
+            tripped += 1
+    assert tripped > 0
