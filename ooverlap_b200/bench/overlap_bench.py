@@ -10,6 +10,7 @@ Ops and shapes (tp = number of ranks):
 * ``gemm_ar``       fp16 ``A[M, 8192/tp] @ B[8192, 8192/tp]^T`` summed over ranks, M in {512, 2048, 8192}
 * ``gemm_rs_norm``  bf16 M = 4096 tokens, hidden 8192, K = 28672/tp, + residual + RMSNorm (eps 1e-6) on the rank's rows
 * ``ag_gemm``       bf16 all-gather of A[4096/tp, 8192] then ``@ B[28672/tp, 8192]^T``
+* ``gemm_a2a``      baseline only (cuBLAS GEMM + NCCL all-to-all of row blocks), as in the reference; not in the default list
 
 For each it times (CUDA-graph replay, CUDA events, max over ranks): the fused kernel over a few
 communication-CTA budgets and with/without NVLS, this library's unfused GEMM + collective, and
@@ -87,6 +88,7 @@ def main() -> int:
     p.add_argument("--join", default="on", help="on | off | both: GEMM CTAs join the reduction when out of tiles")
     p.add_argument("--ms", default="512,2048,8192")
     p.add_argument("--out", default="")
+    p.add_argument("--extra", default="", help="comma list of additional arms: chunked (GemmAllReduce strategy 'chunked')")
     args = p.parse_args()
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -148,8 +150,34 @@ def main() -> int:
             op = GemmAllReduce(comm, M, N, dt)  # the library's own choice for this shape
             emit({**base, "impl": "ours_auto", "strategy": op.strategy, "us": round(timed(lambda: op(a, b), args.iters, args.warmup), 1)})
             op.release()
+            if "chunked" in args.extra:
+                # slab GEMMs on this stream, in-switch all-reduce of each finished slab on a side stream
+                op = GemmAllReduce(comm, M, N, dt, strategy="chunked")
+                if op.strategy == "chunked":
+                    us = timed(lambda: op(a, b), args.iters, args.warmup)
+                    emit({**base, "impl": "ours_chunked", "chunks": op.chunks, "us": round(us, 1),
+                          "roofline_frac": round(roof_nvls / us, 3)})
+                op.release()
             torch.cuda.synchronize()
             comm.check_status()
+
+    if "gemm_a2a" in args.ops and world > 1:
+        # Baseline only, as in the reference (BaselineImpl::GemmAll2All, src/baseline_impl.cu:178-267): cuBLAS GEMM,
+        # then every rank sends row block r of its output to rank r.  This library has no all-to-all of its own.
+        N, K, dt = 8192, 8192, torch.float16
+        for M in [int(m) for m in args.ms.split(",")]:
+            if M % world:
+                continue
+            a = torch.randn(M, K, device="cuda", generator=gen).to(dt)
+            b = (torch.randn(N, K, device="cuda", generator=gen) / K ** 0.5).to(dt)
+            out = torch.empty(M, N, dtype=dt, device="cuda")
+            recv = torch.empty_like(out)
+
+            def cublas_a2a():
+                torch.matmul(a, b.t(), out=out)
+                dist.all_to_all_single(recv, out)
+            emit(dict(op="gemm_a2a", M=M, N=N, K=K, tp=world, dtype="fp16", impl="cublas+nccl_all_to_all",
+                      us=round(timed(cublas_a2a, args.iters, args.warmup), 1)))
 
     if "gemm_rs_norm" in args.ops and 4096 % (128 * world) == 0:
         M, H, K = 4096, 8192, 28672 // world
