@@ -112,6 +112,12 @@ int oob_reduce_scatter(oob_comm* c, int dtype, int op, int algo, int in_reg, uin
 int oob_all_gather(oob_comm* c, int dtype, int algo, int out_reg, uint64_t out_off, const void* src_local,
                    void* dst_local, uint64_t count, int max_ctas, void* stream);
 
+/* All-to-all: `src_local` holds `world` chunks of count_per_peer elements; chunk j goes to rank j and lands as
+ * chunk (this rank) of its registered output buffer (world * count_per_peer elements).  No counterpart in the
+ * reference (it only has an NCCL send/recv baseline). */
+int oob_all_to_all(oob_comm* c, int dtype, int out_reg, uint64_t out_off, const void* src_local, uint64_t count_per_peer,
+                   int max_ctas, void* stream);
+
 typedef struct {
   int dtype, rows, hidden;
   float eps;

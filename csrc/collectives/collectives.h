@@ -25,6 +25,11 @@ cudaError_t launch_all_gather(const CommCtx& ctx, int dtype, int algo, const Pee
                               size_t src_local_emu_stride, void* dst_local, size_t dst_local_emu_stride,
                               size_t count, int max_ctas, cudaStream_t stream);
 
+// Rank r's chunk j (chunk_bytes each, `src_local` holds `world` of them) lands as chunk r of rank j's registered
+// `out` buffer (all_to_all.cu).
+cudaError_t launch_all_to_all(const CommCtx& ctx, const PeerPtrs& out, const void* src_local, size_t src_emu_stride,
+                              size_t chunk_bytes, int max_ctas, cudaStream_t stream);
+
 // Residual-add + RMSNorm, stand-alone and fused into the all-reduce /
 // reduce-scatter (see fused_norm.cu).
 enum NormAlgo : int {

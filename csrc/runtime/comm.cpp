@@ -830,6 +830,23 @@ int oob_all_gather(oob_comm* c, int dtype, int algo, int out_reg, uint64_t out_o
   return OOB_OK;
 }
 
+int oob_all_to_all(oob_comm* c, int dtype, int out_reg, uint64_t out_off, const void* src_local, uint64_t count_per_peer,
+                   int max_ctas, void* stream) {
+  int rc = check_comm(c);
+  if (rc != OOB_OK) return rc;
+  if (count_per_peer == 0) return OOB_OK;
+  if (dtype != OOB_F16 && dtype != OOB_BF16 && dtype != OOB_F32) return set_error(OOB_ERR_INVALID, "bad dtype");
+  if (src_local == nullptr) return set_error(OOB_ERR_INVALID, "all-to-all needs src_local");
+  const uint64_t chunk = count_per_peer * (dtype == OOB_F32 ? 4 : 2);
+  PeerPtrs out;
+  if (!c->peer_ptrs(out_reg, out_off, &out) || (out_off & 15)) return set_error(OOB_ERR_INVALID, "bad registered buffer");
+  const uint64_t src_stride = c->emulated ? chunk * c->world : 0;
+  cudaError_t e = launch_all_to_all(c->make_ctx(), out, src_local, src_stride, chunk, max_ctas,
+                                    static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "all-to-all launch");
+  return OOB_OK;
+}
+
 int oob_fused_norm(oob_comm* c, int algo, const oob_norm_args_t* a, int max_ctas, void* stream) {
   if (a == nullptr) return set_error(OOB_ERR_INVALID, "null argument");
   if (c == nullptr) {

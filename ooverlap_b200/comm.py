@@ -418,6 +418,39 @@ class Communicator:
             return result.view((self.world * shard.shape[0],) + tuple(shard.shape[1:]))
         return result
 
+    # ------------------------------------------------------------ all-to-all
+    def all_to_all(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, *, max_ctas: int = 0) -> torch.Tensor:
+        """``x`` is ``[world, ...]``: slice j goes to rank j.  Returns ``[world, ...]`` whose slice i came from rank i
+        (registered memory: ``out`` if it is registered, else a cached scratch).  Every rank must pass the same shape."""
+        if x.shape[0] != self.world:
+            raise ValueError("the first dimension must be the number of ranks")
+        if not x.is_cuda:
+            return self._cpu_all_to_all(x, out)
+        src = x if x.is_contiguous() else x.contiguous()
+        per = src[0].numel()
+        if out is not None and self._locate(out) is not None and out.is_contiguous() and out.shape == x.shape:
+            loc, result = self._locate(out), out
+        else:
+            off = self._scratch_for(("a2a", x.dtype, tuple(x.shape)), x.numel() * x.element_size())
+            loc, result = (0, off), self.view(off, tuple(x.shape), x.dtype)
+        if per:
+            _lib.check(_lib.lib().oob_all_to_all(self._h, dtype_code(x.dtype), loc[0], loc[1], ctypes.c_void_p(src.data_ptr()),
+                                                 per, max_ctas or self.config.max_ctas, ctypes.c_void_p(_current_stream_ptr())))
+        if out is not None and result is not out:
+            out.copy_(result)
+            return out
+        return result
+
+    def _cpu_all_to_all(self, x: torch.Tensor, out: Optional[torch.Tensor]) -> torch.Tensor:
+        import torch.distributed as dist
+        result = out if out is not None else torch.empty_like(x)
+        # gloo has no all_to_all: gather everybody's tensor and keep the slices addressed to this rank
+        parts = [torch.empty_like(x) for _ in range(self.world)]
+        dist.all_gather(parts, x.contiguous(), group=self._cpu_group)
+        for i in range(self.world):
+            result[i].copy_(parts[i][self.rank])
+        return result
+
     # ------------------------------------------------------ round-robin pools
     def init_round_robin_slots(self, dtype: torch.dtype, capacity_bytes: int, slot_count: int) -> None:
         """All-reduce slot ring: ``slot_count`` registered buffers of ``capacity_bytes``.  Collective."""

@@ -130,6 +130,13 @@ class EmulatedGroup:
             ctypes.c_void_p(src_local.data_ptr()) if src_local is not None else None,
             ctypes.c_void_p(dst_local.data_ptr()) if dst_local is not None else None, count, max_ctas, _stream()))
 
+    def all_to_all(self, out_off: int, count_per_peer: int, dtype: torch.dtype, src_local: torch.Tensor, *,
+                   max_ctas: int = 4) -> None:
+        """``src_local`` is ``[world (sender), world (destination), count_per_peer]``; afterwards the heap region at
+        ``out_off`` of rank j holds ``[world (sender), count_per_peer]``."""
+        _lib.check(_lib.lib().oob_all_to_all(self._h, dtype_code(dtype), 0, out_off, ctypes.c_void_p(src_local.data_ptr()),
+                                             count_per_peer, max_ctas, _stream()))
+
     def fused_norm(self, algo: int, *, x_off: int, rows: int, hidden: int, dtype: torch.dtype, weight: torch.Tensor,
                    eps: float, residual: Optional[torch.Tensor] = None, y_off: Optional[int] = None,
                    y_local: Optional[torch.Tensor] = None, res_out_off: Optional[int] = None,

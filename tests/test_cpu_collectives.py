@@ -53,6 +53,11 @@ def _rank(rank, world, port):
     assert comm.all_reduce(y.clone(), "min").tolist() == [0.0, -float(world - 1), 3.0]
     h = torch.full((5,), 1.5, dtype=torch.bfloat16)
     assert comm.all_reduce(h).tolist() == [1.5 * world] * 5
+    # all-to-all: slice j of every rank's [world, 3, 5] tensor goes to rank j
+    t = torch.arange(world * 15, dtype=torch.float32).view(world, 3, 5) + 1000 * rank
+    got = comm.all_to_all(t)
+    want = torch.stack([torch.arange(world * 15, dtype=torch.float32).view(world, 3, 5)[rank] + 1000 * r for r in range(world)])
+    report.append(("a2a", 15, float((got - want).abs().max())))
     comm.barrier()
     dist.destroy_process_group()
     return report
