@@ -25,7 +25,7 @@ import torch.nn.functional as F
 
 from ..ops import (attn_decode, fused_allreduce_rmsnorm, gemm, gemm_rope_kv_write, gemm_swiglu, rmsnorm, rope_kv_write,
                    rope_tables, silu_mul)
-from ..utils.config import env_flag
+from ..utils.config import env_flag, env_int
 from ..utils.tracing import nvtx_range
 
 
@@ -114,6 +114,11 @@ class LlamaTP:
         # RoPE + cache write and SwiGLU applied by the kernel that sums the K splits of the preceding GEMM (two
         # launches fewer per layer in a decode step).  Off unless OOB_FUSED_EPILOGUES=1.
         self.fused_epilogues = backend == "ours" and env_flag("OOB_FUSED_EPILOGUES", False)
+        # Prefill: row-parallel projections of at least OOB_PREFILL_CHUNK_MIN_ROWS tokens are computed in
+        # OOB_PREFILL_CHUNKS slabs whose all-reduce + norm overlaps the next slab's GEMM (1 = off).
+        self.prefill_chunks = max(1, env_int("OOB_PREFILL_CHUNKS", 1)) if backend == "ours" else 1
+        self.prefill_chunk_min_rows = env_int("OOB_PREFILL_CHUNK_MIN_ROWS", 4096)
+        self._side, self._joined, self._slab_events = None, None, []
 
     # ------------------------------------------------------------ primitives
     def _mm(self, x, wt):
@@ -138,6 +143,9 @@ class LlamaTP:
                 pool.advance()
             else:  # prefill chunks larger than a slot: a cached registered scratch of that shape
                 slot = self.comm.scratch_view(("rp", x.shape[0], wt.shape[0]), (x.shape[0], wt.shape[0]), x.dtype)
+            chunks = self.prefill_chunks
+            if chunks > 1 and x.shape[0] >= self.prefill_chunk_min_rows and x.shape[0] % chunks == 0:
+                return self._row_parallel_norm_chunked(x, wt, residual, norm_w, slot, chunks)
             gemm(x, wt, out=slot)
             return fused_allreduce_rmsnorm(self.comm, slot, norm_w, self.cfg.eps, residual)
         part = torch.mm(x, wt.t())
@@ -146,6 +154,37 @@ class LlamaTP:
             dist.all_reduce(part, group=self.nccl_group)
         h = part + residual
         return F.rms_norm(h, (h.shape[-1],), norm_w, self.cfg.eps), h
+
+    def _row_parallel_norm_chunked(self, x, wt, residual, norm_w, slot, chunks):
+        """Prefill-sized inputs: the rows are cut into slabs; the GEMM of slab i runs on the caller's stream while
+        the all-reduce + residual + RMSNorm of slab i - 1 runs on a side stream (a handful of CTAs next to the
+        GEMM's), so that only the first GEMM slab and the last all-reduce are exposed."""
+        if self._side is None:
+            self._side = torch.cuda.Stream()
+            self._joined = torch.cuda.Event()
+        while len(self._slab_events) < chunks:
+            self._slab_events.append(torch.cuda.Event())
+        main = torch.cuda.current_stream()
+        rows = x.shape[0] // chunks
+        # Outputs in registered memory (the two-shot all-reduce + norm broadcasts into them); one pair per shape,
+        # reused by the next projection of the same shape exactly as the unchunked path reuses its scratch.
+        shape = (x.shape[0], wt.shape[0])
+        y = self.comm.scratch_view(("rp_y",) + shape, shape, x.dtype)
+        h = self.comm.scratch_view(("rp_h",) + shape, shape, x.dtype)
+        for i in range(chunks):
+            sl = slice(i * rows, (i + 1) * rows)
+            gemm(x[sl], wt, out=slot[sl])
+            self._slab_events[i].record(main)
+            self._side.wait_event(self._slab_events[i])
+            with torch.cuda.stream(self._side):
+                ys, hs = fused_allreduce_rmsnorm(self.comm, slot[sl], norm_w, self.cfg.eps, residual[sl], out=y[sl],
+                                                 residual_out=h[sl])
+                if ys.data_ptr() != y[sl].data_ptr():  # small slabs take the one-shot form with its own outputs
+                    y[sl].copy_(ys)
+                    h[sl].copy_(hs)
+        self._joined.record(self._side)
+        main.wait_event(self._joined)
+        return y, h
 
     # --------------------------------------------------------------- forward
     def forward(self, tokens: torch.Tensor, pos, attn_mask: Optional[torch.Tensor] = None, batch0: int = 0):

@@ -29,6 +29,11 @@ def _flag(name: str, default: bool = False) -> bool:
     return v.strip().lower() not in ("", "0", "false", "no", "off")
 
 
+def env_int(name: str, default: int) -> int:
+    """Integer environment variable (unset or empty: ``default``)."""
+    return _int(name, default)
+
+
 def env_flag(name: str, default: bool = False) -> bool:
     """Boolean environment variable ("", 0, false, no, off are false)."""
     return _flag(name, default)
@@ -41,6 +46,8 @@ def env_flag(name: str, default: bool = False) -> bool:
 #   OOB_SPLITK_REDUCE_MIN_M=n  split-K: sum inside the GEMM kernel below n rows (default 1: always the second kernel)
 #   OOB_ATTN_STAGES=3          decode attention: three pipeline stages per warp (192 KiB of shared memory per CTA)
 #   OOB_FUSED_EPILOGUES=1      model runner: RoPE + cache write and SwiGLU in the split-K sum of the preceding GEMM
+#   OOB_PREFILL_CHUNKS=n       model runner, prefill: row-parallel GEMM in n slabs overlapped with the all-reduce + norm
+#   OOB_PREFILL_CHUNK_MIN_ROWS from how many tokens on (default 4096)
 #   OOB_NVTX=1                 NVTX ranges around the model runner's layers (utils/tracing.py)
 #   OOB_RUN_UNVALIDATED=1      tests: also run the GPU tests of paths that have not been run on hardware yet
 

@@ -322,3 +322,48 @@ def test_llama_tensor_parallel_matches_nccl_backend(cfg_name):
         assert kind == "ok", val
         cos, same, agree = val
         assert cos > 0.99 and same and agree
+
+
+def _rank_llama_prefill_chunks(rank, world, key, port):
+    """Prefill with the row-parallel projections cut into slabs (GEMM of slab i overlapped with the all-reduce + norm
+    of slab i - 1 on a side stream) against the same model without slabs."""
+    import torch.distributed as dist
+    from ooverlap_b200 import Communicator
+    from ooverlap_b200.models import TINY128, LlamaTP
+    torch.cuda.set_device(rank)
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    comm = Communicator(list(range(world)), rank, key, heap_bytes=512 << 20)
+    comm.init_round_robin_slots(torch.bfloat16, 1 << 20, 4)
+    os.environ["OOB_PREFILL_CHUNKS"] = "1"
+    plain = LlamaTP(TINY128, comm, rank=rank, world=world, backend="ours", max_batch=2, max_len=1100, seed=5)
+    os.environ["OOB_PREFILL_CHUNKS"], os.environ["OOB_PREFILL_CHUNK_MIN_ROWS"] = "2", "1024"
+    slabs = LlamaTP(TINY128, comm, rank=rank, world=world, backend="ours", max_batch=2, max_len=1100, seed=5)
+    assert slabs.prefill_chunks == 2 and plain.prefill_chunks == 1
+    prompts = torch.randint(0, TINY128.vocab, (2, 1024), device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+    with torch.no_grad():
+        h1 = plain.forward(prompts, 0).clone()
+        h2 = slabs.forward(prompts, 0).clone()
+    torch.cuda.synchronize()
+    cos = torch.nn.functional.cosine_similarity(h1.float(), h2.float(), dim=-1).min().item()
+    err = (h1.float() - h2.float()).abs().max().item()
+    comm.check_status()
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+    return cos, err
+
+
+@needs_multi
+@pytest.mark.skipif(os.environ.get("OOB_RUN_UNVALIDATED", "0") in ("", "0"),
+                    reason="slab-overlapped prefill not yet run on hardware; set OOB_RUN_UNVALIDATED=1")
+def test_llama_prefill_in_slabs_matches_unchunked():
+    from mp_util import free_port
+    world = 2
+    res = run_ranks(_rank_llama_prefill_chunks, world, ("mp_" + uuid.uuid4().hex[:10], free_port()), timeout=600)
+    assert len(res) == world, res
+    for r in range(world):
+        kind, val = res[r]
+        assert kind == "ok", val
+        cos, err = val
+        assert cos > 0.999 and err < 0.1, val
