@@ -201,6 +201,11 @@ int oob_bootstrap_barrier(oob_bootstrap* h);
 int oob_bootstrap_exchange_fds(oob_bootstrap* h, int my_fd, int* fds_out /* world entries */);
 int oob_bootstrap_broadcast_fd(oob_bootstrap* h, int root, int* fd);
 
+/* Byte offset (inside every rank's heap) and number of the general arrival counters of the signal pad, for tools
+ * that verify that an op left them re-armed (all zero between launches). */
+uint64_t oob_pad_counter_offset(void);
+int oob_pad_counter_count(void);
+
 /* Test hook: waits on a flag that nobody sets, with the communicator's
  * timeout, and reports through the status block (bounded-wait self test). */
 int oob_test_bounded_wait(oob_comm* c, void* stream);

@@ -1001,6 +1001,9 @@ int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream) {
   return OOB_OK;
 }
 
+uint64_t oob_pad_counter_offset(void) { return uint64_t(kPadCounterOffset) * sizeof(uint32_t); }
+int oob_pad_counter_count(void) { return kNumCounters; }
+
 int oob_gemm_plan_splits(int M, int N, int K, int max_ctas, int splits) {
   if (M <= 0 || N <= 0 || K <= 0) return 1;
   return gemm_plan_splits(M, N, K, max_ctas, splits);

@@ -122,6 +122,9 @@ def _declare(lib) -> None:
     lib.oob_fused_norm.argtypes = [P, c_int, POINTER(NormArgs), c_int, P]
     lib.oob_gemm.argtypes = [P, POINTER(GemmArgs), P]
     lib.oob_gemm_plan_splits.argtypes = [c_int, c_int, c_int, c_int, c_int]
+    lib.oob_pad_counter_offset.restype = c_uint64
+    lib.oob_pad_counter_offset.argtypes = []
+    lib.oob_pad_counter_count.argtypes = []
     lib.oob_gemm_counters_needed.argtypes = [c_int, c_int, c_int, c_int]
     lib.oob_gemm_partial_bytes.argtypes = [c_int, c_int]
     lib.oob_gemm_partial_bytes.restype = c_uint64

@@ -74,6 +74,13 @@ class EmulatedGroup:
         ptr = int(_lib.lib().oob_heap_ptr(self._h, rank, offset))
         return tensor_from_ptr(ptr, nbytes, self.device, self).view(dtype).view(shape)
 
+    def counters(self, rank: int) -> torch.Tensor:
+        """The general arrival counters of ``rank``'s signal pad (int32 view): every fused op re-arms the ones it
+        used, so they read zero between launches (the check the reference does with
+        tool/verify_signal_tile_counts.py:108+ on its tile counters)."""
+        lib = _lib.lib()
+        return self.view(int(lib.oob_pad_counter_offset()), (int(lib.oob_pad_counter_count()),), torch.int32, rank)
+
     def views(self, offset: int, shape, dtype: torch.dtype) -> list:
         return [self.view(offset, shape, dtype, r) for r in range(self.world)]
 
