@@ -91,7 +91,11 @@ def main() -> int:
                    "batch": b, "in_len": args.in_len, "out_len": args.out_len, "total_s": round(total, 4),
                    "prefill_s": round(t_prefill, 4), "decode_ms_per_token": round((total - t_prefill) / max(1, args.out_len - 1) * 1e3, 3),
                    "output_tok_s": round(b * args.out_len / total, 1), "dtype": "bf16", "data": "synthetic",
-                   "checksum": int(toks.sum().item()) % 1000003, "first": int(first[0, 0])}
+                   "checksum": int(toks.sum().item()) % 1000003, "first": int(first[0, 0]),
+                   # switches that change which kernels run (recorded so that lines from different runs can be told apart)
+                   "switches": {k: os.environ[k] for k in ("OOB_FUSED_EPILOGUES", "OOB_PREFILL_CHUNKS", "OOB_GEMM_GEMV",
+                                                           "OOB_ATTN_STAGES", "OOB_GEMM_SKINNY", "OOB_GEMM_PAIR",
+                                                           "OOB_SPLITK_REDUCE_MIN_M") if k in os.environ}}
             lines.append(rec)
             if rank == 0:
                 print(json.dumps(rec), flush=True)
