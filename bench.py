@@ -5,11 +5,16 @@ One step = the three shapes of the headline config run back to back:
 N = K = 8192.  The reported value is the latency of one step in microseconds
 (lower is better); total work is fixed as ``tp`` grows (strong scaling).
 
-``--impl ours``         fused tcgen05 GEMM + in-kernel all-reduce of this repository (default)
+``--impl ours``         fused tcgen05 GEMM + in-kernel all-reduce of this repository (default).  The same invocation
+                        also times the cuBLAS + NCCL arm below on the same operands, right after its own timed loop,
+                        and reports it as ``baseline_us`` / ``vs_baseline`` (value / baseline; below 1 = faster).
 ``--impl nccl_cublas``  torch.matmul (cuBLAS) followed by NCCL all-reduce: the path the reference's
                         BaselineImpl takes (src/baseline_impl.cu:55-106), measured on this machine
 ``--impl reference``    the unmodified reference package; it cannot be built offline, so this arm prints
                         why and exits 0
+
+Every shape's result is compared with an fp32 reference (matmul in fp32, summed over the ranks) before the timed
+loop and again after it; a mismatch fails the run.
 
 Launch: ``python bench.py`` for one GPU, or through ``python -m torch.distributed.run --nproc-per-node N``.
 """
@@ -25,6 +30,7 @@ MS = (512, 2048, 8192)
 N_DIM = 8192
 K_DIM = 8192
 ROTATE = 4  # operand sets cycled between steps so that no step finds its inputs in L2
+TOL = 1e-2  # the reference's tolerance for 16-bit results (include/ooverlap/testing/test_utils.cuh:87-110)
 
 REFERENCE_UNAVAILABLE = (
     "reference cannot be installed offline: pip reports that the reference tree has neither setup.py nor pyproject.toml, "
@@ -41,6 +47,9 @@ def parse_args():
     p.add_argument("--comm-ctas", type=int, default=int(os.environ.get("OOB_BENCH_COMM_CTAS", "0")),
                    help="communication CTAs of the fused kernel (0 = the library's choice per shape)")
     p.add_argument("--strategy", default="auto", choices=["auto", "fused", "unfused", "chunked"])
+    p.add_argument("--kernel", default=None, choices=["pair", "one_sm"], help="fused kernel (default: the library's choice)")
+    p.add_argument("--nvls", type=int, default=-1, help="fused kernel: 0 = peer loads/stores, 1/2 = through the switch, -1 = default")
+    p.add_argument("--no-baseline", action="store_true", help="skip the cuBLAS + NCCL arm of --impl ours")
     return p.parse_args()
 
 
@@ -69,7 +78,7 @@ def main() -> int:
 
     from ooverlap_b200 import Communicator
     from ooverlap_b200.ops import GemmAllReduce, gemm
-    from ooverlap_b200.utils.timing import ClockSampler
+    from ooverlap_b200.utils.timing import ClockSampler, NvmlClockSampler
 
     dtype = torch.float16
     k_local = K_DIM // world
@@ -78,86 +87,153 @@ def main() -> int:
     a_host = {m: torch.randn(m, k_local, generator=torch.Generator().manual_seed(rank * 7 + m)).to(dtype).pin_memory()
               for m in MS}
     a_dev = {m: [a_host[m].to(dev, non_blocking=True).clone() for _ in range(ROTATE)] for m in MS}
+    for m in MS:  # distinct activations per rotation slot
+        for j in range(1, ROTATE):
+            a_dev[m][j].copy_(torch.randn(m, k_local, device=dev, generator=gen).to(dtype))
     weights = [(torch.randn(N_DIM, k_local, device=dev, generator=gen) / K_DIM ** 0.5).to(dtype) for _ in range(ROTATE)]
-
-    comm = None
-    ops = {}
-    launches_per_step = 0
-    if args.impl == "ours":
-        if world > 1:
-            heap = sum(2 * m * N_DIM * 2 for m in MS) + (64 << 20)
-            comm = Communicator(list(range(world)), rank, heap_bytes=heap)
-            for m in MS:
-                ops[m] = GemmAllReduce(comm, m, N_DIM, dtype, comm_ctas=args.comm_ctas or None, strategy=args.strategy)
-        per_op = {"unfused": lambda op: 2, "chunked": lambda op: 2 * op.chunks}
-        launches_per_step = sum(per_op.get(ops[m].strategy, lambda op: 1)(ops[m]) if m in ops else 1 for m in MS)
-
-    outs = {m: torch.empty(m, N_DIM, dtype=dtype, device=dev) for m in MS}
-
-    def step(i: int, a_of=None):
-        w = weights[i % ROTATE]
-        for m in MS:
-            a = a_of[m] if a_of is not None else a_dev[m][i % ROTATE]
-            if args.impl == "ours":
-                if world > 1:
-                    outs[m] = ops[m](a, w)
-                else:
-                    gemm(a, w, out=outs[m])
-            else:
-                torch.matmul(a, w.t(), out=outs[m])
-                if world > 1:
-                    dist.all_reduce(outs[m])
 
     def fence():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- correctness spot check (outside the timed region) ----------------
+    def all_ranks_agree(ok: bool) -> bool:
+        if world == 1:
+            return ok
+        t = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
+
+    # ---- the two arms ----------------------------------------------------------------------------------------------
+    comm = None
+    ops = {}
+    fallback = {}
+    outs = {m: torch.empty(m, N_DIM, dtype=dtype, device=dev) for m in MS}
+    base_outs = {m: torch.empty(m, N_DIM, dtype=dtype, device=dev) for m in MS}
+
+    def make_op(m, strategy):
+        return GemmAllReduce(comm, m, N_DIM, dtype, comm_ctas=args.comm_ctas or None, strategy=strategy, kernel=args.kernel,
+                             use_nvls=None if args.nvls < 0 else args.nvls)
+
+    if args.impl == "ours" and world > 1:
+        heap = sum(2 * m * N_DIM * 2 for m in MS) + (64 << 20)
+        comm = Communicator(list(range(world)), rank, heap_bytes=heap)
+        for m in MS:
+            ops[m] = make_op(m, args.strategy)
+
+    def ours_one(m, a, w):
+        if world > 1:
+            outs[m] = ops[m](a, w)
+        else:
+            gemm(a, w, out=outs[m])
+
+    def base_one(m, a, w):
+        torch.matmul(a, w.t(), out=base_outs[m])
+        if world > 1:
+            dist.all_reduce(base_outs[m])
+
+    main_one, main_outs = (ours_one, outs) if args.impl == "ours" else (base_one, base_outs)
+
+    def step(i: int, one=None, a_of=None):
+        one = one or main_one
+        w = weights[i % ROTATE]
+        for m in MS:
+            one(m, a_of[m] if a_of is not None else a_dev[m][i % ROTATE], w)
+
+    # ---- correctness: every shape against fp32, before and after the timed loop ---------------------------------
+    def verify(i: int, result_of, shapes=MS):
+        """Compares the results of step i (already run and synchronised).  Returns {m: max abs error} of failures."""
+        bad = {}
+        for m in shapes:
+            ref = a_dev[m][i % ROTATE].float() @ weights[i % ROTATE].float().t()
+            if world > 1:
+                dist.all_reduce(ref)
+            err = (result_of(m).float() - ref).abs().max().item()
+            if not err <= TOL * max(1.0, ref.abs().max().item()):
+                bad[m] = err
+            del ref
+        return bad
+
     step(0)
     fence()
-    ref = a_dev[512][0].float() @ weights[0].float().t()
-    if world > 1:
-        dist.all_reduce(ref)
-    err = (outs[512].float() - ref).abs().max().item()
-    if not err <= 2e-2 * max(1.0, ref.abs().max().item()):
-        print(f"rank {rank}: result check failed, max abs err {err}", file=sys.stderr)
-        return 1
+    bad = verify(0, lambda m: outs[m] if args.impl == "ours" else base_outs[m])
+    for m in MS:
+        m_bad = not all_ranks_agree(m not in bad)
+        if not m_bad:
+            continue
+        if args.impl == "ours" and world > 1 and ops[m].strategy != "unfused":
+            # The fused kernel gave a wrong result for this shape: say so, and measure the unfused pair instead.
+            fallback[str(m)] = f"{ops[m].strategy} strategy failed the result check (max abs err {bad.get(m)}); unfused used"
+            print(f"rank {rank}: M={m}: {fallback[str(m)]}", file=sys.stderr)
+            ops[m].release()
+            ops[m] = make_op(m, "unfused")
+            ours_one(m, a_dev[m][0], weights[0])
+            fence()
+            if not all_ranks_agree(not verify(0, lambda mm: outs[mm], shapes=(m,))):
+                print(f"rank {rank}: M={m}: result check failed with the unfused strategy as well", file=sys.stderr)
+                return 1
+        else:
+            print(f"rank {rank}: M={m}: result check failed, max abs err {bad.get(m)}", file=sys.stderr)
+            return 1
 
-    # ---- device-timed arm ---------------------------------------------------
-    # The clock sampler runs from the warm-up on (nvidia-smi needs a moment to start) and is stopped right
-    # after the timed loop, so its samples are taken under this load.
-    sampler = ClockSampler(local_rank, period_ms=50).start() if rank == 0 else None
-    for i in range(max(3, args.warmup)):
+    per_op = {"unfused": lambda op: 2, "chunked": lambda op: 2 * op.chunks}
+    launches_per_step = 0
+    if args.impl == "ours":
+        launches_per_step = sum(per_op.get(ops[m].strategy, lambda op: 1)(ops[m]) if m in ops else 1 for m in MS)
+
+    # ---- device-timed arm --------------------------------------------------------------------------------------------
+    # The clock sampler (NVML queries from a thread, every 2 ms; nvidia-smi when NVML is not importable) runs from
+    # the warm-up on; only samples taken inside the timed region are summarised.
+    sampler = None
+    if rank == 0:
+        sampler = NvmlClockSampler(local_rank, period_ms=2.0)
+        if not sampler.available:
+            sampler = ClockSampler(local_rank, period_ms=10)
+        sampler.start()
+    warmup = max(3, args.warmup)
+    for i in range(warmup):
         step(i)
     fence()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    per_shape = {m: 0.0 for m in MS}
+    if sampler is not None and hasattr(sampler, "begin"):
+        sampler.begin()
     start.record()
     for i in range(args.steps):
         step(i)
     end.record()
     fence()
+    if sampler is not None and hasattr(sampler, "end"):
+        sampler.end()
     total_ms = start.elapsed_time(end)
     clocks = sampler.stop() if sampler is not None else None
 
+    bad_after = verify(args.steps - 1, lambda m: main_outs[m])
+    if not all_ranks_agree(not bad_after):
+        print(f"rank {rank}: result check after the timed loop failed: {bad_after}", file=sys.stderr)
+        return 1
+
+    # ---- comparison arm: cuBLAS + NCCL on the same operands, same steps and warm-up -------------------------------
+    base_ms = None
+    if args.impl == "ours" and not args.no_baseline:
+        for i in range(warmup):
+            step(i, base_one)
+        fence()
+        bs, be = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        bs.record()
+        for i in range(args.steps):
+            step(i, base_one)
+        be.record()
+        fence()
+        base_ms = bs.elapsed_time(be)
+
     # per-shape breakdown (separate pass, informational)
+    per_shape = {m: 0.0 for m in MS}
     for m in MS:
-        w = weights[0]
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
         fence()
         ev[0].record()
         for i in range(args.steps):
-            a, w = a_dev[m][i % ROTATE], weights[i % ROTATE]
-            if args.impl == "ours":
-                if world > 1:
-                    ops[m](a, w)
-                else:
-                    gemm(a, w, out=outs[m])
-            else:
-                torch.matmul(a, w.t(), out=outs[m])
-                if world > 1:
-                    dist.all_reduce(outs[m])
+            main_one(m, a_dev[m][i % ROTATE], weights[i % ROTATE])
         ev[1].record()
         fence()
         per_shape[m] = ev[0].elapsed_time(ev[1]) / args.steps * 1e3
@@ -169,9 +245,9 @@ def main() -> int:
     def e2e_step(i: int):
         for m in MS:
             stage[m].copy_(a_host[m], non_blocking=True)
-        step(i, stage)
+        step(i, None, stage)
         for m in MS:
-            back[m].copy_(outs[m][0], non_blocking=True)
+            back[m].copy_(main_outs[m][0], non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for i in range(3):
@@ -195,26 +271,41 @@ def main() -> int:
         return float(t.item())
 
     total_ms = rank_max(total_ms)
+    if base_ms is not None:
+        base_ms = rank_max(base_ms)
     e2e_ms = rank_max(max(e2e_ms, e2e_wall_ms))
     per_shape = {m: rank_max(v) for m, v in per_shape.items()}
     status_ok = True
     if comm is not None:
-        comm.check_status()
+        try:
+            comm.check_status()
+        except Exception as e:  # a kernel gave up waiting: the numbers above are not a measurement
+            status_ok = False
+            print(f"rank {rank}: device status: {e}", file=sys.stderr)
+    status_ok = all_ranks_agree(status_ok)
 
     if rank == 0:
         ms_per_step = total_ms / args.steps
+        value = ms_per_step * 1e3
         flops = sum(2.0 * m * N_DIM * K_DIM for m in MS)
+        baseline_us = base_ms / args.steps * 1e3 if base_ms is not None else None
         line = {
             "metric": "gemm_allreduce_overlap_latency_us",
-            "value": round(ms_per_step * 1e3, 2),
+            "value": round(value, 2),
             "unit": "us per step (M=512,2048,8192 back to back)",
             "n_gpus": world,
             "steps": args.steps,
-            "warmup": max(3, args.warmup),
+            "warmup": warmup,
             "ms_per_step": round(ms_per_step, 5),
             "higher_is_better": False,
             "scaling": "strong",
-            "vs_baseline": None,
+            # No published number exists for this metric; the comparison point is the reference's own baseline path
+            # (cuBLAS GEMM + NCCL all-reduce) timed in this same invocation.  value / baseline: below 1 = faster.
+            "vs_baseline": round(value / baseline_us, 4) if baseline_us else None,
+            "baseline_us": round(baseline_us, 2) if baseline_us else None,
+            "baseline": "torch.matmul (cuBLAS) + NCCL all-reduce, same operands, steps and warm-up, timed right after "
+                        "the main loop" if baseline_us else None,
+            "speedup_vs_baseline": round(baseline_us / value, 3) if baseline_us else None,
             "dtype": "fp16",
             "data": "synthetic (A ~ N(0,1), B ~ N(0,1/K), seeded per rank; random-init weights)",
             "impl": args.impl,
@@ -222,7 +313,10 @@ def main() -> int:
                        "global_batch": sum(MS), "seq_len": 1, "parallelism": f"tp{world}",
                        "l2": f"{ROTATE} operand sets rotated between steps; per-step working set exceeds the 126 MB L2",
                        "strategy": {str(m): (ops[m].strategy if m in ops else "gemm") for m in MS},
-                       "comm_ctas": {str(m): (ops[m].comm_ctas if m in ops and ops[m].strategy == "fused" else 0) for m in MS}},
+                       "comm_ctas": {str(m): (ops[m].comm_ctas if m in ops and ops[m].strategy == "fused" else 0) for m in MS},
+                       "fallback": fallback or None},
+            "verified": f"all {len(MS)} shapes against an fp32 reference before and after the timed loop, tolerance "
+                        f"{TOL} x max(1, |ref|max)",
             "per_shape_us": {str(m): round(v, 2) for m, v in per_shape.items()},
             "tflops_aggregate": round(flops / (ms_per_step * 1e-3) / 1e12, 1),
             "clocks": clocks,
@@ -238,7 +332,7 @@ def main() -> int:
         if comm is not None:
             comm.close()
         dist.destroy_process_group()
-    return 0
+    return 0 if status_ok else 1
 
 
 if __name__ == "__main__":

@@ -163,13 +163,16 @@ typedef struct {
   int splits;   /* plain mode: K splits per tile; 0 = chosen from the shape, 1 = off */
   int no_join;  /* fused AR / RS: 1 = only the dedicated communication CTAs reduce */
   void* trace;  /* optional device buffer, 8 x uint64 per CTA: globaltimer stamps of the kernel's phases */
-  int pair;     /* plain mode: 0 = two-SM kernel when the shape suits it, 1 = whenever possible, -1 = never */
+  int pair;     /* 0 = two-SM kernel (CTA pairs, 256x256 tiles) when the shape suits it, 1 = whenever possible,
+                   -1 = never; plain and fused modes (fused GEMM->AR on pairs reduces C in place and ignores partial_*) */
   int splitk_reduce; /* split-K: 0 / 1 = separate reduction kernel, -1 = sum inside the GEMM kernel */
   int skinny;   /* plain mode, M <= 128: 1 = weight-streaming stream-K kernel; 0 / -1 = tiled kernels */
   int epilogue; /* plain mode, split problems only (oob_gemm_plan_splits > 1): OOB_EPILOGUE_* applied by the kernel
                    that sums the K splits */
   const void* epilogue_args; /* host pointer: oob_gemm_epilogue_swiglu_t or oob_rope_args_t (oob_model.h) */
   int gemv;     /* plain mode, M <= 4: 1 = CUDA-core streaming kernel, 0 = only with OOB_GEMM_GEMV=1, -1 = never */
+  int stream_k; /* two-SM kernel, plain and AG modes: stream-K tail; 0 = when it pays for the shape, 1 = whenever the
+                   tile count leaves a remainder, -1 = never */
 } oob_gemm_args_t;
 #define OOB_EPILOGUE_NONE 0
 #define OOB_EPILOGUE_SWIGLU 1  /* N = 2F columns [gate | up]; C is [M, F] = silu(gate) * up */
@@ -182,6 +185,14 @@ int oob_gemm_plan_splits(int M, int N, int K, int max_ctas, int splits);
 /* c may be NULL for OOB_GEMM_PLAIN. */
 int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream);
 int oob_gemm_counters_needed(int mode, int M, int N, int world);
+/* Allocates, on the current device, the scratch memory that later oob_gemm calls would otherwise allocate on first
+ * use: the stream-K workspace of the two-SM kernel (fixed size) and a split-K workspace of at least splitk_bytes
+ * (0 = none; see oob_gemm_splitk_bytes).  Call it before capturing a CUDA graph: an allocation cannot happen during
+ * capture, and oob_gemm then fails with OOB_ERR_UNSUPPORTED instead of growing the workspace.  Workspaces handed
+ * out earlier are never freed or moved, so graphs that were captured with them stay valid. */
+int oob_gemm_reserve_workspace(uint64_t splitk_bytes);
+/* Split-K workspace bytes a plain GEMM of this shape needs (0 when it is not split). */
+uint64_t oob_gemm_splitk_bytes(int M, int N, int K, int max_ctas, int splits);
 uint64_t oob_gemm_partial_bytes(int M, int N);
 
 /* Tuning policy (size -> algorithm, CTA budget). */
@@ -205,6 +216,12 @@ int oob_bootstrap_broadcast_fd(oob_bootstrap* h, int root, int* fd);
  * that verify that an op left them re-armed (all zero between launches). */
 uint64_t oob_pad_counter_offset(void);
 int oob_pad_counter_count(void);
+
+/* Test hook (host only): work items of the two-SM GEMM's schedule for a problem on `pairs` CTA pairs, nine integers
+ * per item: pair, schedule position, m block, n block, first K block, end K block, stream-K workspace slot (-1 for
+ * whole tiles, -2 for the part that starts a tile: its pair owns the tile and parks nothing), parts of the tile, first
+ * pair of the tile.  Returns the item count, -1 when cap is too small. */
+int oob_test_pair_schedule(int mode, int M, int N, int K, int pairs, int stream_k, int world, int rank, int* out, int cap);
 
 /* Test hook: waits on a flag that nobody sets, with the communicator's
  * timeout, and reports through the status block (bounded-wait self test). */

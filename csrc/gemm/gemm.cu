@@ -3,15 +3,15 @@
 #include <cstdlib>
 #include <mutex>
 #include <unordered_map>
+#include <vector>
 
 #include "../runtime/driver_api.h"
 #include "gemm_kernel.cuh"
+#include "gemm_pair.h"
 #include "splitk_epilogues.cuh"
 
 namespace oob {
 
-// gemm_pair.cu
-cudaError_t launch_gemm_pair(const GemmArgs& a, DeviceStatus* status, cudaStream_t stream, gemm_detail::TmapFn make_tmap);
 // gemv.cu
 bool gemv_supported(const GemmArgs& a);
 cudaError_t launch_gemv(const GemmArgs& a, int sms, cudaStream_t stream);
@@ -63,35 +63,54 @@ bool make_tmap_cached(CUtensorMap* out, const void* p, uint64_t rows, uint64_t c
   return true;
 }
 
-// Library-owned scratch, one per device, grown on demand: the split-K workspace and the tensor-map table of the
-// single-GPU emulation.
+// Library-owned scratch.  One split-K workspace per device, shared by every launch on that device: GEMMs that use it
+// (split problems, the weight-streaming kernel) must not overlap on the GPU, i.e. they run on one stream or are
+// ordered by events; the same holds for the stream-K workspace of the two-SM kernel.  A workspace that has been handed
+// out is never freed or moved (a CUDA graph captured earlier keeps launching with its address): when a larger one is
+// needed a new block is allocated and the old one stays alive.  Nothing can be allocated while the stream is being
+// captured: the caller reserves beforehand (gemm_reserve_splitk / oob_gemm_reserve_workspace).
+struct SplitkBlock {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
 struct DeviceScratch {
-  void* splitk = nullptr;
-  size_t splitk_bytes = 0;
+  SplitkBlock splitk;          // current block
+  std::vector<void*> retired;  // outgrown blocks, kept alive for launches in flight and captured graphs
   CUtensorMap* emu_maps = nullptr;
 };
 DeviceScratch g_scratch[64];
 std::mutex g_scratch_mu;
 
+// Caller holds g_scratch_mu.  `stream` orders the clearing of the arrival counters before the launch that follows
+// (null: cleared synchronously).
+cudaError_t grow_splitk(DeviceScratch& s, size_t need, cudaStream_t stream, bool sync_clear) {
+  const size_t cap = need + (need >> 2);
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, cap);
+  if (e != cudaSuccess) return e;
+  e = sync_clear ? cudaMemset(p, 0, kSplitkCounterBytes) : cudaMemsetAsync(p, 0, kSplitkCounterBytes, stream);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return e;
+  }
+  if (s.splitk.ptr) s.retired.push_back(s.splitk.ptr);
+  s.splitk.ptr = p;
+  s.splitk.bytes = cap;
+  return cudaSuccess;
+}
+
 cudaError_t ensure_splitk(int dev, size_t need, cudaStream_t stream, void** out) {
   std::lock_guard<std::mutex> g(g_scratch_mu);
   DeviceScratch& s = g_scratch[dev & 63];
-  if (s.splitk_bytes < need) {
-    // Growing: earlier launches may still use the old block.
-    cudaError_t e = cudaDeviceSynchronize();
+  if (s.splitk.bytes < need) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (stream != nullptr && cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+      return cudaErrorStreamCaptureUnsupported;  // cannot allocate now; see oob_gemm_reserve_workspace
+    (void)cudaGetLastError();
+    cudaError_t e = grow_splitk(s, need, stream, false);
     if (e != cudaSuccess) return e;
-    if (s.splitk) cudaFree(s.splitk);
-    s.splitk = nullptr;
-    s.splitk_bytes = 0;
-    size_t cap = need + (need >> 2);
-    e = cudaMalloc(&s.splitk, cap);
-    if (e != cudaSuccess) return e;
-    e = cudaMemset(s.splitk, 0, kSplitkCounterBytes);
-    if (e != cudaSuccess) return e;
-    s.splitk_bytes = cap;
   }
-  (void)stream;
-  *out = s.splitk;
+  *out = s.splitk.ptr;
   return cudaSuccess;
 }
 
@@ -171,10 +190,25 @@ cudaError_t launch_fmt(const CommCtx& ctx, const GemmArgs& a, cudaStream_t strea
 
 }  // namespace
 
-cudaError_t gemm_library_workspace(size_t bytes, void** out) {
+cudaError_t gemm_library_workspace(size_t bytes, cudaStream_t stream, void** out) {
   int dev = 0;
   cudaGetDevice(&dev);
-  return ensure_splitk(dev, bytes, nullptr, out);
+  return ensure_splitk(dev, bytes, stream, out);
+}
+
+cudaError_t gemm_reserve_splitk(size_t bytes) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> g(g_scratch_mu);
+  DeviceScratch& s = g_scratch[dev & 63];
+  if (bytes == 0 || s.splitk.bytes >= bytes) return cudaSuccess;
+  return grow_splitk(s, bytes, nullptr, true);
+}
+
+size_t gemm_splitk_bytes(int M, int N, int K, int max_ctas, int splits) {
+  const int s = gemm_plan_splits(M, N, K, max_ctas, splits);
+  return s > 1 ? gemm_detail::splitk_workspace_bytes(M, N, s) : 0;
 }
 
 bool encode_tmap_2d(CUtensorMap* out, const void* p, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
@@ -193,8 +227,12 @@ bool encode_tmap_2d(CUtensorMap* out, const void* p, uint64_t rows, uint64_t col
 int gemm_counters_needed(int mode, int M, int N, int world) {
   const int tiles_m = (M + kTileM - 1) / kTileM, tiles_n = (N + kTileN - 1) / kTileN;
   switch (mode) {
-    case kGemmAr:
-      return (tiles_m * tiles_n + world - 1) / world + 1;  // per-tile arrivals + ticket
+    case kGemmAr: {
+      // one-SM kernel: per-tile arrivals + ticket; two-SM kernel: one arrival counter per owned 128x256 half tile
+      const int one_sm = (tiles_m * tiles_n + world - 1) / world + 1;
+      const int pair = (2 * ((M + 2 * kTileM - 1) / (2 * kTileM)) * tiles_n + world - 1) / world;
+      return one_sm > pair ? one_sm : pair;
+    }
     case kGemmRsNorm:
       return 2 * ((M / world + kTileM - 1) / kTileM) + 1;  // arrivals + finished items per row block + ticket
     case kGemmAg:
@@ -301,12 +339,28 @@ cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& args, cudaStream_t s
     }();
     const bool pair_auto = a.M > kTileM && !pair_env_off;
     if (pair_ok && (a.pair > 0 || (a.pair == 0 && pair_auto))) {
-      e = launch_gemm_pair(a, ctx.status, stream, make_tmap_cached);
+      e = launch_gemm_pair(ctx, a, stream, make_tmap_cached, nullptr);
       if (e != cudaErrorNotSupported) return e;
       cudaGetLastError();
     }
   } else {
     a.splits = 1;
+    // Fused modes on CTA pairs: same mainloop as the plain two-SM kernel, communication in clusters of the same
+    // launch.  pair = 0 follows OOB_FUSED_PAIR (default on).
+    static const bool fused_pair_env_off = [] {
+      const char* v = getenv("OOB_FUSED_PAIR");
+      return v != nullptr && v[0] == '0';
+    }();
+    if ((a.pair > 0 || (a.pair == 0 && !fused_pair_env_off)) && gemm_pair_supported(ctx, a)) {
+      CUtensorMap* emu_maps = nullptr;
+      if (ctx.emu_table != nullptr) {
+        e = ensure_emu_maps(dev, &emu_maps);
+        if (e != cudaSuccess) return e;
+      }
+      e = launch_gemm_pair(ctx, a, stream, make_tmap_cached, emu_maps);
+      if (e != cudaErrorNotSupported) return e;
+      cudaGetLastError();
+    }
   }
   if (a.mode == kGemmAr || a.mode == kGemmRsNorm) {
     e = ensure_push_maps(ctx, a, &a.push_maps);

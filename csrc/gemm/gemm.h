@@ -70,9 +70,13 @@ struct GemmArgs {
   int gemv;
   int epilogue;               // 0 = none, 1 = SwiGLU (oob_gemm_epilogue_swiglu_t), 2 = RoPE + KV write (oob_rope_args_t)
   const void* epilogue_args;
-  // Plain mode: 0 = the two-SM kernel (256x256 tiles on CTA pairs) when the shape suits it, 1 = always when
-  // possible, -1 = never.
+  // 0 = the two-SM kernel (256x256 tiles on CTA pairs) when the shape suits it, 1 = always when possible,
+  // -1 = never (the one-SM kernel with 128x256 tiles).  Applies to the plain GEMM and to the fused modes.
   int pair;
+  // Two-SM kernel, plain and AG modes: stream-K tail (the last wave and the remainder are cut along K so that no
+  // pair idles; partial accumulators meet in a library-owned workspace).  0 = when it pays for the shape, 1 = whenever
+  // the tile count leaves a remainder, -1 = never.
+  int stream_k;
   // Plain mode, M <= 128: 1 = the weight-streaming kernel (gemm_skinny.cu), 0 / -1 = the tiled kernels (0 follows
   // OOB_GEMM_SKINNY=1 for M <= 16).
   int skinny;
@@ -106,6 +110,12 @@ int gemm_counters_needed(int mode, int M, int N, int world);
 
 // Split count the plain GEMM picks for a shape on `sms` SMs (1 = no split).
 int gemm_auto_splits(int M, int N, int K, int sms);
+
+// Split-K workspace: bytes a plain GEMM needs (0 = not split), and an ahead-of-time reservation on the current device
+// (see oob_gemm_reserve_workspace in the C API).
+size_t gemm_splitk_bytes(int M, int N, int K, int max_ctas, int splits);
+cudaError_t gemm_reserve_splitk(size_t bytes);
+cudaError_t gemm_pair_reserve_workspace();
 
 // Split count launch_gemm uses for a plain GEMM given the caller's `splits` (0 = by shape) and CTA budget.
 int gemm_plan_splits(int M, int N, int K, int max_ctas, int splits);

@@ -24,7 +24,7 @@
 namespace oob {
 
 // gemm.cu: the library-owned workspace (arrival counters, zero between calls, then partials).
-cudaError_t gemm_library_workspace(size_t bytes, void** out);
+cudaError_t gemm_library_workspace(size_t bytes, cudaStream_t stream, void** out);
 
 namespace gemm_skinny {
 
@@ -334,7 +334,7 @@ cudaError_t launch_fmt(const GemmArgs& a, DeviceStatus* status, cudaStream_t str
   p.tmem_cols = cols;
   if (size_t(p.num_tiles) * 4 * sizeof(uint32_t) > kSplitkCounterBytes) return cudaErrorInvalidValue;
   void* ws = nullptr;
-  cudaError_t e = gemm_library_workspace(kSplitkCounterBytes + size_t(grid) * 2 * p.Mp * kRowsW * sizeof(float), &ws);
+  cudaError_t e = gemm_library_workspace(kSplitkCounterBytes + size_t(grid) * 2 * p.Mp * kRowsW * sizeof(float), stream, &ws);
   if (e != cudaSuccess) return e;
   p.counters = static_cast<uint32_t*>(ws);
   p.partials = splitk_partials(ws);

@@ -10,6 +10,7 @@
 #include "../api/oob_model.h"
 #include "../collectives/collectives.h"
 #include "../gemm/gemm.h"
+#include "../gemm/gemm_pair.h"
 #include "driver_api.h"
 #include "errors.h"
 
@@ -944,6 +945,7 @@ int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream) {
   g.skinny = a->skinny;
   g.splitk_reduce = a->splitk_reduce;
   g.gemv = a->gemv;
+  g.stream_k = a->stream_k;
   g.epilogue = a->epilogue;
   g.epilogue_args = a->epilogue_args;
   if (a->epilogue != OOB_EPILOGUE_NONE) {
@@ -997,6 +999,11 @@ int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream) {
       return set_error(OOB_ERR_INVALID, "bad gathered-A buffer");
   }
   cudaError_t e = launch_gemm(ctx, g, static_cast<cudaStream_t>(stream));
+  if (e == cudaErrorStreamCaptureUnsupported) {
+    (void)cudaGetLastError();
+    return set_error(OOB_ERR_UNSUPPORTED, "this GEMM needs a larger scratch workspace and the stream is being captured: "
+                                          "call oob_gemm_reserve_workspace before the capture");
+  }
   if (e != cudaSuccess) return cuda_fail(e, "GEMM launch");
   return OOB_OK;
 }
@@ -1010,6 +1017,24 @@ int oob_gemm_plan_splits(int M, int N, int K, int max_ctas, int splits) {
 }
 
 int oob_gemm_counters_needed(int mode, int M, int N, int world) { return gemm_counters_needed(mode, M, N, world); }
+
+int oob_gemm_reserve_workspace(uint64_t splitk_bytes) {
+  cudaError_t e = gemm_pair_reserve_workspace();
+  if (e != cudaSuccess) return cuda_fail(e, "reserving the stream-K workspace");
+  e = gemm_reserve_splitk(splitk_bytes);
+  if (e != cudaSuccess) return cuda_fail(e, "reserving the split-K workspace");
+  return OOB_OK;
+}
+
+int oob_test_pair_schedule(int mode, int M, int N, int K, int pairs, int stream_k, int world, int rank, int* out, int cap) {
+  if (M <= 0 || N <= 0 || K <= 0 || pairs < 1 || out == nullptr) return -1;
+  return pair_schedule_dump(mode, M, N, K, pairs, stream_k, world, rank, out, cap);
+}
+
+uint64_t oob_gemm_splitk_bytes(int M, int N, int K, int max_ctas, int splits) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  return gemm_splitk_bytes(M, N, K, max_ctas, splits);
+}
 
 uint64_t oob_gemm_partial_bytes(int M, int N) {
   // One slice per (tile, source rank) in the owner's buffer: tiles rounded up to a whole number per rank.

@@ -17,7 +17,7 @@ from ._lib import DeviceTimeout, OobError  # noqa: F401
 from .comm import Communicator, SlotPool  # noqa: F401
 from .emulated import EmulatedGroup  # noqa: F401
 
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 
 
 def build(force: bool = False):

@@ -70,7 +70,7 @@ class GemmArgs(Structure):
                 ("weight", c_void_p), ("eps", c_float), ("y_local", c_void_p), ("res_out_local", c_void_p),
                 ("rs_emu_stride", c_uint64), ("a_full_reg", c_int), ("a_full_off", c_uint64), ("use_nvls", c_int),
                 ("splits", c_int), ("no_join", c_int), ("trace", c_void_p), ("pair", c_int), ("splitk_reduce", c_int), ("skinny", c_int), ("epilogue", c_int),
-                ("epilogue_args", c_void_p), ("gemv", c_int)]
+                ("epilogue_args", c_void_p), ("gemv", c_int), ("stream_k", c_int)]
 
 
 class SwigluEpilogue(Structure):
@@ -126,6 +126,10 @@ def _declare(lib) -> None:
     lib.oob_pad_counter_offset.argtypes = []
     lib.oob_pad_counter_count.argtypes = []
     lib.oob_gemm_counters_needed.argtypes = [c_int, c_int, c_int, c_int]
+    lib.oob_test_pair_schedule.argtypes = [c_int] * 8 + [POINTER(c_int), c_int]
+    lib.oob_gemm_reserve_workspace.argtypes = [c_uint64]
+    lib.oob_gemm_splitk_bytes.argtypes = [c_int, c_int, c_int, c_int, c_int]
+    lib.oob_gemm_splitk_bytes.restype = c_uint64
     lib.oob_gemm_partial_bytes.argtypes = [c_int, c_int]
     lib.oob_gemm_partial_bytes.restype = c_uint64
     lib.oob_rope_kv_write.argtypes = [POINTER(RopeArgs), P]

@@ -56,7 +56,8 @@ def timed(fn, iters, warmup, flush):
     return ms[len(ms) // 2]
 
 
-OPS = ["gemm", "gemm_splitk", "cublas", "rmsnorm", "allreduce", "gemm_ar", "attn_decode", "sdpa_decode", "silu_mul", "rope"]
+OPS = ["gemm", "gemm_splitk", "cublas", "rmsnorm", "allreduce", "reduce_scatter", "all_gather", "fused_norm_ar", "gemm_ar",
+       "gemm_rs", "ag_gemm", "attn_decode", "sdpa_decode", "silu_mul", "rope"]
 
 
 def main() -> int:
@@ -72,6 +73,11 @@ def main() -> int:
     p.add_argument("--bytes", type=int, default=64 << 20)
     p.add_argument("--splits", type=int, default=0)
     p.add_argument("--pair", type=int, default=0, help="plain GEMM: 1 = two-SM kernel, -1 = one-SM kernel, 0 = auto")
+    p.add_argument("--stream-k", type=int, default=0, help="two-SM kernel: 1 = stream-K tail, -1 = whole tiles only, 0 = auto")
+    p.add_argument("--kernel", default=None, choices=["pair", "one_sm"], help="fused ops: two-SM or one-SM kernel")
+    p.add_argument("--algo", type=int, default=1, help="emulated collectives: algorithm number of the C API")
+    p.add_argument("--ctas", type=int, default=0, help="emulated collectives: CTAs per rank (0 = 148 / world)")
+    p.add_argument("--comm-ctas", type=int, default=4, help="fused ops: communication CTAs per rank")
     p.add_argument("--skinny", type=int, default=0, help="plain GEMM, M <= 128: 1 = weight-streaming kernel, -1 = never")
     p.add_argument("--splitk-reduce", type=int, default=0, help="split-K sum: 1 = second kernel, -1 = inside the GEMM kernel")
     p.add_argument("--gemv", type=int, default=0, help="plain GEMM, M <= 4: 1 = CUDA-core streaming kernel")
@@ -114,8 +120,9 @@ def probe(args, flush) -> dict:
         else:
             splits = args.splits if args.op == "gemm_splitk" else 1
             rec["pair"], rec["skinny"], rec["splitk_reduce"], rec["gemv"] = args.pair, args.skinny, args.splitk_reduce, args.gemv
+            rec["stream_k"] = args.stream_k
             fn = lambda: gemm(a, b, out=out, splits=splits, pair=args.pair, skinny=args.skinny,  # noqa: E731
-                              splitk_reduce=args.splitk_reduce, gemv=args.gemv)
+                              splitk_reduce=args.splitk_reduce, gemv=args.gemv, stream_k=args.stream_k)
         ms = timed(fn, args.iters, args.warmup, flush)
         tflops = 2.0 * args.m * args.n * args.k / (ms * 1e-3) / 1e12
         gbs = (args.m * args.k + args.n * args.k + args.m * args.n) * 2 / (ms * 1e-3) / 1e9
@@ -172,17 +179,88 @@ def probe(args, flush) -> dict:
         off = g.alloc(args.bytes)
         for r in range(args.world):
             g.view(off, (n,), dt, r).fill_(0.001 * (r + 1))
-        ms = timed(lambda: g.all_reduce(off, n, dt, algo=_lib.AR_TWOSHOT_P2P, out_off=off, max_ctas=148 // args.world),
-                   args.iters, args.warmup, flush)
+        ctas = args.ctas or 148 // args.world
+        if args.algo in (_lib.AR_ONESHOT_P2P,):
+            out_local = torch.empty(args.world, n, device="cuda", dtype=dt)
+            fn = lambda: g.all_reduce(off, n, dt, algo=args.algo, out_local=out_local, max_ctas=ctas)  # noqa: E731
+        else:
+            fn = lambda: g.all_reduce(off, n, dt, algo=_lib.AR_TWOSHOT_P2P, out_off=off, max_ctas=ctas)  # noqa: E731
+        rec["algo"], rec["ctas"] = args.algo, ctas
+        ms = timed(fn, args.iters, args.warmup, flush)
         g.check_status()
         # every emulated rank reads all ranks' shards and writes them back to all ranks (all on this GPU)
         gbs = 2.0 * args.world * args.bytes / (ms * 1e-3) / 1e9
         rec.update(world=args.world, bytes=args.bytes, us=round(ms * 1e3, 2), local_traffic_gbs=round(gbs, 1),
                    frac_of_peak_hbm=round(gbs / bw_peak, 3))
         g.close()
+    elif args.op in ("reduce_scatter", "all_gather"):
+        g = EmulatedGroup(args.world, heap_bytes=args.bytes + (32 << 20))
+        n = args.bytes // 2
+        shard = (n + args.world - 1) // args.world
+        off = g.alloc(args.bytes)
+        for r in range(args.world):
+            g.view(off, (n,), dt, r).fill_(0.001 * (r + 1))
+        local = torch.full((args.world, shard), 0.5, device="cuda", dtype=dt)
+        ctas = args.ctas or 148 // args.world
+        if args.op == "reduce_scatter":
+            fn = lambda: g.reduce_scatter(off, n, dt, local, algo=_lib.RS_P2P, max_ctas=ctas)  # noqa: E731
+            traffic = args.world * args.bytes + args.bytes  # every rank reads its shard of all ranks, writes its shard
+        else:
+            fn = lambda: g.all_gather(off, n, dt, src_local=local, algo=_lib.AG_PUSH_P2P, max_ctas=ctas)  # noqa: E731
+            traffic = args.bytes + args.world * args.bytes  # every rank reads its shard, writes it to all ranks
+        ms = timed(fn, args.iters, args.warmup, flush)
+        g.check_status()
+        gbs = traffic / (ms * 1e-3) / 1e9
+        rec.update(world=args.world, bytes=args.bytes, ctas=ctas, us=round(ms * 1e3, 2), local_traffic_gbs=round(gbs, 1),
+                   frac_of_peak_hbm=round(gbs / bw_peak, 3))
+        g.close()
+    elif args.op == "fused_norm_ar":
+        # all-reduce (two-shot, peer loads) + residual + RMSNorm of [m, n] per rank, emulated ranks
+        rows, hidden = args.m, args.n
+        nbytes = rows * hidden * 2
+        g = EmulatedGroup(args.world, heap_bytes=3 * nbytes + (32 << 20))
+        x_off, y_off, ro_off = g.alloc(nbytes), g.alloc(nbytes), g.alloc(nbytes)
+        for r in range(args.world):
+            g.view(x_off, (rows, hidden), dt, r).normal_()
+        res = torch.randn(args.world, rows, hidden, device="cuda").to(dt)
+        w = torch.ones(hidden, device="cuda", dtype=dt)
+        ctas = args.ctas or 148 // args.world
+        fn = lambda: g.fused_norm(_lib.NORM_AR_TWOSHOT, x_off=x_off, rows=rows, hidden=hidden, dtype=dt, weight=w,  # noqa: E731
+                                  eps=1e-6, residual=res, y_off=y_off, res_out_off=ro_off,
+                                  local_stride_bytes=nbytes, max_ctas=ctas)
+        ms = timed(fn, args.iters, args.warmup, flush)
+        g.check_status()
+        gbs = (args.world * nbytes + nbytes + 2 * args.world * nbytes) / (ms * 1e-3) / 1e9
+        rec.update(world=args.world, rows=rows, hidden=hidden, ctas=ctas, us=round(ms * 1e3, 2),
+                   local_traffic_gbs=round(gbs, 1), frac_of_peak_hbm=round(gbs / bw_peak, 3))
+        g.close()
+    elif args.op in ("gemm_rs", "ag_gemm"):
+        from ..ops import AllGatherGemm, GemmReduceScatterNorm
+        g = EmulatedGroup(args.world, heap_bytes=(args.m * max(args.n, args.k) * 2) * 3 + (64 << 20))
+        rows = args.m // args.world
+        if args.op == "gemm_rs":
+            op = GemmReduceScatterNorm(g, args.m, args.n, dt, comm_ctas=args.comm_ctas, kernel=args.kernel)
+            a = torch.randn(args.world, args.m, args.k, device="cuda").to(dt)
+            b = (torch.randn(args.world, args.n, args.k, device="cuda") / args.k ** 0.5).to(dt)
+            res = torch.randn(args.world, rows, args.n, device="cuda").to(dt)
+            w = torch.ones(args.n, device="cuda", dtype=dt)
+            fn = lambda: op(a, b, w, res)  # noqa: E731
+        else:
+            op = AllGatherGemm(g, args.m, args.k, dt, comm_ctas=args.comm_ctas, kernel=args.kernel)
+            a = torch.randn(args.world, rows, args.k, device="cuda").to(dt)
+            b = (torch.randn(args.world, args.n, args.k, device="cuda") / args.k ** 0.5).to(dt)
+            out = torch.empty(args.world, args.m, args.n, device="cuda", dtype=dt)
+            fn = lambda: op(a, b, out=out)  # noqa: E731
+        ms = timed(fn, args.iters, args.warmup, flush)
+        g.check_status()
+        tflops = 2.0 * args.world * args.m * args.n * args.k / (ms * 1e-3) / 1e12
+        rec.update(world=args.world, M=args.m, N=args.n, K=args.k, kernel=args.kernel or "auto", comm_ctas=args.comm_ctas,
+                   us=round(ms * 1e3, 2), tflops_all_ranks=round(tflops, 1))
+        g.close()
     else:
         g = EmulatedGroup(args.world, heap_bytes=(args.m * args.n * 2) * 3 + (64 << 20))
-        op = GemmAllReduce(g, args.m, args.n, dt, comm_ctas=4)
+        op = GemmAllReduce(g, args.m, args.n, dt, comm_ctas=args.comm_ctas, kernel=args.kernel)
+        rec["kernel"], rec["comm_ctas"] = args.kernel or "auto", args.comm_ctas
         a = torch.randn(args.world, args.m, args.k, device="cuda").to(dt)
         b = (torch.randn(args.world, args.n, args.k, device="cuda") / args.k ** 0.5).to(dt)
         ms = timed(lambda: op(a, b), args.iters, args.warmup, flush)

@@ -36,46 +36,25 @@ from ..ops import AllGatherGemm, GemmAllReduce, GemmReduceScatterNorm, gemm, rms
 GEMM_PEAK_TFLOPS = 1629.9   # measured cuBLAS bf16 burst on this machine class
 LINK_GBS = 770.0            # measured peer copy, per direction per GPU
 PER_GRAPH = 5
+TOL = 1e-2                  # the reference's tolerance for 16-bit results (include/ooverlap/testing/test_utils.cuh:87-110)
 
 
-def timed(fn, iters, warmup):
-    for _ in range(warmup):
-        fn()
-    torch.cuda.synchronize()
-    graph = None
-    try:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            for _ in range(PER_GRAPH):
-                fn()
-        graph.replay()
-    except Exception:
-        graph = None
-    torch.cuda.synchronize()
+def timed(fn, iters, warmup) -> dict:
+    """Microseconds per call (max over ranks): ``us`` = median of three runs, plus p50 / p90 / p99 over the replays."""
+    from ..utils.timing import graph_timed
+    t = graph_timed(fn, iters, warmup, per_graph=PER_GRAPH, min_ms=30.0)
+    return {"us": round(t["us"], 1), "p50": round(t["p50"], 1), "p90": round(t["p90"], 1), "p99": round(t["p99"], 1)}
 
-    def once(reps):
-        dist.barrier()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(reps):
-            if graph is not None:
-                graph.replay()
-            else:
-                for _ in range(PER_GRAPH):
-                    fn()
-        b.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([a.elapsed_time(b) / (reps * PER_GRAPH)], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()) * 1e3  # microseconds per call, max over ranks
 
-    # The ranks never start a measurement at exactly the same instant; the skew (tens of microseconds of host
-    # jitter) is paid once per measurement, so each measurement runs for at least ~30 ms of device time.
-    pilot = once(max(1, iters // PER_GRAPH))
-    reps = max(1, int(min(400, max(iters // PER_GRAPH, 30000.0 / max(pilot * PER_GRAPH, 1.0)))))
-    trials = sorted(once(reps) for _ in range(3))
-    return trials[1]
+def check(name: str, got: torch.Tensor, want: torch.Tensor, tol: float = TOL) -> float:
+    """Max abs error of a result against its fp32 reference; raises when any rank is outside the tolerance."""
+    err = (got.float() - want).abs().max().item()
+    ok = err <= tol * max(1.0, want.abs().max().item())
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if not flag.item():
+        raise RuntimeError(f"{name}: result check failed on some rank (this rank: max abs err {err:.4g})")
+    return err
 
 
 def main() -> int:
@@ -89,6 +68,8 @@ def main() -> int:
     p.add_argument("--ms", default="512,2048,8192")
     p.add_argument("--out", default="")
     p.add_argument("--extra", default="", help="comma list of additional arms: chunked (GemmAllReduce strategy 'chunked')")
+    p.add_argument("--kernels", default="pair", help="comma list of fused kernels to time: pair (two-SM, CTA pairs), one_sm")
+    p.add_argument("--no-baselines", action="store_true", help="skip the cuBLAS + NCCL arms")
     args = p.parse_args()
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -99,6 +80,7 @@ def main() -> int:
     ctas = [int(c) for c in args.comm_ctas.split(",")]
     nvls_opts = {"auto": [None], "on": [True], "off": [False], "pull": [2], "both": [True, False], "all": [2, True, False]}[args.nvls]
     join_opts = {"on": [True], "off": [False], "both": [True, False]}[args.join]
+    kernels = [k for k in args.kernels.split(",") if k]
     lines = []
     gen = torch.Generator(device="cuda").manual_seed(100 + rank)
 
@@ -123,41 +105,52 @@ def main() -> int:
             base = dict(op="gemm_ar", M=M, N=N, K=K, tp=world, dtype="fp16", roofline_p2p_us=round(roof, 1),
                         roofline_nvls_us=round(roof_nvls, 1))
             out = torch.empty(M, N, dtype=dt, device="cuda")
+            want = a.float() @ b.float().t()
+            dist.all_reduce(want)
 
             def cublas_nccl():
                 torch.matmul(a, b.t(), out=out)
                 dist.all_reduce(out)
-            us = timed(cublas_nccl, args.iters, args.warmup)
-            emit({**base, "impl": "cublas+nccl", "us": round(us, 1)})
-            us_gemm = timed(lambda: torch.matmul(a, b.t(), out=out), args.iters, args.warmup)
-            emit({**base, "impl": "cublas_gemm_only", "us": round(us_gemm, 1)})
+            if not args.no_baselines:
+                emit({**base, "impl": "cublas+nccl", **timed(cublas_nccl, args.iters, args.warmup)})
+                emit({**base, "impl": "cublas_gemm_only", **timed(lambda: torch.matmul(a, b.t(), out=out), args.iters, args.warmup)})
             sym = comm.empty((M, N), dt)
 
             def ours_unfused():
                 gemm(a, b, out=sym, splits=1)
                 comm.all_reduce(sym)
-            emit({**base, "impl": "ours_unfused", "us": round(timed(ours_unfused, args.iters, args.warmup), 1)})
-            emit({**base, "impl": "ours_gemm_only", "us": round(timed(lambda: gemm(a, b, out=sym, splits=1), args.iters, args.warmup), 1)})
-            for c in ctas:
-                for nv in nvls_opts:
-                    for jn in join_opts:
-                        op = GemmAllReduce(comm, M, N, dt, comm_ctas=c, use_nvls=nv, strategy="fused")
-                        op.join = jn
-                        us = timed(lambda: op(a, b), args.iters, args.warmup)
-                        emit({**base, "impl": "ours_fused", "comm_ctas": c, "nvls": nv, "join": jn, "us": round(us, 1),
-                              "roofline_frac": round((roof_nvls if comm.nvls and nv is not False else roof) / us, 3)})
-                        op.release()
+            ours_unfused()
+            check(f"gemm_ar M={M} unfused", sym, want)
+            emit({**base, "impl": "ours_unfused", **timed(ours_unfused, args.iters, args.warmup)})
+            emit({**base, "impl": "ours_gemm_only", **timed(lambda: gemm(a, b, out=sym, splits=1), args.iters, args.warmup)})
+            for kernel in kernels:
+                for c in ctas:
+                    for nv in nvls_opts:
+                        for jn in (join_opts if kernel == "one_sm" else [True]):
+                            if kernel == "pair" and nv == 2:
+                                continue
+                            op = GemmAllReduce(comm, M, N, dt, comm_ctas=c, use_nvls=nv, strategy="fused", kernel=kernel)
+                            op.join = jn
+                            err = check(f"gemm_ar M={M} {kernel} ctas={c} nvls={nv}", op(a, b), want)
+                            t = timed(lambda: op(a, b), args.iters, args.warmup)
+                            emit({**base, "impl": "ours_fused", "kernel": kernel, "comm_ctas": c, "nvls": nv, "join": jn, **t,
+                                  "max_abs_err": round(err, 5),
+                                  "roofline_frac": round((roof_nvls if comm.nvls and nv is not False and nv != 0 else roof) / t["us"], 3)})
+                            op.release()
             op = GemmAllReduce(comm, M, N, dt)  # the library's own choice for this shape
-            emit({**base, "impl": "ours_auto", "strategy": op.strategy, "us": round(timed(lambda: op(a, b), args.iters, args.warmup), 1)})
+            check(f"gemm_ar M={M} auto", op(a, b), want)
+            emit({**base, "impl": "ours_auto", "strategy": op.strategy, **timed(lambda: op(a, b), args.iters, args.warmup)})
             op.release()
             if "chunked" in args.extra:
                 # slab GEMMs on this stream, in-switch all-reduce of each finished slab on a side stream
                 op = GemmAllReduce(comm, M, N, dt, strategy="chunked")
                 if op.strategy == "chunked":
-                    us = timed(lambda: op(a, b), args.iters, args.warmup)
-                    emit({**base, "impl": "ours_chunked", "chunks": op.chunks, "us": round(us, 1),
-                          "roofline_frac": round(roof_nvls / us, 3)})
+                    check(f"gemm_ar M={M} chunked", op(a, b), want)
+                    t = timed(lambda: op(a, b), args.iters, args.warmup)
+                    emit({**base, "impl": "ours_chunked", "chunks": op.chunks, **t, "roofline_frac": round(roof_nvls / t["us"], 3)})
                 op.release()
+            comm.free(comm.heap_offset(sym))
+            del want
             torch.cuda.synchronize()
             comm.check_status()
 
@@ -177,7 +170,7 @@ def main() -> int:
                 torch.matmul(a, b.t(), out=out)
                 dist.all_to_all_single(recv, out)
             emit(dict(op="gemm_a2a", M=M, N=N, K=K, tp=world, dtype="fp16", impl="cublas+nccl_all_to_all",
-                      us=round(timed(cublas_a2a, args.iters, args.warmup), 1)))
+                      **timed(cublas_a2a, args.iters, args.warmup)))
 
     if "gemm_rs_norm" in args.ops and 4096 % (128 * world) == 0:
         M, H, K = 4096, 8192, 28672 // world
@@ -196,18 +189,29 @@ def main() -> int:
             torch.matmul(a, b.t(), out=full)
             dist.reduce_scatter_tensor(shard, full)
             return rmsnorm_reference(shard, w, 1e-6, res)
-        emit({**base, "impl": "cublas+nccl_rs+torch_norm", "us": round(timed(cublas_nccl_rs, args.iters, args.warmup), 1)})
-        emit({**base, "impl": "cublas_gemm_only", "us": round(timed(lambda: torch.matmul(a, b.t(), out=full), args.iters, args.warmup), 1)})
-        for c in ctas:
-            for nv in nvls_opts:
-                op = GemmReduceScatterNorm(comm, M, H, dt, eps=1e-6, comm_ctas=c, use_nvls=nv)
-                y = torch.empty(rows, H, dtype=dt, device="cuda")
-                ro = torch.empty(rows, H, dtype=dt, device="cuda")
-                us = timed(lambda: op(a, b, w, res, y=y, residual_out=ro), args.iters, args.warmup)
-                emit({**base, "impl": "ours_fused", "comm_ctas": c, "nvls": nv, "us": round(us, 1),
-                      "roofline_frac": round(roof / us, 3)})
-                comm.free(op.partial_off)
-                comm.release_counters(op.counter_base)
+        if not args.no_baselines:
+            emit({**base, "impl": "cublas+nccl_rs+torch_norm", **timed(cublas_nccl_rs, args.iters, args.warmup)})
+            emit({**base, "impl": "cublas_gemm_only", **timed(lambda: torch.matmul(a, b.t(), out=full), args.iters, args.warmup)})
+        # fp32 reference of this rank's rows: sum over ranks of the partial products, + residual, RMSNorm
+        part = a[:, :].float() @ b.float().t()
+        dist.all_reduce(part)
+        srow = (part[rank * rows:(rank + 1) * rows] + res.float()).to(dt).float()
+        del part
+        want_y = srow * torch.rsqrt(srow.pow(2).mean(-1, keepdim=True) + 1e-6) * w.float()
+        for kernel in kernels:
+            for c in ctas:
+                for nv in nvls_opts:
+                    if kernel == "pair" and nv == 2:
+                        continue
+                    op = GemmReduceScatterNorm(comm, M, H, dt, eps=1e-6, comm_ctas=c, use_nvls=nv, kernel=kernel)
+                    y = torch.empty(rows, H, dtype=dt, device="cuda")
+                    ro = torch.empty(rows, H, dtype=dt, device="cuda")
+                    op(a, b, w, res, y=y, residual_out=ro)
+                    err = check(f"gemm_rs_norm {kernel} ctas={c} nvls={nv}", y, want_y, tol=6e-2)
+                    t = timed(lambda: op(a, b, w, res, y=y, residual_out=ro), args.iters, args.warmup)
+                    emit({**base, "impl": "ours_fused", "kernel": kernel, "comm_ctas": c, "nvls": nv, **t,
+                          "max_abs_err": round(err, 5), "roofline_frac": round(roof / t["us"], 3)})
+                    op.release()
         torch.cuda.synchronize()
         comm.check_status()
 
@@ -225,16 +229,25 @@ def main() -> int:
         def nccl_ag_cublas():
             dist.all_gather_into_tensor(a_full, a_shard)
             torch.matmul(a_full, b.t(), out=out)
-        emit({**base, "impl": "nccl_ag+cublas", "us": round(timed(nccl_ag_cublas, args.iters, args.warmup), 1)})
-        emit({**base, "impl": "cublas_gemm_only", "us": round(timed(lambda: torch.matmul(a_full, b.t(), out=out), args.iters, args.warmup), 1)})
-        for c in ctas:
-            for nv in nvls_opts:
-                op = AllGatherGemm(comm, M, K, dt, comm_ctas=c, use_nvls=nv)
-                us = timed(lambda: op(a_shard, b, out=out), args.iters, args.warmup)
-                emit({**base, "impl": "ours_fused", "comm_ctas": c, "nvls": nv, "us": round(us, 1),
-                      "roofline_frac": round(roof / us, 3)})
-                comm.free(op.a_full_off)
-                comm.release_counters(op.counter_base)
+        nccl_ag_cublas()
+        want_c = a_full.float() @ b.float().t()
+        if not args.no_baselines:
+            emit({**base, "impl": "nccl_ag+cublas", **timed(nccl_ag_cublas, args.iters, args.warmup)})
+            emit({**base, "impl": "cublas_gemm_only", **timed(lambda: torch.matmul(a_full, b.t(), out=out), args.iters, args.warmup)})
+        for kernel in kernels:
+            for c in ctas:
+                for nv in nvls_opts:
+                    if kernel == "pair" and nv == 2:
+                        continue
+                    for sk in ([0, -1] if kernel == "pair" else [0]):
+                        op = AllGatherGemm(comm, M, K, dt, comm_ctas=c, use_nvls=nv, kernel=kernel, stream_k=sk)
+                        out.zero_()
+                        op(a_shard, b, out=out)
+                        err = check(f"ag_gemm {kernel} ctas={c} nvls={nv} stream_k={sk}", out, want_c)
+                        t = timed(lambda: op(a_shard, b, out=out), args.iters, args.warmup)
+                        emit({**base, "impl": "ours_fused", "kernel": kernel, "comm_ctas": c, "nvls": nv, "stream_k": sk, **t,
+                              "max_abs_err": round(err, 5), "roofline_frac": round(roof / t["us"], 3)})
+                        op.release()
         torch.cuda.synchronize()
         comm.check_status()
 

@@ -496,6 +496,20 @@ class Communicator:
         pool.advance()
         return self.all_reduce(view, op, **kw)
 
+    def all_reduce_slot_capacity(self) -> int:
+        """Bytes per slot of the all-reduce ring (0 when the ring is not initialised)."""
+        return self._ar_pool.capacity_bytes if self._ar_pool is not None else 0
+
+    def commit_all_reduce_slot(self, view: torch.Tensor) -> torch.Tensor:
+        """Hands the slot returned by ``acquire_all_reduce_slot`` over to an op that reduces it itself (for instance
+        the fused all-reduce + RMSNorm): checks that ``view`` is the current slot and advances the ring, so that
+        the next ``acquire`` returns a different buffer.  The ring's bookkeeping stays in this class."""
+        pool = self._ar_pool
+        if pool is None or self.heap_offset(view) != pool.offsets[pool.next_index]:
+            raise ValueError("tensor is not the current all-reduce slot")
+        pool.advance()
+        return view
+
     def all_reduce_round_robin(self, x: torch.Tensor, op: str = "sum", **kw) -> torch.Tensor:
         slot = self.acquire_all_reduce_slot(x.shape)
         slot.copy_(x)

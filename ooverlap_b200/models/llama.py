@@ -137,10 +137,8 @@ class LlamaTP:
             if self.world == 1:
                 return rmsnorm(gemm(x, wt), norm_w, self.cfg.eps, residual)
             nbytes = x.shape[0] * wt.shape[0] * x.element_size()
-            pool = self.comm._ar_pool
-            if pool is not None and nbytes <= pool.capacity_bytes:
-                slot = self.comm.acquire_all_reduce_slot((x.shape[0], wt.shape[0]))
-                pool.advance()
+            if nbytes <= self.comm.all_reduce_slot_capacity():
+                slot = self.comm.commit_all_reduce_slot(self.comm.acquire_all_reduce_slot((x.shape[0], wt.shape[0])))
             else:  # prefill chunks larger than a slot: a cached registered scratch of that shape
                 slot = self.comm.scratch_view(("rp", x.shape[0], wt.shape[0]), (x.shape[0], wt.shape[0]), x.dtype)
             chunks = self.prefill_chunks

@@ -37,7 +37,7 @@ def fill_gemm_args(args: _lib.GemmArgs, a: torch.Tensor, b: torch.Tensor) -> Non
 
 def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, max_ctas: int = 0,
          splits: int = 0, pair: int = 0, skinny: int = 0, splitk_reduce: int = 0,
-         gemv: int = 0) -> torch.Tensor:
+         gemv: int = 0, stream_k: int = 0) -> torch.Tensor:
     """``out = a @ b.T`` with fp32 accumulation in TMEM.
 
     ``splits`` > 1 splits K over that many CTAs per output tile (fp32 partials in the library's workspace,
@@ -47,6 +47,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     ``pair`` selects the two-SM kernel (256x256 tiles computed by CTA pairs with ``tcgen05.mma.cta_group::2``; each
     CTA stages half of the B block): 0 uses it for unsplit problems with more than 128 rows, 1 whenever the problem
     is unsplit, -1 never.
+
+    ``stream_k`` (two-SM kernel): when the tile count is not a multiple of the pair count, the last wave and the
+    remainder are cut along K into equal ranges, one per pair, so that no pair idles; pairs that compute part of a tile
+    park fp32 accumulators in a library-owned workspace and the part that arrives last sums them in pair order
+    (bit-reproducible).  0 uses it when the idle share would exceed 3 % of the run, 1 whenever there is a remainder,
+    -1 never.
 
     ``skinny`` selects the weight-streaming kernel for ``M <= 128`` (the weight rows fill the tensor-core
     instruction's 128-row dimension, the tokens are its narrow dimension; stream-K split, deterministic) with 1.
@@ -74,8 +80,22 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     args.skinny = skinny
     args.splitk_reduce = splitk_reduce
     args.gemv = gemv
+    args.stream_k = stream_k
     _lib.check(_lib.lib().oob_gemm(None, ctypes.byref(args), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return out
+
+
+def reserve_workspace(splitk_bytes: int = 0) -> None:
+    """Allocates the library's GEMM scratch on the current device now: the stream-K workspace of the two-SM kernel and,
+    when ``splitk_bytes`` > 0, a split-K workspace of that size (see :func:`splitk_workspace_bytes`).  Call it before
+    capturing a CUDA graph: nothing can be allocated during capture, and a GEMM that would need to grow its workspace
+    then fails instead."""
+    _lib.check(_lib.lib().oob_gemm_reserve_workspace(int(splitk_bytes)))
+
+
+def splitk_workspace_bytes(M: int, N: int, K: int, *, max_ctas: int = 0, splits: int = 0) -> int:
+    """Split-K workspace bytes :func:`gemm` needs for this shape (0 when the problem is not split)."""
+    return int(_lib.lib().oob_gemm_splitk_bytes(M, N, K, max_ctas, splits))
 
 
 def gemm_plan_splits(M: int, N: int, K: int, *, max_ctas: int = 0, splits: int = 0) -> int:

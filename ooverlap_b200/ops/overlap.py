@@ -51,6 +51,18 @@ def _use_nvls(comm, choice) -> int:
     return int(choice)  # 0 = peer pushes only, 1 = push + multimem.st, 2 = in-switch reduce (pull) + multimem.st
 
 
+_KERNELS = {None: 0, "auto": 0, "pair": 1, "one_sm": -1}
+
+
+def _kernel_code(kernel) -> int:
+    """``kernel``: None / "auto" = the two-SM (CTA pair, 256x256 tiles) kernel whenever it supports the shape, "pair" =
+    the same, asked for explicitly, "one_sm" = the one-SM kernel (128x256 tiles; partial tiles are pushed to their owner
+    rank with bulk tensor stores)."""
+    if kernel not in _KERNELS:
+        raise ValueError(f"kernel must be one of {sorted(k for k in _KERNELS if k)}")
+    return _KERNELS[kernel]
+
+
 def _operands(comm, a: torch.Tensor, b: torch.Tensor):
     """In emulation ``a`` and ``b`` are stacked ``[world, ...]``; returns (a0, b0, a_stride, b_stride)."""
     if _emulated(comm):
@@ -116,9 +128,10 @@ class GemmAllReduce:
     """
 
     def __init__(self, comm, M: int, N: int, dtype: torch.dtype, *, comm_ctas: Optional[int] = None, max_ctas: int = 0,
-                 use_nvls=None, strategy: str = "auto", chunks: Optional[int] = None):
+                 use_nvls=None, strategy: str = "auto", chunks: Optional[int] = None, kernel: Optional[str] = None):
         self.comm, self.M, self.N, self.dtype = comm, M, N, dtype
         self.max_ctas = max_ctas
+        self.kernel = _kernel_code(kernel)
         self.multi = comm.world > 1
         sol = None
         if strategy == "auto" and not _emulated(comm):
@@ -193,6 +206,7 @@ class GemmAllReduce:
         fill_gemm_args(args, a0, b0)
         args.a_emu_stride, args.b_emu_stride = sa, sb
         args.comm_ctas, args.max_ctas = self.comm_ctas, self.max_ctas
+        args.pair = self.kernel
         args.use_nvls = _use_nvls(self.comm, self.use_nvls)
         args.no_join = 0 if getattr(self, "join", True) else 1
         trace = getattr(self, "trace_buffer", None)  # [ctas, 8] int64 device tensor: per-CTA phase stamps
@@ -209,7 +223,8 @@ class GemmReduceScatterNorm:
 
     def __init__(self, comm, M: int, N: int, dtype: torch.dtype, *, eps: float = 1e-6, comm_ctas: int = 16,
                  use_nvls: Optional[bool] = None,
-                 max_ctas: int = 0):
+                 max_ctas: int = 0, kernel: Optional[str] = None):
+        self.kernel = _kernel_code(kernel)
         if comm.world < 2:
             raise ValueError("needs at least two ranks")
         if M % comm.world or (M // comm.world) % TILE_M:
@@ -221,6 +236,13 @@ class GemmReduceScatterNorm:
         self.partial_off = comm.alloc(int(lib.oob_gemm_partial_bytes(M, N)))
         self.counter_base = comm.reserve_counters(lib.oob_gemm_counters_needed(_lib.GEMM_RS_NORM, M, N, comm.world))
         self.rows = M // comm.world
+
+    def release(self) -> None:
+        """Gives the op's registered buffer and counters back (collective by convention)."""
+        if self.partial_off is not None:
+            self.comm.free(self.partial_off)
+            self.comm.release_counters(self.counter_base)
+            self.partial_off = None
 
     def __call__(self, a: torch.Tensor, b: torch.Tensor, weight: Optional[torch.Tensor] = None,
                  residual: Optional[torch.Tensor] = None, *, y: Optional[torch.Tensor] = None,
@@ -239,6 +261,7 @@ class GemmReduceScatterNorm:
         fill_gemm_args(args, a0, b0)
         args.a_emu_stride, args.b_emu_stride = sa, sb
         args.comm_ctas, args.max_ctas = self.comm_ctas, self.max_ctas
+        args.pair = self.kernel
         args.use_nvls = _use_nvls(self.comm, self.use_nvls)
         args.no_join = 0 if getattr(self, "join", True) else 1
         trace = getattr(self, "trace_buffer", None)  # [ctas, 8] int64 device tensor: per-CTA phase stamps
@@ -257,8 +280,10 @@ class GemmReduceScatterNorm:
 
 class AllGatherGemm:
     def __init__(self, comm, M: int, K: int, dtype: torch.dtype, *, comm_ctas: int = 16, max_ctas: int = 0,
-                 use_nvls: Optional[bool] = None):
+                 use_nvls: Optional[bool] = None, kernel: Optional[str] = None, stream_k: int = 0):
         self.use_nvls = use_nvls
+        self.kernel = _kernel_code(kernel)
+        self.stream_k = stream_k
         if comm.world < 2:
             raise ValueError("needs at least two ranks")
         if M % comm.world or (M // comm.world) % TILE_M:
@@ -267,6 +292,13 @@ class AllGatherGemm:
         self.comm_ctas, self.max_ctas = comm_ctas, max_ctas
         self.a_full_off = comm.alloc(M * K * 2)
         self.counter_base = comm.reserve_counters(_lib.lib().oob_gemm_counters_needed(_lib.GEMM_AG, M, 8, comm.world))
+
+    def release(self) -> None:
+        """Gives the gathered buffer and the chunk flags back (collective by convention)."""
+        if self.a_full_off is not None:
+            self.comm.free(self.a_full_off)
+            self.comm.release_counters(self.counter_base)
+            self.a_full_off = None
 
     def gathered(self, rank: Optional[int] = None) -> torch.Tensor:
         """The gathered A ([M, K]) as it landed in this rank's registered memory.  Rows of the rank's own
@@ -292,6 +324,7 @@ class AllGatherGemm:
         args.a_emu_stride, args.b_emu_stride = sa, sb
         args.c_emu_stride = self.M * N * 2 if emu else 0
         args.comm_ctas, args.max_ctas = self.comm_ctas, self.max_ctas
+        args.pair, args.stream_k = self.kernel, self.stream_k
         args.use_nvls = _use_nvls(self.comm, self.use_nvls)
         args.no_join = 0 if getattr(self, "join", True) else 1
         trace = getattr(self, "trace_buffer", None)  # [ctas, 8] int64 device tensor: per-CTA phase stamps

@@ -62,6 +62,5 @@ class RowParallelLinear:
         if self.comm is None or self.comm.world == 1:
             from ..ops import rmsnorm
             return rmsnorm(gemm(x, self.weight), norm_weight, eps, residual)
-        slot = self.partial_into_slot(x)
-        self.comm._ar_pool.advance()
+        slot = self.comm.commit_all_reduce_slot(self.partial_into_slot(x))
         return fused_allreduce_rmsnorm(self.comm, slot, norm_weight, eps, residual)

@@ -16,7 +16,14 @@ as the reference's forced-backend switch does.
 
 Environment (names follow the reference's ``VLLM_OOVERLAP_*`` family):
 
-  VLLM_FORCE_ALLREDUCE_BACKEND   auto | ooverlap | custom | pynccl  (``auto`` / unset: leave vLLM alone)
+  VLLM_FORCE_ALLREDUCE_BACKEND   auto | ooverlap | custom | pynccl | nccl_symm  (``auto`` / unset: leave vLLM alone).
+                                 A forced backend serves EVERY tensor-parallel all-reduce or the call raises: nothing
+                                 falls through to another backend unnoticed.  ``custom`` = vLLM's own CustomAllreduce,
+                                 ``pynccl`` = NCCL through vLLM's PyNccl wrapper, ``nccl_symm`` = NCCL on symmetric
+                                 memory (needs vLLM's ``VLLM_USE_NCCL_SYMM_MEM`` machinery to load); these three are the
+                                 comparison arms of the serving benchmark.
+  VLLM_OOVERLAP_STRICT           1 (default): a tensor the ooverlap backend cannot take raises; 0: it is counted as
+                                 declined and handed to vLLM's own chain (the counts are logged when the group closes)
   VLLM_OOVERLAP_RR_SLOTS         all-reduce ring slots (default 32)
   VLLM_OOVERLAP_RR_CAPACITY_BYTES  bytes per slot (default 8 MiB)
   VLLM_OOVERLAP_RR_DTYPE         bf16 | fp16 | fp32 (default bf16)
@@ -89,6 +96,11 @@ class OoverlapAllReduce:
         self.ag_slots = _env_int("VLLM_OOVERLAP_AG_SLOTS", 4)
         self.ag_capacity = _env_int("VLLM_OOVERLAP_AG_CAPACITY_BYTES", 64 << 20)
         self.max_size = max_size if max_size is not None else self.rr_capacity
+        # What this backend did for its group: all-reduces served from a ring slot, served in slot-sized pieces
+        # (tensors larger than a slot), and declined by reason.  Logged at close; read with stats().
+        self.served = 0
+        self.served_chunked = 0
+        self.declined: dict[str, int] = {}
         if communicator is None:
             communicator = self._build_communicator(group, device)
         self.comm = communicator
@@ -125,22 +137,61 @@ class OoverlapAllReduce:
         return Communicator(devices, rank, short_broker_key(key), heap_bytes=heap)
 
     # ---------------------------------------------------- vLLM CustomAllreduce
-    def should_custom_ar(self, inp: torch.Tensor) -> bool:
-        if self.disabled or not inp.is_cuda or inp.device != self.device:
-            return False
-        if inp.dtype != self.rr_dtype or not inp.is_contiguous():
-            return False
+    def why_not(self, inp: torch.Tensor) -> Optional[str]:
+        """None when a ring slot can take ``inp`` as it is, else the reason it cannot."""
+        if self.disabled:
+            return "backend disabled"
+        if not inp.is_cuda or inp.device != self.device:
+            return "not on this rank's device"
+        if inp.dtype != self.rr_dtype:
+            return f"dtype {inp.dtype} is not the pool's {self.rr_dtype}"
+        if not inp.is_contiguous():
+            return "not contiguous"
         nbytes = inp.numel() * inp.element_size()
-        return 0 < nbytes <= self.max_size and nbytes % 16 == 0
+        if nbytes == 0:
+            return "empty"
+        if nbytes % 16:
+            return "size is not a multiple of 16 bytes"
+        if nbytes > self.max_size:
+            return "larger than a slot"
+        return None
+
+    def should_custom_ar(self, inp: torch.Tensor) -> bool:
+        return self.why_not(inp) is None
 
     should_ooverlap_ar = should_custom_ar
 
     def all_reduce(self, inp: torch.Tensor) -> Optional[torch.Tensor]:
         """Copy into the next ring slot, reduce in place, return the slot view (it aliases pool memory and
-        stays valid until the ring wraps: ``VLLM_OOVERLAP_RR_SLOTS`` later all-reduces)."""
-        if not self.should_custom_ar(inp):
+        stays valid until the ring wraps: ``VLLM_OOVERLAP_RR_SLOTS`` later all-reduces).  None when the tensor
+        is not eligible (see :meth:`why_not`)."""
+        why = self.why_not(inp)
+        if why is not None:
+            self.declined[why] = self.declined.get(why, 0) + 1
             return None
+        self.served += 1
         return self.comm.all_reduce_round_robin(inp)
+
+    def all_reduce_any_size(self, inp: torch.Tensor) -> Optional[torch.Tensor]:
+        """Like :meth:`all_reduce`, and a tensor that is only too large for a slot is reduced in slot-sized pieces of
+        whole rows into a fresh tensor (prefill batches; the ring stays the only registered memory)."""
+        why = self.why_not(inp)
+        if why is None:
+            self.served += 1
+            return self.comm.all_reduce_round_robin(inp)
+        row_bytes = (inp.numel() // max(1, inp.shape[0])) * inp.element_size() if inp.dim() > 0 else 0
+        if why != "larger than a slot" or row_bytes == 0 or row_bytes > self.max_size or row_bytes % 16:
+            self.declined[why] = self.declined.get(why, 0) + 1
+            return None
+        rows = max(1, self.max_size // row_bytes)
+        out = torch.empty_like(inp)
+        for r0 in range(0, inp.shape[0], rows):
+            out[r0:r0 + rows].copy_(self.comm.all_reduce_round_robin(inp[r0:r0 + rows]))
+        self.served_chunked += 1
+        return out
+
+    def stats(self) -> dict:
+        return {"served": self.served, "served_in_pieces": self.served_chunked, "declined": dict(self.declined)}
 
     def custom_all_reduce(self, inp: torch.Tensor) -> Optional[torch.Tensor]:
         out = self.all_reduce(inp)
@@ -160,6 +211,13 @@ class OoverlapAllReduce:
 
     def close(self) -> None:
         if self.comm is not None:
+            logger.info("ooverlap backend rank %d: all-reduces served %d (+%d in slot-sized pieces), declined %s",
+                        self.rank, self.served, self.served_chunked, self.declined or "none")
+            path = os.environ.get("VLLM_OOVERLAP_STATS_FILE")
+            if path:  # one JSON line per rank, for the serving benchmark's record
+                import json
+                with open(path, "a") as f:
+                    f.write(json.dumps({"rank": self.rank, "world": self.world_size, **self.stats()}) + "\n")
             self.comm.close()
             self.comm = None
         self.disabled = True
@@ -279,29 +337,77 @@ def _patch_row_parallel_linear() -> bool:
 _installed = False
 
 
+def _strict() -> bool:
+    return os.environ.get("VLLM_OOVERLAP_STRICT", "1") not in ("0", "")
+
+
+def forced_all_reduce(self, input_, mode: str, original_all_reduce):
+    """``CudaCommunicator.all_reduce`` under a forced backend (the reference's ``_all_reduce_forced``,
+    cuda_communicator.py:328-343): the named backend serves the tensor, or the call raises.  ``self`` is the vLLM
+    communicator.  Pure dispatch, so that it can be tested with stand-ins."""
+    if mode == "ooverlap":
+        ca = getattr(self, "ca_comm", None)
+        if not isinstance(ca, OoverlapAllReduce):
+            raise RuntimeError("VLLM_FORCE_ALLREDUCE_BACKEND=ooverlap, but this group has no ooverlap backend")
+        out = ca.all_reduce_any_size(input_)
+        if out is not None:
+            return out
+        if _strict():
+            raise RuntimeError(f"VLLM_FORCE_ALLREDUCE_BACKEND=ooverlap: tensor {tuple(input_.shape)} {input_.dtype} cannot "
+                               f"be served ({ca.why_not(input_)}); set VLLM_OOVERLAP_RR_DTYPE / "
+                               "VLLM_OOVERLAP_RR_CAPACITY_BYTES to fit the model, or VLLM_OOVERLAP_STRICT=0 to let such "
+                               "tensors fall through to vLLM's own chain (they are counted)")
+        return original_all_reduce(self, input_)
+    if mode == "custom":
+        ca = getattr(self, "ca_comm", None)
+        if ca is None or ca.disabled or not ca.should_custom_ar(input_):
+            raise RuntimeError(f"VLLM_FORCE_ALLREDUCE_BACKEND=custom: vLLM's custom all-reduce cannot take tensor "
+                               f"{tuple(input_.shape)} {input_.dtype}")
+        out = ca.custom_all_reduce(input_)
+        if out is None:
+            raise RuntimeError("VLLM_FORCE_ALLREDUCE_BACKEND=custom: custom_all_reduce declined the tensor")
+        return out
+    if mode == "pynccl":
+        nc = getattr(self, "pynccl_comm", None)
+        if nc is None or nc.disabled:
+            raise RuntimeError("VLLM_FORCE_ALLREDUCE_BACKEND=pynccl: this group has no PyNccl communicator")
+        out = nc.all_reduce(input_)
+        if out is None:
+            raise RuntimeError("VLLM_FORCE_ALLREDUCE_BACKEND=pynccl: PyNccl declined the tensor")
+        return out
+    if mode == "nccl_symm":
+        from vllm.distributed.device_communicators.pynccl_allocator import is_symmetric_memory_enabled
+        if not is_symmetric_memory_enabled() or getattr(self, "pynccl_comm", None) is None:
+            raise RuntimeError("VLLM_FORCE_ALLREDUCE_BACKEND=nccl_symm: NCCL symmetric memory is not available in this "
+                               "vLLM process (VLLM_USE_NCCL_SYMM_MEM machinery did not load)")
+        out = torch.ops.vllm.all_reduce_symmetric_with_copy(input_)
+        if out is None:
+            raise RuntimeError("VLLM_FORCE_ALLREDUCE_BACKEND=nccl_symm: the symmetric-memory all-reduce declined the tensor")
+        return out
+    return original_all_reduce(self, input_)
+
+
 def install() -> bool:
-    """Patches vLLM's ``CudaCommunicator`` in this process.  Returns True when the ``ooverlap`` backend is forced
-    and the patch is in place.  Call before vLLM builds its distributed groups (e.g. from a ``sitecustomize`` or at
-    the top of the serving script of every worker)."""
+    """Patches vLLM's ``CudaCommunicator`` in this process according to ``VLLM_FORCE_ALLREDUCE_BACKEND``.  Returns
+    True when a backend is forced and the patch is in place.  Call before vLLM builds its distributed groups (the
+    ``vllm.general_plugins`` entry point of this package does, in every engine and worker process)."""
     global _installed
     mode = forced_backend()
-    if mode != "ooverlap":
+    if mode == "auto":
         return False
     if _installed:
         return True
+    if mode == "nccl_symm":
+        os.environ.setdefault("VLLM_USE_NCCL_SYMM_MEM", "1")
     from vllm.distributed.device_communicators import cuda_communicator as cc
 
     original_init = cc.CudaCommunicator.__init__
+    original_all_reduce = cc.CudaCommunicator.all_reduce
     original_all_gather = cc.CudaCommunicator.all_gather
     original_destroy = cc.CudaCommunicator.destroy
 
-    def patched_init(self, *args, **kwargs):
-        original_init(self, *args, **kwargs)
-        if getattr(self, "world_size", 1) <= 1:
-            return
-        # Forced: no silent fallback.  Any failure to build the backend propagates.
-        self.ca_comm = OoverlapAllReduce(group=self.cpu_group, device=self.device)
-        for name in ("qr_comm", "fi_ar_comm", "symm_mem_comm"):
+    def drop(self, names):
+        for name in names:
             other = getattr(self, name, None)
             if other is not None and hasattr(other, "destroy"):
                 try:
@@ -309,7 +415,43 @@ def install() -> bool:
                 except Exception:  # noqa: BLE001
                     pass
             setattr(self, name, None)
-        logger.info("vLLM all-reduce backend forced to ooverlap")
+
+    def patched_init(self, *args, **kwargs):
+        original_init(self, *args, **kwargs)
+        if getattr(self, "world_size", 1) <= 1:
+            return
+        self._oob_forced = mode
+        if mode == "ooverlap":
+            # Forced: no silent fallback.  Any failure to build the backend propagates.
+            old = getattr(self, "ca_comm", None)
+            if old is not None and hasattr(old, "close"):
+                try:
+                    old.close()
+                except Exception:  # noqa: BLE001
+                    pass
+            self.ca_comm = OoverlapAllReduce(group=self.cpu_group, device=self.device)
+            drop(self, ("qr_comm", "fi_ar_comm", "symm_mem_comm"))
+        elif mode == "custom":
+            drop(self, ("qr_comm", "fi_ar_comm", "symm_mem_comm"))
+            if getattr(self, "ca_comm", None) is None or self.ca_comm.disabled:
+                raise RuntimeError("VLLM_FORCE_ALLREDUCE_BACKEND=custom, but vLLM's custom all-reduce is not available "
+                                   "for this group")
+        elif mode in ("pynccl", "nccl_symm"):
+            drop(self, ("qr_comm", "fi_ar_comm", "symm_mem_comm"))
+            old = getattr(self, "ca_comm", None)
+            if old is not None and hasattr(old, "close"):
+                try:
+                    old.close()
+                except Exception:  # noqa: BLE001
+                    pass
+            self.ca_comm = None
+        logger.info("vLLM all-reduce backend forced to %s", mode)
+
+    def patched_all_reduce(self, input_):
+        forced = getattr(self, "_oob_forced", None)
+        if forced is None:
+            return original_all_reduce(self, input_)
+        return forced_all_reduce(self, input_, forced, original_all_reduce)
 
     def patched_all_gather(self, input_, dim: int = -1):
         ca = getattr(self, "ca_comm", None)
@@ -323,12 +465,14 @@ def install() -> bool:
         ca = getattr(self, "ca_comm", None)
         if isinstance(ca, OoverlapAllReduce):
             ca.close()
+            self.ca_comm = None
         return original_destroy(self)
 
     cc.CudaCommunicator.__init__ = patched_init
+    cc.CudaCommunicator.all_reduce = patched_all_reduce
     cc.CudaCommunicator.all_gather = patched_all_gather
     cc.CudaCommunicator.destroy = patched_destroy
-    if _env_int("VLLM_OOVERLAP_ROW_PARALLEL", 0):
+    if mode == "ooverlap" and _env_int("VLLM_OOVERLAP_ROW_PARALLEL", 0):
         _patch_row_parallel_linear()
         logger.info("vLLM RowParallelLinear routed through the direct-slot GEMM + all-reduce")
     _installed = True

@@ -75,24 +75,45 @@ def test_vllm_bench_model_dir_env_and_commands(tmp_path):
     from transformers import AutoConfig
     hf = AutoConfig.from_pretrained(d)
     assert hf.model_type == "llama" and hf.intermediate_size == 28672 and hf.vocab_size == 128256
-    env = vllm_bench.child_env("ooverlap", "/some/repo", base={"PYTHONPATH": "/x"})
-    assert env["VLLM_FORCE_ALLREDUCE_BACKEND"] == "ooverlap" and env["PYTHONPATH"].split(os.pathsep) == ["/some/repo", "/x"]
+    env = vllm_bench.child_env("ooverlap", "/some/repo", base={"PYTHONPATH": "/x"}, plugin_dir="/plug", stats_file="/s.jsonl")
+    assert env["VLLM_FORCE_ALLREDUCE_BACKEND"] == "ooverlap"
+    assert env["PYTHONPATH"].split(os.pathsep) == ["/plug", "/some/repo", "/x"] and env["VLLM_OOVERLAP_STATS_FILE"] == "/s.jsonl"
     env2 = vllm_bench.child_env("pynccl", "/some/repo", base={"VLLM_FORCE_ALLREDUCE_BACKEND": "ooverlap"})
-    assert "VLLM_FORCE_ALLREDUCE_BACKEND" not in env2 and env2["MASTER_ADDR"] == "127.0.0.1"
+    assert env2["VLLM_FORCE_ALLREDUCE_BACKEND"] == "pynccl" and env2["MASTER_ADDR"] == "127.0.0.1"
+    env3 = vllm_bench.child_env("default", "/some/repo", base={"VLLM_FORCE_ALLREDUCE_BACKEND": "ooverlap"})
+    assert "VLLM_FORCE_ALLREDUCE_BACKEND" not in env3
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     out = subprocess.run([sys.executable, "-m", "ooverlap_b200.bench.vllm_bench", "--dry-run", "--model", "tiny", "--tp", "2",
                           "--batches", "1,4", "--backends", "pynccl,ooverlap", "--orders", "all"], cwd=root,
                          capture_output=True, text=True, check=True).stdout
     recs = [json.loads(ln) for ln in out.splitlines()]
-    assert len(recs) == 2 * 2 * 2  # orders x batches x backends
-    assert {r["backend"] for r in recs} == {"pynccl", "ooverlap"}
+    assert len(recs) == 2 * 2  # orders x backends: one engine per backend runs every batch size
+    assert {r["backend"] for r in recs} == {"pynccl", "ooverlap"} and all(r["batches"] == "1,4" for r in recs)
     assert all("--worker" in r["cmd"] and "--model-dir" in r["cmd"] for r in recs)
+    out = subprocess.run([sys.executable, "-m", "ooverlap_b200.bench.vllm_bench", "--dry-run", "--model", "tiny", "--tp", "2",
+                          "--batches", "1,4", "--backends", "default,ooverlap", "--per-batch-engines"], cwd=root,
+                         capture_output=True, text=True, check=True).stdout
+    assert len(out.splitlines()) == 2 * 2  # batches x backends
+    # per-rank statistics written by the backend at shutdown are summed for the record
+    sf = tmp_path / "stats.jsonl"
+    sf.write_text('{"rank": 0, "world": 2, "served": 5, "served_in_pieces": 1, "declined": {"x": 1}}\n'
+                  '{"rank": 1, "world": 2, "served": 5, "served_in_pieces": 1, "declined": {"x": 2}}\n')
+    assert vllm_bench.read_stats(str(sf)) == {"ranks": 2, "served": 10, "served_in_pieces": 2, "declined": {"x": 3}}
+    assert vllm_bench.read_stats(str(tmp_path / "none")) is None
 
 
-def test_vllm_plugin_entry_point_is_discoverable_from_the_repository_root():
+def test_vllm_plugin_entry_point_is_discoverable_without_an_installation(tmp_path):
+    """pyproject.toml declares the vllm.general_plugins entry point; for runs from the source tree the benchmark driver
+    writes the same metadata into a scratch directory, and with that directory and the repository root on PYTHONPATH a
+    fresh interpreter (as vLLM's engine and worker processes are) finds and loads the hook."""
     import subprocess
     import sys
+    from ooverlap_b200.bench import vllm_bench
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    text = open(os.path.join(root, "pyproject.toml")).read()
+    assert '[project.entry-points."vllm.general_plugins"]' in text
+    assert 'ooverlap_b200 = "ooverlap_b200.parallel.vllm_adapter:install"' in text
+    plug = vllm_bench.write_plugin_metadata(str(tmp_path / "plug"))
     code = ("from importlib.metadata import entry_points\n"
             "eps = [e for e in entry_points(group='vllm.general_plugins') if e.name == 'ooverlap_b200']\n"
             "assert len(eps) == 1, eps\n"
@@ -101,6 +122,6 @@ def test_vllm_plugin_entry_point_is_discoverable_from_the_repository_root():
             "os.environ.pop('VLLM_FORCE_ALLREDUCE_BACKEND', None)\n"
             "assert f() is False  # not forced: the hook leaves vLLM alone\n"
             "print('ok')\n")
-    env = dict(os.environ, PYTHONPATH=root)
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([plug, root]))
     out = subprocess.run([sys.executable, "-c", code], cwd="/", env=env, capture_output=True, text=True)
     assert out.returncode == 0 and "ok" in out.stdout, out.stderr[-800:]

@@ -35,7 +35,7 @@ def test_gemm_swiglu(M, F, K, dtype):
 
 def test_gemm_swiglu_falls_back_when_not_split():
     from ooverlap_b200.ops import gemm_plan_splits, gemm_swiglu
-    M, F, K = 1024, 1024, 512
+    M, F, K = 2048, 2048, 512  # 256 tiles: more than the SMs, so the problem is not split
     assert gemm_plan_splits(M, 2 * F, K) == 1
     x = torch.randn(M, K, device="cuda").bfloat16()
     w = (torch.randn(2 * F, K, device="cuda") / K ** 0.5).bfloat16()

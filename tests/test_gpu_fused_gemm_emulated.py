@@ -13,15 +13,21 @@ def _operands(world, M, N, K, dtype, seed=0):
     return a, b
 
 
-@pytest.mark.parametrize("world", [2, 4])
-@pytest.mark.parametrize("shape", [(256, 512, 256), (1024, 1024, 512), (200, 264, 72)])
+KERNELS = ["pair", "one_sm"]  # two-SM kernel (CTA pairs, in-place reduction) and one-SM kernel (pushed partial tiles)
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("shape", [(256, 512, 256), (1024, 1024, 512), (200, 264, 72), (640, 1280, 128)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_gemm_all_reduce(world, shape, dtype):
+def test_gemm_all_reduce(world, shape, dtype, kernel):
     from ooverlap_b200 import EmulatedGroup
     from ooverlap_b200.ops import GemmAllReduce
     M, N, K = shape
+    if world == 8 and kernel == "one_sm" and M * N > 256 * 512:
+        pytest.skip("eight emulated ranks of the one-SM kernel are covered by the small shape")
     g = EmulatedGroup(world, heap_bytes=64 << 20)
-    op = GemmAllReduce(g, M, N, dtype, comm_ctas=4)
+    op = GemmAllReduce(g, M, N, dtype, comm_ctas=4, kernel=kernel)
     a, b = _operands(world, M, N, K, dtype, seed=M + world)
     want = sum(a[r].float() @ b[r].float().t() for r in range(world))
     for it in range(3):  # repeated calls re-arm the tile counters
@@ -36,15 +42,16 @@ def test_gemm_all_reduce(world, shape, dtype):
     g.close()
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("world,blocks,N", [(2, 2, 1024), (4, 2, 1024), (4, 1, 8192), (2, 3, 2560), (8, 1, 512)])
 @pytest.mark.parametrize("with_norm", [True, False])
-def test_gemm_reduce_scatter_residual_rmsnorm(world, with_norm):
+def test_gemm_reduce_scatter_residual_rmsnorm(world, blocks, N, with_norm, kernel):
     from ooverlap_b200 import EmulatedGroup
     from ooverlap_b200.ops import GemmReduceScatterNorm
     dtype, eps = torch.bfloat16, 1e-6
-    M, N, K = 128 * world * 2, 1024, 256
-    g = EmulatedGroup(world, heap_bytes=64 << 20)
-    op = GemmReduceScatterNorm(g, M, N, dtype, eps=eps, comm_ctas=3)
+    M, K = 128 * world * blocks, 256
+    g = EmulatedGroup(world, heap_bytes=96 << 20)
+    op = GemmReduceScatterNorm(g, M, N, dtype, eps=eps, comm_ctas=3, kernel=kernel)
     a, b = _operands(world, M, N, K, dtype, seed=7)
     rows = M // world
     residual = torch.randn(world, rows, N, device="cuda").to(dtype)
@@ -60,14 +67,15 @@ def test_gemm_reduce_scatter_residual_rmsnorm(world, with_norm):
     g.close()
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_all_gather_gemm(world):
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("world,blocks", [(2, 2), (4, 2), (4, 3), (8, 1)])
+def test_all_gather_gemm(world, blocks, kernel):
     from ooverlap_b200 import EmulatedGroup
     from ooverlap_b200.ops import AllGatherGemm
     dtype = torch.bfloat16
-    M, N, K = 128 * world * 2, 520, 320
+    M, N, K = 128 * world * blocks, 520, 320
     g = EmulatedGroup(world, heap_bytes=64 << 20)
-    op = AllGatherGemm(g, M, K, dtype, comm_ctas=3)
+    op = AllGatherGemm(g, M, K, dtype, comm_ctas=3, kernel=kernel)
     gen = torch.Generator(device="cuda").manual_seed(3)
     a_full = torch.randn(M, K, device="cuda", generator=gen).to(dtype)
     a_shards = a_full.view(world, M // world, K).contiguous()
@@ -81,10 +89,9 @@ def test_all_gather_gemm(world):
     g.close()
 
 
-@pytest.mark.skipif(__import__("os").environ.get("OOB_RUN_UNVALIDATED", "0") in ("", "0"),
-                    reason="counter read-back not yet run on hardware; set OOB_RUN_UNVALIDATED=1")
+@pytest.mark.parametrize("kernel", KERNELS)
 @pytest.mark.parametrize("world", [2, 4])
-def test_fused_ops_leave_every_arrival_counter_re_armed(world):
+def test_fused_ops_leave_every_arrival_counter_re_armed(world, kernel):
     """After each fused op (all three kinds, odd and even tile counts) every general counter of every rank's signal
     pad reads zero again: tile arrivals, row-block arrivals, chunk flags and tickets are all re-armed in-kernel."""
     from ooverlap_b200 import EmulatedGroup
@@ -95,9 +102,9 @@ def test_fused_ops_leave_every_arrival_counter_re_armed(world):
         assert int(g.counters(r).abs().max()) == 0
     M, N, K = 128 * world * 2, 768, 256  # 3 column tiles: an odd number of tiles per rank for world = 2
     a, b = _operands(world, M, N, K, dtype, seed=3)
-    ar = GemmAllReduce(g, M, N, dtype, comm_ctas=3)
-    rs = GemmReduceScatterNorm(g, M, N, dtype, eps=1e-6, comm_ctas=2)
-    ag = AllGatherGemm(g, M, K, dtype, comm_ctas=2)
+    ar = GemmAllReduce(g, M, N, dtype, comm_ctas=3, kernel=kernel)
+    rs = GemmReduceScatterNorm(g, M, N, dtype, eps=1e-6, comm_ctas=2, kernel=kernel)
+    ag = AllGatherGemm(g, M, K, dtype, comm_ctas=2, kernel=kernel)
     residual = torch.randn(world, M // world, N, device="cuda").to(dtype)
     a_shards = a[0].reshape(world, M // world, K).contiguous()
     for it in range(2):

@@ -110,8 +110,8 @@ def test_two_sm_kernel(shape, dtype):
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
     a = torch.randn(M, K, device="cuda", generator=g).to(dtype)
     b = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).to(dtype)
-    c_pair = gemm(a, b, splits=1, pair=1)
-    c_pair2 = gemm(a, b, splits=1, pair=1)
+    c_pair = gemm(a, b, splits=1, pair=1, stream_k=-1)
+    c_pair2 = gemm(a, b, splits=1, pair=1, stream_k=-1)
     c_one = gemm(a, b, splits=1, pair=-1)
     torch.cuda.synchronize()
     ref = _ref(a, b)
@@ -119,6 +119,106 @@ def test_two_sm_kernel(shape, dtype):
     assert err <= 1e-2 * max(1.0, ref.abs().max().item()), (shape, dtype, err)
     assert torch.equal(c_pair, c_pair2)
     assert torch.equal(c_pair, c_one)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape,max_ctas", [((512, 8192, 8192), 0), ((2048, 8192, 4096), 0), ((2048, 2048, 2048), 0),
+                                            ((1280, 1536, 1024), 0), ((1000, 520, 1096), 0), ((4096, 3584, 2048), 0),
+                                            ((768, 768, 4096), 10), ((2304, 1280, 2048), 14), ((256, 512, 8192), 0)])
+def test_two_sm_kernel_stream_k_tail(shape, max_ctas, dtype):
+    """Stream-K tail of the two-SM kernel: pairs that compute part of a tile park fp32 accumulators in the workspace
+    and the last arrival sums them in pair order.  Against fp32; bit-identical from call to call (the order of
+    addition is fixed); close to the result without a tail (which adds the same products in a different grouping);
+    and calls back to back re-use the workspace flags (they are re-armed in the kernel)."""
+    from ooverlap_b200.ops import gemm
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g).to(dtype)
+    b = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).to(dtype)
+    outs = [gemm(a, b, splits=1, pair=1, stream_k=1, max_ctas=max_ctas) for _ in range(3)]
+    c_whole = gemm(a, b, splits=1, pair=1, stream_k=-1, max_ctas=max_ctas)
+    c_auto = gemm(a, b, max_ctas=max_ctas)
+    torch.cuda.synchronize()
+    ref = _ref(a, b)
+    tol = 1e-2 * max(1.0, ref.abs().max().item())
+    assert (outs[0].float() - ref).abs().max().item() <= tol, (shape, dtype)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert (outs[0].float() - c_whole.float()).abs().max().item() <= tol
+    assert (c_auto.float() - ref).abs().max().item() <= tol
+
+
+def test_two_sm_kernel_stream_k_graph_replay_and_reserved_workspace():
+    """The stream-K workspace is allocated once per device and never moves: a captured launch stays valid when other
+    shapes run in between.  reserve_workspace() makes the allocation happen before the capture."""
+    from ooverlap_b200.ops import gemm, reserve_workspace
+    reserve_workspace()
+    a = torch.randn(512, 2048, device="cuda").bfloat16()
+    b = (torch.randn(4096, 2048, device="cuda") / 45.0).bfloat16()
+    out = torch.empty(512, 4096, device="cuda", dtype=torch.bfloat16)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        gemm(a, b, out=out, splits=1, pair=1, stream_k=1)
+    for i in range(3):
+        a.normal_()
+        other = torch.randn(2048, 1024, device="cuda").bfloat16()
+        gemm(other, torch.randn(1536, 1024, device="cuda").bfloat16(), splits=1, pair=1, stream_k=1)
+        graph.replay()
+        torch.cuda.synchronize()
+        ref = _ref(a, b)
+        assert (out.float() - ref).abs().max().item() <= 1e-2 * max(1.0, ref.abs().max().item()), i
+
+
+def test_split_k_workspace_survives_growth_under_a_captured_graph():
+    """A captured split-K GEMM keeps launching with the workspace it was captured with: a later, larger problem gets
+    a new block and the old one stays alive.  Growing during capture is refused with a clear error; reserving first
+    makes the same capture work."""
+    from ooverlap_b200._lib import OobError
+    from ooverlap_b200.ops import gemm, reserve_workspace, splitk_workspace_bytes
+    a = torch.randn(64, 2048, device="cuda").bfloat16()
+    b = (torch.randn(1024, 2048, device="cuda") / 45.0).bfloat16()
+    out = torch.empty(64, 1024, device="cuda", dtype=torch.bfloat16)
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        gemm(a, b, out=out, splits=4, skinny=-1)  # first use: the workspace exists before the capture
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            gemm(a, b, out=out, splits=4, skinny=-1)
+        # a larger split problem on the same stream grows the workspace
+        a2 = torch.randn(128, 4096, device="cuda").bfloat16()
+        b2 = (torch.randn(8192, 4096, device="cuda") / 64.0).bfloat16()
+        c2 = gemm(a2, b2, splits=8, skinny=-1)
+        for _ in range(2):
+            a.normal_()
+            graph.replay()
+            s.synchronize()
+            assert (out.float() - _ref(a, b)).abs().max().item() <= 1e-2 * max(1.0, _ref(a, b).abs().max().item())
+        assert (c2.float() - _ref(a2, b2)).abs().max().item() <= 1e-2 * max(1.0, _ref(a2, b2).abs().max().item())
+    # growth during capture: refused, and the capture can be redone after a reservation
+    s2 = torch.cuda.Stream()
+    a3 = torch.randn(128, 8192, device="cuda").bfloat16()
+    b3 = (torch.randn(16384, 8192, device="cuda") / 90.0).bfloat16()
+    out3 = torch.empty(128, 16384, device="cuda", dtype=torch.bfloat16)
+    need = splitk_workspace_bytes(128, 16384, 8192, splits=16)  # 128 MiB of partial tiles: more than any test before
+    assert need > (128 << 20)
+    with torch.cuda.stream(s2):
+        g2 = torch.cuda.CUDAGraph()
+        failed = False
+        try:
+            with torch.cuda.graph(g2, stream=s2):
+                gemm(a3, b3, out=out3, splits=16, skinny=-1)
+        except OobError as e:
+            failed = True
+            assert "oob_gemm_reserve_workspace" in str(e)
+        assert failed
+    torch.cuda.synchronize()
+    reserve_workspace(need)
+    with torch.cuda.stream(s2):
+        g3 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g3, stream=s2):
+            gemm(a3, b3, out=out3, splits=16, skinny=-1)
+        g3.replay()
+        s2.synchronize()
+    assert (out3.float() - _ref(a3, b3)).abs().max().item() <= 1e-2 * max(1.0, _ref(a3, b3).abs().max().item())
 
 
 def test_two_sm_kernel_cta_budget_and_padded_output():

@@ -157,55 +157,71 @@ def _rank_fused(rank, world, key):
             x.copy_(xs[rank].cuda())
             y2, _ = fused_reduce_scatter_rmsnorm(comm, x, w.cuda(), eps, res[b:e].cuda())
             out.append((f"rs_norm {rows}", (y2.float().cpu() - want[b:e]).abs().max().item(), 6e-2))
-    # fused GEMM ops
-    M, N, K = 128 * world * 2, 1024, 512
-    a = [gen((M, K), 200 + r) for r in range(world)]
-    bw = [gen((N, K), 300 + r, (K * world) ** -0.5) for r in range(world)]
-    want = sum(a[r].float() @ bw[r].float().t() for r in range(world))
-    # every data path of the fused all-reduce: peer pushes, pushes + multicast result, in-switch reduction
-    for variant in ([0, 1, 2] if comm.nvls else [0]):
-        op = GemmAllReduce(comm, M, N, dt, comm_ctas=8, use_nvls=variant, strategy="fused")
-        for it in range(3):
+    # fused GEMM ops: both kernels (CTA pairs with in-place reduction; one-SM with pushed partial tiles), every data
+    # path (peer loads/stores, through the switch), a small shape and one with several waves of tiles per rank
+    nvls_variants = [0, 1, 2] if comm.nvls else [0]
+    for (M, N, K) in ((128 * world * 2, 1024, 512), (256 * world * 2, 4096, 256)):
+        a = [gen((M, K), 200 + r) for r in range(world)]
+        bw = [gen((N, K), 300 + r, (K * world) ** -0.5) for r in range(world)]
+        want = sum(a[r].float() @ bw[r].float().t() for r in range(world))
+        tol_c = 3e-2 * max(1, want.abs().max().item())
+        for kernel in ("pair", "one_sm"):
+            for variant in nvls_variants:
+                if kernel == "pair" and variant == 2:
+                    continue  # the pair kernel has one path through the switch
+                op = GemmAllReduce(comm, M, N, dt, comm_ctas=8, use_nvls=variant, strategy="fused", kernel=kernel)
+                for it in range(3):
+                    c = op(a[rank].cuda(), bw[rank].cuda())
+                    torch.cuda.synchronize()
+                    out.append((f"gemm_ar {kernel} nvls{variant} M{M} {it}", (c.float().cpu() - want).abs().max().item(), tol_c))
+                    c.zero_()
+                    comm.barrier()  # nobody starts the next call while a peer still zeroes its output
+                op.release()
+        for strat in ("auto", "unfused"):
+            op = GemmAllReduce(comm, M, N, dt, strategy=strat)
             c = op(a[rank].cuda(), bw[rank].cuda())
             torch.cuda.synchronize()
-            out.append((f"gemm_ar nvls{variant} {it}", (c.float().cpu() - want).abs().max().item(),
-                        3e-2 * max(1, want.abs().max().item())))
-            c.zero_()
-        op.release()
-    for strat in ("auto", "unfused"):
-        op = GemmAllReduce(comm, M, N, dt, strategy=strat)
-        c = op(a[rank].cuda(), bw[rank].cuda())
-        torch.cuda.synchronize()
-        out.append((f"gemm_ar {strat}", (c.float().cpu() - want).abs().max().item(), 3e-2 * max(1, want.abs().max().item())))
-        op.release()
-    if os.environ.get("OOB_RUN_UNVALIDATED", "0") not in ("", "0"):
-        # slabs of rows: GEMM on the caller's stream, all-reduce of each slab on a side stream (not yet run on hardware)
-        op = GemmAllReduce(comm, M, N, dt, strategy="chunked", chunks=2)
-        for it in range(3):
-            c = op(a[rank].cuda(), bw[rank].cuda())
-            torch.cuda.synchronize()
-            out.append((f"gemm_ar chunked {it}", (c.float().cpu() - want).abs().max().item(),
-                        3e-2 * max(1, want.abs().max().item())))
-            c.zero_()
-            torch.cuda.synchronize()
-        op.release()
-    rs = GemmReduceScatterNorm(comm, M, N, dt, eps=eps, comm_ctas=8)
-    wn = (1 + 0.02 * torch.randn(N, generator=torch.Generator().manual_seed(6))).to(dt)
-    res = gen((M, N), 400)
-    rows = M // world
-    s = (want + res.float()).to(dt).float()
-    wanty = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + eps) * wn.float()
-    for it in range(2):
-        y, ro = rs(a[rank].cuda(), bw[rank].cuda(), wn.cuda(), res[rank * rows:(rank + 1) * rows].cuda())
-        torch.cuda.synchronize()
-        out.append((f"gemm_rs_norm {it}", (y.float().cpu() - wanty[rank * rows:(rank + 1) * rows]).abs().max().item(), 8e-2))
-    ag = AllGatherGemm(comm, M, K, dt, comm_ctas=8)
-    a_full = gen((M, K), 500)
-    for it in range(2):
-        c = ag(a_full[rank * rows:(rank + 1) * rows].cuda(), bw[rank].cuda())
-        torch.cuda.synchronize()
+            out.append((f"gemm_ar {strat} M{M}", (c.float().cpu() - want).abs().max().item(), tol_c))
+            op.release()
+        if M == 128 * world * 2:
+            # slabs of rows: GEMM on the caller's stream, all-reduce of each slab on a side stream
+            op = GemmAllReduce(comm, M, N, dt, strategy="chunked", chunks=2)
+            for it in range(3):
+                c = op(a[rank].cuda(), bw[rank].cuda())
+                torch.cuda.synchronize()
+                out.append((f"gemm_ar chunked {it}", (c.float().cpu() - want).abs().max().item(), tol_c))
+                c.zero_()
+                torch.cuda.synchronize()
+                comm.barrier()
+            op.release()
+        wn = (1 + 0.02 * torch.randn(N, generator=torch.Generator().manual_seed(6))).to(dt)
+        res = gen((M, N), 400)
+        rows = M // world
+        s = (want + res.float()).to(dt).float()
+        wanty = s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + eps) * wn.float()
+        a_full = gen((M, K), 500)
         wantc = a_full.float() @ bw[rank].float().t()
-        out.append((f"ag_gemm {it}", (c.float().cpu() - wantc).abs().max().item(), 3e-2 * max(1, wantc.abs().max().item())))
+        for kernel in ("pair", "one_sm"):
+            for variant in ([0, 1] if comm.nvls else [0]):
+                rs = GemmReduceScatterNorm(comm, M, N, dt, eps=eps, comm_ctas=8, use_nvls=variant, kernel=kernel)
+                for it in range(2):
+                    y, ro = rs(a[rank].cuda(), bw[rank].cuda(), wn.cuda(), res[rank * rows:(rank + 1) * rows].cuda())
+                    torch.cuda.synchronize()
+                    out.append((f"gemm_rs_norm {kernel} nvls{variant} M{M} {it}",
+                                (y.float().cpu() - wanty[rank * rows:(rank + 1) * rows]).abs().max().item(), 8e-2))
+                    # the switch rounds the sum of the partials before the residual is added: allow for that
+                    allow = (want[rank * rows:(rank + 1) * rows].abs() + res[rank * rows:(rank + 1) * rows].float().abs()) * 2 ** -6
+                    out.append((f"gemm_rs_res {kernel} nvls{variant} M{M} {it}",
+                                ((ro.float().cpu() - s[rank * rows:(rank + 1) * rows]).abs() - allow).max().item(), 1e-2))
+                ag = AllGatherGemm(comm, M, K, dt, comm_ctas=8, use_nvls=variant, kernel=kernel)
+                for it in range(2):
+                    c = ag(a_full[rank * rows:(rank + 1) * rows].cuda(), bw[rank].cuda())
+                    torch.cuda.synchronize()
+                    out.append((f"ag_gemm {kernel} nvls{variant} M{M} {it}", (c.float().cpu() - wantc).abs().max().item(),
+                                3e-2 * max(1, wantc.abs().max().item())))
+                    comm.barrier()
+                ag.release()
+                rs.release()
     comm.check_status()
     comm.barrier()
     nv = comm.nvls

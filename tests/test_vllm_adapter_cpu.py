@@ -227,3 +227,66 @@ def test_row_parallel_patch_falls_back_to_vllm(monkeypatch):
         assert out is seen["orig"]
     finally:
         vl.RowParallelLinear.forward = orig
+
+
+def test_forced_all_reduce_serves_or_raises(adapter, monkeypatch):
+    """A forced backend serves every all-reduce or raises (no silent fall-through); tensors larger than a slot go
+    through the ring in pieces; with VLLM_OOVERLAP_STRICT=0 the rest is counted and handed on."""
+    monkeypatch.setattr(torch.Tensor, "is_cuda", property(lambda self: True))
+
+    class Host:  # stands in for vLLM's CudaCommunicator
+        ca_comm = adapter
+        pynccl_comm = None
+
+    def original(self, t):
+        return "vllm-chain"
+
+    small = torch.ones(8, 16)
+    assert torch.equal(va.forced_all_reduce(Host(), small, "ooverlap", original), small * 4)
+    big = torch.ones(64, 64)  # 16 KiB against 4 KiB slots: four pieces of 16 rows
+    out = va.forced_all_reduce(Host(), big, "ooverlap", original)
+    assert torch.equal(out, big * 4) and out.data_ptr() != big.data_ptr()
+    assert adapter.stats() == {"served": 1, "served_in_pieces": 1, "declined": {}}
+    assert [c for c in adapter.comm.calls if c[0] == "ar"][-4:] == [("ar", (16, 64))] * 4
+    wrong = torch.ones(8, 16, dtype=torch.float16)
+    monkeypatch.setenv("VLLM_OOVERLAP_STRICT", "1")
+    with pytest.raises(RuntimeError, match="cannot be served"):
+        va.forced_all_reduce(Host(), wrong, "ooverlap", original)
+    monkeypatch.setenv("VLLM_OOVERLAP_STRICT", "0")
+    assert va.forced_all_reduce(Host(), wrong, "ooverlap", original) == "vllm-chain"
+    assert sum(adapter.stats()["declined"].values()) == 2
+    # the comparison arms raise as well when their backend is missing
+    with pytest.raises(RuntimeError, match="pynccl"):
+        va.forced_all_reduce(Host(), small, "pynccl", original)
+
+    class NoBackend:
+        ca_comm = None
+
+    with pytest.raises(RuntimeError):
+        va.forced_all_reduce(NoBackend(), small, "ooverlap", original)
+    with pytest.raises(RuntimeError, match="custom"):
+        va.forced_all_reduce(NoBackend(), small, "custom", original)
+
+    class Pynccl:
+        disabled = False
+
+        def all_reduce(self, t):
+            return t + 1
+
+    class Host2:
+        ca_comm = None
+        pynccl_comm = Pynccl()
+
+    assert torch.equal(va.forced_all_reduce(Host2(), small, "pynccl", original), small + 1)
+
+
+def test_stats_file_written_at_close(adapter, monkeypatch, tmp_path):
+    import json
+    monkeypatch.setattr(torch.Tensor, "is_cuda", property(lambda self: True))
+    path = tmp_path / "stats.jsonl"
+    monkeypatch.setenv("VLLM_OOVERLAP_STATS_FILE", str(path))
+    adapter.custom_all_reduce(torch.ones(8, 16))
+    adapter.custom_all_reduce(torch.ones(3))
+    adapter.close()
+    rec = json.loads(path.read_text().strip())
+    assert rec["served"] == 1 and rec["declined"] == {"size is not a multiple of 16 bytes": 1} and rec["world"] == 4
