@@ -25,6 +25,13 @@ cudaError_t launch_all_gather(const CommCtx& ctx, int dtype, int algo, const Pee
                               size_t src_local_emu_stride, void* dst_local, size_t dst_local_emu_stride,
                               size_t count, int max_ctas, cudaStream_t stream);
 
+// One-barrier push all-reduce for small messages (allreduce_push.cu): `in_local` / `out_local` are ordinary device
+// memory; `staging` is a registered area of world * piece_bytes that must come from a ring of two or more areas used
+// round robin.  `use_mc`: push with multimem.st through the switch.
+cudaError_t launch_allreduce_push(const CommCtx& ctx, int dtype, int op, bool use_mc, const PeerPtrs& staging,
+                                  size_t piece_bytes, const void* in_local, size_t in_emu_stride, void* out_local,
+                                  size_t out_emu_stride, size_t count, int max_ctas, cudaStream_t stream);
+
 // Rank r's chunk j (chunk_bytes each, `src_local` holds `world` of them) lands as chunk r of rank j's registered
 // `out` buffer (all_to_all.cu).
 cudaError_t launch_all_to_all(const CommCtx& ctx, const PeerPtrs& out, const void* src_local, size_t src_emu_stride,

@@ -1183,6 +1183,10 @@ cudaError_t launch_mode(const CommCtx& ctx, const GemmArgs& a, cudaStream_t stre
   const int tiles = ((a.M + kTileM - 1) / kTileM) * ((a.N + kTileN - 1) / kTileN);
   const int splits = (MODE == kGemmPlain && a.splits > 1) ? a.splits : 1;
   int budget = a.max_ctas > 0 ? a.max_ctas : sm_count();
+  // The fused modes use blockIdx.x as the slot of their rank barriers: the grid must stay inside the inbox rows of
+  // the signal pad (a larger part, or a caller asking for more CTAs, would write into the peers' epoch words).
+  static_assert(kPadInboxWords == kMaxCommBlocks * kMaxRanks, "one inbox row per CTA that may take part in a rank barrier");
+  if (MODE != kGemmPlain && budget > kMaxCommBlocks) budget = kMaxCommBlocks;
   if (emu) budget = budget / world;
   int comm = MODE == kGemmPlain ? 0 : (a.comm_ctas > 0 ? a.comm_ctas : 16);
   if (comm > budget / 2) comm = budget / 2;

@@ -53,16 +53,16 @@ CommCtx oob_comm::make_ctx() const {
   return c;
 }
 
-bool oob_comm::peer_ptrs(int reg, uint64_t off, PeerPtrs* out) const {
+bool oob_comm::peer_ptrs(int reg, uint64_t off, uint64_t bytes, PeerPtrs* out) const {
   std::memset(out, 0, sizeof(*out));
   if (reg == 0) {
-    if (off > heap_bytes) return false;
+    if (off > heap_bytes || bytes > heap_bytes - off) return false;
     for (int r = 0; r < world; ++r) out->p[r] = heap[r] + off;
     out->mc = heap_mc ? heap_mc + off : nullptr;
     return true;
   }
   auto it = regs.find(reg);
-  if (it == regs.end() || off > it->second.bytes) return false;
+  if (it == regs.end() || off > it->second.bytes || bytes > it->second.bytes - off) return false;
   for (int r = 0; r < world; ++r) out->p[r] = static_cast<char*>(it->second.peer[r]) + off;
   out->mc = nullptr;
   return true;
@@ -647,6 +647,12 @@ int oob_register_ipc(oob_comm* c, void* ptr, uint64_t bytes, int* reg) {
   int rc = check_comm(c);
   if (rc != OOB_OK) return rc;
   if (ptr == nullptr || reg == nullptr || bytes == 0) return set_error(OOB_ERR_INVALID, "bad argument");
+  // The kernels move 16-byte packs: a registered view that starts off a 16-byte boundary (a tensor slice with a
+  // storage offset) would trap in them.  Every rank checks its own pointer and all ranks agree on the outcome below,
+  // so that nobody registers while a peer refuses.
+  const bool aligned = (reinterpret_cast<uintptr_t>(ptr) & 15) == 0;
+  if ((c->emulated || c->world == 1) && !aligned)
+    return set_error(OOB_ERR_INVALID, "registered memory must start on a 16-byte boundary");
   oob_comm::Registration R;
   R.local = ptr;
   R.bytes = bytes;
@@ -667,6 +673,7 @@ int oob_register_ipc(oob_comm* c, void* ptr, uint64_t bytes, int* reg) {
     int pad;
   } mine{};
   mine.ok = 0;
+  mine.pad = aligned ? 0 : 1;
   CUdeviceptr base = 0;
   size_t range = 0;
   if (d && d->cuMemGetAddressRange(&base, &range, reinterpret_cast<CUdeviceptr>(ptr)) == CUDA_SUCCESS) {
@@ -680,6 +687,10 @@ int oob_register_ipc(oob_comm* c, void* ptr, uint64_t bytes, int* reg) {
   }
   std::vector<Desc> all(c->world);
   if (!c->boot->allgather(&mine, all.data(), sizeof(Desc))) return set_error(OOB_ERR_BOOTSTRAP, c->boot->last_error());
+  for (auto& x : all)
+    if (x.pad != 0)
+      return set_error(OOB_ERR_INVALID, "registered memory must start on a 16-byte boundary on every rank (a rank passed "
+                                        "a view with a storage offset that is not a multiple of 16 bytes)");
   for (auto& x : all)
     if (!x.ok)
       return set_error(OOB_ERR_UNSUPPORTED,
@@ -762,13 +773,14 @@ int oob_allreduce(oob_comm* c, int dtype, int op, int algo, int in_reg, uint64_t
   }
   if (max_ctas <= 0) max_ctas = 16;
   PeerPtrs in, out;
-  if (!c->peer_ptrs(in_reg, in_off, &in)) return set_error(OOB_ERR_INVALID, "bad input buffer");
+  if (!c->peer_ptrs(in_reg, in_off, count * esize, &in))
+    return set_error(OOB_ERR_INVALID, "bad input buffer (offset + count lies outside the heap / the registration)");
   const bool one_shot = (algo == OOB_AR_ONESHOT_P2P || algo == OOB_AR_ONESHOT_NVLS);
   if (one_shot) {
     if (out_local == nullptr) return set_error(OOB_ERR_INVALID, "one-shot all-reduce needs out_local");
     std::memset(&out, 0, sizeof(out));
-  } else if (!c->peer_ptrs(out_reg, out_off, &out)) {
-    return set_error(OOB_ERR_INVALID, "two-shot all-reduce needs a registered output buffer");
+  } else if (!c->peer_ptrs(out_reg, out_off, count * esize, &out)) {
+    return set_error(OOB_ERR_INVALID, "two-shot all-reduce needs a registered output buffer that holds count elements");
   }
   if ((in_off & 15) || (!one_shot && (out_off & 15)))
     return set_error(OOB_ERR_INVALID, "registered all-reduce buffers must be 16-byte aligned");
@@ -793,7 +805,7 @@ int oob_reduce_scatter(oob_comm* c, int dtype, int op, int algo, int in_reg, uin
   }
   if (max_ctas <= 0) max_ctas = 16;
   PeerPtrs in;
-  if (!c->peer_ptrs(in_reg, in_off, &in) || (in_off & 15)) return set_error(OOB_ERR_INVALID, "bad input buffer");
+  if (!c->peer_ptrs(in_reg, in_off, count * esize, &in) || (in_off & 15)) return set_error(OOB_ERR_INVALID, "bad input buffer");
   if (out_local == nullptr) return set_error(OOB_ERR_INVALID, "null output");
   // Emulation: rank r's output block is out_local + r * ceil(count / world) elements.
   const uint64_t emu_stride = c->emulated ? ((count + c->world - 1) / c->world) * esize : 0;
@@ -816,7 +828,10 @@ int oob_all_gather(oob_comm* c, int dtype, int algo, int out_reg, uint64_t out_o
   }
   if (max_ctas <= 0) max_ctas = 16;
   PeerPtrs out;
-  if (!c->peer_ptrs(out_reg, out_off, &out) || (out_off & 15)) return set_error(OOB_ERR_INVALID, "bad registered buffer");
+  // Push: the registered buffer receives all `count` elements.  Pull: it holds this rank's shard.
+  const uint64_t reg_elems = algo == OOB_AG_PULL_P2P ? (count + c->world - 1) / c->world : count;
+  if (!c->peer_ptrs(out_reg, out_off, reg_elems * esize, &out) || (out_off & 15))
+    return set_error(OOB_ERR_INVALID, "bad registered buffer");
   if (algo == OOB_AG_PULL_P2P) {
     if (dst_local == nullptr) return set_error(OOB_ERR_INVALID, "pull all-gather needs dst_local");
   } else if (src_local == nullptr) {
@@ -831,6 +846,28 @@ int oob_all_gather(oob_comm* c, int dtype, int algo, int out_reg, uint64_t out_o
   return OOB_OK;
 }
 
+int oob_allreduce_push(oob_comm* c, int dtype, int op, int stage_reg, uint64_t stage_off, uint64_t piece_bytes,
+                       const void* in_local, void* out_local, uint64_t count, int use_nvls, int max_ctas, void* stream) {
+  int rc = check_comm(c);
+  if (rc != OOB_OK) return rc;
+  if (count == 0) return OOB_OK;
+  if (dtype != OOB_F16 && dtype != OOB_BF16 && dtype != OOB_F32) return set_error(OOB_ERR_INVALID, "bad dtype");
+  if (op != OOB_SUM && op != OOB_MIN && op != OOB_MAX) return set_error(OOB_ERR_INVALID, "bad reduction");
+  if (in_local == nullptr || out_local == nullptr) return set_error(OOB_ERR_INVALID, "null input or output");
+  const uint64_t esize = dtype == OOB_F32 ? 4 : 2;
+  if ((piece_bytes & 15) || count * esize > piece_bytes)
+    return set_error(OOB_ERR_INVALID, "piece_bytes must be a multiple of 16 and hold the message");
+  PeerPtrs st;
+  if ((stage_off & 15) || !c->peer_ptrs(stage_reg, stage_off, piece_bytes * c->world, &st))
+    return set_error(OOB_ERR_INVALID, "bad staging area (16-byte aligned, world * piece_bytes inside the registration)");
+  const bool mc = use_nvls != 0 && st.mc != nullptr;
+  const uint64_t emu_stride = c->emulated ? count * esize : 0;
+  cudaError_t e = launch_allreduce_push(c->make_ctx(), dtype, op, mc, st, piece_bytes, in_local, emu_stride, out_local,
+                                        emu_stride, count, max_ctas, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "push all-reduce launch");
+  return OOB_OK;
+}
+
 int oob_all_to_all(oob_comm* c, int dtype, int out_reg, uint64_t out_off, const void* src_local, uint64_t count_per_peer,
                    int max_ctas, void* stream) {
   int rc = check_comm(c);
@@ -840,7 +877,8 @@ int oob_all_to_all(oob_comm* c, int dtype, int out_reg, uint64_t out_off, const 
   if (src_local == nullptr) return set_error(OOB_ERR_INVALID, "all-to-all needs src_local");
   const uint64_t chunk = count_per_peer * (dtype == OOB_F32 ? 4 : 2);
   PeerPtrs out;
-  if (!c->peer_ptrs(out_reg, out_off, &out) || (out_off & 15)) return set_error(OOB_ERR_INVALID, "bad registered buffer");
+  if (!c->peer_ptrs(out_reg, out_off, chunk * c->world, &out) || (out_off & 15))
+    return set_error(OOB_ERR_INVALID, "bad registered buffer");
   const uint64_t src_stride = c->emulated ? chunk * c->world : 0;
   cudaError_t e = launch_all_to_all(c->make_ctx(), out, src_local, src_stride, chunk, max_ctas,
                                     static_cast<cudaStream_t>(stream));
@@ -879,16 +917,19 @@ int oob_fused_norm(oob_comm* c, int algo, const oob_norm_args_t* a, int max_ctas
   n.rows = a->rows;
   n.hidden = a->hidden;
   n.eps = a->eps;
-  if (!c->peer_ptrs(a->x_reg, a->x_off, &n.x) || (a->x_off & 15)) return set_error(OOB_ERR_INVALID, "bad x buffer");
+  if (a->rows <= 0 || a->hidden <= 0) return set_error(OOB_ERR_INVALID, "bad shape");
+  const uint64_t norm_bytes = uint64_t(a->rows) * a->hidden * (a->dtype == OOB_F32 ? 4 : 2);
+  if (!c->peer_ptrs(a->x_reg, a->x_off, norm_bytes, &n.x) || (a->x_off & 15)) return set_error(OOB_ERR_INVALID, "bad x buffer");
   n.residual = a->residual;
   n.residual_emu_stride = c->emulated ? a->emu_stride_local : 0;
   n.weight = a->weight;
   if (a->weight == nullptr) return set_error(OOB_ERR_INVALID, "null norm weight");
   const bool push = (algo == OOB_NORM_AR_TWOSHOT || algo == OOB_NORM_AR_TWOSHOT_NVLS);
   if (push) {
-    if (!c->peer_ptrs(a->y_reg, a->y_off, &n.y) || (a->y_off & 15)) return set_error(OOB_ERR_INVALID, "bad y buffer");
+    if (!c->peer_ptrs(a->y_reg, a->y_off, norm_bytes, &n.y) || (a->y_off & 15)) return set_error(OOB_ERR_INVALID, "bad y buffer");
     if (a->res_out_reg >= 0) {
-      if (!c->peer_ptrs(a->res_out_reg, a->res_out_off, &n.res_out)) return set_error(OOB_ERR_INVALID, "bad res_out buffer");
+      if (!c->peer_ptrs(a->res_out_reg, a->res_out_off, norm_bytes, &n.res_out) || (a->res_out_off & 15))
+        return set_error(OOB_ERR_INVALID, "bad res_out buffer");
     } else {
       std::memset(&n.res_out, 0, sizeof(n.res_out));
     }
@@ -987,15 +1028,19 @@ int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream) {
   g.res_out_local = a->res_out_local;
   g.rs_emu_stride = emu ? a->rs_emu_stride : 0;
   if (a->mode == OOB_GEMM_AR || a->mode == OOB_GEMM_RS_NORM) {
-    if (!c->peer_ptrs(a->partial_reg, a->partial_off, &g.partial)) return set_error(OOB_ERR_INVALID, "bad partial buffer");
+    if (a->M <= 0 || a->N <= 0) return set_error(OOB_ERR_INVALID, "bad shape");
+    if (!c->peer_ptrs(a->partial_reg, a->partial_off, oob_gemm_partial_bytes(a->M, a->N), &g.partial))
+      return set_error(OOB_ERR_INVALID, "bad partial buffer (it must hold oob_gemm_partial_bytes(M, N))");
     if (a->partial_off & 1023) return set_error(OOB_ERR_INVALID, "partial buffer must be 1 KiB aligned");
   }
   if (a->mode == OOB_GEMM_AR) {
-    if (!c->peer_ptrs(a->c_reg, a->c_off, &g.c_sym) || (a->c_off & 15)) return set_error(OOB_ERR_INVALID, "bad C buffer");
+    if (!c->peer_ptrs(a->c_reg, a->c_off, uint64_t(a->M) * a->N * 2, &g.c_sym) || (a->c_off & 15))
+      return set_error(OOB_ERR_INVALID, "bad C buffer");
   }
   if (a->mode == OOB_GEMM_RS_NORM && a->y_local == nullptr) return set_error(OOB_ERR_INVALID, "null y_local");
   if (a->mode == OOB_GEMM_AG) {
-    if (!c->peer_ptrs(a->a_full_reg, a->a_full_off, &g.a_full) || (a->a_full_off & 127))
+    if (a->M <= 0 || a->K <= 0 || !c->peer_ptrs(a->a_full_reg, a->a_full_off, uint64_t(a->M) * a->K * 2, &g.a_full) ||
+        (a->a_full_off & 127))
       return set_error(OOB_ERR_INVALID, "bad gathered-A buffer");
   }
   cudaError_t e = launch_gemm(ctx, g, static_cast<cudaStream_t>(stream));

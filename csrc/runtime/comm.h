@@ -62,5 +62,7 @@ struct oob_comm {
   uint64_t use_clock = 0;
 
   oob::CommCtx make_ctx() const;
-  bool peer_ptrs(int reg, uint64_t off, oob::PeerPtrs* out) const;
+  // Pointer table of the `bytes` bytes at `off` of registration `reg` (0 = the heap); false when the range does not lie
+  // inside the heap / the registration.
+  bool peer_ptrs(int reg, uint64_t off, uint64_t bytes, oob::PeerPtrs* out) const;
 };

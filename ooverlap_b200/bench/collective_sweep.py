@@ -79,8 +79,33 @@ def timed(fn, iters, warmup, world):
     return min(once(reps), once(reps))
 
 
+def latency_stats(fn, iters, warmup) -> dict:
+    """p50 / p90 / p99 of the per-replay latencies (microseconds per call, max over ranks), for the latency tables."""
+    from ..utils.timing import graph_timed
+    t = graph_timed(fn, iters, warmup, per_graph=PER_GRAPH, min_ms=5.0, max_reps=200)
+    return {k: round(t[k], 2) for k in ("p50", "p90", "p99")}
+
+
+def merge_policies(paths, out_path: str, comment: str = "") -> int:
+    """Merges policy files (as written by ``--policy``) into one: points of the same (world, collective, nvls, bytes)
+    are replaced by the later file's.  Returns the number of points."""
+    merged = {}
+    for path in paths:
+        with open(path) as f:
+            data = json.load(f)
+        comment = comment or data.get("comment", "")
+        for pt in data["points"]:
+            merged[(pt["world"], pt["collective"], pt["nvls"], pt["bytes"])] = pt
+    pts = [merged[k] for k in sorted(merged)]
+    with open(out_path, "w") as f:
+        json.dump({"comment": comment, "points": pts}, f, indent=1)
+    return len(pts)
+
+
 def main() -> int:
     p = argparse.ArgumentParser()
+    p.add_argument("--merge", nargs="+", default=None, metavar="POLICY.json",
+                   help="no measurement: merge these policy files (later files win) into --policy and exit")
     p.add_argument("--min-bytes", type=int, default=1 << 10)
     p.add_argument("--max-bytes", type=int, default=1 << 30)
     p.add_argument("--iters", type=int, default=50)
@@ -89,7 +114,14 @@ def main() -> int:
     p.add_argument("--collectives", default="all_reduce,reduce_scatter,all_gather")
     p.add_argument("--out", default="")
     p.add_argument("--policy", default="")
+    p.add_argument("--stats-max-bytes", type=int, default=0,
+                   help="for messages up to this size also report p50 / p90 / p99 of the best configuration and of NCCL")
     args = p.parse_args()
+    if args.merge:
+        if not args.policy:
+            raise SystemExit("--merge needs --policy OUT.json")
+        print(f"{merge_policies(args.merge, args.policy)} points -> {args.policy}")
+        return 0
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -107,13 +139,14 @@ def main() -> int:
     nccl_out = torch.empty_like(src)
     cta_list = [int(c) for c in args.ctas.split(",")]
     lines, best = [], {}
+    comm.init_round_robin_slots(dtype, 8 << 20, 8)  # the ring behind all_reduce_round_robin / the push kernel
 
     def record(coll, nbytes, impl, algo_name, algo, ctas, sec):
         rec = {"collective": coll, "world": world, "bytes": nbytes, "impl": impl, "algo": algo_name, "ctas": ctas,
                "us": round(sec * 1e6, 2), "bus_gbs": round(bus_bandwidth_gbs(coll, world, nbytes, sec), 1),
                "nvls": int(comm.nvls)}
         lines.append(rec)
-        if impl == "ours":
+        if impl == "ours":  # registered-buffer algorithms only: the ring arms are not policy candidates
             # Two policies: for communicators with an NVLS alias (any algorithm may win) and without one.
             for has_nvls in ((1, 0) if "nvls" not in algo_name else (1,)):
                 if has_nvls and not comm.nvls:
@@ -144,6 +177,35 @@ def main() -> int:
                         fn = lambda: comm.all_reduce(sym_in[:n], algo=algo, max_ctas=ctas)  # noqa: E731
                     record("all_reduce", size, "ours", AR_NAMES[algo], algo, ctas, timed(fn, iters, args.warmup, world))
             sym_in.copy_(src)  # in-place sums grow; refresh
+            # The ring path an application (the vLLM hook) takes for an ordinary tensor: the one-barrier push kernel
+            # for small messages, else copy into the slot + in-place all-reduce.
+            if size <= (8 << 20) // (world + 1):
+                x = src[:n]
+                if comm.all_reduce_push(x) is not None:
+                    record("all_reduce", size, "ours_ring", "push", -2, 0,
+                           timed(lambda: comm.all_reduce_push(x), iters, args.warmup, world))
+                saved = comm.config.push_max_bytes
+                comm.config.push_max_bytes = 0
+                record("all_reduce", size, "ours_ring", "copy+inplace", -3, 0,
+                       timed(lambda: comm.all_reduce_round_robin(x), iters, args.warmup, world))
+                comm.config.push_max_bytes = saved
+            if size <= args.stats_max_bytes:
+                x = src[:n]
+                arms = {"nccl": lambda: dist.all_reduce(nccl_buf[:n]), "ours_ring": lambda: comm.all_reduce_round_robin(x)}
+                key = ("all_reduce", size, 1 if comm.nvls else 0)
+                if key in best:
+                    _, b_algo, b_ctas = best[key]
+                    if b_algo in (_lib.AR_ONESHOT_P2P, _lib.AR_ONESHOT_NVLS):
+                        arms["ours_best"] = lambda: comm.all_reduce_out(sym_in[:n], sym_out[:n], algo=b_algo, max_ctas=b_ctas)
+                    else:
+                        arms["ours_best"] = lambda: comm.all_reduce(sym_in[:n], algo=b_algo, max_ctas=b_ctas)
+                for name, fn in arms.items():
+                    rec = {"collective": "all_reduce", "world": world, "bytes": size, "impl": name, "stat": "latency_us",
+                           **latency_stats(fn, iters, args.warmup)}
+                    lines.append(rec)
+                    if rank == 0:
+                        print(json.dumps(rec), flush=True)
+                sym_in.copy_(src)
         if "reduce_scatter" in args.collectives and n >= world:
             b, e = partition(n, world, rank)
             sec = timed(lambda: dist.reduce_scatter_tensor(nccl_out[: n // world], nccl_buf[: n // world * world]), iters,

@@ -45,6 +45,7 @@ def main() -> int:
     p.add_argument("--comm-ctas", type=int, default=16)
     p.add_argument("--nvls", default="auto", choices=["auto", "on", "off", "pull"])
     p.add_argument("--no-join", action="store_true")
+    p.add_argument("--kernel", default=None, choices=["pair", "one_sm"], help="fused kernel (default: the library's choice)")
     args = p.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -57,10 +58,10 @@ def main() -> int:
     a = torch.randn(args.m, kl, device="cuda").to(dt)
     b = (torch.randn(args.n, kl, device="cuda") / args.k ** 0.5).to(dt)
     if args.op == "gemm_ar":
-        op = GemmAllReduce(comm, args.m, args.n, dt, comm_ctas=args.comm_ctas, use_nvls=nv, strategy="fused")
+        op = GemmAllReduce(comm, args.m, args.n, dt, comm_ctas=args.comm_ctas, use_nvls=nv, strategy="fused", kernel=args.kernel)
         run = lambda: op(a, b)  # noqa: E731
     else:
-        op = GemmReduceScatterNorm(comm, args.m, args.n, dt, comm_ctas=args.comm_ctas, use_nvls=nv)
+        op = GemmReduceScatterNorm(comm, args.m, args.n, dt, comm_ctas=args.comm_ctas, use_nvls=nv, kernel=args.kernel)
         w = torch.ones(args.n, device="cuda", dtype=dt)
         res = torch.zeros(args.m // world, args.n, device="cuda", dtype=dt)
         run = lambda: op(a, b, w, res)  # noqa: E731
@@ -84,7 +85,7 @@ def main() -> int:
     rel = lambda col, rows: [(int(v) - t0) / 1e3 if int(v) > 0 else None for v in rows[:, col]]  # noqa: E731
     gemm_rows, comm_rows = used[used[:, 7] == 0], used[used[:, 7] == 1]
     out = {"rank": rank, "op": args.op, "M": args.m, "N": args.n, "K": args.k, "tp": world, "comm_ctas": args.comm_ctas,
-           "nvls": args.nvls, "join": not args.no_join, "kernel_us": round(e0.elapsed_time(e1) * 1e3, 1),
+           "nvls": args.nvls, "join": not args.no_join, "kernel": args.kernel or "auto", "kernel_us": round(e0.elapsed_time(e1) * 1e3, 1),
            "ctas": int(used.shape[0]), "gemm_ctas": int(gemm_rows.shape[0])}
     out.update(summarize("gemm_done_us", rel(1, gemm_rows)))
     out.update(summarize("gemm_cta_first_reduce_ready_us", rel(2, gemm_rows)))

@@ -6,9 +6,10 @@ Launch with one process per GPU::
         -m ooverlap_b200.bench.serving_bench --model llama3-70b --batches 1,16,64,256 --in-len 1024 --out-len 128
 
 Random-init bf16 weights of the named architecture, uniform-random token-id prompts, greedy decoding.  For every
-batch size it runs the ``ours`` backend (tcgen05 GEMMs, fused all-reduce + residual + RMSNorm over NVLink, decode
-step replayed from a CUDA graph) and the ``nccl`` backend (cuBLAS + NCCL all-reduce + PyTorch RMSNorm, eager, the
-way the reference's paper-like vLLM runs were configured) and prints one JSON line per (backend, batch) with the
+batch size it runs the ``ours`` backend (tcgen05 GEMMs, fused all-reduce + residual + RMSNorm over NVLink) and the
+``nccl`` backend (cuBLAS + NCCL all-reduce + PyTorch RMSNorm), BOTH with the decode step replayed from a CUDA graph
+(``--no-graph`` runs both eagerly; a backend whose capture fails is re-run eagerly and its line says so), and
+prints one JSON line per (backend, batch) with the
 wall time of prefill + decode, the decode-only time, and output tokens per second (batch * out_len / total).
 
 Capability parity: test/benchmark_vllm_paperlike.py:1-140 and evalution/run_vllm_paperlike.sh:7-120 of the
@@ -80,7 +81,20 @@ def main() -> int:
                 dist.barrier()
             torch.cuda.synchronize()
             t0 = time.perf_counter()
-            toks = model.generate(prompts, args.out_len, use_graph=(backend == "ours" and not args.no_graph))
+            graphed = not args.no_graph
+            try:
+                toks = model.generate(prompts, args.out_len, use_graph=graphed)
+            except Exception as e:  # capture refused (e.g. a collective that cannot be captured): measure eagerly
+                if not graphed:
+                    raise
+                if rank == 0:
+                    print(f"{backend}: CUDA-graph capture failed ({type(e).__name__}: {e}); eager run", file=sys.stderr)
+                graphed = False
+                torch.cuda.synchronize()
+                if world > 1:
+                    dist.barrier()
+                t0 = time.perf_counter()
+                toks = model.generate(prompts, args.out_len, use_graph=False)
             torch.cuda.synchronize()
             total = time.perf_counter() - t0
             t = torch.tensor([total, t_prefill], dtype=torch.float64, device=dev)
@@ -91,6 +105,7 @@ def main() -> int:
                    "batch": b, "in_len": args.in_len, "out_len": args.out_len, "total_s": round(total, 4),
                    "prefill_s": round(t_prefill, 4), "decode_ms_per_token": round((total - t_prefill) / max(1, args.out_len - 1) * 1e3, 3),
                    "output_tok_s": round(b * args.out_len / total, 1), "dtype": "bf16", "data": "synthetic",
+                   "decode_graph": graphed,
                    "checksum": int(toks.sum().item()) % 1000003, "first": int(first[0, 0]),
                    # switches that change which kernels run (recorded so that lines from different runs can be told apart)
                    "switches": {k: os.environ[k] for k in ("OOB_FUSED_EPILOGUES", "OOB_PREFILL_CHUNKS", "OOB_GEMM_GEMV",

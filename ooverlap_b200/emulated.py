@@ -120,6 +120,15 @@ class EmulatedGroup:
             self._h, dtype_code(dtype), op_code(op), algo, 0, in_off, 0 if out_off is not None else -1, out_off or 0,
             ctypes.c_void_p(out_local.data_ptr()) if out_local is not None else None, count, max_ctas, _stream()))
 
+    def all_reduce_push(self, stage_off: int, piece_bytes: int, x: torch.Tensor, out: torch.Tensor, op: str = "sum", *,
+                        max_ctas: int = 4) -> None:
+        """One-barrier push all-reduce: ``x`` and ``out`` are ``[world, count]`` (row r = rank r's input / result),
+        the staging area is ``world * piece_bytes`` at ``stage_off`` of every rank's heap."""
+        assert x.shape[0] == self.world and out.shape == x.shape and x.is_contiguous() and out.is_contiguous()
+        _lib.check(_lib.lib().oob_allreduce_push(self._h, dtype_code(x.dtype), op_code(op), 0, stage_off, piece_bytes,
+                                                 ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+                                                 x.shape[1], 0, max_ctas, _stream()))
+
     def reduce_scatter(self, in_off: int, count: int, dtype: torch.dtype, out_local: torch.Tensor, op: str = "sum", *,
                        algo: int = _lib.RS_P2P, max_ctas: int = 4) -> None:
         """``out_local`` is ``[world, ceil(count / world)]``; row r receives rank r's partition."""

@@ -121,6 +121,8 @@ class GemmAllReduce:
                       the GEMM of slab i + 1 runs on the other SMs: the all-reduce moves each byte once per direction
                       through the switch, which the fused kernel's peer pushes cannot, and only the first GEMM slab
                       is exposed.  For large M from four ranks on;
+      * ``"autotune"`` decided at the first call: every fused variant and the unfused pair are checked and timed on the
+                      real operands, all ranks agree on the fastest (see ``_autotune``; ``tuning`` holds the table);
       * ``"auto"``    (default) what measured best on B200 / NVSwitch: between two ranks the fused kernel; from four
                       ranks on the unfused pair for messages up to 64 MiB (a single wave or few waves of tiles leave
                       nothing to overlap and the NVLS all-reduce moves the message once per direction) and the fused
@@ -133,6 +135,16 @@ class GemmAllReduce:
         self.max_ctas = max_ctas
         self.kernel = _kernel_code(kernel)
         self.multi = comm.world > 1
+        self._tuned = None
+        self.tuning = None
+        if strategy == "autotune":
+            if self.multi and not _emulated(comm):
+                # Decided at the first call, on the real operands (K is not known before): see _autotune.
+                self.strategy, self.chunks, self.use_nvls = "autotune", 1, use_nvls
+                self.comm_ctas = comm_ctas or 0
+                self._tune_args = dict(max_ctas=max_ctas, kernel=kernel)
+                return
+            strategy = "auto"
         sol = None
         if strategy == "auto" and not _emulated(comm):
             # A tuned solution for this shape (OOB_OVERLAP_SOLUTIONS, written by bench.tune_overlap) wins.
@@ -160,8 +172,71 @@ class GemmAllReduce:
     def fused(self) -> bool:
         return self.multi and self.strategy == "fused"
 
+    # ------------------------------------------------------------------------------------------------ autotune
+    def _candidates(self):
+        """(strategy, kernel, use_nvls, comm_ctas) to try: the unfused pair; the two-SM kernel over a few CTA budgets,
+        through the switch when the heap has a multicast alias (and with peer loads/stores between two ranks, where
+        both move the same bytes); the one-SM kernel with pushed partial tiles."""
+        nvls = bool(getattr(self.comm, "nvls", False))
+        cands = [("unfused", None, None, None)]
+        for c in (8, 16, 24, 32):
+            if nvls:
+                cands.append(("fused", "pair", 1, c))
+            if not nvls or self.comm.world == 2:
+                cands.append(("fused", "pair", 0, c))
+        cands.append(("fused", "one_sm", None, 16))
+        return cands
+
+    def _autotune(self, a: torch.Tensor, b: torch.Tensor):
+        """First call of ``strategy="autotune"``: every candidate is built, checked against the unfused pair's result
+        and timed on the real operands (CUDA events, maximum over ranks through this communicator's own all-reduce);
+        the fastest correct one is kept.  All ranks take the same decision.  Costs a few tens of milliseconds and
+        synchronises the device, so the first call must not be inside a CUDA-graph capture."""
+        comm = self.comm
+        cands = self._candidates()
+        times = torch.full((len(cands),), float("inf"), dtype=torch.float32, device=a.device)
+        ref = None
+        iters = 6
+        for i, (strat, kern, nv, c) in enumerate(cands):
+            op = GemmAllReduce(comm, self.M, self.N, self.dtype, comm_ctas=c, use_nvls=nv, strategy=strat, kernel=kern,
+                               max_ctas=self._tune_args["max_ctas"])
+            out = op(a, b)
+            torch.cuda.synchronize()
+            if ref is None:
+                ref = out.clone()
+                ok = True
+            else:
+                scale = max(1.0, float(ref.float().abs().max()))
+                ok = bool((out.float() - ref.float()).abs().max() <= 2e-2 * scale)
+            if ok:
+                op(a, b)
+                comm.barrier()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(iters):
+                    op(a, b)
+                e1.record()
+                torch.cuda.synchronize()
+                times[i] = e0.elapsed_time(e1) / iters * 1e3
+            op.release()
+        # a candidate that failed its check on ANY rank has an infinite time on that rank: the maximum keeps it out
+        finite = torch.where(torch.isinf(times), torch.full_like(times, 3.0e38), times)
+        agreed = comm.all_reduce(finite, op="max").clone()
+        best = int(torch.argmin(agreed).item())
+        strat, kern, nv, c = cands[best]
+        self.tuning = [dict(strategy=s_, kernel=k_, use_nvls=n_, comm_ctas=c_, us=round(float(t), 1) if float(t) < 1e37 else None)
+                       for (s_, k_, n_, c_), t in zip(cands, agreed.tolist())]
+        self._tuned = GemmAllReduce(comm, self.M, self.N, self.dtype, comm_ctas=c, use_nvls=nv, strategy=strat, kernel=kern,
+                                    max_ctas=self._tune_args["max_ctas"])
+        self.strategy, self.comm_ctas, self.use_nvls = self._tuned.strategy, self._tuned.comm_ctas, self._tuned.use_nvls
+        self.kernel = self._tuned.kernel
+        return self._tuned
+
     def output(self, rank: Optional[int] = None) -> torch.Tensor:
         """The [M, N] result buffer in registered memory (of ``rank`` in emulation)."""
+        if self._tuned is not None:
+            return self._tuned.output(rank)
         if _emulated(self.comm):
             return self.comm.view(self.c_off, (self.M, self.N), self.dtype, rank or 0)
         return self._out
@@ -169,6 +244,11 @@ class GemmAllReduce:
     def release(self) -> None:
         """Gives the op's registered buffers and counters back (collective by convention)."""
         if not self.multi:
+            return
+        if self._tuned is not None or self.strategy == "autotune":
+            if self._tuned is not None:
+                self._tuned.release()
+            self.multi = False
             return
         if self.strategy == "fused":
             self.comm.free(self.partial_off)
@@ -179,6 +259,10 @@ class GemmAllReduce:
     def __call__(self, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         if not self.multi:
             return gemm(a, b, max_ctas=self.max_ctas)
+        if self._tuned is not None:
+            return self._tuned(a, b)
+        if self.strategy == "autotune":
+            return self._autotune(a, b)(a, b)
         if self.strategy == "unfused":
             gemm(a, b, out=self._out, max_ctas=self.max_ctas, splits=1)
             return self.comm.all_reduce(self._out)

@@ -1,8 +1,10 @@
 """Per-shape tuning results ("solutions") for the overlap ops.
 
 A solution file is a JSON object ``{"<op>:<M>x<N>x<K>:tp<world>:<dtype>": {"strategy": ..., "comm_ctas": ...,
-"use_nvls": ..., "us": ...}, ...}`` written by ``ooverlap_b200.bench.tune_overlap``.  ``GemmAllReduce`` consults the
-file named by ``OOB_OVERLAP_SOLUTIONS`` before falling back to its built-in rule.
+"use_nvls": ..., "kernel": ..., "us": ...}, ...}`` written by ``ooverlap_b200.bench.tune_overlap``.  ``GemmAllReduce``
+consults the file named by ``OOB_OVERLAP_SOLUTIONS``, else the packaged ``policy/overlap_solutions.json`` (the tuner's
+result on 8 x B200 / NVSwitch for the headline shapes), before falling back to its built-in rule;
+``OOB_OVERLAP_SOLUTIONS=none`` turns the lookup off.
 
 Capability parity: the reference saves one solution JSON per (M, N, K, backend) with the searched segment sizes,
 tile order and SM split (tool/search.py:355-421, test/test.py:805-820) and its benchmark loads it back.
@@ -15,6 +17,7 @@ import tempfile
 from typing import Optional
 
 _cache = {}
+PACKAGED = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "policy", "overlap_solutions.json")
 
 
 def key(op: str, M: int, N: int, K: int, world: int, dtype: str) -> str:
@@ -36,8 +39,8 @@ def load(path: str) -> dict:
 
 def lookup(op: str, M: int, N: int, K: int, world: int, dtype: str, path: Optional[str] = None) -> Optional[dict]:
     """The stored solution for a shape; K == 0 matches any K of that (op, M, N)."""
-    path = path or os.environ.get("OOB_OVERLAP_SOLUTIONS", "")
-    if not path:
+    path = path or os.environ.get("OOB_OVERLAP_SOLUTIONS", "") or PACKAGED
+    if path == "none" or not os.path.exists(path):
         return None
     table = load(path)
     hit = table.get(key(op, M, N, K, world, dtype))

@@ -178,3 +178,27 @@ def test_heap_allocator_reuses_freed_blocks():
     with pytest.raises(OobError):
         g.free(12345)
     g.close()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("n", [1, 7, 8, 4096, 4097, 65536 + 24])
+@pytest.mark.parametrize("op", ["sum", "max"])
+def test_all_reduce_push_one_barrier(group, n, dtype, op):
+    """Every rank pushes its unregistered input into its piece of a staging area on all ranks, one barrier, local sum in
+    rank order.  Odd counts make the ranks' rows start off a 16-byte boundary (element-wise local accesses) while the
+    staging pieces stay aligned.  Two staging areas are used in turn, as a ring would, for three calls in a row."""
+    esize = torch.empty((), dtype=dtype).element_size()
+    piece = (n * esize + 255) // 256 * 256
+    stages = [group.alloc(group.world * piece) for _ in range(2)]
+    for it in range(3):
+        gen = torch.Generator(device="cuda").manual_seed(n * 10 + it)
+        x = (torch.rand(group.world, n, device="cuda", generator=gen) * 2 - 1).to(dtype)
+        out = torch.zeros_like(x)
+        group.all_reduce_push(stages[it % 2], piece, x, out, op, max_ctas=3)
+        group.check_status()
+        want = _reduce(list(x), op)
+        for r in range(group.world):
+            assert (out[r].float() - want).abs().max().item() <= TOL[dtype] * group.world, (it, r)
+            assert torch.equal(out[r], out[0])
+    for s in reversed(stages):
+        group.free(s)
