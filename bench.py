@@ -46,7 +46,7 @@ def parse_args():
     p.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl_cublas"])
     p.add_argument("--comm-ctas", type=int, default=int(os.environ.get("OOB_BENCH_COMM_CTAS", "0")),
                    help="communication CTAs of the fused kernel (0 = the library's choice per shape)")
-    p.add_argument("--strategy", default="auto", choices=["auto", "fused", "unfused", "chunked"])
+    p.add_argument("--strategy", default="auto", choices=["auto", "autotune", "fused", "unfused", "chunked"])
     p.add_argument("--kernel", default=None, choices=["pair", "one_sm"], help="fused kernel (default: the library's choice)")
     p.add_argument("--nvls", type=int, default=-1, help="fused kernel: 0 = peer loads/stores, 1/2 = through the switch, -1 = default")
     p.add_argument("--no-baseline", action="store_true", help="skip the cuBLAS + NCCL arm of --impl ours")
@@ -116,7 +116,7 @@ def main() -> int:
                              use_nvls=None if args.nvls < 0 else args.nvls)
 
     if args.impl == "ours" and world > 1:
-        heap = sum(2 * m * N_DIM * 2 for m in MS) + (64 << 20)
+        heap = sum(3 * m * N_DIM * 2 for m in MS) + (128 << 20)
         comm = Communicator(list(range(world)), rank, heap_bytes=heap)
         for m in MS:
             ops[m] = make_op(m, args.strategy)
@@ -154,8 +154,27 @@ def main() -> int:
             del ref
         return bad
 
-    step(0)
-    fence()
+    timed_out = False
+    try:
+        step(0)
+        fence()
+        if comm is not None:
+            comm.check_status()
+    except Exception as e:  # a kernel gave up waiting for a peer (bounded wait): say so, recover, use the unfused pair
+        if comm is None:
+            raise
+        print(f"rank {rank}: first step failed: {e}", file=sys.stderr)
+        timed_out = True
+    if not all_ranks_agree(not timed_out):
+        comm.recover()
+        for m in MS:
+            if ops[m].strategy != "unfused":
+                fallback[str(m)] = f"{ops[m].strategy} strategy hit a device timeout on the first step; unfused used"
+                ops[m].release()
+                ops[m] = make_op(m, "unfused")
+        step(0)
+        fence()
+        comm.check_status()
     bad = verify(0, lambda m: outs[m] if args.impl == "ours" else base_outs[m])
     for m in MS:
         m_bad = not all_ranks_agree(m not in bad)
@@ -314,6 +333,9 @@ def main() -> int:
                        "l2": f"{ROTATE} operand sets rotated between steps; per-step working set exceeds the 126 MB L2",
                        "strategy": {str(m): (ops[m].strategy if m in ops else "gemm") for m in MS},
                        "comm_ctas": {str(m): (ops[m].comm_ctas if m in ops and ops[m].strategy == "fused" else 0) for m in MS},
+                       "kernel": {str(m): ({1: "pair", -1: "one_sm", 0: "auto"}.get(ops[m].kernel, "auto")
+                                           if m in ops and ops[m].strategy == "fused" else "") for m in MS},
+                       "autotune": {str(m): ops[m].tuning for m in MS if m in ops and getattr(ops[m], "tuning", None)} or None,
                        "fallback": fallback or None},
             "verified": f"all {len(MS)} shapes against an fp32 reference before and after the timed loop, tolerance "
                         f"{TOL} x max(1, |ref|max)",

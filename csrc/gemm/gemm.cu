@@ -228,9 +228,10 @@ int gemm_counters_needed(int mode, int M, int N, int world) {
   const int tiles_m = (M + kTileM - 1) / kTileM, tiles_n = (N + kTileN - 1) / kTileN;
   switch (mode) {
     case kGemmAr: {
-      // one-SM kernel: per-tile arrivals + ticket; two-SM kernel: one arrival counter per owned 128x256 half tile
+      // one-SM kernel: per-tile arrivals + ticket; two-SM kernel: arrivals + finished work items per owned 128x256
+      // half tile
       const int one_sm = (tiles_m * tiles_n + world - 1) / world + 1;
-      const int pair = (2 * ((M + 2 * kTileM - 1) / (2 * kTileM)) * tiles_n + world - 1) / world;
+      const int pair = 2 * ((2 * ((M + 2 * kTileM - 1) / (2 * kTileM)) * tiles_n + world - 1) / world) + 1;  // + ticket
       return one_sm > pair ? one_sm : pair;
     }
     case kGemmRsNorm:

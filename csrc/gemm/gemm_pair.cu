@@ -212,26 +212,46 @@ __device__ __forceinline__ void copy_out_half(uint32_t stage_u32, int lane, char
 // ---- communication roles ---------------------------------------------------------------------------------------
 // All of them run in the `comm` CTAs behind the GEMM pairs (j = index among them, R = their number), with
 // THREADS = kThreadsFusedP threads each.
+//
+// The reducers work WARP by warp: every warp draws its own small work items, waits for its own flag and keeps its own
+// loads in flight, with no block-wide synchronisation between items.  Loads through the switch (and peer loads) have
+// microseconds of latency under load, so throughput is bytes in flight / latency: twelve independent warps with 8 KiB
+// each keep ~96 KiB per CTA in flight all the time, where a block that synchronised per item idled half of it.
 
-// GEMM->AR.  Unit u = 2 * seq + cta is the 128x256 half tile that CTA `cta` of a pair stores for schedule position
-// seq.  Its owner is rank u % world; the k-th unit of a rank (u = k * world + rank) has arrival counter
-// counter_base + k on that rank, bumped once by every rank.  Reducer j takes the owned units j, j + R, ... in
-// schedule order, i.e. in the order in which the GEMMs finish them.
-template <typename T, int THREADS, int NR, bool MC>
-__device__ __forceinline__ void ar_reduce_unit(const GemmArgs& a, int world, int rank, size_t c_off0, size_t row_bytes,
-                                               int rows_valid, int packs_valid_row) {
-  // Packs per thread and batch: bounded by registers (a peer reduction holds NR raw packs per result).
-  constexpr int U = MC ? 11 : (NR == 0 ? 1 : (NR >= 8 ? 2 : (NR == 4 ? 4 : 8)));
-  for (int base = 0; base < kPacksPerTile; base += THREADS * U) {
+constexpr int kArSubRows = 16;                        // rows of a 128x256 half tile per work item (8 KiB)
+constexpr int kArSubsPerUnit = kTileM / kArSubRows;   // 8
+
+// Work items are handed out by a ticket counter, one ticket per warp and item, in schedule order (the order in which
+// the GEMMs finish them).  Dedicated communication CTAs draw from the start; every GEMM CTA joins with all its warps
+// once it has run out of tiles, so whatever the reduction still has to do when the GEMM ends is spread over the whole
+// GPU.  The counter is re-armed by whoever draws the last ticket that can ever be drawn: `total` in-range tickets plus
+// one out-of-range ticket per drawing warp.
+__device__ __forceinline__ int draw_ticket_warp(uint32_t* ticket, int total, int drawers, int lane) {
+  uint32_t t = 0;
+  if (lane == 0) {
+    t = atomicAdd(ticket, 1u);
+    if (t == uint32_t(total + drawers - 1)) {
+      *ticket = 0;
+      __threadfence();
+    }
+  }
+  return static_cast<int>(__shfl_sync(0xffffffffu, t, 0));
+}
+
+// One work item of the GEMM->AR reduction: kArSubRows rows x 256 columns, one 512-byte row per warp instruction.
+template <typename T, int NR, bool MC>
+__device__ __forceinline__ void ar_reduce_sub(const GemmArgs& a, int world, int rank, size_t off0, size_t row_bytes,
+                                              int rows_valid, int packs_valid_row, int lane) {
+  // Rows per batch: bounded by registers (a peer reduction holds NR raw packs per result).
+  constexpr int U = MC ? kArSubRows : (NR == 0 ? 1 : (NR >= 8 ? 2 : (NR == 4 ? 4 : 8)));
+  const bool col_live = lane < packs_valid_row;
+#pragma unroll 1
+  for (int u0 = 0; u0 < kArSubRows; u0 += U) {
     uint4 v[U];
-    bool live[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int p = base + u * THREADS + threadIdx.x;
-      const int row = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
-      live[u] = p < kPacksPerTile && row < rows_valid && cp < packs_valid_row;
-      if (live[u]) {
-        const size_t off = c_off0 + size_t(row) * row_bytes + size_t(cp) * 16;
+      if (col_live && u0 + u < rows_valid) {
+        const size_t off = off0 + size_t(u0 + u) * row_bytes + size_t(lane) * 16;
         if constexpr (MC)
           v[u] = reduce_pack_mc<T, kSum>(static_cast<const char*>(a.c_sym.mc) + off);
         else
@@ -240,227 +260,188 @@ __device__ __forceinline__ void ar_reduce_unit(const GemmArgs& a, int world, int
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      if (!live[u]) continue;
-      const int p = base + u * THREADS + threadIdx.x;
-      const int row = p / kPacksPerTileRow, cp = p % kPacksPerTileRow;
-      const size_t off = c_off0 + size_t(row) * row_bytes + size_t(cp) * 16;
-      if constexpr (MC) {
-        ptx::multimem_st_v4(static_cast<char*>(a.c_sym.mc) + off, v[u]);
-      } else if constexpr (NR > 0) {
+      if (col_live && u0 + u < rows_valid) {
+        const size_t off = off0 + size_t(u0 + u) * row_bytes + size_t(lane) * 16;
+        if constexpr (MC) {
+          ptx::multimem_st_v4(static_cast<char*>(a.c_sym.mc) + off, v[u]);
+        } else if constexpr (NR > 0) {
 #pragma unroll
-        for (int r = 0; r < NR; ++r) ptx::st_v4(static_cast<char*>(a.c_sym.p[(rank + r) % NR]) + off, v[u]);
-      } else {
-        for (int r = 0; r < world; ++r) ptx::st_v4(static_cast<char*>(a.c_sym.p[(rank + r) % world]) + off, v[u]);
+          for (int r = 0; r < NR; ++r) ptx::st_v4(static_cast<char*>(a.c_sym.p[(rank + r) % NR]) + off, v[u]);
+        } else {
+          for (int r = 0; r < world; ++r) ptx::st_v4(static_cast<char*>(a.c_sym.p[(rank + r) % world]) + off, v[u]);
+        }
       }
     }
   }
 }
 
+// GEMM->AR.  Unit u = 2 * seq + cta is the 128x256 half tile that CTA `cta` of a pair stores for schedule position
+// seq.  Its owner is rank u % world; the k-th unit of a rank (u = k * world + rank) has two counters on that rank:
+// counter_base + k counts the ranks that have stored it, counter_base + owned_max + k the finished work items (whoever
+// finishes the last one re-arms both); counter_base + 2 * owned_max is the ticket counter.  Work item i = (unit i / 8,
+// rows 16 * (i % 8) ...).  `drawers` = warps of the launch that draw tickets.
 template <typename T, int THREADS>
-__device__ void pair_ar_reducer(const CommCtx& ctx, const GemmArgs& a, const PairSched& sc, int j, int R) {
-  __shared__ int s_ok;
+__device__ void pair_ar_reducer(const CommCtx& ctx, const GemmArgs& a, const PairSched& sc, int drawers) {
   const int world = ctx.world, rank = ctx.rank;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int W = THREADS / 32;
   const bool use_mc = a.c_sym.mc != nullptr && a.use_nvls != 0;
   const size_t row_bytes = size_t(a.N) * 2;
   const int units = 2 * sc.tiles;
   const int owned = (units - rank + world - 1) / world;
+  const int owned_max = (units + world - 1) / world;
+  const int items = owned * kArSubsPerUnit;
+  uint32_t* ticket = counter_ptr(ctx, rank, a.counter_base + 2 * owned_max);
+  (void)W;
   bool ok = true;
   unsigned long long t_wait = 0, n_items = 0;
-  for (int k = j; k < owned; k += R) {
-    const int u = k * world + rank;
-    if (threadIdx.x == 0) {
-      uint32_t* cnt = counter_ptr(ctx, rank, a.counter_base + k);
-      const unsigned long long tw = a.trace ? ptx::globaltimer_ns() : 0;
-      s_ok = (ok && wait_word_ge(ctx, cnt, world, kDevTimeoutCounter, -1, 52)) ? 1 : 0;
-      // Single consumer: re-arm now.  The next call's arrivals cannot come before this launch has ended on every
-      // rank (the closing rank barrier), and a counter that timed out is zeroed by recover().
-      if (s_ok) *cnt = 0;
-      if (a.trace) {
+  // The next ticket is drawn before the current item is processed: its round trip hides behind the item's loads.
+  int next = draw_ticket_warp(ticket, items, drawers, lane);
+  while (true) {
+    const int i = next;
+    if (i >= items) break;
+    next = draw_ticket_warp(ticket, items, drawers, lane);
+    if (!ok) continue;  // after a timeout: keep drawing so that every warp ends with its one out-of-range ticket
+    const int k = i / kArSubsPerUnit, sub = i % kArSubsPerUnit;
+    uint32_t* cnt = counter_ptr(ctx, rank, a.counter_base + k);
+    uint32_t* done = counter_ptr(ctx, rank, a.counter_base + owned_max + k);
+    int good = 1;
+    if (lane == 0) {
+      const unsigned long long tw = (a.trace && warp == 0) ? ptx::globaltimer_ns() : 0;
+      good = wait_word_ge(ctx, cnt, world, kDevTimeoutCounter, -1, 52) ? 1 : 0;
+      if (a.trace && warp == 0) {
         const unsigned long long now = ptx::globaltimer_ns();
         t_wait += now - tw;
-        if (n_items == 0) trace_put(a, kTraceFirstReady, now);
-        ++n_items;
+        if (n_items == 0 && threadIdx.x == 0) trace_put(a, kTraceFirstReady, now);
       }
     }
-    __syncthreads();
-    if (s_ok == 0) ok = false;
-    __syncthreads();
-    if (!ok) break;
+    good = __shfl_sync(0xffffffffu, good, 0);
+    if (!good) {
+      ok = false;
+      continue;
+    }
+    ++n_items;
+    const int u = k * world + rank;
     int m_blk, n_blk;
     sc.coord(u >> 1, m_blk, n_blk);
-    const int m0 = m_blk * kPairTileM + (u & 1) * kTileM, n0 = n_blk * kTileN;
-    const int rows_valid = min(kTileM, a.M - m0);
+    const int m0 = m_blk * kPairTileM + (u & 1) * kTileM + sub * kArSubRows, n0 = n_blk * kTileN;
+    const int rows_valid = min(kArSubRows, a.M - m0);
     const int packs_valid_row = min(kPacksPerTileRow, (a.N - n0) / 8);
-    if (rows_valid <= 0) continue;
-    const size_t c_off0 = size_t(m0) * row_bytes + size_t(n0) * 2;
-    if (use_mc)
-      ar_reduce_unit<T, THREADS, 0, true>(a, world, rank, c_off0, row_bytes, rows_valid, packs_valid_row);
-    else if (world == 2)
-      ar_reduce_unit<T, THREADS, 2, false>(a, world, rank, c_off0, row_bytes, rows_valid, packs_valid_row);
-    else if (world == 4)
-      ar_reduce_unit<T, THREADS, 4, false>(a, world, rank, c_off0, row_bytes, rows_valid, packs_valid_row);
-    else if (world == 8)
-      ar_reduce_unit<T, THREADS, 8, false>(a, world, rank, c_off0, row_bytes, rows_valid, packs_valid_row);
-    else
-      ar_reduce_unit<T, THREADS, 0, false>(a, world, rank, c_off0, row_bytes, rows_valid, packs_valid_row);
+    if (rows_valid > 0 && packs_valid_row > 0) {
+      const size_t off0 = size_t(m0) * row_bytes + size_t(n0) * 2;
+      if (use_mc)
+        ar_reduce_sub<T, 0, true>(a, world, rank, off0, row_bytes, rows_valid, packs_valid_row, lane);
+      else if (world == 2)
+        ar_reduce_sub<T, 2, false>(a, world, rank, off0, row_bytes, rows_valid, packs_valid_row, lane);
+      else if (world == 4)
+        ar_reduce_sub<T, 4, false>(a, world, rank, off0, row_bytes, rows_valid, packs_valid_row, lane);
+      else if (world == 8)
+        ar_reduce_sub<T, 8, false>(a, world, rank, off0, row_bytes, rows_valid, packs_valid_row, lane);
+      else
+        ar_reduce_sub<T, 0, false>(a, world, rank, off0, row_bytes, rows_valid, packs_valid_row, lane);
+    }
+    // Whoever finishes the last item of a unit re-arms its counters.  The next call's arrivals cannot come before
+    // this launch has ended on every rank (the closing rank barrier); counters that timed out are zeroed by recover().
+    __syncwarp();
+    if (lane == 0) {
+      if (atomicAdd(done, 1u) == uint32_t(kArSubsPerUnit - 1)) {
+        *cnt = 0;
+        *done = 0;
+        __threadfence();
+      }
+    }
   }
+  const int all_ok = __syncthreads_and(ok ? 1 : 0);
   if (a.trace) {
     trace_put(a, kTraceCommDone, ptx::globaltimer_ns());
     trace_put(a, kTraceItems, n_items);
     trace_put(a, kTraceWaitNs, t_wait);
   }
-  // Reducer j of every rank is past its last unit: together (all reducers) this means every result has been
-  // written into this rank's C, and nobody reads this rank's partial products any more.
-  if (ok) rank_barrier(ctx, j, 53);
+  // CTA b of every rank is past its last item: together (all drawing CTAs) this means every result has been written
+  // into this rank's C, and nobody reads this rank's partial products any more.
+  if (all_ok) rank_barrier(ctx, blockIdx.x, 53);
   if (a.trace) trace_put(a, kTraceEnd, ptx::globaltimer_ns());
 }
 
 // GEMM->RS + residual + RMSNorm.  The owner of a 128-row block (local index lb) has two counters for it:
-// counter_base + lb counts stored half tiles (tiles_n per rank), counter_base + blocks + lb counts finished row
-// groups (whoever finishes the last one re-arms both).  Work item t = (lb, group of RB rows); reducer j takes the
-// items j, j + R, ...  For every item the sums of RB rows are read in one go (all loads in flight together), the
-// residual is added, the rows' mean squares are reduced over the CTA at once, and the normalised rows are written.
-template <typename T, int THREADS, int PPT, int RB, int NR, bool MC>
-__device__ __forceinline__ void rs_rows(int N, float eps, const char* partial_mc, const PeerPtrs& partial, int world,
-                                        size_t grow0, size_t lrow0, const char* res, char* y, char* ro, const char* wgt,
-                                        float (*s_part)[THREADS / 32]) {
+// counter_base + lb counts stored half tiles (tiles_n per rank), counter_base + blocks + lb counts finished rows
+// (whoever finishes the last one re-arms both).  A work item is ONE ROW of the rank's shard, handled by one warp:
+//   pass 1  the row's sums are read 8 packs per lane at a time (through the switch, or from all peers), the residual is
+//           added, the 16-bit rounded values are written to the residual output (or to y, as scratch) and their squares
+//           accumulated;
+//   pass 2  the warp reduces the sum of squares with shuffles, re-reads its own rounded values (each lane the packs it
+//           wrote: L2 hits, ordered by program order) and writes the normalised row.
+// No block-wide synchronisation, any N that is a multiple of 8.
+template <typename T, int NR, bool MC>
+__device__ __forceinline__ void rs_row(const GemmArgs& a, int world, size_t grow, size_t lrow, const char* res, char* y,
+                                       char* ro, const char* wgt, int lane) {
   using PT = PackTraits<T>;
-  const int packs_per_row = N / 8;
-  const size_t row_bytes = size_t(N) * 2;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // The rows are held as 16-bit packs: the normalisation works on the rounded value that is also written out as
-  // the new residual, so nothing is lost and the registers of RB rows fit.
-  uint4 v[RB][PPT];
-  if constexpr (MC) {
-    // All loads of the item are issued before the first use: RB * PPT in-switch reductions in flight per thread.
+  constexpr int U = MC ? 8 : (NR == 2 ? 4 : (NR == 4 ? 2 : 1));
+  const int packs_per_row = a.N / 8;
+  const size_t row_bytes = size_t(a.N) * 2;
+  const size_t g_off = grow * row_bytes, l_off = lrow * row_bytes;
+  char* stash = ro != nullptr ? ro : y;
+  float ss = 0.f;
+#pragma unroll 1
+  for (int c0 = 0; c0 < packs_per_row; c0 += 32 * U) {
+    float f[U][8];
+    if constexpr (MC) {
+      uint4 v[U];
 #pragma unroll
-    for (int r = 0; r < RB; ++r)
-#pragma unroll
-      for (int q = 0; q < PPT; ++q) {
-        const int p = threadIdx.x + q * THREADS;
-        // Lanes past the end of the row load nothing: a load through the switch is link traffic on every rank.
-        v[r][q] = make_uint4(0u, 0u, 0u, 0u);
-        if (p < packs_per_row)
-          v[r][q] = reduce_pack_mc<T, kSum>(partial_mc + (grow0 + r) * row_bytes + size_t(p) * 16);
+      for (int u = 0; u < U; ++u) {
+        const int p = c0 + u * 32 + lane;
+        v[u] = make_uint4(0u, 0u, 0u, 0u);
+        // lanes past the end of the row load nothing: a load through the switch is link traffic on every rank
+        if (p < packs_per_row) v[u] = reduce_pack_mc<T, kSum>(static_cast<const char*>(a.partial.mc) + g_off + size_t(p) * 16);
       }
-  }
-  float ss[RB];
 #pragma unroll
-  for (int r = 0; r < RB; ++r) {
-    ss[r] = 0.f;
-    const size_t lrow_off = (lrow0 + r) * row_bytes;
+      for (int u = 0; u < U; ++u) PT::unpack(v[u], f[u]);
+    } else {
 #pragma unroll
-    for (int q = 0; q < PPT; ++q) {
-      const int p = threadIdx.x + q * THREADS;
-      if (p < packs_per_row) {
-        float f[8];
-        if constexpr (MC)
-          PT::unpack(v[r][q], f);
-        else
-          reduce_pack_p2p_f32<T, kSum, NR>(partial, (grow0 + r) * row_bytes + size_t(p) * 16, world, f);
-        if (res != nullptr) {
-          float rf[8];
-          PT::unpack(ptx::ld_nc_v4(res + lrow_off + size_t(p) * 16), rf);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] += rf[i];
-        }
-        v[r][q] = PT::pack(f);
-        PT::unpack(v[r][q], f);
-        if (ro != nullptr) ptx::st_v4(ro + lrow_off + size_t(p) * 16, v[r][q]);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ss[r] += f[i] * f[i];
+      for (int u = 0; u < U; ++u) {
+        const int p = c0 + u * 32 + lane;
+        if (p < packs_per_row) reduce_pack_p2p_f32<T, kSum, NR>(a.partial, g_off + size_t(p) * 16, world, f[u]);
       }
     }
-  }
-  float scale[RB];
 #pragma unroll
-  for (int r = 0; r < RB; ++r) scale[r] = 1.f;
-  if (wgt != nullptr) {
+    for (int u = 0; u < U; ++u) {
+      const int p = c0 + u * 32 + lane;
+      if (p >= packs_per_row) continue;
+      if (res != nullptr) {
+        float rf[8];
+        PT::unpack(ptx::ld_nc_v4(res + l_off + size_t(p) * 16), rf);
 #pragma unroll
-    for (int r = 0; r < RB; ++r) {
+        for (int i = 0; i < 8; ++i) f[u][i] += rf[i];
+      }
+      // The normalisation sees the 16-bit value that is also written out as the new residual.
+      const uint4 rounded = PT::pack(f[u]);
+      PT::unpack(rounded, f[u]);
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], o);
-    }
-    __syncthreads();  // s_part is free again (previous item's readers are done)
-    if (lane == 0) {
-#pragma unroll
-      for (int r = 0; r < RB; ++r) s_part[r][warp] = ss[r];
-    }
-    __syncthreads();
-#pragma unroll
-    for (int r = 0; r < RB; ++r) {
-      float t = 0.f;
-#pragma unroll
-      for (int w = 0; w < THREADS / 32; ++w) t += s_part[r][w];
-      scale[r] = rsqrtf(t / float(N) + eps);
+      for (int i = 0; i < 8; ++i) ss += f[u][i] * f[u][i];
+      ptx::st_v4(stash + l_off + size_t(p) * 16, rounded);
+      if (wgt == nullptr && ro != nullptr) ptx::st_v4(y + l_off + size_t(p) * 16, rounded);
     }
   }
+  if (wgt == nullptr) return;
 #pragma unroll
-  for (int q = 0; q < PPT; ++q) {
-    const int p = threadIdx.x + q * THREADS;
-    if (p >= packs_per_row) continue;
-    if (wgt == nullptr) {
-#pragma unroll
-      for (int r = 0; r < RB; ++r) ptx::st_v4(y + (lrow0 + r) * row_bytes + size_t(p) * 16, v[r][q]);
-      continue;
-    }
-    float wf[8];
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float scale = rsqrtf(ss / float(a.N) + a.eps);
+#pragma unroll 2
+  for (int p = lane; p < packs_per_row; p += 32) {
+    float f[8], wf[8], o[8];
+    PT::unpack(ptx::ld_nc_v4(stash + l_off + size_t(p) * 16), f);
     PT::unpack(*reinterpret_cast<const uint4*>(wgt + size_t(p) * 16), wf);
 #pragma unroll
-    for (int r = 0; r < RB; ++r) {
-      float f[8], o[8];
-      PT::unpack(v[r][q], f);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o[i] = f[i] * scale[r] * wf[i];
-      ptx::st_v4(y + (lrow0 + r) * row_bytes + size_t(p) * 16, PT::pack(o));
-    }
+    for (int i = 0; i < 8; ++i) o[i] = f[i] * scale * wf[i];
+    ptx::st_v4(y + l_off + size_t(p) * 16, PT::pack(o));
   }
 }
 
-// One work item (RB rows).  Through the switch all RB rows are in flight at once; the peer-load fallback holds NR raw
-// packs per result, so it takes fewer rows at a time to stay within the register file.  Both are separate functions
-// (own register allocation; arguments by value so that the kernel's parameter block is never copied to the stack).
-template <typename T, int THREADS, int PPT, int RB, int NR>
-__device__ __noinline__ void rs_rows_p2p(int N, float eps, PeerPtrs partial, int world, size_t grow0, size_t lrow0,
-                                         const char* res, char* y, char* ro, const char* wgt,
-                                         float (*s_part)[THREADS / 32]) {
-  constexpr int STEP = NR == 2 ? RB : (NR == 4 ? (RB >= 2 ? 2 : 1) : 1);
-#pragma unroll 1
-  for (int r = 0; r < RB; r += STEP)
-    rs_rows<T, THREADS, PPT, STEP, NR, false>(N, eps, nullptr, partial, world, grow0 + r, lrow0 + r, res, y, ro, wgt, s_part);
-}
-
-template <typename T, int THREADS, int PPT, int RB>
-__device__ __noinline__ void rs_rows_mc(int N, float eps, const char* partial_mc, size_t grow0, size_t lrow0,
-                                        const char* res, char* y, char* ro, const char* wgt,
-                                        float (*s_part)[THREADS / 32]) {
-  PeerPtrs none{};
-  rs_rows<T, THREADS, PPT, RB, 0, true>(N, eps, partial_mc, none, 0, grow0, lrow0, res, y, ro, wgt, s_part);
-}
-
-template <typename T, int THREADS, int PPT, int RB>
-__device__ __forceinline__ void rs_rows_dispatch(const GemmArgs& a, int world, bool use_mc, size_t grow0, size_t lrow0,
-                                                 const char* res, char* y, char* ro, const char* wgt,
-                                                 float (*s_part)[THREADS / 32]) {
-  if (use_mc)
-    rs_rows_mc<T, THREADS, PPT, RB>(a.N, a.eps, static_cast<const char*>(a.partial.mc), grow0, lrow0, res, y, ro, wgt, s_part);
-  else if (world == 2)
-    rs_rows_p2p<T, THREADS, PPT, RB, 2>(a.N, a.eps, a.partial, world, grow0, lrow0, res, y, ro, wgt, s_part);
-  else if (world == 4)
-    rs_rows_p2p<T, THREADS, PPT, RB, 4>(a.N, a.eps, a.partial, world, grow0, lrow0, res, y, ro, wgt, s_part);
-  else if (world == 8)
-    rs_rows_p2p<T, THREADS, PPT, RB, 8>(a.N, a.eps, a.partial, world, grow0, lrow0, res, y, ro, wgt, s_part);
-  else
-    rs_rows_p2p<T, THREADS, PPT, RB, 0>(a.N, a.eps, a.partial, world, grow0, lrow0, res, y, ro, wgt, s_part);
-}
-
-constexpr int kRsGroupRows = 4;  // rows per work item of the RS tail
-
 template <typename T, int THREADS>
-__device__ void pair_rs_reducer(const CommCtx& ctx, const GemmArgs& a, const PairSched& sc, int j, int R) {
-  __shared__ int s_ok;
-  __shared__ float s_part[kRsGroupRows][THREADS / 32];
+__device__ void pair_rs_reducer(const CommCtx& ctx, const GemmArgs& a, const PairSched& sc, int drawers) {
   const int world = ctx.world, rank = ctx.rank;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int W = THREADS / 32;
   const bool use_mc = a.partial.mc != nullptr && a.use_nvls != 0;
   const int rows_per_rank = a.M / world;
   const int blocks = rows_per_rank / kTileM;
@@ -468,63 +449,71 @@ __device__ void pair_rs_reducer(const CommCtx& ctx, const GemmArgs& a, const Pai
   char* y = static_cast<char*>(a.y_local) + a.rs_emu_stride * blockIdx.y;
   char* ro = a.res_out_local ? static_cast<char*>(a.res_out_local) + a.rs_emu_stride * blockIdx.y : nullptr;
   const char* wgt = static_cast<const char*>(a.weight);
-  constexpr int kGroups = kTileM / kRsGroupRows;
-  const int total = blocks * kGroups;
-  const int ppt = (a.N / 8 + THREADS - 1) / THREADS;
+  uint32_t* ticket = counter_ptr(ctx, rank, a.counter_base + 2 * blocks);
+  (void)W;
   bool ok = true;
   unsigned long long t_wait = 0, n_items = 0;
   int ready_lb = -1;  // blocks up to here are known to be complete
-  for (int t = j; t < total; t += R) {
-    const int lb = t / kGroups, grp = t % kGroups;
+  int next = draw_ticket_warp(ticket, rows_per_rank, drawers, lane);
+  while (true) {
+    const int r = next;
+    if (r >= rows_per_rank) break;
+    next = draw_ticket_warp(ticket, rows_per_rank, drawers, lane);
+    if (!ok) continue;
+    const int lb = r / kTileM;
     uint32_t* cnt = counter_ptr(ctx, rank, a.counter_base + lb);
     uint32_t* done = counter_ptr(ctx, rank, a.counter_base + blocks + lb);
     if (lb > ready_lb) {
-      if (threadIdx.x == 0) {
-        const unsigned long long tw = a.trace ? ptx::globaltimer_ns() : 0;
-        s_ok = wait_word_ge(ctx, cnt, uint32_t(world) * sc.tiles_n, kDevTimeoutCounter, -1, 62) ? 1 : 0;
-        if (a.trace) {
+      int good = 1;
+      if (lane == 0) {
+        const unsigned long long tw = (a.trace && warp == 0) ? ptx::globaltimer_ns() : 0;
+        good = wait_word_ge(ctx, cnt, uint32_t(world) * sc.tiles_n, kDevTimeoutCounter, -1, 62) ? 1 : 0;
+        if (a.trace && warp == 0) {
           const unsigned long long now = ptx::globaltimer_ns();
           t_wait += now - tw;
-          if (n_items == 0) trace_put(a, kTraceFirstReady, now);
+          if (n_items == 0 && threadIdx.x == 0) trace_put(a, kTraceFirstReady, now);
         }
       }
-      __syncthreads();
-      if (s_ok == 0) ok = false;
-      __syncthreads();
-      if (!ok) break;
+      good = __shfl_sync(0xffffffffu, good, 0);
+      if (!good) {
+        ok = false;
+        continue;
+      }
       ready_lb = lb;
     }
     ++n_items;
-    const size_t lrow0 = size_t(lb) * kTileM + size_t(grp) * kRsGroupRows;
-    const size_t grow0 = size_t(rank) * rows_per_rank + lrow0;
-    if (ppt <= 1)
-      rs_rows_dispatch<T, THREADS, 1, kRsGroupRows>(a, world, use_mc, grow0, lrow0, res, y, ro, wgt, s_part);
-    else if (ppt <= 2)
-      rs_rows_dispatch<T, THREADS, 2, kRsGroupRows>(a, world, use_mc, grow0, lrow0, res, y, ro, wgt, s_part);
+    const size_t grow = size_t(rank) * rows_per_rank + r;
+    if (use_mc)
+      rs_row<T, 0, true>(a, world, grow, r, res, y, ro, wgt, lane);
+    else if (world == 2)
+      rs_row<T, 2, false>(a, world, grow, r, res, y, ro, wgt, lane);
+    else if (world == 4)
+      rs_row<T, 4, false>(a, world, grow, r, res, y, ro, wgt, lane);
+    else if (world == 8)
+      rs_row<T, 8, false>(a, world, grow, r, res, y, ro, wgt, lane);
     else
-      rs_rows_dispatch<T, THREADS, 3, kRsGroupRows>(a, world, use_mc, grow0, lrow0, res, y, ro, wgt, s_part);
-    // Whoever finishes the last row group of a block re-arms the block's counters for the next call.
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      if (atomicAdd(done, 1u) == uint32_t(kGroups - 1)) {
+      rs_row<T, 0, false>(a, world, grow, r, res, y, ro, wgt, lane);
+    // Whoever finishes the last row of a block re-arms the block's counters for the next call.
+    __syncwarp();
+    if (lane == 0) {
+      if (atomicAdd(done, 1u) == uint32_t(kTileM - 1)) {
         *cnt = 0;
         *done = 0;
         __threadfence();
       }
     }
   }
+  const int all_ok = __syncthreads_and(ok ? 1 : 0);
   if (a.trace) {
     trace_put(a, kTraceCommDone, ptx::globaltimer_ns());
     trace_put(a, kTraceItems, n_items);
     trace_put(a, kTraceWaitNs, t_wait);
   }
-  // Nobody reads this rank's partial products any more once reducer j of every rank is here.
-  if (ok) rank_barrier(ctx, j, 63);
+  // Nobody reads this rank's partial products any more once CTA b of every rank is here.
+  if (all_ok) rank_barrier(ctx, blockIdx.x, 63);
   if (a.trace) trace_put(a, kTraceEnd, ptx::globaltimer_ns());
 }
 
-// AG->GEMM pusher: broadcasts this rank's shard, one 128-row chunk at a time, into every rank's gathered buffer.
-// Flag of chunk c of rank r: counter_base + r * chunks + c, bumped once per pusher on every other rank.
 // The last CTA of the launch (GEMM CTAs and pushers) to get here zeroes the chunk flags: every flag has reached its
 // final value by then.
 __device__ __forceinline__ void ag_rearm_flags(const CommCtx& ctx, const GemmArgs& a, int ctas) {
@@ -644,8 +633,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == kGemmPlain ?
   if constexpr (MODE != kGemmPlain) {
     if (pair >= plan.gemm_pairs) {
       const int j = int(blockIdx.x) - 2 * plan.gemm_pairs, R = int(gridDim.x) - 2 * plan.gemm_pairs;
-      if constexpr (MODE == kGemmAr) pair_ar_reducer<T, THREADS>(ctx, a, sc, j, R);
-      if constexpr (MODE == kGemmRsNorm) pair_rs_reducer<T, THREADS>(ctx, a, sc, j, R);
+      const int drawers = (a.no_join ? R : int(gridDim.x)) * (THREADS / 32);
+      if constexpr (MODE == kGemmAr) pair_ar_reducer<T, THREADS>(ctx, a, sc, drawers);
+      if constexpr (MODE == kGemmRsNorm) pair_rs_reducer<T, THREADS>(ctx, a, sc, drawers);
       if constexpr (MODE == kGemmAg) pair_ag_pusher<THREADS>(ctx, a, j, R, 2 * plan.gemm_pairs);
       return;
     }
@@ -1013,6 +1003,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == kGemmPlain ?
   cluster_sync_all();  // the peer has no MMA, commit or remote arrival left that targets this CTA
   ptx::tc_fence_after_sync();
   if (warp == 1) tmem_dealloc_pair(tmem_base, kTmemCols);
+  // GEMM CTAs that are out of tiles help with the reduction of what is still in flight.
+  if constexpr (kSignals) {
+    if (!aborted && !a.no_join) {
+      __syncthreads();
+      const int drawers = int(gridDim.x) * (THREADS / 32);
+      if constexpr (MODE == kGemmAr) pair_ar_reducer<T, THREADS>(ctx, a, sc, drawers);
+      if constexpr (MODE == kGemmRsNorm) pair_rs_reducer<T, THREADS>(ctx, a, sc, drawers);
+      return;
+    }
+  }
   if (a.trace) trace_put(a, kTraceEnd, ptx::globaltimer_ns());
 }
 
@@ -1216,7 +1216,7 @@ bool gemm_pair_supported(const CommCtx& ctx, const GemmArgs& a) {
   if (a.mode == kGemmAr) return a.N % 8 == 0;
   const int rows_per_rank = a.M / ctx.world;
   if (a.M % ctx.world != 0 || rows_per_rank % kTileM != 0) return false;
-  if (a.mode == kGemmRsNorm) return a.N % 8 == 0 && a.N <= 3 * gemm_pair::kThreadsFusedP * 8;
+  if (a.mode == kGemmRsNorm) return a.N % 8 == 0;
   return true;
 }
 

@@ -85,6 +85,17 @@ def _rank_collectives(rank, world, key, flags_env):
         check(f"slot {it}", got, torch.full((64, 128), float(sum(r + it for r in range(world)))), 1e-2 * world)
     got = comm.all_reduce_round_robin(torch.full((10,), 2.0, dtype=torch.bfloat16, device="cuda"))
     check("rr", got, torch.full((10,), 2.0 * world), 1e-2)
+    # small tensors take the one-barrier push kernel (pieces + result inside the slot); the ring of three wraps twice,
+    # odd sizes exercise the element tail and a misaligned view the element-wise local path
+    for it in range(7):
+        for n in (1, 8, 4097, 32768):
+            xs = _inputs(world, n + 1, torch.bfloat16, 1000 * it + n)
+            x = xs[rank].cuda()[1:] if it % 2 else xs[rank].cuda()[:n]
+            ref = torch.stack([(t[1:] if it % 2 else t[:n]).float() for t in xs]).sum(0)
+            got = comm.all_reduce_push(x)
+            assert got is not None
+            check(f"push {it} {n}", got, ref, 1e-2 * world)
+    assert comm.all_reduce_push(torch.zeros(1 << 19, dtype=torch.bfloat16, device="cuda")) is None  # 1 MiB: too large
     comm.init_all_gather_slots(torch.bfloat16, 1 << 20, 2)
     got = comm.all_gather_round_robin(torch.full((4, 8), float(rank), dtype=torch.bfloat16, device="cuda"))
     check("ag_rr", got, torch.arange(world).float().repeat_interleave(4).unsqueeze(1).expand(-1, 8), 0.0)
@@ -182,6 +193,15 @@ def _rank_fused(rank, world, key):
             c = op(a[rank].cuda(), bw[rank].cuda())
             torch.cuda.synchronize()
             out.append((f"gemm_ar {strat} M{M}", (c.float().cpu() - want).abs().max().item(), tol_c))
+            op.release()
+        if M != 128 * world * 2:
+            # decided at the first call: every candidate is checked and timed on these operands, all ranks agree
+            op = GemmAllReduce(comm, M, N, dt, strategy="autotune")
+            for it in range(2):
+                c = op(a[rank].cuda(), bw[rank].cuda())
+                torch.cuda.synchronize()
+                out.append((f"gemm_ar autotune {it}", (c.float().cpu() - want).abs().max().item(), tol_c))
+            assert op.strategy in ("fused", "unfused") and op.tuning and any(t["us"] for t in op.tuning)
             op.release()
         if M == 128 * world * 2:
             # slabs of rows: GEMM on the caller's stream, all-reduce of each slab on a side stream

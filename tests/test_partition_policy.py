@@ -89,6 +89,7 @@ def test_policy_rejects_malformed(lib, tmp_path):
 def test_gemm_bookkeeping_helpers(lib):
     assert lib.oob_gemm_partial_bytes(8192, 8192) == (64 * 32 + 16) * 128 * 256 * 2
     assert lib.oob_gemm_partial_bytes(100, 100) == (1 + 16) * 128 * 256 * 2
-    assert lib.oob_gemm_counters_needed(_lib.GEMM_AR, 8192, 8192, 8) == 257
+    # two-SM kernel: arrivals + finished work items per owned half tile (2 * 2048 / 8) + ticket; one-SM kernel: 256 tiles + ticket
+    assert lib.oob_gemm_counters_needed(_lib.GEMM_AR, 8192, 8192, 8) == 513
     assert lib.oob_gemm_counters_needed(_lib.GEMM_RS_NORM, 4096, 8192, 8) == 9
     assert lib.oob_gemm_counters_needed(_lib.GEMM_AG, 4096, 3584, 8) == 33
