@@ -46,7 +46,7 @@ def parse_args():
     p.add_argument("--impl", default="ours", choices=["ours", "reference", "nccl_cublas"])
     p.add_argument("--comm-ctas", type=int, default=int(os.environ.get("OOB_BENCH_COMM_CTAS", "0")),
                    help="communication CTAs of the fused kernel (0 = the library's choice per shape)")
-    p.add_argument("--strategy", default="auto", choices=["auto", "autotune", "fused", "unfused", "chunked"])
+    p.add_argument("--strategy", default="autotune", choices=["auto", "autotune", "fused", "unfused", "chunked"])
     p.add_argument("--kernel", default=None, choices=["pair", "one_sm"], help="fused kernel (default: the library's choice)")
     p.add_argument("--nvls", type=int, default=-1, help="fused kernel: 0 = peer loads/stores, 1/2 = through the switch, -1 = default")
     p.add_argument("--no-baseline", action="store_true", help="skip the cuBLAS + NCCL arm of --impl ours")

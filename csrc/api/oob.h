@@ -85,6 +85,9 @@ int oob_comm_destroy(oob_comm* c);
 int oob_comm_info(const oob_comm* c, oob_comm_info_t* info);
 int oob_comm_set_timeout_ms(oob_comm* c, int ms);
 int oob_comm_barrier(oob_comm* c);                       /* host-side, through the rendezvous */
+/* Host-side all-gather of `bytes` bytes per rank through the rendezvous (out holds world x bytes, in rank order).  Works
+ * while the device side is poisoned, so ranks can agree on what to do after a device timeout. */
+int oob_comm_host_allgather(oob_comm* c, const void* in, void* out, uint64_t bytes);
 int oob_comm_status(oob_comm* c, oob_device_status_t* s);/* 0 = clean, OOB_ERR_DEVICE_TIMEOUT otherwise */
 /* Collective: zeroes every rank's signal pad and status after a device
  * timeout.  No kernel of this communicator may be in flight. */

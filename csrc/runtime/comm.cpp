@@ -544,6 +544,16 @@ int oob_comm_barrier(oob_comm* c) {
   return OOB_OK;
 }
 
+int oob_comm_host_allgather(oob_comm* c, const void* in, void* out, uint64_t bytes) {
+  if (c == nullptr || in == nullptr || out == nullptr || bytes == 0) return set_error(OOB_ERR_INVALID, "bad argument");
+  if (c->boot == nullptr || c->world == 1 || c->emulated) {
+    std::memcpy(out, in, bytes);
+    return OOB_OK;
+  }
+  if (!c->boot->allgather(in, out, bytes)) return set_error(OOB_ERR_BOOTSTRAP, c->boot->last_error());
+  return OOB_OK;
+}
+
 int oob_comm_status(oob_comm* c, oob_device_status_t* s) {
   if (c == nullptr) return set_error(OOB_ERR_INVALID, "null communicator");
   const int n = c->emulated ? c->world : 1;

@@ -105,6 +105,7 @@ def _declare(lib) -> None:
     lib.oob_comm_info.argtypes = [P, POINTER(CommInfo)]
     lib.oob_comm_set_timeout_ms.argtypes = [P, c_int]
     lib.oob_comm_barrier.argtypes = [P]
+    lib.oob_comm_host_allgather.argtypes = [P, ctypes.c_void_p, ctypes.c_void_p, c_uint64]
     lib.oob_comm_status.argtypes = [P, POINTER(DeviceStatus)]
     lib.oob_comm_recover.argtypes = [P]
     lib.oob_alloc.argtypes = [P, c_uint64, c_uint64, POINTER(c_uint64)]

@@ -101,6 +101,15 @@ class Communicator:
         self.rank = int(local_rank)
         self.world = len(devices)
         self.device = int(devices[self.rank])
+        # The kernels load and store peer memory directly: every other rank's GPU must be reachable from this one
+        # (NVLink / NVSwitch, or at least PCIe peer access).  There is no host-staged path: say so instead of failing
+        # later inside the memory mapping.
+        if torch.cuda.is_available():
+            for r, d in enumerate(devices):
+                if r != self.rank and int(d) != self.device and not torch.cuda.can_device_access_peer(self.device, int(d)):
+                    raise _lib.OobError(_lib.ERR_UNSUPPORTED,
+                                        f"unsupported topology: cuda:{self.device} (rank {self.rank}) has no peer access to "
+                                        f"cuda:{int(d)} (rank {r}); see `oob_topology` for the link table")
         flags = 0
         if self.config.disable_nvls:
             flags |= _lib.FLAG_NO_NVLS
@@ -246,6 +255,29 @@ class Communicator:
             dist.barrier(self._cpu_group)
             return
         _lib.check(_lib.lib().oob_comm_barrier(self._h))
+
+    def host_all_gather(self, values: Sequence[int]) -> list:
+        """Host-side all-gather of a few 64-bit integers per rank through the rendezvous: ``result[r]`` is rank r's
+        list.  No kernel runs, so ranks can still agree on what to do while the device side is poisoned by a timeout."""
+        vals = [int(v) for v in values]
+        n = len(vals)
+        if self.world == 1:
+            return [vals]
+        if self._h is None:  # CPU fallback: through the gloo group
+            parts = self._cpu_gather_all(torch.tensor(vals, dtype=torch.int64))
+            return [p.tolist() for p in parts]
+        mine = (ctypes.c_int64 * n)(*vals)
+        out = (ctypes.c_int64 * (n * self.world))()
+        _lib.check(_lib.lib().oob_comm_host_allgather(self._h, mine, out, n * 8))
+        return [list(out[r * n:(r + 1) * n]) for r in range(self.world)]
+
+    def status_ok(self) -> bool:
+        """True when no kernel of this rank has given up a wait since the last ``recover``."""
+        try:
+            self.check_status()
+            return True
+        except _lib.OobError:
+            return False
 
     def check_status(self) -> None:
         """Raises ``DeviceTimeout`` when a kernel of this rank gave up waiting."""

@@ -176,61 +176,93 @@ class GemmAllReduce:
     def _candidates(self):
         """(strategy, kernel, use_nvls, comm_ctas) to try: the unfused pair; the two-SM kernel over a few CTA budgets,
         through the switch when the heap has a multicast alias (and with peer loads/stores between two ranks, where
-        both move the same bytes); the one-SM kernel with pushed partial tiles."""
+        both move the same bytes); the one-SM kernel with pushed partial tiles (and, from four ranks on, with the
+        in-switch pull); from four ranks on and for tall outputs also the slab pipeline on two streams."""
         nvls = bool(getattr(self.comm, "nvls", False))
+        world = self.comm.world
         cands = [("unfused", None, None, None)]
         for c in (8, 16, 24, 32):
             if nvls:
                 cands.append(("fused", "pair", 1, c))
-            if not nvls or self.comm.world == 2:
+            if not nvls or world == 2:
                 cands.append(("fused", "pair", 0, c))
-        cands.append(("fused", "one_sm", None, 16))
+        cands.append(("fused", "one_sm", 0, 16))
+        if nvls and world >= 4:
+            cands.append(("fused", "one_sm", 2, 16))
+            if self.M % 2048 == 0 and self.M >= 4096:
+                cands.append(("chunked", None, None, None))
         return cands
 
     def _autotune(self, a: torch.Tensor, b: torch.Tensor):
         """First call of ``strategy="autotune"``: every candidate is built, checked against the unfused pair's result
-        and timed on the real operands (CUDA events, maximum over ranks through this communicator's own all-reduce);
-        the fastest correct one is kept.  All ranks take the same decision.  Costs a few tens of milliseconds and
-        synchronises the device, so the first call must not be inside a CUDA-graph capture."""
+        and timed on the real operands (CUDA events).  The ranks exchange their times on the host; a candidate counts
+        with its slowest rank, and one that raised, failed its check or hit a device timeout on ANY rank is out (after
+        a timeout all ranks recover the communicator together before the next candidate).  The fastest one is kept, so
+        all ranks take the same decision.  Costs a few tens of milliseconds and synchronises the device: the first
+        call must not be inside a CUDA-graph capture."""
         comm = self.comm
         cands = self._candidates()
-        times = torch.full((len(cands),), float("inf"), dtype=torch.float32, device=a.device)
+        agreed = []
         ref = None
         iters = 6
-        for i, (strat, kern, nv, c) in enumerate(cands):
-            op = GemmAllReduce(comm, self.M, self.N, self.dtype, comm_ctas=c, use_nvls=nv, strategy=strat, kernel=kern,
-                               max_ctas=self._tune_args["max_ctas"])
-            out = op(a, b)
-            torch.cuda.synchronize()
-            if ref is None:
-                ref = out.clone()
-                ok = True
-            else:
-                scale = max(1.0, float(ref.float().abs().max()))
-                ok = bool((out.float() - ref.float()).abs().max() <= 2e-2 * scale)
-            if ok:
-                op(a, b)
-                comm.barrier()
+        INF = 1 << 60
+        def agree(value: int) -> list:
+            """Host-side exchange of one value per rank; recovers the communicator on all ranks if any rank's device
+            side reports a timeout.  Returns (values, any_timeout)."""
+            rows = comm.host_all_gather([value, 0 if comm.status_ok() else 1])
+            timed_out = any(r[1] for r in rows)
+            if timed_out:
+                comm.recover()
+            return [r[0] for r in rows], timed_out
+
+        for strat, kern, nv, c in cands:
+            op, ok = None, False
+            try:
+                op = GemmAllReduce(comm, self.M, self.N, self.dtype, comm_ctas=c, use_nvls=nv, strategy=strat, kernel=kern,
+                                   max_ctas=self._tune_args["max_ctas"])
+                out = op(a, b)
                 torch.cuda.synchronize()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                for _ in range(iters):
+                comm.check_status()
+                if ref is None:
+                    ref = out.clone()
+                    ok = True
+                else:
+                    scale = max(1.0, float(ref.float().abs().max()))
+                    ok = bool((out.float() - ref.float()).abs().max() <= 2e-2 * scale)
+            except _lib.OobError:
+                ok = False
+            oks, timed_out = agree(1 if ok else 0)
+            ns = INF
+            if all(oks) and not timed_out:
+                try:
                     op(a, b)
-                e1.record()
-                torch.cuda.synchronize()
-                times[i] = e0.elapsed_time(e1) / iters * 1e3
-            op.release()
-        # a candidate that failed its check on ANY rank has an infinite time on that rank: the maximum keeps it out
-        finite = torch.where(torch.isinf(times), torch.full_like(times, 3.0e38), times)
-        agreed = comm.all_reduce(finite, op="max").clone()
-        best = int(torch.argmin(agreed).item())
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    for _ in range(iters):
+                        op(a, b)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    comm.check_status()
+                    ns = int(e0.elapsed_time(e1) / iters * 1e6)
+                except _lib.OobError:
+                    ns = INF
+                times, timed_out = agree(ns)
+                ns = INF if timed_out else max(times)
+            if op is not None:
+                op.release()
+            agreed.append(ns)
+        if min(agreed) >= INF:
+            raise _lib.OobError(_lib.ERR_UNSUPPORTED, "autotune: no candidate ran correctly on every rank")
+        best = min(range(len(cands)), key=lambda i: agreed[i])
         strat, kern, nv, c = cands[best]
-        self.tuning = [dict(strategy=s_, kernel=k_, use_nvls=n_, comm_ctas=c_, us=round(float(t), 1) if float(t) < 1e37 else None)
-                       for (s_, k_, n_, c_), t in zip(cands, agreed.tolist())]
+        self.tuning = [dict(strategy=s_, kernel=k_, use_nvls=n_, comm_ctas=c_, us=round(t / 1e3, 1) if t < INF else None)
+                       for (s_, k_, n_, c_), t in zip(cands, agreed)]
         self._tuned = GemmAllReduce(comm, self.M, self.N, self.dtype, comm_ctas=c, use_nvls=nv, strategy=strat, kernel=kern,
                                     max_ctas=self._tune_args["max_ctas"])
         self.strategy, self.comm_ctas, self.use_nvls = self._tuned.strategy, self._tuned.comm_ctas, self._tuned.use_nvls
         self.kernel = self._tuned.kernel
+        self.chunks = self._tuned.chunks
         return self._tuned
 
     def output(self, rank: Optional[int] = None) -> torch.Tensor:

@@ -49,7 +49,6 @@ def env_flag(name: str, default: bool = False) -> bool:
 #   OOB_PREFILL_CHUNKS=n       model runner, prefill: row-parallel GEMM in n slabs overlapped with the all-reduce + norm
 #   OOB_PREFILL_CHUNK_MIN_ROWS from how many tokens on (default 4096)
 #   OOB_NVTX=1                 NVTX ranges around the model runner's layers (utils/tracing.py)
-#   OOB_RUN_UNVALIDATED=1      tests: also run the GPU tests of paths that have not been run on hardware yet
 
 
 @dataclass

@@ -53,6 +53,9 @@ def _rank(rank, world, port):
     assert comm.all_reduce(y.clone(), "min").tolist() == [0.0, -float(world - 1), 3.0]
     h = torch.full((5,), 1.5, dtype=torch.bfloat16)
     assert comm.all_reduce(h).tolist() == [1.5 * world] * 5
+    # host-side exchange of a few integers per rank (what the autotuner agrees through)
+    assert comm.host_all_gather([rank, 7 - rank]) == [[r, 7 - r] for r in range(world)]
+    assert comm.status_ok()
     # all-to-all: slice j of every rank's [world, 3, 5] tensor goes to rank j
     t = torch.arange(world * 15, dtype=torch.float32).view(world, 3, 5) + 1000 * rank
     got = comm.all_to_all(t)

@@ -1,9 +1,5 @@
 """All-to-all kernel with the ranks emulated as block rows of one cooperative launch, and across real GPUs when
-there are several.  Oracle: index arithmetic on the host (the kernel moves bytes, it does no arithmetic).
-
-Written after the last hardware run of this build: the module only runs with OOB_RUN_UNVALIDATED=1 until it has
-passed on a GPU once."""
-import os
+there are several.  Oracle: index arithmetic on the host (the kernel moves bytes, it does no arithmetic)."""
 import uuid
 
 import pytest
@@ -11,9 +7,7 @@ import torch
 
 from mp_util import run_ranks
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("OOB_RUN_UNVALIDATED", "0") in ("", "0"),
-                                 reason="not yet run on hardware; set OOB_RUN_UNVALIDATED=1")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])

@@ -1,16 +1,9 @@
 """Epilogues applied by the kernel that sums the K splits of a GEMM (SwiGLU; RoPE + KV-cache write), against plain
-PyTorch fp32 references and against the unfused pair of kernels.
-
-These paths were written after the last hardware run of this build, so the module only runs with
-OOB_RUN_UNVALIDATED=1 until it has passed on a GPU once."""
-import os
-
+PyTorch fp32 references and against the unfused pair of kernels."""
 import pytest
 import torch
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("OOB_RUN_UNVALIDATED", "0") in ("", "0"),
-                                 reason="not yet run on hardware; set OOB_RUN_UNVALIDATED=1")]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])

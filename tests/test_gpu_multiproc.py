@@ -391,8 +391,6 @@ def _rank_llama_prefill_chunks(rank, world, key, port):
 
 
 @needs_multi
-@pytest.mark.skipif(os.environ.get("OOB_RUN_UNVALIDATED", "0") in ("", "0"),
-                    reason="slab-overlapped prefill not yet run on hardware; set OOB_RUN_UNVALIDATED=1")
 def test_llama_prefill_in_slabs_matches_unchunked():
     from mp_util import free_port
     world = 2
