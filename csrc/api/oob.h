@@ -187,6 +187,9 @@ typedef struct {
   int gemv;     /* plain mode, M <= 4: 1 = CUDA-core streaming kernel, 0 = only with OOB_GEMM_GEMV=1, -1 = never */
   int stream_k; /* two-SM kernel, plain and AG modes: stream-K tail; 0 = when it pays for the shape, 1 = whenever the
                    tile count leaves a remainder, -1 = never */
+  void* order;  /* two-SM kernel: optional device buffer, 2 x uint64 per 128-row half of every 256x256 tile (index
+                   2 * tile's number in the schedule + CTA of the pair): [0] globaltimer ns at which the half was
+                   complete (fused AR / RS: published to its reducer), [1] = pair << 32 | index in the pair's sequence */
 } oob_gemm_args_t;
 #define OOB_EPILOGUE_NONE 0
 #define OOB_EPILOGUE_SWIGLU 1  /* N = 2F columns [gate | up]; C is [M, F] = silu(gate) * up */
@@ -215,6 +218,17 @@ int oob_policy_select(int world, int collective /*0 AR,1 RS,2 AG*/, uint64_t byt
 
 /* Topology probe; writes a JSON document into buf (truncated to cap). */
 int oob_topology_json(char* buf, uint64_t cap, int run_probes);
+/* The same document with every switch: `flags` is a mask of OOB_TOPO_*, `devices` lists the device indices to describe
+ * (NULL / 0 = all visible ones).  OOB_TOPO_TEXT writes a table instead of JSON.  With OOB_TOPO_REQUIRE_PEER the call
+ * fails with OOB_ERR_UNSUPPORTED (the message names the pairs) when a listed pair has no peer access. */
+#define OOB_TOPO_PROBES 1u            /* live probes: remote ld/st, remote atomic, timed peer copy, multimem */
+#define OOB_TOPO_NO_ENABLE_PEER 2u    /* never switch peer access on (the per-pair probes are then skipped) */
+#define OOB_TOPO_NO_ATOMIC_PROBE 4u
+#define OOB_TOPO_NO_COPY_PROBE 8u
+#define OOB_TOPO_NO_MULTIMEM_PROBE 16u
+#define OOB_TOPO_REQUIRE_PEER 32u
+#define OOB_TOPO_TEXT 64u
+int oob_topology_describe(char* buf, uint64_t cap, unsigned flags, const int* devices, int n_devices);
 
 /* Node-local rendezvous on its own (host only): all-gather of small blobs,
  * barrier, file-descriptor exchange.  Every call has the creation timeout. */

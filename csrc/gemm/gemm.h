@@ -77,6 +77,11 @@ struct GemmArgs {
   // pair idles; partial accumulators meet in a library-owned workspace).  0 = when it pays for the shape, 1 = whenever
   // the tile count leaves a remainder, -1 = never.
   int stream_k;
+  // Two-SM kernel, every mode: optional tile-order record.  Two 64-bit words per 128-row half of every 256x256 tile,
+  // indexed 2 * (tile's number in the schedule) + (CTA of the pair): [0] globaltimer nanoseconds at which the half
+  // was complete in this GPU's memory (fused AR / RS: when it was published to the rank that reduces it),
+  // [1] = pair << 32 | index of the tile in that pair's own sequence.  Sorting by [0] gives the completion order.
+  unsigned long long* order;
   // Plain mode, M <= 128: 1 = the weight-streaming kernel (gemm_skinny.cu), 0 / -1 = the tiled kernels (0 follows
   // OOB_GEMM_SKINNY=1 for M <= 16).
   int skinny;

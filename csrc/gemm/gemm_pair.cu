@@ -825,6 +825,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == kGemmPlain ?
           copy_out_half(stage_u32, lane, dst_rows, dst_row_bytes, h, row0, col0, a.M, a.N, vec_ok);
           __syncwarp();
         }
+        if constexpr (!kSignals) {
+          if (a.order != nullptr && q == 3 && lane == 0) {
+            unsigned long long* rec = a.order + 2 * (2 * size_t(it.seq) + cta);
+            rec[0] = ptx::globaltimer_ns();
+            rec[1] = (static_cast<unsigned long long>(pair) << 32) | idx;
+          }
+        }
         if constexpr (kSignals) {
           // This warp's rows of the tile are stored (to LOCAL memory).  The signal warp publishes the tile once
           // all four epilogue warps are here; the fence below orders this warp's stores before the count.
@@ -978,6 +985,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == kGemmPlain ?
           }
           ptx::fence_acq_rel_sys();
           ptx::red_release_sys_add(counter_ptr(ctx, owner, cidx), 1u);
+          if (a.order != nullptr) {
+            unsigned long long* rec = a.order + 2 * (2 * size_t(it.seq) + cta);
+            rec[0] = ptx::globaltimer_ns();
+            rec[1] = (static_cast<unsigned long long>(pair) << 32) | idx;
+          }
         }
       }
     }

@@ -997,6 +997,7 @@ int oob_gemm(oob_comm* c, const oob_gemm_args_t* a, void* stream) {
   g.splitk_reduce = a->splitk_reduce;
   g.gemv = a->gemv;
   g.stream_k = a->stream_k;
+  g.order = static_cast<unsigned long long*>(a->order);
   g.epilogue = a->epilogue;
   g.epilogue_args = a->epilogue_args;
   if (a->epilogue != OOB_EPILOGUE_NONE) {

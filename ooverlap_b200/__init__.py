@@ -26,10 +26,25 @@ def build(force: bool = False):
     return _build.build(force=force)
 
 
-def topology(run_probes: bool = False) -> dict:
-    """Topology of the visible GPUs as a dict (see ``lib/oob_topology`` for the CLI)."""
+def topology(run_probes: bool = False, *, devices=None, enable_peer: bool = True, atomic_probe: bool = True,
+             copy_probe: bool = True, multimem_probe: bool = True, require_peer: bool = False, text: bool = False):
+    """Topology of the visible GPUs (or of ``devices``) as a dict, or as a table when ``text`` is set (the CLI
+    ``lib/oob_topology`` prints the same).  ``run_probes`` runs the live probes: per directed pair a remote store / load,
+    a remote atomic and a timed peer copy, and over all devices a multimem store / add / in-switch sum; the keyword
+    switches take single probes out (``enable_peer=False``: peer access is never switched on, so no per-pair probe
+    runs).  ``require_peer`` raises ``OobError`` when a pair has no peer access."""
     import ctypes
     import json
+    flags = _lib.TOPO_PROBES if run_probes else 0
+    flags |= 0 if enable_peer else _lib.TOPO_NO_ENABLE_PEER
+    flags |= 0 if atomic_probe else _lib.TOPO_NO_ATOMIC_PROBE
+    flags |= 0 if copy_probe else _lib.TOPO_NO_COPY_PROBE
+    flags |= 0 if multimem_probe else _lib.TOPO_NO_MULTIMEM_PROBE
+    flags |= _lib.TOPO_REQUIRE_PEER if require_peer else 0
+    flags |= _lib.TOPO_TEXT if text else 0
+    devs = [int(d) for d in devices] if devices else []
+    arr = (ctypes.c_int * len(devs))(*devs) if devs else None
     buf = ctypes.create_string_buffer(1 << 20)
-    _lib.check(_lib.lib().oob_topology_json(buf, len(buf), 1 if run_probes else 0))
-    return json.loads(buf.value.decode())
+    _lib.check(_lib.lib().oob_topology_describe(buf, len(buf), flags, arr, len(devs)))
+    out = buf.value.decode()
+    return out if text else json.loads(out)

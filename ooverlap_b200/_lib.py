@@ -20,6 +20,9 @@ from . import _build
 OOB_OK = 0
 ERR_INVALID, ERR_CUDA, ERR_BOOTSTRAP, ERR_UNSUPPORTED, ERR_NOMEM, ERR_DEVICE_TIMEOUT, ERR_POISONED = -1, -2, -3, -4, -5, -6, -7
 
+TOPO_PROBES, TOPO_NO_ENABLE_PEER, TOPO_NO_ATOMIC_PROBE, TOPO_NO_COPY_PROBE = 1, 2, 4, 8
+TOPO_NO_MULTIMEM_PROBE, TOPO_REQUIRE_PEER, TOPO_TEXT = 16, 32, 64
+
 F16, BF16, F32 = 0, 1, 2
 SUM, MIN, MAX = 0, 1, 2
 ALGO_AUTO = -1
@@ -70,7 +73,7 @@ class GemmArgs(Structure):
                 ("weight", c_void_p), ("eps", c_float), ("y_local", c_void_p), ("res_out_local", c_void_p),
                 ("rs_emu_stride", c_uint64), ("a_full_reg", c_int), ("a_full_off", c_uint64), ("use_nvls", c_int),
                 ("splits", c_int), ("no_join", c_int), ("trace", c_void_p), ("pair", c_int), ("splitk_reduce", c_int), ("skinny", c_int), ("epilogue", c_int),
-                ("epilogue_args", c_void_p), ("gemv", c_int), ("stream_k", c_int)]
+                ("epilogue_args", c_void_p), ("gemv", c_int), ("stream_k", c_int), ("order", c_void_p)]
 
 
 class SwigluEpilogue(Structure):
@@ -143,6 +146,7 @@ def _declare(lib) -> None:
     lib.oob_policy_load.argtypes = [c_char_p]
     lib.oob_policy_select.argtypes = [c_int, c_int, c_uint64, c_int, POINTER(c_int), POINTER(c_int)]
     lib.oob_topology_json.argtypes = [c_char_p, c_uint64, c_int]
+    lib.oob_topology_describe.argtypes = [c_char_p, c_uint64, c_uint, POINTER(c_int), c_int]
     lib.oob_test_bounded_wait.argtypes = [P, P]
     lib.oob_bootstrap_create.argtypes = [c_int, c_int, c_char_p, c_int, POINTER(P)]
     lib.oob_bootstrap_destroy.argtypes = [P]

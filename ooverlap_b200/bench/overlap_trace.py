@@ -26,6 +26,7 @@ import torch
 import torch.distributed as dist
 
 from .. import Communicator
+from ..ops.gemm import order_buffer, tile_order
 from ..ops import GemmAllReduce, GemmReduceScatterNorm
 
 
@@ -71,6 +72,8 @@ def main() -> int:
     torch.cuda.synchronize()
     trace = torch.zeros(160, 8, dtype=torch.int64, device="cuda")
     op.trace_buffer = trace
+    if (args.kernel or "pair") == "pair":
+        op.order_buffer = order_buffer(args.m, args.n)
     dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -97,6 +100,14 @@ def main() -> int:
     out["items_by_comm_ctas"] = int(comm_rows[:, 5].sum())
     out["items_by_gemm_ctas"] = int(gemm_rows[:, 5].sum())
     out["comm_cta_wait_us_med"] = round(statistics.median([int(v) / 1e3 for v in comm_rows[:, 6]]), 1) if len(comm_rows) else None
+    if getattr(op, "order_buffer", None) is not None:
+        rec = tile_order(op.order_buffer)
+        if rec:
+            # Tile-order record of the two-SM kernel: when each 128-row half-tile was published to its reducer.
+            out["half_tiles_published"] = len(rec)
+            out["publish_order_first_units"] = [r["unit"] for r in rec[:16]]
+            out["publish_span_us"] = round(rec[-1]["t_us"], 1)
+            out["publish_us_quartiles"] = [round(rec[len(rec) * q // 4 - (1 if q == 4 else 0)]["t_us"], 1) for q in (1, 2, 3, 4)]
     gathered = [None] * world
     dist.all_gather_object(gathered, out)
     if rank == 0:

@@ -37,8 +37,12 @@ def fill_gemm_args(args: _lib.GemmArgs, a: torch.Tensor, b: torch.Tensor) -> Non
 
 def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, max_ctas: int = 0,
          splits: int = 0, pair: int = 0, skinny: int = 0, splitk_reduce: int = 0,
-         gemv: int = 0, stream_k: int = 0) -> torch.Tensor:
+         gemv: int = 0, stream_k: int = 0, order: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out = a @ b.T`` with fp32 accumulation in TMEM.
+
+    ``order`` (two-SM kernel): an int64 CUDA tensor ``[2 * tiles, 2]`` (``tiles`` = 256x256 tiles of the output) that
+    the kernel fills with the tile-order record: per 128-row half of every tile the globaltimer nanoseconds at which
+    it was stored and ``pair << 32 | index in the pair's sequence``; see :func:`tile_order`.
 
     ``splits`` > 1 splits K over that many CTAs per output tile (fp32 partials in the library's workspace,
     summed in split order); 0 picks a split from the shape (small-M problems that would otherwise leave most
@@ -81,8 +85,40 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     args.splitk_reduce = splitk_reduce
     args.gemv = gemv
     args.stream_k = stream_k
+    if order is not None:
+        check_order_buffer(order, M, N)
+        args.order = order.data_ptr()
     _lib.check(_lib.lib().oob_gemm(None, ctypes.byref(args), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return out
+
+
+def order_buffer(M: int, N: int, device="cuda") -> torch.Tensor:
+    """A zeroed tile-order record for an [M, N] output of the two-SM kernel (``order=`` of :func:`gemm`,
+    ``order_buffer`` of the overlap ops)."""
+    tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    return torch.zeros((2 * tiles, 2), dtype=torch.int64, device=device)
+
+
+def check_order_buffer(order: torch.Tensor, M: int, N: int) -> None:
+    tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    if order.dtype != torch.int64 or not order.is_cuda or not order.is_contiguous() or order.numel() < 4 * tiles:
+        raise ValueError(f"order must be a contiguous int64 CUDA tensor of at least {2 * tiles} x 2 words")
+
+
+def tile_order(order: torch.Tensor) -> list:
+    """Decodes a tile-order record into a list of dicts sorted by completion time: ``unit`` (2 * tile's number in the
+    schedule + CTA of the pair), ``t_us`` (microseconds after the first completion), ``pair`` and ``index`` (the
+    tile's position in that pair's own sequence).  Halves the kernel never wrote (rows past M) are left out.
+
+    Capability parity: the reference records in which order its GEMM finishes tiles to derive reorder hints
+    (tool/search.py, the tile-order capture of src/gemm/gemm_with_signal_sm90.h); here the schedule is fixed by the
+    kernel (PairSched) and the record shows how the hardware actually ran it."""
+    rows = order.detach().cpu().tolist()
+    done = [(t, u, w) for u, (t, w) in enumerate(rows) if t > 0]
+    if not done:
+        return []
+    t0 = min(t for t, _, _ in done)
+    return [dict(unit=u, t_us=(t - t0) / 1e3, pair=int(w >> 32), index=int(w & 0xFFFFFFFF)) for t, u, w in sorted(done)]
 
 
 def reserve_workspace(splitk_bytes: int = 0) -> None:

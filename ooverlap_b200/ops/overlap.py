@@ -327,6 +327,8 @@ class GemmAllReduce:
         args.no_join = 0 if getattr(self, "join", True) else 1
         trace = getattr(self, "trace_buffer", None)  # [ctas, 8] int64 device tensor: per-CTA phase stamps
         args.trace = trace.data_ptr() if trace is not None else None
+        order = getattr(self, "order_buffer", None)  # tile-order record of the two-SM kernel (ops.gemm.order_buffer)
+        args.order = order.data_ptr() if order is not None else None
         args.partial_reg, args.partial_off = 0, self.partial_off
         args.c_reg, args.c_off = 0, self.c_off
         args.counter_base = self.counter_base
@@ -382,6 +384,8 @@ class GemmReduceScatterNorm:
         args.no_join = 0 if getattr(self, "join", True) else 1
         trace = getattr(self, "trace_buffer", None)  # [ctas, 8] int64 device tensor: per-CTA phase stamps
         args.trace = trace.data_ptr() if trace is not None else None
+        order = getattr(self, "order_buffer", None)  # tile-order record of the two-SM kernel (ops.gemm.order_buffer)
+        args.order = order.data_ptr() if order is not None else None
         args.partial_reg, args.partial_off = 0, self.partial_off
         args.counter_base = self.counter_base
         args.residual = residual.data_ptr() if residual is not None else None
@@ -445,6 +449,8 @@ class AllGatherGemm:
         args.no_join = 0 if getattr(self, "join", True) else 1
         trace = getattr(self, "trace_buffer", None)  # [ctas, 8] int64 device tensor: per-CTA phase stamps
         args.trace = trace.data_ptr() if trace is not None else None
+        order = getattr(self, "order_buffer", None)  # tile-order record of the two-SM kernel (ops.gemm.order_buffer)
+        args.order = order.data_ptr() if order is not None else None
         args.a_full_reg, args.a_full_off = 0, self.a_full_off
         args.counter_base = self.counter_base
         _lib.check(_lib.lib().oob_gemm(self.comm._h, ctypes.byref(args), _stream()))

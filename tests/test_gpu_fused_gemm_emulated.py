@@ -42,6 +42,26 @@ def test_gemm_all_reduce(world, shape, dtype, kernel):
     g.close()
 
 
+def test_fused_two_sm_kernel_writes_the_tile_order_record():
+    """The signal warp stamps every half-tile when it publishes it to its reducer (the emulated ranks share the
+    buffer; the last writer's stamp stays)."""
+    from ooverlap_b200 import EmulatedGroup
+    from ooverlap_b200.ops import GemmAllReduce, order_buffer, tile_order
+    world, M, N, K = 2, 1024, 1024, 256
+    g = EmulatedGroup(world, heap_bytes=64 << 20)
+    op = GemmAllReduce(g, M, N, torch.bfloat16, comm_ctas=4, kernel="pair")
+    op.order_buffer = order_buffer(M, N)
+    a, b = _operands(world, M, N, K, torch.bfloat16, seed=5)
+    op(a, b)
+    g.check_status()
+    rec = tile_order(op.order_buffer)
+    tiles = (M // 256) * (N // 256)
+    assert sorted(r["unit"] for r in rec) == list(range(2 * tiles))
+    want = sum(a[r].float() @ b[r].float().t() for r in range(world))
+    assert (op.output(0).float() - want).abs().max().item() <= 2e-2 * max(1.0, want.abs().max().item())
+    g.close()
+
+
 @pytest.mark.parametrize("kernel", KERNELS)
 @pytest.mark.parametrize("world,blocks,N", [(2, 2, 1024), (4, 2, 1024), (4, 1, 8192), (2, 3, 2560), (8, 1, 512)])
 @pytest.mark.parametrize("with_norm", [True, False])

@@ -235,6 +235,32 @@ def test_two_sm_kernel_cta_budget_and_padded_output():
     assert big[:, 1024:].abs().max().item() == 0
 
 
+def test_two_sm_kernel_tile_order_record():
+    """Every 128-row half of every 256x256 tile reports when it was stored, by which pair and as which of the pair's
+    tiles; within a pair the completion times follow the pair's own sequence."""
+    from ooverlap_b200.ops import gemm, order_buffer, tile_order
+    M, N, K = 2048, 4096, 512
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = torch.randn(N, K, device="cuda").bfloat16()
+    order = order_buffer(M, N)
+    c = gemm(a, b, splits=1, pair=1, stream_k=-1, max_ctas=32, order=order)
+    torch.cuda.synchronize()
+    assert torch.equal(c, gemm(a, b, splits=1, pair=1, stream_k=-1))
+    rec = tile_order(order)
+    tiles = (M // 256) * (N // 256)
+    assert len(rec) == 2 * tiles and sorted(r["unit"] for r in rec) == list(range(2 * tiles))
+    assert {r["pair"] for r in rec} == set(range(16))  # 32 CTAs = 16 pairs, all of them got tiles
+    per_pair = {}
+    for r in rec:  # rec is sorted by time
+        per_pair.setdefault(r["pair"], []).append(r["index"])
+    for pair, idx in per_pair.items():
+        assert len(idx) == 2 * tiles // 16
+        assert idx == sorted(idx), (pair, idx)
+    assert rec[-1]["t_us"] > rec[0]["t_us"]
+    with pytest.raises(ValueError):
+        gemm(a, b, order=torch.zeros(4, 2, dtype=torch.int64, device="cuda"))
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("shape", [(1, 256, 64), (1, 1280, 8192), (7, 7168, 8192), (16, 8192, 1024), (64, 8192, 3584),
                                    (100, 200, 72), (128, 2048, 4096), (33, 1000, 1096), (17, 16032, 2048)])
