@@ -52,6 +52,33 @@ def lookup(op: str, M: int, N: int, K: int, world: int, dtype: str, path: Option
     return hit
 
 
+PACKAGED_GEMM = os.path.join(os.path.dirname(PACKAGED), "gemm_solutions.json")
+_gemm_path = None  # resolved once: "" = no table
+
+
+def gemm_key(M: int, N: int, K: int, dtype: str) -> str:
+    return f"gemm:{M}x{N}x{K}:{dtype}"
+
+
+def lookup_gemm(M: int, N: int, K: int, dtype: str) -> Optional[dict]:
+    """The profiled configuration of a plain GEMM shape (written by ``ooverlap_b200.bench.gemm_profile``): the file
+    named by ``OOB_GEMM_SOLUTIONS``, else the packaged ``policy/gemm_solutions.json``; ``OOB_GEMM_SOLUTIONS=none`` turns
+    the lookup off.  The path is resolved once per process."""
+    global _gemm_path
+    if _gemm_path is None:
+        path = os.environ.get("OOB_GEMM_SOLUTIONS", "") or PACKAGED_GEMM
+        _gemm_path = path if path != "none" and os.path.exists(path) else ""
+    if not _gemm_path:
+        return None
+    return load(_gemm_path).get(gemm_key(M, N, K, dtype))
+
+
+def reset_gemm_lookup() -> None:
+    """Forget the resolved table path (tests change the environment variable)."""
+    global _gemm_path
+    _gemm_path = None
+
+
 def save(path: str, table: dict) -> None:
     """Atomic replace, so that an interrupted tuning run never leaves a truncated file."""
     d = os.path.dirname(os.path.abspath(path)) or "."

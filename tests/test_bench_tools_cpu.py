@@ -64,6 +64,26 @@ def test_solutions_roundtrip(tmp_path, monkeypatch):
     assert solutions.load(str(tmp_path / "missing.json")) == {}
 
 
+def test_gemm_solution_table_lookup_and_profiler_candidates(tmp_path, monkeypatch):
+    from ooverlap_b200.bench.gemm_profile import candidates
+    path = str(tmp_path / "gemm.json")
+    solutions.save(path, {solutions.gemm_key(512, 8192, 8192, "bf16"): {"pair": 1, "splits": 1, "stream_k": 1, "us": 60.0}})
+    monkeypatch.setenv("OOB_GEMM_SOLUTIONS", path)
+    solutions.reset_gemm_lookup()
+    assert solutions.lookup_gemm(512, 8192, 8192, "bf16")["stream_k"] == 1
+    assert solutions.lookup_gemm(512, 8192, 8192, "fp16") is None
+    monkeypatch.setenv("OOB_GEMM_SOLUTIONS", "none")
+    solutions.reset_gemm_lookup()
+    assert solutions.lookup_gemm(512, 8192, 8192, "bf16") is None
+    monkeypatch.delenv("OOB_GEMM_SOLUTIONS")
+    solutions.reset_gemm_lookup()
+    names = [c["name"] for c in candidates(64, 8192, 3584)]
+    assert "weight_streaming" in names and "pair" not in names and "one_sm/split8" in names and "one_sm/split16" not in names
+    names = [c["name"] for c in candidates(2048, 8192, 8192)]
+    assert names[:4] == ["rule", "pair", "pair+stream_k", "one_sm"] and "cuda_core" not in names
+    assert "cuda_core" in [c["name"] for c in candidates(1, 7168, 8192)]
+
+
 def test_vllm_bench_model_dir_env_and_commands(tmp_path):
     import json
     import subprocess
