@@ -72,6 +72,13 @@ typedef struct {
 } oob_device_status_t;
 
 const char* oob_last_error(void);
+/* Logging of the native runtime: level 0 error, 1 warn (default), 2 info, 3 debug; OOB_LOG_LEVEL sets it from the
+ * environment.  Records go to stderr unless a sink is installed (the sink may be called from any thread). */
+typedef void (*oob_log_sink_t)(int level, const char* message);
+int oob_set_log_level(int level);
+int oob_get_log_level(void);
+int oob_set_log_sink(oob_log_sink_t sink);
+int oob_log_message(int level, const char* message);
 const char* oob_version(void);
 
 /* One call per rank process.  `key` names the rendezvous (<= 80 chars). */

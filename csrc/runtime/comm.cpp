@@ -13,6 +13,7 @@
 #include "../gemm/gemm_pair.h"
 #include "driver_api.h"
 #include "errors.h"
+#include "log.h"
 
 using namespace oob;
 
@@ -25,6 +26,7 @@ thread_local std::string g_last_error;
 
 int set_error(int code, const std::string& msg) {
   g_last_error = msg;
+  OOB_LOG(kLogInfo, "error %d: %s", code, msg.c_str());
   return code;
 }
 
@@ -320,6 +322,12 @@ int setup_vmm(oob_comm* c, unsigned flags, std::string* why) {
       }
     }
     c->nvls = mok;
+    if (!mok)
+      OOB_LOG(kLogWarn, "rank %d: the NVLink multicast alias could not be set up (last driver answer: %s); using peer "
+              "loads and stores", c->rank, cu_str(d, r).c_str());
+  } else if (c->world > 1) {
+    OOB_LOG(kLogInfo, "rank %d: no multicast alias (%s)", c->rank,
+            !mc_ok ? "the device does not report multicast support" : "switched off by flag or OOB_DISABLE_NVLS");
   }
   return OOB_OK;
 }
@@ -418,6 +426,8 @@ int oob_comm_create(int rank, int world, int device, const char* key, uint64_t h
   std::string why;
   if (!(flags & OOB_FLAG_LEGACY_IPC)) rc = setup_vmm(c, flags, &why);
   if (rc != OOB_OK && rc != OOB_ERR_BOOTSTRAP) {
+    if (!(flags & OOB_FLAG_LEGACY_IPC))
+      OOB_LOG(kLogWarn, "rank %d: no VMM heap (%s); falling back to cudaMalloc + CUDA IPC, without NVLS", rank, why.c_str());
     std::string why2;
     rc = setup_legacy_ipc(c, &why2);
     if (rc != OOB_OK) why = why + "; " + why2;
@@ -440,6 +450,9 @@ int oob_comm_create(int rank, int world, int device, const char* key, uint64_t h
     return rc;
   }
   allocator_init(c);
+  OOB_LOG(kLogInfo, "rank %d/%d on device %d: heap %llu MiB (%s), NVLS %s, device-wait budget %llu ms", rank, world, device,
+          static_cast<unsigned long long>(c->heap_bytes >> 20), c->memory_kind == 0 ? "VMM, fd export" : "cudaMalloc + CUDA IPC",
+          c->nvls ? "on" : "off", static_cast<unsigned long long>(c->timeout_ns / 1000000ull));
   *out = c;
   return OOB_OK;
 }
@@ -570,6 +583,10 @@ int oob_comm_status(oob_comm* c, oob_device_status_t* s) {
         s->where = d->where;
         s->pad = 0;
       }
+      if (!c->poisoned)
+        OOB_LOG(kLogWarn, "rank %d: a kernel gave up waiting (code %d, peer %d, block %d, expected %u, observed %u, site %d); "
+                "the communicator is poisoned until oob_comm_recover", c->rank, int(d->code), int(d->peer), int(d->block),
+                unsigned(d->expected), unsigned(d->observed), int(d->where));
       c->poisoned = true;
       return set_error(OOB_ERR_DEVICE_TIMEOUT,
                        "device wait gave up: code " + std::to_string(d->code) + " rank " + std::to_string(d->rank) +
@@ -598,6 +615,7 @@ int oob_comm_recover(oob_comm* c) {
   std::memset(c->status_host, 0, sizeof(DeviceStatus) * n);
   if (c->boot && c->world > 1 && !c->boot->barrier()) return set_error(OOB_ERR_BOOTSTRAP, c->boot->last_error());
   c->poisoned = false;
+  OOB_LOG(kLogInfo, "rank %d: signal pad and status cleared, communicator back in service", c->rank);
   return OOB_OK;
 }
 
@@ -736,11 +754,13 @@ int oob_register_ipc(oob_comm* c, void* ptr, uint64_t bytes, int* reg) {
         for (auto it = cache.begin(); it != cache.end(); ++it)
           if (it->refs == 0 && (victim == cache.end() || it->last_use < victim->last_use)) victim = it;
         if (victim != cache.end()) {
+          OOB_LOG(kLogDebug, "rank %d: IPC import cache of peer %d is full, closing the least recently used mapping", c->rank, p);
           cudaIpcCloseMemHandle(victim->base);
           cache.erase(victim);
         }
       }
       cache.push_back({all[p].handle, mapped, ++c->use_clock, 0});
+      OOB_LOG(kLogDebug, "rank %d: opened an IPC mapping of peer %d's allocation (%zu cached)", c->rank, p, cache.size());
     }
     for (auto& im : cache)
       if (im.base == mapped) ++im.refs;

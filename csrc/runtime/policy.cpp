@@ -21,6 +21,7 @@
 
 #include "../api/oob.h"
 #include "errors.h"
+#include "log.h"
 
 namespace oob {
 namespace {
@@ -245,6 +246,7 @@ int oob_policy_load(const char* json_path) {
   }
   std::string err;
   if (!load_file(json_path, &err)) return set_error(OOB_ERR_INVALID, err);
+  OOB_LOG(kLogInfo, "tuning policy %s: %zu points", json_path, g_points.size());
   return OOB_OK;
 }
 

@@ -16,6 +16,7 @@ from . import _lib  # noqa: F401
 from ._lib import DeviceTimeout, OobError  # noqa: F401
 from .comm import Communicator, SlotPool  # noqa: F401
 from .emulated import EmulatedGroup  # noqa: F401
+from .local_group import LocalGroup  # noqa: F401
 
 __version__ = "0.2.0"
 

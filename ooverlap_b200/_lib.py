@@ -23,6 +23,9 @@ ERR_INVALID, ERR_CUDA, ERR_BOOTSTRAP, ERR_UNSUPPORTED, ERR_NOMEM, ERR_DEVICE_TIM
 TOPO_PROBES, TOPO_NO_ENABLE_PEER, TOPO_NO_ATOMIC_PROBE, TOPO_NO_COPY_PROBE = 1, 2, 4, 8
 TOPO_NO_MULTIMEM_PROBE, TOPO_REQUIRE_PEER, TOPO_TEXT = 16, 32, 64
 
+LOG_SINK = ctypes.CFUNCTYPE(None, c_int, c_char_p)
+LOG_ERROR, LOG_WARN, LOG_INFO, LOG_DEBUG = 0, 1, 2, 3
+
 F16, BF16, F32 = 0, 1, 2
 SUM, MIN, MAX = 0, 1, 2
 ALGO_AUTO = -1
@@ -102,6 +105,10 @@ def _declare(lib) -> None:
     P = c_void_p
     lib.oob_last_error.restype = c_char_p
     lib.oob_version.restype = c_char_p
+    lib.oob_set_log_level.argtypes = [c_int]
+    lib.oob_get_log_level.argtypes = []
+    lib.oob_set_log_sink.argtypes = [LOG_SINK]
+    lib.oob_log_message.argtypes = [c_int, c_char_p]
     lib.oob_comm_create.argtypes = [c_int, c_int, c_int, c_char_p, c_uint64, c_uint, c_int, POINTER(P)]
     lib.oob_comm_create_emulated.argtypes = [c_int, c_int, c_uint64, POINTER(P)]
     lib.oob_comm_destroy.argtypes = [P]

@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import threading
 import uuid
 from dataclasses import dataclass
 from typing import Optional, Sequence
@@ -55,6 +56,9 @@ class SlotPool:
         i = self.next_index
         self.next_index = (i + 1) % len(self.offsets)
         return i
+
+
+_policy_lock = threading.Lock()
 
 
 def _current_stream_ptr() -> int:
@@ -123,7 +127,8 @@ class Communicator:
             packaged = os.path.join(os.path.dirname(os.path.abspath(__file__)), "policy", "b200_nvswitch.json")
             policy = packaged if os.path.exists(packaged) else ""
         if policy and policy != "builtin":
-            _lib.check(lib.oob_policy_load(policy.encode()))
+            with _policy_lock:  # the table is process-wide; several ranks of one process may be created at once
+                _lib.check(lib.oob_policy_load(policy.encode()))
         handle = ctypes.c_void_p()
         _lib.check(lib.oob_comm_create(self.rank, self.world, self.device, broker_key.encode(),
                                        heap_bytes or self.config.heap_bytes, flags, self.config.timeout_ms,
