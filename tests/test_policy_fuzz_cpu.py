@@ -16,6 +16,7 @@ def test_policy_parser_under_sanitizers(tmp_path):
     exe = tmp_path / "policy_fuzz"
     cmd = ["g++", "-std=c++17", "-O1", "-g", "-fsanitize=address,undefined", "-fno-omit-frame-pointer", "-I", CUDA_INC,
            os.path.join(ROOT, "tests", "native", "policy_fuzz.cpp"), os.path.join(ROOT, "csrc", "runtime", "policy.cpp"),
+           os.path.join(ROOT, "csrc", "runtime", "log.cpp"),
            "-o", str(exe)]
     built = subprocess.run(cmd, capture_output=True, text=True)
     if built.returncode != 0 and "sanitize" in (built.stderr or ""):
