@@ -43,20 +43,25 @@ def predict_us(cand: dict, t_gemm: float, t_ar: dict, sms: int, t_first: float) 
     all-reduce time; budgets in between take the nearest measured one."""
     if cand["strategy"] == "unfused":
         return t_gemm + min(t_ar.values())
+    if cand["strategy"] == "chunked":
+        slabs = max(1, cand.get("slabs", 4))
+        return t_gemm / slabs + max(t_gemm * (slabs - 1) / slabs, min(t_ar.values())) + 10.0
     c = cand["comm_ctas"]
     nearest = min(t_ar, key=lambda k: abs(k - c))
     comm = t_ar[nearest] * (1.75 if not cand["use_nvls"] else 1.0)  # peer stores move 1.75 x the bytes of the switch path
     return max(t_gemm * sms / max(1, sms - c), comm) + t_first
 
 
-def candidates(comm_ctas, nvls_paths, kernels):
+def candidates(comm_ctas, nvls_paths, kernels, M=0, world=0):
     out = [dict(strategy="unfused", kernel="", comm_ctas=0, use_nvls=0)]
     for k in kernels:
         for c in comm_ctas:
             for nv in nvls_paths:
                 if k == "pair" and nv == 2:
-                    continue
+                    continue  # the two-SM kernel has one switch path (in-place reduce), selected by 1
                 out.append(dict(strategy="fused", kernel=k, comm_ctas=c, use_nvls=nv))
+    if world >= 4 and M >= 4096 and M % 2048 == 0:
+        out.append(dict(strategy="chunked", kernel="", comm_ctas=0, use_nvls=1))  # slab pipeline on two streams
     return out
 
 
@@ -101,7 +106,10 @@ def main() -> int:
         tiles = ((M + 255) // 256) * ((N + 255) // 256)
         waves = max(1.0, tiles / (sms / 2))
         t_first = t_gemm / waves + 5.0
-        cands = candidates(ctas, paths, kernels)
+        cands = candidates(ctas, paths, kernels, M, world)
+        for c in cands:
+            if c["strategy"] == "chunked":
+                c["slabs"] = M // 2048
         for c in cands:
             c["predicted_us"] = round(predict_us(c, t_gemm, t_ar, sms, t_first), 1)
         cands.sort(key=lambda c: c["predicted_us"])
@@ -109,7 +117,8 @@ def main() -> int:
         for cand in cands:
             if not args.exhaustive and best is not None and cand["predicted_us"] > best["us"] * (1.0 + args.slack):
                 break
-            op = GemmAllReduce(comm, M, N, dt, comm_ctas=cand["comm_ctas"] or None, use_nvls=cand["use_nvls"],
+            op = GemmAllReduce(comm, M, N, dt, comm_ctas=cand["comm_ctas"] or None,
+                               use_nvls=cand["use_nvls"] if cand["strategy"] == "fused" else None,
                                strategy=cand["strategy"], kernel=cand["kernel"] or None)
             check(f"{k} {cand}", op(a, b), want)
             t = timed(lambda: op(a, b), args.iters, 3)

@@ -73,10 +73,12 @@ def _operands(comm, a: torch.Tensor, b: torch.Tensor):
 
 
 def plan_gemm_all_reduce(world: int, M: int, N: int, emulated: bool, strategy: str = "auto", chunks: Optional[int] = None,
-                         use_nvls=None, comm_ctas: Optional[int] = None, solution: Optional[dict] = None):
-    """Resolves what :class:`GemmAllReduce` will run: ``(strategy, chunks, use_nvls, comm_ctas)`` with ``strategy``
-    one of fused / unfused / chunked.  Pure function of its arguments (``solution`` is a tuned entry for the shape,
-    or None), so that the rule can be read and tested without a GPU."""
+                         use_nvls=None, comm_ctas: Optional[int] = None, solution: Optional[dict] = None,
+                         kernel: Optional[str] = None):
+    """Resolves what :class:`GemmAllReduce` will run: ``(strategy, chunks, use_nvls, comm_ctas, kernel)`` with
+    ``strategy`` one of fused / unfused / chunked and ``kernel`` one of None (the library's default), "pair", "one_sm".
+    Pure function of its arguments (``solution`` is a tuned entry for the shape, or None), so that the rule can be read
+    and tested without a GPU.  What the caller fixed (``use_nvls``, ``comm_ctas``, ``kernel``) is never overridden."""
     if strategy not in ("auto", "fused", "unfused", "chunked"):
         raise ValueError(strategy)
     if strategy == "auto" and solution is not None and not emulated:
@@ -85,15 +87,20 @@ def plan_gemm_all_reduce(world: int, M: int, N: int, emulated: bool, strategy: s
             raise ValueError(f"solution names an unknown strategy {strategy!r}")
         if comm_ctas is None and solution.get("comm_ctas"):
             comm_ctas = int(solution["comm_ctas"])
-        if use_nvls is None and "use_nvls" in solution:
+        if use_nvls is None and "use_nvls" in solution and solution["use_nvls"] is not None:
             use_nvls = int(solution["use_nvls"])
         if chunks is None and solution.get("chunks"):
             chunks = int(solution["chunks"])
+        if kernel is None and solution.get("kernel"):
+            kernel = str(solution["kernel"])
     if strategy == "auto":
-        big = M * N * 2 > (64 << 20)
-        strategy = "fused" if (world < 4 or big or emulated) else "unfused"
-        if use_nvls is None and world >= 4:
-            use_nvls = 0  # measured: peer pushes beat both NVLS variants inside the fused kernel
+        strategy, nv, ctas, kern = _auto_rule(world, M * N * 2, emulated)
+        if use_nvls is None:
+            use_nvls = nv
+        if comm_ctas is None:
+            comm_ctas = ctas
+        if kernel is None:
+            kernel = kern
     if strategy == "chunked":
         if chunks is None:
             chunks = M // 2048 if M % 2048 == 0 else 1  # slabs of 2048 rows: several waves of tiles each
@@ -105,7 +112,26 @@ def plan_gemm_all_reduce(world: int, M: int, N: int, emulated: bool, strategy: s
             strategy = "unfused"  # nothing to pipeline against
     if strategy != "chunked":
         chunks = 1
-    return strategy, chunks, use_nvls, comm_ctas
+    return strategy, chunks, use_nvls, comm_ctas, kernel
+
+
+def _auto_rule(world: int, out_bytes: int, emulated: bool):
+    """The measured choices on B200 / NVSwitch: (strategy, use_nvls, comm_ctas, kernel); None = the op's default.
+
+    * emulation: one launch per op, so always fused;
+    * two ranks: fused; outputs of 64 MiB and more on the two-SM kernel reducing in place through the switch with 24
+      communication CTAs, smaller ones on the one-SM kernel that pushes partial tiles (it starts reducing earlier, which
+      is what counts for one or two waves of tiles);
+    * four ranks and more: up to 64 MiB this library's GEMM followed by its in-switch all-reduce, above that the fused
+      one-SM kernel with peer pushes."""
+    big = out_bytes > (64 << 20)
+    if emulated:
+        return "fused", None, None, None
+    if world < 4:
+        return ("fused", 1, 24, "pair") if big else ("fused", None, 16, "one_sm")
+    if big:
+        return "fused", 0, None, "one_sm"
+    return "unfused", None, None, None
 
 
 class GemmAllReduce:
@@ -150,8 +176,9 @@ class GemmAllReduce:
             # A tuned solution for this shape (OOB_OVERLAP_SOLUTIONS, written by bench.tune_overlap) wins.
             from . import solutions
             sol = solutions.lookup("gemm_ar", M, N, 0, comm.world, "bf16" if dtype == torch.bfloat16 else "fp16")
-        strategy, chunks, use_nvls, comm_ctas = plan_gemm_all_reduce(comm.world, M, N, _emulated(comm), strategy, chunks,
-                                                                     use_nvls, comm_ctas, sol)
+        strategy, chunks, use_nvls, comm_ctas, planned_kernel = plan_gemm_all_reduce(
+            comm.world, M, N, _emulated(comm), strategy, chunks, use_nvls, comm_ctas, sol, kernel)
+        self.kernel = _kernel_code(planned_kernel)
         self.chunks = chunks
         self.strategy = strategy
         self.use_nvls = use_nvls

@@ -11,8 +11,13 @@ def test_measured_choices_on_nvswitch():
     # ... above 64 MiB the fused kernel with peer pushes wins (use_nvls 0)
     assert plan(8, 8192, 8192, False)[:3] == ("fused", 1, 0)
     assert plan(4, 2048, 8192, False)[0] == "unfused" and plan(4, 8192, 8192, False)[0] == "fused"
-    # two ranks: always the fused kernel, and the NVLS choice is left to the op's default
-    assert plan(2, 512, 8192, False)[0] == "fused" and plan(2, 8192, 8192, False)[2] is None
+    # two ranks: always a fused kernel; one or two waves of tiles on the one-SM kernel with pushed tiles, 64 MiB and
+    # more on the two-SM kernel that reduces in place through the switch with 24 communication CTAs
+    assert plan(2, 512, 8192, False) == ("fused", 1, None, 16, "one_sm")
+    assert plan(2, 2048, 8192, False)[4] == "one_sm"
+    assert plan(2, 8192, 8192, False) == ("fused", 1, 1, 24, "pair")
+    # what the caller fixed stays
+    assert plan(2, 8192, 8192, False, "auto", None, 0, 8, None, "one_sm") == ("fused", 1, 0, 8, "one_sm")
     # emulation runs one launch per op
     assert plan(8, 512, 8192, True)[0] == "fused"
 
@@ -31,12 +36,13 @@ def test_chunked_strategy_resolution():
 
 def test_tuned_solution_overrides_the_rule():
     sol = {"strategy": "fused", "comm_ctas": 24, "use_nvls": 2}
-    assert plan(8, 512, 8192, False, "auto", None, None, None, sol) == ("fused", 1, 2, 24)
+    assert plan(8, 512, 8192, False, "auto", None, None, None, sol) == ("fused", 1, 2, 24, None)
     # explicit arguments win over the solution's
-    assert plan(8, 512, 8192, False, "auto", None, 0, 8, sol) == ("fused", 1, 0, 8)
+    assert plan(8, 512, 8192, False, "auto", None, 0, 8, sol) == ("fused", 1, 0, 8, None)
     assert plan(8, 8192, 8192, False, "auto", None, None, None, {"strategy": "chunked", "chunks": 8})[:2] == ("chunked", 8)
     # a solution is ignored in emulation and when the caller named a strategy
     assert plan(8, 512, 8192, True, "auto", None, None, None, sol)[0] == "fused"
     assert plan(8, 512, 8192, False, "unfused", None, None, None, sol)[0] == "unfused"
+    assert plan(8, 512, 8192, False, "auto", None, None, None, dict(sol, kernel="pair"))[4] == "pair"
     with pytest.raises(ValueError):
         plan(8, 512, 8192, False, "auto", None, None, None, {"strategy": "bogus"})
