@@ -8,6 +8,10 @@ role; every ``yield`` is a point where any other role may run) and executed unde
 * ticket + arrival counters   fused GEMM -> all-reduce: producers bump the owner's per-tile counter, reducer CTAs draw
                               tickets, wait for ``world`` arrivals, re-arm the counter; the ticket counter is re-armed
                               by whoever draws the last ticket (csrc/gemm/gemm_kernel.cuh: draw_ticket, ar_reducer_role)
+* two-SM in-place reduction   warps draw sub-unit items (next ticket drawn ahead), the unit's last finished item re-arms
+                              its arrival and done counters, GEMM CTAs join the reducers, ranks run ahead into the next
+                              launch; only the closing rank barrier keeps a new arrival from meeting an un-re-armed unit
+                              (csrc/gemm/gemm_pair.cu: signal warp, draw_ticket_warp, pair_ar_reducer)
 * last-arriver split-K sum    per-quadrant arrival counter re-armed by the CTA that completes it
                               (csrc/gemm/gemm_kernel.cuh, csrc/gemm/gemm_skinny.cu)
 
@@ -158,6 +162,125 @@ def test_fused_all_reduce_counters_and_tickets(world, tiles, gemm_ctas, comm_cta
 
 
 # ---------------------------------------------------------------------------------------------------------------------
+# two-SM fused GEMM -> all-reduce: in-place reduction by WARPS that draw sub-unit items, a per-unit "done" counter whose
+# last increment re-arms the unit, GEMM CTAs that join the reducers, and ranks that run ahead into the next launch
+# (csrc/gemm/gemm_pair.cu: signal warp, draw_ticket_warp, pair_ar_reducer)
+# ---------------------------------------------------------------------------------------------------------------------
+class PairArState:
+    def __init__(self, world, units, subs, launches):
+        self.world, self.units, self.subs = world, units, subs
+        self.owned_max = (units + world - 1) // world
+        self.cnt = [[0] * self.owned_max for _ in range(world)]     # arrivals per owned unit (owner's pad)
+        self.done = [[0] * self.owned_max for _ in range(world)]    # finished items per owned unit
+        self.ticket = [0] * world
+        self.arrived = [[set() for _ in range(self.owned_max)] for _ in range(world)]  # (launch, source rank)
+        self.reduced = {}                                           # (launch, rank, k, sub) -> times
+        self.gemm_done = {}                                         # (launch, rank, cta) -> True once its tiles are out
+        self.warps_done = {}                                        # (launch, rank, cta) -> warps that left the item loop
+        self.ctas_done = [[0] * launches for _ in range(world)]     # CTAs of (rank, launch) that have ended
+
+    def owned(self, rank):
+        return (self.units - rank + self.world - 1) // self.world
+
+
+def pair_signal_part(st, rank, cta, my_units, launch, ctas_per_rank):
+    """The GEMM part of a CTA: starts when the rank's previous launch has ended (stream order), stores each of its
+    half-tiles into the rank's own copy of C and adds one arrival on the owner's counter."""
+    while launch > 0 and st.ctas_done[rank][launch - 1] < ctas_per_rank:
+        yield "blocked"
+    for u in my_units:
+        owner, k = u % st.world, u // st.world
+        yield
+        # an arrival of this launch must find the unit re-armed: nothing of an earlier launch may be left in it
+        assert all(l == launch for l, _ in st.arrived[owner][k]), (launch, rank, u, st.arrived[owner][k])
+        assert st.cnt[owner][k] < st.world
+        st.arrived[owner][k].add((launch, rank))
+        st.cnt[owner][k] += 1                     # fence.acq_rel.sys + red.release.sys.add
+        yield
+    st.gemm_done[(launch, rank, cta)] = True
+    yield
+
+
+def pair_reducer_warp(st, rank, cta, launch, drawers, ctas_per_rank, is_comm_cta):
+    """One warp of a CTA in the reducer role (communication CTAs from the start, GEMM CTAs after their tiles)."""
+    while launch > 0 and st.ctas_done[rank][launch - 1] < ctas_per_rank:
+        yield "blocked"
+    while not is_comm_cta and not st.gemm_done.get((launch, rank, cta)):
+        yield "blocked"
+    items = st.owned(rank) * st.subs
+
+    def draw():
+        t = st.ticket[rank]                       # lane 0: atomicAdd(ticket, 1)
+        st.ticket[rank] += 1
+        if t == items + drawers - 1:
+            st.ticket[rank] = 0                   # the last ticket that can ever be drawn re-arms the ticket counter
+        return t
+
+    nxt = draw()
+    yield
+    while True:
+        i = nxt
+        if i >= items:
+            break
+        nxt = draw()                              # drawn before the item is processed
+        yield
+        k, sub = divmod(i, st.subs)
+        while st.cnt[rank][k] < st.world:         # lane 0: wait_word_ge(cnt, world)
+            yield "blocked"
+        yield
+        assert st.arrived[rank][k] == {(launch, r) for r in range(st.world)}, (launch, rank, k, st.arrived[rank][k])
+        key = (launch, rank, k, sub)
+        st.reduced[key] = st.reduced.get(key, 0) + 1   # multimem.ld_reduce + multimem.st of the item's rows
+        yield
+        d = st.done[rank][k]                      # lane 0: atomicAdd(done, 1)
+        st.done[rank][k] += 1
+        if d == st.subs - 1:                      # the unit's last item: re-arm both counters
+            st.arrived[rank][k] = set()
+            st.cnt[rank][k] = 0
+            st.done[rank][k] = 0
+        yield
+    st.warps_done[(launch, rank, cta)] = st.warps_done.get((launch, rank, cta), 0) + 1
+    yield
+
+
+def pair_cta_tail(st, rank, cta, launch, warps, pads):
+    """__syncthreads_and over the CTA's warps, then the rank barrier between CTA `cta` of every rank, then the end."""
+    while st.warps_done.get((launch, rank, cta), 0) < warps:
+        yield "blocked"
+    yield from barrier_block(pads, st.world, rank, cta, 1, [])
+    st.ctas_done[rank][launch] += 1
+    yield
+
+
+@pytest.mark.parametrize("world,units,gemm_ctas,comm_ctas,subs,warps",
+                         [(2, 6, 2, 1, 2, 2), (2, 9, 3, 1, 3, 2), (4, 10, 2, 1, 2, 2), (3, 7, 2, 2, 2, 3)])
+def test_two_sm_in_place_reduction_with_joining_warps_and_ranks_running_ahead(world, units, gemm_ctas, comm_ctas, subs, warps):
+    ctas, launches = gemm_ctas + comm_ctas, 3
+    for seed in range(120):
+        rng = random.Random(seed * 611953 + units)
+        st, pads = PairArState(world, units, subs, launches), Pads(world, ctas)
+        roles = []
+        for launch in range(launches):  # all launches are live at once: only stream order per rank holds them apart
+            for rank in range(world):
+                for c in range(ctas):
+                    is_comm = c >= gemm_ctas
+                    if not is_comm:
+                        roles.append(pair_signal_part(st, rank, c, list(range(c, units, gemm_ctas)), launch, ctas))
+                    for _ in range(warps):
+                        roles.append(pair_reducer_warp(st, rank, c, launch, ctas * warps, ctas, is_comm))
+                    roles.append(pair_cta_tail(st, rank, c, launch, warps, pads))
+        run_schedule(roles, rng, max_steps=2000000)
+        for launch in range(launches):
+            for rank in range(world):
+                for k in range(st.owned(rank)):
+                    for sub in range(subs):
+                        assert st.reduced.get((launch, rank, k, sub)) == 1, (seed, launch, rank, k, sub)
+        assert len(st.reduced) == launches * units * subs
+        for rank in range(world):
+            assert st.ticket[rank] == 0 and not any(st.cnt[rank]) and not any(st.done[rank]), (seed, rank)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
 # split-K: last arriver sums and re-arms
 # ---------------------------------------------------------------------------------------------------------------------
 def splitk_cta(state, tile, split, splits, launch):
@@ -255,3 +378,20 @@ def test_the_simulator_catches_a_counter_that_is_not_re_armed():
         except AssertionError:
             tripped += 1
     assert tripped > 0
+
+
+def test_the_simulator_needs_the_closing_barrier_of_the_two_sm_reduction(monkeypatch):
+    """Without the rank barrier at the end of the launch a rank that runs ahead delivers an arrival of the next launch
+    into a unit its peer has not re-armed yet: the simulation must find that."""
+    import sys
+    me = sys.modules[__name__]
+
+    def tail_without_barrier(st, rank, cta, launch, warps, pads):
+        while st.warps_done.get((launch, rank, cta), 0) < warps:
+            yield "blocked"
+        st.ctas_done[rank][launch] += 1
+        yield
+
+    monkeypatch.setattr(me, "pair_cta_tail", tail_without_barrier)
+    with pytest.raises(AssertionError):
+        test_two_sm_in_place_reduction_with_joining_warps_and_ranks_running_ahead(2, 6, 2, 1, 2, 2)
