@@ -23,6 +23,7 @@ from typing import Optional
 import torch
 
 from .. import _lib
+from ..utils.logging import logger
 from ..utils.partition import partition
 from .gemm import _check_operands, fill_gemm_args, gemm
 
@@ -188,8 +189,17 @@ class GemmAllReduce:
             self.c_off = comm.alloc(M * N * 2)
             self._out = None if _emulated(comm) else comm.view(self.c_off, (M, N), dtype)
             if self.strategy == "fused":
-                self.partial_off = comm.alloc(int(lib.oob_gemm_partial_bytes(M, N)))
-                self.counter_base = comm.reserve_counters(lib.oob_gemm_counters_needed(_lib.GEMM_AR, M, N, comm.world))
+                try:
+                    self.partial_off = comm.alloc(int(lib.oob_gemm_partial_bytes(M, N)))
+                    try:
+                        self.counter_base = comm.reserve_counters(lib.oob_gemm_counters_needed(_lib.GEMM_AR, M, N, comm.world))
+                    except Exception:
+                        comm.free(self.partial_off)
+                        raise
+                except Exception:  # nothing of a half-built op stays allocated (every rank fails alike)
+                    comm.free(self.c_off)
+                    self.multi = False
+                    raise
             if self.strategy == "chunked":
                 self._side = torch.cuda.Stream()
                 self._slab_done = [torch.cuda.Event() for _ in range(self.chunks)]
@@ -256,7 +266,8 @@ class GemmAllReduce:
                 else:
                     scale = max(1.0, float(ref.float().abs().max()))
                     ok = bool((out.float() - ref.float()).abs().max() <= 2e-2 * scale)
-            except _lib.OobError:
+            except Exception as e:  # noqa: BLE001 - any failure of a candidate takes the candidate out, on every rank
+                logger.info("autotune: %s/%s/nvls=%s/ctas=%s failed on rank %d: %s", strat, kern, nv, c, comm.rank, e)
                 ok = False
             oks, timed_out = agree(1 if ok else 0)
             ns = INF
@@ -272,7 +283,8 @@ class GemmAllReduce:
                     torch.cuda.synchronize()
                     comm.check_status()
                     ns = int(e0.elapsed_time(e1) / iters * 1e6)
-                except _lib.OobError:
+                except Exception as e:  # noqa: BLE001
+                    logger.info("autotune: timing %s/%s/nvls=%s/ctas=%s failed on rank %d: %s", strat, kern, nv, c, comm.rank, e)
                     ns = INF
                 times, timed_out = agree(ns)
                 ns = INF if timed_out else max(times)
