@@ -13,7 +13,9 @@ Candidates per shape (each verified against an fp32 reference before it is timed
 * the library's own rule (all arguments 0) and cuBLAS (``torch.matmul``) as the yardsticks.
 
 Timing: CUDA-graph replay, CUDA events, ``--rotate`` operand sets cycled inside the graph so that shapes smaller than
-L2 are not measured L2-warm (set ``--rotate 1`` to measure the warm case on purpose).
+L2 are not measured L2-warm (set ``--rotate 1`` to measure the warm case on purpose); the candidates are measured round
+robin in ``--rounds`` passes and the median per candidate is kept, so that clock drift over the run is not credited to a
+kernel.
 
 Capability parity: tool/gen_config_sm90.py:175-357 and the profiling pass of src/gemm/gemm_with_signal_sm90.h:238-292
 in the reference pick one of its generated tile / cluster / stream-K instances per shape; here the instances are the
@@ -55,7 +57,8 @@ def main() -> int:
     p = argparse.ArgumentParser()
     p.add_argument("--shapes", default="512x8192x8192,2048x8192x8192,8192x8192x8192", help="MxNxK, comma separated")
     p.add_argument("--dtype", default="bf16", choices=["bf16", "fp16"])
-    p.add_argument("--iters", type=int, default=20)
+    p.add_argument("--iters", type=int, default=10)
+    p.add_argument("--rounds", type=int, default=3, help="round-robin passes over the candidates (median is kept)")
     p.add_argument("--rotate", type=int, default=0, help="operand sets cycled per graph (0 = enough to exceed L2)")
     p.add_argument("--out", default="gemm_solutions.json")
     p.add_argument("--log", default="", help="append one JSON line per measured candidate")
@@ -82,6 +85,7 @@ def main() -> int:
             for i in range(rotate):
                 fn(a[i], b[i])
 
+        runnable = []
         for cand in candidates(M, N, K):
             kw = cand["kw"]
             try:
@@ -94,10 +98,25 @@ def main() -> int:
             if not err <= 1e-2 * scale:
                 rows.append(dict(name=cand["name"], us=None, error=f"max abs err {err:.3g}"))
                 continue
-            t = graph_timed(lambda: run_all(lambda x, w: gemm(x, w, out=out, **kw)), args.iters, 3, per_graph=2, min_ms=20.0)
-            rows.append(dict(name=cand["name"], kw=kw, us=round(t["us"] / rotate, 2), p90=round(t["p90"] / rotate, 2)))
-        t = graph_timed(lambda: run_all(lambda x, w: torch.matmul(x, w.t(), out=out)), args.iters, 3, per_graph=2, min_ms=20.0)
-        cublas_us = round(t["us"] / rotate, 2)
+            runnable.append(cand)
+        # Round robin over the candidates, several rounds, median per candidate: the GPU's clock state drifts over a run
+        # (power cap, temperature), and measuring one candidate after the other would credit that drift to the kernels.
+        samples = {c["name"]: [] for c in runnable}
+        samples["cublas"] = []
+        for _ in range(args.rounds):
+            for cand in runnable:
+                kw = cand["kw"]
+                t = graph_timed(lambda: run_all(lambda x, w: gemm(x, w, out=out, **kw)), args.iters, 2, per_graph=2,
+                                min_ms=8.0)
+                samples[cand["name"]].append(t["us"] / rotate)
+            t = graph_timed(lambda: run_all(lambda x, w: torch.matmul(x, w.t(), out=out)), args.iters, 2, per_graph=2,
+                            min_ms=8.0)
+            samples["cublas"].append(t["us"] / rotate)
+        med = {k: sorted(v)[len(v) // 2] for k, v in samples.items()}
+        for cand in runnable:
+            rows.append(dict(name=cand["name"], kw=cand["kw"], us=round(med[cand["name"]], 2),
+                             spread=round(max(samples[cand["name"]]) - min(samples[cand["name"]]), 2)))
+        cublas_us = round(med["cublas"], 2)
         ok = [r for r in rows if r.get("us") and r["name"] != "rule"]
         best = min(ok, key=lambda r: r["us"])
         rule = next((r for r in rows if r["name"] == "rule"), None)
