@@ -123,13 +123,13 @@ int oob_all_gather(oob_comm* c, int dtype, int algo, int out_reg, uint64_t out_o
                    void* dst_local, uint64_t count, int max_ctas, void* stream);
 
 /* Small-message all-reduce with ONE rank barrier and no separate copy: `in_local` (any device memory, `count`
- * elements) is pushed into piece `rank` of the registered staging area (stage_reg, stage_off; world * piece_bytes
- * bytes, piece_bytes a multiple of 16 and >= the message) on every rank, the ranks meet once, and every rank sums the
- * pieces from its own memory in rank order (fp32) into `out_local` (any device memory; may alias in_local).
- * use_nvls != 0 pushes with multimem.st when the heap has a multicast alias.  The caller must not push into the same
- * staging area again before every rank has finished reading it: take staging areas from a ring of two or more, round
- * robin (call k + 2 can only start once every rank has finished call k).  Moves (world - 1) x the message per rank:
- * for messages up to a few hundred KiB. */
+ * elements) is pushed into piece `rank` of the registered staging area (stage_reg, stage_off) on every rank, the ranks
+ * meet once, and every rank sums the pieces from its own memory in rank order (fp32) into `out_local` (any device
+ * memory; may alias in_local).  The staging area holds TWO sets of world * piece_bytes bytes (piece_bytes a multiple
+ * of 16 and >= the message); consecutive calls alternate between the sets, decided by a call counter on the device,
+ * so calls may follow one another at once, also as replays of captured graphs.  Only this entry point may write to
+ * the staging area, and every rank must make the same sequence of calls.  use_nvls != 0 pushes with multimem.st when
+ * the heap has a multicast alias.  Moves (world - 1) x the message per rank: for messages up to a few hundred KiB. */
 int oob_allreduce_push(oob_comm* c, int dtype, int op, int stage_reg, uint64_t stage_off, uint64_t piece_bytes,
                        const void* in_local, void* out_local, uint64_t count, int use_nvls, int max_ctas, void* stream);
 

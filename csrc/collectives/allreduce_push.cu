@@ -8,9 +8,12 @@
 // the critical path: what remains is one NVLink traversal for the data with the flag right behind it.  It moves
 // (world - 1) x the message per rank, so it is for messages up to a few hundred KiB (decode-step all-reduces).
 //
-// Contract (what lets the closing barrier go): the staging area must not be pushed into again before every rank has
-// finished reading it.  A ring of two or more staging areas used round robin guarantees that: a rank that starts
-// call k + 2 has passed the barrier of call k + 1, which every rank enters only after finishing call k.
+// What lets the closing barrier go: the staging area holds TWO sets of pieces and consecutive calls alternate between
+// them.  Which set a call uses is decided on the device (a call counter in the rank's signal pad, bumped by the block
+// that finishes last), so the alternation also holds when a captured CUDA graph is replayed or when graphs captured
+// at different times follow one another.  A rank that starts call k + 2 (same set as call k) has passed the barrier of
+// call k + 1, which every rank enters only after it has finished reading the pieces of call k.  The staging area is
+// used by this kernel only; results go wherever the caller wants them (local stores).
 //
 // Capability parity: the reference's fast one-shot all-reduce (src/comm/fast_multi_gpu_allreduce_sm90.cu:155-257)
 // is also a push (cp.reduce.async.bulk of the own chunk into every peer, element-wise atomics in the storage dtype,
@@ -25,6 +28,8 @@ namespace oob {
 namespace {
 
 constexpr int kPushThreads = 512;
+constexpr int kPushCallSlot = 0;  // call-epoch words of the pad: calls made so far, and blocks of the running call done
+constexpr int kPushDoneSlot = 1;
 
 // Block b of every rank owns the same stripe of the message (whole 16-byte packs; the last block also takes the
 // elements that do not fill a pack), so one barrier between the blocks of equal index is all the ordering needed,
@@ -46,7 +51,13 @@ __global__ void __launch_bounds__(kPushThreads)
   const size_t p0 = min(packs, per * blockIdx.x), p1 = min(packs, p0 + per);
   const bool has_tail = blockIdx.x == gridDim.x - 1;
   const size_t tail0 = packs * E;
-  const size_t my_piece = size_t(rank) * piece_bytes;
+  // Set of pieces of this call: every block reads the counter before any block of this launch can bump it (the bump
+  // needs all blocks to have finished), and all ranks have made the same number of calls.
+  __shared__ uint32_t s_set;
+  if (threadIdx.x == 0) s_set = ptx::ld_relaxed_sys(call_epoch_ptr(ctx, kPushCallSlot)) & 1u;
+  __syncthreads();
+  const size_t set_off = size_t(s_set) * size_t(world) * piece_bytes;
+  const size_t my_piece = set_off + size_t(rank) * piece_bytes;
 
   // ---- push this block's stripe of the input into piece `rank` of every rank's staging area ----------------------
   for (size_t p = p0 + threadIdx.x; p < p1; p += kPushThreads) {
@@ -80,7 +91,9 @@ __global__ void __launch_bounds__(kPushThreads)
   // ---- sum the pieces from LOCAL memory, rank order, fp32 ---------------------------------------------------------
   // Through the switch this rank's own piece comes back over NVLink as well; nothing orders that copy before the
   // loads below (the rank's own flag is a plain local store), so the own contribution is taken from the input.
-  const char* mine = static_cast<const char*>(staging.p[rank]);
+  // The pieces were written by other GPUs during this kernel: they are read with coherent loads (never through the
+  // read-only path).
+  const char* mine = static_cast<const char*>(staging.p[rank]) + set_off;
   for (size_t p = p0 + threadIdx.x; p < p1; p += kPushThreads) {
     float acc[E];
     uint4 own;
@@ -96,7 +109,7 @@ __global__ void __launch_bounds__(kPushThreads)
     if constexpr (NR > 0) {
       uint4 v[NR];
 #pragma unroll
-      for (int r = 0; r < NR; ++r) v[r] = ptx::ld_nc_v4(mine + size_t(r) * piece_bytes + p * 16);
+      for (int r = 0; r < NR; ++r) v[r] = ptx::ld_relaxed_sys_v4(mine + size_t(r) * piece_bytes + p * 16);
       if (MC) {
 #pragma unroll
         for (int r = 0; r < NR; ++r)
@@ -111,10 +124,10 @@ __global__ void __launch_bounds__(kPushThreads)
         for (int i = 0; i < int(E); ++i) acc[i] = combine<OP>(acc[i], f[i]);
       }
     } else {
-      PackTraits<T>::unpack((MC && rank == 0) ? own : ptx::ld_nc_v4(mine + p * 16), acc);
+      PackTraits<T>::unpack((MC && rank == 0) ? own : ptx::ld_relaxed_sys_v4(mine + p * 16), acc);
       for (int r = 1; r < world; ++r) {
         float f[E];
-        PackTraits<T>::unpack((MC && r == rank) ? own : ptx::ld_nc_v4(mine + size_t(r) * piece_bytes + p * 16), f);
+        PackTraits<T>::unpack((MC && r == rank) ? own : ptx::ld_relaxed_sys_v4(mine + size_t(r) * piece_bytes + p * 16), f);
 #pragma unroll
         for (int i = 0; i < int(E); ++i) acc[i] = combine<OP>(acc[i], f[i]);
       }
@@ -134,6 +147,16 @@ __global__ void __launch_bounds__(kPushThreads)
       for (int r = 1; r < world; ++r)
         acc = combine<OP>(acc, PackTraits<T>::to_float(ld_elem_sys<T>(mine + size_t(r) * piece_bytes + e * sizeof(T))));
       st_elem<T>(dst + e * sizeof(T), PackTraits<T>::from_float(acc));
+    }
+  }
+  // The block that finishes last moves the rank on to the other set of pieces.
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* ticket = call_epoch_ptr(ctx, kPushDoneSlot);
+    if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+      *ticket = 0;
+      atomicAdd(call_epoch_ptr(ctx, kPushCallSlot), 1u);
+      __threadfence();
     }
   }
 }
@@ -189,7 +212,7 @@ cudaError_t push_dispatch_op(int op, const CommCtx& ctx, bool mc, const PeerPtrs
 }  // namespace
 
 // `piece_bytes` (a multiple of 16, at least the message size) is the distance between the ranks' pieces in the staging
-// area, which holds world * piece_bytes.
+// area, which holds two sets of world * piece_bytes.
 cudaError_t launch_allreduce_push(const CommCtx& ctx, int dtype, int op, bool use_mc, const PeerPtrs& staging,
                                   size_t piece_bytes, const void* in_local, size_t in_emu_stride, void* out_local,
                                   size_t out_emu_stride, size_t count, int max_ctas, cudaStream_t stream) {

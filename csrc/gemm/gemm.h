@@ -24,7 +24,8 @@ constexpr int kTileBytes = kTileM * kTileN * 2;  // one 16-bit output tile
 enum TraceSlot : int {
   kTraceStart = 0,       // kernel entry
   kTraceGemmDone = 1,    // GEMM CTAs: all tiles computed and stored / pushed
-  kTraceFirstReady = 2,  // communication role: first work item became ready
+  kTraceFirstReady = 2,  // communication role: first work item became ready; GEMM CTAs of the two-SM fused kernel:
+                         // the last tile has left the epilogue (its publication may still be under way)
   kTraceCommDone = 3,    // communication role: last work item finished (before the final rank barrier)
   kTraceEnd = 4,         // after the final rank barrier
   kTraceItems = 5,       // communication work items this CTA processed

@@ -16,8 +16,9 @@
 //             two-CTA mask releases the stage in both CTAs / publishes the accumulator to both epilogues
 //   warps 2-5 epilogue (both CTAs): each CTA drains its own 128 accumulator rows from its own TMEM (two
 //             accumulator stages), converts, stages through shared memory and writes whole 256-byte row segments
-//   warp 6    (fused all-reduce / reduce-scatter) signal warp: when the four epilogue warps have stored a tile it
-//             orders those stores system-wide and bumps an arrival counter on the rank that reduces the tile
+//   warps 6-11 (fused all-reduce / reduce-scatter) signal warps, sharing the CTA's tiles round robin: when the four
+//             epilogue warps have stored a tile, one of them orders those stores system-wide and bumps an arrival
+//             counter on the rank that reduces the tile
 //
 // Work distribution.  Tiles are dealt to the pairs round robin, whole waves first.  When the tile count is not a
 // multiple of the pair count, the last wave would leave pairs idle; the host may then ask for a STREAM-K TAIL: the
@@ -281,7 +282,8 @@ __device__ __forceinline__ void ar_reduce_sub(const GemmArgs& a, int world, int 
 // finishes the last one re-arms both); counter_base + 2 * owned_max is the ticket counter.  Work item i = (unit i / 8,
 // rows 16 * (i % 8) ...).  `drawers` = warps of the launch that draw tickets.
 template <typename T, int THREADS>
-__device__ void pair_ar_reducer(const CommCtx& ctx, const GemmArgs& a, const PairSched& sc, int drawers) {
+__device__ void pair_ar_reducer(const CommCtx& ctx, const GemmArgs& a, const PairSched& sc, int drawers,
+                                bool stamp_first = true) {
   const int world = ctx.world, rank = ctx.rank;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int W = THREADS / 32;
@@ -312,7 +314,7 @@ __device__ void pair_ar_reducer(const CommCtx& ctx, const GemmArgs& a, const Pai
       if (a.trace && warp == 0) {
         const unsigned long long now = ptx::globaltimer_ns();
         t_wait += now - tw;
-        if (n_items == 0 && threadIdx.x == 0) trace_put(a, kTraceFirstReady, now);
+        if (n_items == 0 && threadIdx.x == 0 && stamp_first) trace_put(a, kTraceFirstReady, now);
       }
     }
     good = __shfl_sync(0xffffffffu, good, 0);
@@ -429,7 +431,8 @@ __device__ __forceinline__ void rs_row(const GemmArgs& a, int world, size_t grow
 #pragma unroll 2
   for (int p = lane; p < packs_per_row; p += 32) {
     float f[8], wf[8], o[8];
-    PT::unpack(ptx::ld_nc_v4(stash + l_off + size_t(p) * 16), f);
+    // Written a moment ago by this same lane: a plain (coherent) load, not the read-only path.
+    PT::unpack(*reinterpret_cast<const uint4*>(stash + l_off + size_t(p) * 16), f);
     PT::unpack(*reinterpret_cast<const uint4*>(wgt + size_t(p) * 16), wf);
 #pragma unroll
     for (int i = 0; i < 8; ++i) o[i] = f[i] * scale * wf[i];
@@ -438,7 +441,8 @@ __device__ __forceinline__ void rs_row(const GemmArgs& a, int world, size_t grow
 }
 
 template <typename T, int THREADS>
-__device__ void pair_rs_reducer(const CommCtx& ctx, const GemmArgs& a, const PairSched& sc, int drawers) {
+__device__ void pair_rs_reducer(const CommCtx& ctx, const GemmArgs& a, const PairSched& sc, int drawers,
+                                bool stamp_first = true) {
   const int world = ctx.world, rank = ctx.rank;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int W = THREADS / 32;
@@ -471,7 +475,7 @@ __device__ void pair_rs_reducer(const CommCtx& ctx, const GemmArgs& a, const Pai
         if (a.trace && warp == 0) {
           const unsigned long long now = ptx::globaltimer_ns();
           t_wait += now - tw;
-          if (n_items == 0 && threadIdx.x == 0) trace_put(a, kTraceFirstReady, now);
+          if (n_items == 0 && threadIdx.x == 0 && stamp_first) trace_put(a, kTraceFirstReady, now);
         }
       }
       good = __shfl_sync(0xffffffffu, good, 0);
@@ -583,6 +587,12 @@ __device__ void pair_ag_pusher(const CommCtx& ctx, const GemmArgs& a, int j, int
     ptx::fence_acq_rel_sys();
     ag_rearm_flags(ctx, a, gemm_ctas + R);
   }
+}
+
+// True when all four epilogue warps have stored item `idx` of this CTA (see epi_done).  Safe for any idx: the four
+// warps are never more than the two accumulator stages apart, and the counts only grow.
+__device__ __forceinline__ bool ctl_epi_done_ge(const SmemCtlP* ctl, uint32_t idx) {
+  return *reinterpret_cast<const volatile uint32_t*>(&ctl->epi_done[idx & 3]) >= 4u * (idx / 4u + 1u);
 }
 
 // ---- the kernel ------------------------------------------------------------------------------------------------
@@ -943,21 +953,54 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == kGemmPlain ?
         acc_phase ^= 1;
       }
     }
-  } else if (warp == 6) {
-    // --------------------------- signal warp (fused AR / RS) -----------------------------
-    // One thread follows the CTA's items in order.  When all four epilogue warps have stored their rows of a tile it
-    // orders those stores system-wide (the fence is cumulative over what it observed through the CTA-scope counter)
-    // and publishes one arrival on the rank that reduces the tile.
+    // Trace: when this CTA's last tile had left the epilogue (the signal warps may still be publishing).
     if constexpr (kSignals) {
+      if (a.trace != nullptr && q == 0 && lane == 0)  // not thread 0 of the CTA: written directly
+        a.trace[(size_t(blockIdx.y) * gridDim.x + blockIdx.x) * kTraceWords + kTraceFirstReady] = ptx::globaltimer_ns();
+    }
+  } else if (warp >= 6) {
+    // --------------------------- signal warps (fused AR / RS) ----------------------------
+    // Warps 6 .. 11 share the CTA's items round robin (item idx belongs to warp 6 + idx % kSignalWarps); one thread of
+    // each follows its items in order.  When all four epilogue warps have stored their rows of a tile it orders those
+    // stores system-wide (the fence is cumulative over what it observed through the CTA-scope counter) and publishes
+    // one arrival on the rank that reduces the tile.  Several warps, because a publication is a chain of a
+    // system-scope fence and a remote reduction that takes far longer than a short tile (K / world of a few hundred)
+    // takes to compute: one warp alone would publish the tiles later than they are produced.
+    if constexpr (kSignals) {
+      constexpr int kSignalWarps = THREADS / 32 - 6;
+      const int sw = warp - 6;
       if (lane == 0) {
+        // Tiles whose epilogue is complete are published in batches: one fence covers every tile of this warp that
+        // is ready at that moment, so the publication rate does not depend on how long a fence takes under load.
+        constexpr int kMaxPend = 4;
+        uint32_t* pend[kMaxPend];
+        unsigned long long pend_rec[kMaxPend];
+        int npend = 0;
+        auto flush = [&]() {
+          if (npend == 0) return;
+          // The fence is the release (and the acquire of what the epilogue warps published through epi_done); the
+          // reductions after it need no ordering of their own.
+          ptx::fence_acq_rel_sys();
+          for (int j = 0; j < npend; ++j) ptx::red_relaxed_sys_add(pend[j], 1u);
+          if (a.order != nullptr) {
+            const unsigned long long now = ptx::globaltimer_ns();
+            for (int j = 0; j < npend; ++j) {
+              unsigned long long* rec = a.order + 2 * (pend_rec[j] >> 32);
+              rec[0] = now;
+              rec[1] = (static_cast<unsigned long long>(pair) << 32) | (pend_rec[j] & 0xffffffffull);
+            }
+          }
+          npend = 0;
+        };
         uint32_t idx = 0;
         ItemIter iter(sc, pair);
         Item it;
+        bool ok = true;
         for (; iter.next(sc, pair, it); ++idx) {
+          if (int(idx % uint32_t(kSignalWarps)) != sw) continue;
           const uint32_t expected = 4u * (idx / 4u + 1u);
           volatile uint32_t* cnt = &ctl->epi_done[idx & 3];
           uint32_t polls = 0;
-          bool ok = true;
           while (*cnt < expected) {
             if (*abort || ++polls > (1u << 26)) {
               ok = false;
@@ -971,26 +1014,30 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == kGemmPlain ?
           }
           int m_blk, n_blk;
           sc.coord(it.seq, m_blk, n_blk);
-          int owner, cidx;
+          int owner = -1, cidx = 0;
           if constexpr (MODE == kGemmAr) {
             const int u = 2 * it.seq + int(cta);
             owner = u % ctx.world;
             cidx = a.counter_base + u / ctx.world;
           } else {
             const int m0 = m_blk * kPairTileM + int(cta) * kTileM;
-            if (m0 >= a.M) continue;  // the pair's second half lies past the last row: nobody waits for it
-            const int rows_per_rank = a.M / ctx.world;
-            owner = m0 / rows_per_rank;
-            cidx = a.counter_base + (m0 - owner * rows_per_rank) / kTileM;
+            if (m0 < a.M) {  // a second half past the last row is waited for by nobody
+              const int rows_per_rank = a.M / ctx.world;
+              owner = m0 / rows_per_rank;
+              cidx = a.counter_base + (m0 - owner * rows_per_rank) / kTileM;
+            }
           }
-          ptx::fence_acq_rel_sys();
-          ptx::red_release_sys_add(counter_ptr(ctx, owner, cidx), 1u);
-          if (a.order != nullptr) {
-            unsigned long long* rec = a.order + 2 * (2 * size_t(it.seq) + cta);
-            rec[0] = ptx::globaltimer_ns();
-            rec[1] = (static_cast<unsigned long long>(pair) << 32) | idx;
+          if (owner >= 0) {
+            pend[npend] = counter_ptr(ctx, owner, cidx);
+            pend_rec[npend] = (static_cast<unsigned long long>(2 * size_t(it.seq) + cta) << 32) | idx;
+            ++npend;
           }
+          // This warp's next tile: if it is complete already, it shares the fence.
+          const uint32_t nxt = idx + uint32_t(kSignalWarps);
+          const bool next_ready = ctl_epi_done_ge(ctl, nxt);
+          if (npend == kMaxPend || !next_ready) flush();
         }
+        if (ok) flush();
       }
     }
   }
@@ -1020,8 +1067,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == kGemmPlain ?
     if (!aborted && !a.no_join) {
       __syncthreads();
       const int drawers = int(gridDim.x) * (THREADS / 32);
-      if constexpr (MODE == kGemmAr) pair_ar_reducer<T, THREADS>(ctx, a, sc, drawers);
-      if constexpr (MODE == kGemmRsNorm) pair_rs_reducer<T, THREADS>(ctx, a, sc, drawers);
+      if constexpr (MODE == kGemmAr) pair_ar_reducer<T, THREADS>(ctx, a, sc, drawers, false);
+      if constexpr (MODE == kGemmRsNorm) pair_rs_reducer<T, THREADS>(ctx, a, sc, drawers, false);
       return;
     }
   }

@@ -888,8 +888,8 @@ int oob_allreduce_push(oob_comm* c, int dtype, int op, int stage_reg, uint64_t s
   if ((piece_bytes & 15) || count * esize > piece_bytes)
     return set_error(OOB_ERR_INVALID, "piece_bytes must be a multiple of 16 and hold the message");
   PeerPtrs st;
-  if ((stage_off & 15) || !c->peer_ptrs(stage_reg, stage_off, piece_bytes * c->world, &st))
-    return set_error(OOB_ERR_INVALID, "bad staging area (16-byte aligned, world * piece_bytes inside the registration)");
+  if ((stage_off & 15) || !c->peer_ptrs(stage_reg, stage_off, 2 * piece_bytes * c->world, &st))
+    return set_error(OOB_ERR_INVALID, "bad staging area (16-byte aligned, 2 * world * piece_bytes inside the registration)");
   const bool mc = use_nvls != 0 && st.mc != nullptr;
   const uint64_t emu_stride = c->emulated ? count * esize : 0;
   cudaError_t e = launch_allreduce_push(c->make_ctx(), dtype, op, mc, st, piece_bytes, in_local, emu_stride, out_local,

@@ -86,6 +86,7 @@ class Communicator:
         self._ipc_cache = {}
         self._ar_pool: Optional[SlotPool] = None
         self._ag_pool: Optional[SlotPool] = None
+        self._push_arena = None  # (heap offset, piece capacity) of the push kernels' staging area
         self._counter_next = 0
         if devices is None:
             import torch.distributed as dist
@@ -550,8 +551,8 @@ class Communicator:
     def all_reduce_round_robin(self, x: torch.Tensor, op: str = "sum", **kw) -> torch.Tensor:
         """All-reduce of an ordinary tensor through the next slot of the ring; the result aliases the slot and stays
         valid until the ring wraps.  Small messages (``OOB_PUSH_MAX_BYTES``, 256 KiB by default) take the one-barrier
-        push kernel: no copy into the slot first, the ranks' inputs land in pieces of the slot and the sum is written
-        behind them.  Larger ones are copied into the slot and reduced in place."""
+        push kernel: no copy into the slot first, the ranks' inputs land in a staging area of their own and the sum is
+        written into the slot.  Larger ones are copied into the slot and reduced in place."""
         out = self.all_reduce_push(x, op) if not kw else None
         if out is not None:
             return out
@@ -559,19 +560,32 @@ class Communicator:
         slot.copy_(x)
         return self.all_reduce_preloaded_slot(slot, op, **kw)
 
+    def _push_staging(self, piece: int) -> Optional[int]:
+        """Heap offset of the staging area of the push kernels (two sets of ``world`` pieces; allocated at the first
+        use, on every rank alike, sized for ``config.push_max_bytes``).  None when ``piece`` does not fit."""
+        if self._push_arena is None:
+            cap = (max(self.config.push_max_bytes, 4096) + 255) // 256 * 256
+            self._push_arena = (self.alloc(2 * self.world * cap), cap)
+        off, cap = self._push_arena
+        return off if piece <= cap else None
+
     def all_reduce_push(self, x: torch.Tensor, op: str = "sum", *, max_ctas: int = 0,
                         use_nvls: Optional[bool] = None) -> Optional[torch.Tensor]:
-        """One-barrier all-reduce of a small tensor through the next ring slot (see ``oob_allreduce_push``): every rank
-        pushes ``x`` into its piece of the slot on all ranks, the ranks meet once, each sums the pieces locally.  The
-        slot holds ``world`` pieces followed by the result, which is returned (a view of the slot, valid until the ring
-        wraps).  None when the push path does not apply: no ring of at least two slots, a message above
-        ``config.push_max_bytes``, or one that does not fit the slot ``world + 1`` times."""
+        """One-barrier all-reduce of a small tensor (see ``oob_allreduce_push``): every rank pushes ``x`` into its
+        piece of a staging area on all ranks, the ranks meet once, each sums the pieces locally into the next ring
+        slot, which is returned (valid until the ring wraps).  The staging area belongs to the push kernels alone and
+        holds two sets of pieces that consecutive calls alternate between (decided on the device), so calls may follow
+        one another at once, also as replays of captured CUDA graphs.  None when the push path does not apply: no
+        ring, a message above ``config.push_max_bytes``, or one that does not fit a slot."""
         pool = self._ar_pool
-        if pool is None or len(pool.offsets) < 2 or not x.is_cuda or not x.is_contiguous() or x.dtype != pool.dtype:
+        if pool is None or not x.is_cuda or not x.is_contiguous() or x.dtype != pool.dtype:
             return None
         nbytes = x.numel() * x.element_size()
         piece = (nbytes + 255) // 256 * 256
-        if nbytes == 0 or nbytes > self.config.push_max_bytes or (self.world + 1) * piece > pool.capacity_bytes:
+        if nbytes == 0 or nbytes > self.config.push_max_bytes or piece > pool.capacity_bytes:
+            return None
+        stage = self._push_staging(piece)
+        if stage is None:
             return None
         off = pool.offsets[pool.next_index]
         key = ("push", off, tuple(x.shape), x.dtype)
@@ -579,10 +593,10 @@ class Communicator:
         if out is None:
             if len(self._view_cache) > 4096:
                 self._view_cache.clear()
-            out = self._view_cache[key] = self.view(off + self.world * piece, tuple(x.shape), x.dtype)
+            out = self._view_cache[key] = self.view(off, tuple(x.shape), x.dtype)
         pool.advance()
         nvls = self.nvls if use_nvls is None else (bool(use_nvls) and self.nvls)
-        _lib.check(_lib.lib().oob_allreduce_push(self._h, dtype_code(x.dtype), op_code(op), 0, off, piece,
+        _lib.check(_lib.lib().oob_allreduce_push(self._h, dtype_code(x.dtype), op_code(op), 0, stage, piece,
                                                  ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()), x.numel(),
                                                  1 if nvls else 0, max_ctas or self.config.max_ctas,
                                                  ctypes.c_void_p(_current_stream_ptr())))

@@ -123,7 +123,8 @@ class EmulatedGroup:
     def all_reduce_push(self, stage_off: int, piece_bytes: int, x: torch.Tensor, out: torch.Tensor, op: str = "sum", *,
                         max_ctas: int = 4) -> None:
         """One-barrier push all-reduce: ``x`` and ``out`` are ``[world, count]`` (row r = rank r's input / result),
-        the staging area is ``world * piece_bytes`` at ``stage_off`` of every rank's heap."""
+        the staging area is two sets of ``world * piece_bytes`` at ``stage_off`` of every rank's heap (consecutive calls
+        alternate between the sets, decided on the device)."""
         assert x.shape[0] == self.world and out.shape == x.shape and x.is_contiguous() and out.is_contiguous()
         _lib.check(_lib.lib().oob_allreduce_push(self._h, dtype_code(x.dtype), op_code(op), 0, stage_off, piece_bytes,
                                                  ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()),

@@ -123,15 +123,19 @@ def _auto_rule(world: int, out_bytes: int, emulated: bool):
     * two ranks: fused; outputs of 64 MiB and more on the two-SM kernel reducing in place through the switch with 24
       communication CTAs, smaller ones on the one-SM kernel that pushes partial tiles (it starts reducing earlier, which
       is what counts for one or two waves of tiles);
-    * four ranks and more: up to 64 MiB this library's GEMM followed by its in-switch all-reduce, above that the fused
-      one-SM kernel with peer pushes."""
+    * four ranks and more (measured at eight): up to 16 MiB the one-SM kernel with the in-switch pull (59 against
+      78 us unfused at M = 512); up to 64 MiB this library's GEMM followed by its in-switch all-reduce (131 us at
+      M = 2048; the fused variants are within 2 %); above that the two-SM kernel reducing in place through the switch
+      with 8 communication CTAs (374 against 393 us unfused at M = 8192)."""
     big = out_bytes > (64 << 20)
     if emulated:
         return "fused", None, None, None
     if world < 4:
         return ("fused", 1, 24, "pair") if big else ("fused", None, 16, "one_sm")
     if big:
-        return "fused", 0, None, "one_sm"
+        return "fused", 1, 8, "pair"
+    if out_bytes <= (16 << 20):
+        return "fused", 2, 16, "one_sm"
     return "unfused", None, None, None
 
 
@@ -218,7 +222,7 @@ class GemmAllReduce:
         nvls = bool(getattr(self.comm, "nvls", False))
         world = self.comm.world
         cands = [("unfused", None, None, None)]
-        for c in (8, 16, 24, 32):
+        for c in (4, 8, 16, 24, 32):
             if nvls:
                 cands.append(("fused", "pair", 1, c))
             if not nvls or world == 2:

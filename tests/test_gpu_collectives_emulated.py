@@ -186,15 +186,16 @@ def test_heap_allocator_reuses_freed_blocks():
 def test_all_reduce_push_one_barrier(group, n, dtype, op):
     """Every rank pushes its unregistered input into its piece of a staging area on all ranks, one barrier, local sum in
     rank order.  Odd counts make the ranks' rows start off a 16-byte boundary (element-wise local accesses) while the
-    staging pieces stay aligned.  Two staging areas are used in turn, as a ring would, for three calls in a row."""
+    staging pieces stay aligned.  The same staging area serves five calls in a row: it holds two sets of pieces and the
+    kernel alternates between them by a call counter kept on the device."""
     esize = torch.empty((), dtype=dtype).element_size()
     piece = (n * esize + 255) // 256 * 256
-    stages = [group.alloc(group.world * piece) for _ in range(2)]
-    for it in range(3):
+    stages = [group.alloc(2 * group.world * piece)]
+    for it in range(5):
         gen = torch.Generator(device="cuda").manual_seed(n * 10 + it)
         x = (torch.rand(group.world, n, device="cuda", generator=gen) * 2 - 1).to(dtype)
         out = torch.zeros_like(x)
-        group.all_reduce_push(stages[it % 2], piece, x, out, op, max_ctas=3)
+        group.all_reduce_push(stages[0], piece, x, out, op, max_ctas=3 if it % 2 else 2)
         group.check_status()
         want = _reduce(list(x), op)
         for r in range(group.world):

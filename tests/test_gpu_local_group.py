@@ -25,12 +25,14 @@ def test_collectives_from_one_process():
             for r in range(world):
                 xs[r].copy_(host[r])
             g.synchronize()
-            # reduce-scatter first (it does not modify its input), then all-reduce in place
+            # reduce-scatter of a registered tensor leaves the result in the rank's own partition of it
             rs = g.reduce_scatter(xs)
             g.check_status()
             per = n // world
             for r in range(world):
                 assert (rs[r].float().cpu() - total[r * per:(r + 1) * per]).abs().max().item() <= 0.05 * world, (n, r)
+                xs[r].copy_(host[r])
+            g.synchronize()
             ag = g.all_gather([x[:per] for x in xs])
             g.check_status()
             want = torch.cat([h[:per] for h in host])

@@ -85,7 +85,8 @@ def _rank_collectives(rank, world, key, flags_env):
         check(f"slot {it}", got, torch.full((64, 128), float(sum(r + it for r in range(world)))), 1e-2 * world)
     got = comm.all_reduce_round_robin(torch.full((10,), 2.0, dtype=torch.bfloat16, device="cuda"))
     check("rr", got, torch.full((10,), 2.0 * world), 1e-2)
-    # small tensors take the one-barrier push kernel (pieces + result inside the slot); the ring of three wraps twice,
+    # small tensors take the one-barrier push kernel (pieces in its own staging area, result in the slot); the ring of
+    # three wraps twice,
     # odd sizes exercise the element tail and a misaligned view the element-wise local path
     for it in range(7):
         for n in (1, 8, 4097, 32768):

@@ -5,11 +5,12 @@ from ooverlap_b200.ops.overlap import plan_gemm_all_reduce as plan
 
 
 def test_measured_choices_on_nvswitch():
-    # tp8, N = 8192: single-wave / few-wave shapes run the GEMM and the in-switch all-reduce back to back ...
-    assert plan(8, 512, 8192, False)[0] == "unfused"
+    # tp8, N = 8192: one partial wave of tiles on the one-SM kernel with the in-switch pull ...
+    assert plan(8, 512, 8192, False) == ("fused", 1, 2, 16, "one_sm")
+    # ... a few waves: the GEMM and the in-switch all-reduce back to back ...
     assert plan(8, 2048, 8192, False)[0] == "unfused"
-    # ... above 64 MiB the fused kernel with peer pushes wins (use_nvls 0)
-    assert plan(8, 8192, 8192, False)[:3] == ("fused", 1, 0)
+    # ... above 64 MiB the two-SM kernel that reduces in place through the switch, 8 communication CTAs
+    assert plan(8, 8192, 8192, False) == ("fused", 1, 1, 8, "pair")
     assert plan(4, 2048, 8192, False)[0] == "unfused" and plan(4, 8192, 8192, False)[0] == "fused"
     # two ranks: always a fused kernel; one or two waves of tiles on the one-SM kernel with pushed tiles, 64 MiB and
     # more on the two-SM kernel that reduces in place through the switch with 24 communication CTAs
