@@ -191,7 +191,8 @@ typedef struct {
   int epilogue; /* plain mode, split problems only (oob_gemm_plan_splits > 1): OOB_EPILOGUE_* applied by the kernel
                    that sums the K splits */
   const void* epilogue_args; /* host pointer: oob_gemm_epilogue_swiglu_t or oob_rope_args_t (oob_model.h) */
-  int gemv;     /* plain mode, M <= 4: 1 = CUDA-core streaming kernel, 0 = only with OOB_GEMM_GEMV=1, -1 = never */
+  int gemv;     /* plain mode, M <= 4: 1 = CUDA-core streaming kernel, 0 = by shape (M = 1; M = 2 with N x K <= 12 M),
+                   -1 = never */
   int stream_k; /* two-SM kernel, plain and AG modes: stream-K tail; 0 = when it pays for the shape, 1 = whenever the
                    tile count leaves a remainder, -1 = never */
   void* order;  /* two-SM kernel: optional device buffer, 2 x uint64 per 128-row half of every 256x256 tile (index

@@ -288,14 +288,19 @@ cudaError_t launch_gemm(const CommCtx& ctx, const GemmArgs& args, cudaStream_t s
   int dev = 0;
   cudaGetDevice(&dev);
   if (a.mode == kGemmPlain) {
-    // One to four rows: the CUDA-core streaming kernel.  Opt-in (argument, or OOB_GEMM_GEMV=1 for every call that
-    // leaves the choice open) until it has been measured against the split-K path.
-    static const bool gemv_env_on = [] {
+    // One to four rows: the CUDA-core streaming kernel.  By argument, or when the call leaves the choice open: for one
+    // row always, for two rows when the weight matrix is small (N x K up to 12 M elements), which is where it measured
+    // faster than the tensor-core paths on B200 (M = 1: 6.1 / 8.6 / 13.9 us against 10.6 / 14.3 / 17.2 us for
+    // 8192 x 1024, 1280 x 8192, 8192 x 3584; M = 2 on the two smaller ones: 8.0 / 11.7 against 10.4 / 14.3 us; from
+    // M = 4 on it loses everywhere).  OOB_GEMM_GEMV=0 switches the rule off, =1 widens it to every M <= 4.
+    static const int gemv_env = [] {
       const char* v = getenv("OOB_GEMM_GEMV");
-      return v != nullptr && v[0] == '1';
+      return v == nullptr ? -1 : (v[0] == '1' ? 1 : 0);
     }();
+    const bool gemv_by_shape =
+        gemv_env != 0 && (a.M == 1 || (a.M == 2 && static_cast<long long>(a.N) * a.K <= 12ll * 1000 * 1000));
     if (a.epilogue == 0 && gemv_supported(a) && ctx.emu_table == nullptr && a.c_emu_stride == 0 && a.splitk_ws == nullptr &&
-        (a.gemv > 0 || (a.gemv == 0 && a.splits == 0 && a.skinny <= 0 && gemv_env_on)))
+        (a.gemv > 0 || (a.gemv == 0 && a.splits == 0 && a.skinny <= 0 && (gemv_env == 1 || gemv_by_shape))))
       return launch_gemv(a, a.max_ctas > 0 ? a.max_ctas : sm_count(), stream);
     // The weight-streaming kernel (stream-K over 128-row weight tiles) is opt-in: measured on B200, inside a replayed
     // decode step it is 2 - 12 % slower at M <= 16 than the 128x256 split-K tiles followed by the reduction kernel,

@@ -67,7 +67,8 @@ struct GemmArgs {
   int splitk_reduce;
   // Plain mode, split problems only: an elementwise op applied by the kernel that sums the splits (see
   // splitk_epilogues.cuh).  epilogue_args is a HOST pointer to the op's argument block.
-  // Plain mode, M <= 4: 1 = the CUDA-core streaming kernel (gemv.cu); 0 follows OOB_GEMM_GEMV=1; -1 = never.
+  // Plain mode, M <= 4: 1 = the CUDA-core streaming kernel (gemv.cu); 0 = by shape (M = 1, and M = 2 with a small
+  // weight matrix; OOB_GEMM_GEMV=1 widens that to every M <= 4, =0 switches it off); -1 = never.
   int gemv;
   int epilogue;               // 0 = none, 1 = SwiGLU (oob_gemm_epilogue_swiglu_t), 2 = RoPE + KV write (oob_rope_args_t)
   const void* epilogue_args;

@@ -68,7 +68,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     The order of summation, and so the result, is the same.
 
     ``gemv`` = 1 uses the CUDA-core streaming kernel for ``M <= 4`` (a warp per weight row, no tensor cores, no
-    split-K hand-off); 0 uses it only when ``OOB_GEMM_GEMV=1``."""
+    split-K hand-off); 0 uses it where it measured faster (one row; two rows with ``N * K`` up to 12 M), -1 never."""
     _check_operands(a, b)
     M, N = a.shape[0], b.shape[0]
     if out is None:

@@ -42,7 +42,8 @@ def env_flag(name: str, default: bool = False) -> bool:
 # Names read directly by the native library (csrc/gemm/gemm.cu) or by single call sites:
 #   OOB_GEMM_PAIR=0            plain GEMM: never use the two-SM kernel
 #   OOB_GEMM_SKINNY=1          plain GEMM: weight-streaming kernel for M <= 16
-#   OOB_GEMM_GEMV=1            plain GEMM: CUDA-core streaming kernel for M <= 4
+#   OOB_GEMM_GEMV=0 / 1        plain GEMM, CUDA-core streaming kernel: 0 = never by default, 1 = for every M <= 4
+#                              (unset: M = 1, and M = 2 with a small weight matrix)
 #   OOB_SPLITK_REDUCE_MIN_M=n  split-K: sum inside the GEMM kernel below n rows (default 1: always the second kernel)
 #   OOB_ATTN_STAGES=3          decode attention: three pipeline stages per warp (192 KiB of shared memory per CTA)
 #   OOB_FUSED_EPILOGUES=1      model runner: RoPE + cache write and SwiGLU in the split-K sum of the preceding GEMM
