@@ -7,8 +7,11 @@ followed by PyTorch's residual add and RMSNorm.
 For every row count (message = rows x hidden bf16: 16 KiB for one token of a hidden-8192 model, 4 MiB for 256) the
 tool times, from CUDA graphs, with CUDA events, as the maximum over ranks and with p50 / p90 / p99 over the replays:
 
-* ``ours_fused``     one kernel: all-reduce of the registered partial sums + residual add + RMSNorm
-* ``ours_unfused``   this library's all-reduce, then its stand-alone residual + RMSNorm kernel
+* ``ours_fused``     one kernel: all-reduce of the registered partial sums + residual add + RMSNorm (what
+                     ``fused_allreduce_rmsnorm`` picks for the size)
+* ``ours_push+norm`` the one-barrier push all-reduce into a ring slot, then the stand-alone residual + RMSNorm kernel
+                     (messages up to ``OOB_PUSH_MAX_BYTES``)
+* ``ours_unfused``   this library's in-place all-reduce, then its stand-alone residual + RMSNorm kernel
 * ``nccl+torch``     ``dist.all_reduce`` + ``residual.add_`` + ``torch.nn.functional.rms_norm``
 
 and checks each arm's output against an fp32 reference first.
@@ -44,6 +47,7 @@ def main() -> int:
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     comm = Communicator(list(range(world)), rank, heap_bytes=1 << 30)
+    comm.init_round_robin_slots(torch.bfloat16, 32 << 20, 4)
     dt = torch.bfloat16
     H = args.hidden
     gen = torch.Generator(device="cuda").manual_seed(7 + rank)
@@ -67,6 +71,9 @@ def main() -> int:
             x.copy_(part)  # the in-place all-reduce overwrites its input
             return rmsnorm(comm.all_reduce(x), w, args.eps, res)
 
+        def ours_push_norm():
+            return rmsnorm(comm.all_reduce_push(x), w, args.eps, res)
+
         def nccl_torch():
             nccl_buf.copy_(part)
             dist.all_reduce(nccl_buf)
@@ -75,7 +82,10 @@ def main() -> int:
 
         base = dict(bench="fused_allreduce_rmsnorm", world=world, rows=rows, hidden=H, bytes=rows * H * 2, dtype="bf16",
                     nvls=int(comm.nvls))
-        for name, fn in (("ours_fused", ours_fused), ("ours_unfused", ours_unfused), ("nccl+torch", nccl_torch)):
+        arms = [("ours_fused", ours_fused), ("ours_unfused", ours_unfused), ("nccl+torch", nccl_torch)]
+        if rows * H * 2 <= comm.config.push_max_bytes:
+            arms.insert(1, ("ours_push+norm", ours_push_norm))
+        for name, fn in arms:
             y = fn()[0]
             torch.cuda.synchronize()
             err = (y.float() - want).abs().max().item()
