@@ -12,6 +12,8 @@ role; every ``yield`` is a point where any other role may run) and executed unde
                               its arrival and done counters, GEMM CTAs join the reducers, ranks run ahead into the next
                               launch; only the closing rank barrier keeps a new arrival from meeting an un-re-armed unit
                               (csrc/gemm/gemm_pair.cu: signal warp, draw_ticket_warp, pair_ar_reducer)
+* push all-reduce             one barrier per call; two sets of pieces selected by a call counter that the last block
+                              of a call bumps; ranks run ahead into later calls (csrc/collectives/allreduce_push.cu)
 * last-arriver split-K sum    per-quadrant arrival counter re-armed by the CTA that completes it
                               (csrc/gemm/gemm_kernel.cuh, csrc/gemm/gemm_skinny.cu)
 
@@ -395,3 +397,61 @@ def test_the_simulator_needs_the_closing_barrier_of_the_two_sm_reduction(monkeyp
     monkeypatch.setattr(me, "pair_cta_tail", tail_without_barrier)
     with pytest.raises(AssertionError):
         test_two_sm_in_place_reduction_with_joining_warps_and_ranks_running_ahead(2, 6, 2, 1, 2, 2)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# push all-reduce: ONE barrier per call, two sets of pieces selected by a call counter kept on the device
+# (csrc/collectives/allreduce_push.cu, push_norm_kernel in csrc/collectives/fused_norm.cu)
+# ---------------------------------------------------------------------------------------------------------------------
+class PushState:
+    def __init__(self, world, blocks, sets):
+        self.world, self.blocks, self.sets = world, blocks, sets
+        self.calls = [0] * world                  # call-epoch word: push calls this rank has completed
+        self.ticket = [0] * world                 # blocks of the running call that have finished
+        # staging[rank][set][block][source] = id of the call whose piece lies there
+        self.staging = [[[[None] * world for _ in range(blocks)] for _ in range(sets)] for _ in range(world)]
+        self.kernels_done = [[0] * 64 for _ in range(world)]  # blocks of (rank, call) that have ended
+
+
+def push_block(st, pads, rank, block, call):
+    """Block `block` of call `call` on `rank`; a rank's calls run in stream order, its blocks concurrently."""
+    while call > 0 and st.kernels_done[rank][call - 1] < st.blocks:
+        yield "blocked"
+    s = st.calls[rank] % st.sets                  # every block reads the counter before any block of this call bumps it
+    yield
+    for peer in range(st.world):                  # push this block's stripe into piece `rank` on every rank
+        if peer != rank:
+            st.staging[peer][s][block][rank] = call
+            yield
+    yield from barrier_block(pads, st.world, rank, block, 1, [])
+    for src in range(st.world):                   # sum the pieces from local memory (the own one comes from the input)
+        if src != rank:
+            assert st.staging[rank][s][block][src] == call, (rank, block, call, src, st.staging[rank][s][block][src])
+            yield
+    t = st.ticket[rank]                           # the block that finishes last moves on to the other set
+    st.ticket[rank] += 1
+    if t == st.blocks - 1:
+        st.ticket[rank] = 0
+        st.calls[rank] += 1
+    st.kernels_done[rank][call] += 1
+    yield
+
+
+def _run_push(world, blocks, sets, calls, seeds):
+    for seed in range(seeds):
+        rng = random.Random(seed * 15485863 + world)
+        st, pads = PushState(world, blocks, sets), Pads(world, blocks)
+        roles = [push_block(st, pads, r, b, c) for c in range(calls) for r in range(world) for b in range(blocks)]
+        run_schedule(roles, rng, max_steps=2000000)
+        assert st.calls == [calls] * world and st.ticket == [0] * world
+
+
+@pytest.mark.parametrize("world,blocks", [(2, 1), (2, 3), (4, 2), (8, 1)])
+def test_push_all_reduce_needs_no_closing_barrier_with_two_sets(world, blocks):
+    _run_push(world, blocks, sets=2, calls=5, seeds=150)
+
+
+def test_push_all_reduce_with_one_set_is_caught():
+    """With a single set of pieces a rank that runs ahead overwrites a piece its peer has not summed yet."""
+    with pytest.raises(AssertionError):
+        _run_push(2, 1, sets=1, calls=4, seeds=200)
