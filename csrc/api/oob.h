@@ -47,7 +47,9 @@ typedef enum {
   OOB_NORM_AR_TWOSHOT = 2,
   OOB_NORM_AR_TWOSHOT_NVLS = 3,
   OOB_NORM_RS = 4,
-  OOB_NORM_RS_NVLS = 5
+  OOB_NORM_RS_NVLS = 5,
+  OOB_NORM_AR_PUSH = 6,      /* decode sizes: push + one barrier + local sum and norm of every row; needs stage_* */
+  OOB_NORM_AR_PUSH_NVLS = 7
 } oob_norm_algo_t;
 typedef enum { OOB_GEMM_PLAIN = 0, OOB_GEMM_AR = 1, OOB_GEMM_RS_NORM = 2, OOB_GEMM_AG = 3 } oob_gemm_mode_t;
 
@@ -153,6 +155,9 @@ typedef struct {
   uint64_t res_out_off; /* reg < 0: no residual output */
   void* res_out_local;
   uint64_t emu_stride_local; /* emulation: byte stride between ranks of residual / y_local / res_out_local */
+  int stage_reg;             /* push algorithms: staging area of the push kernels (see oob_allreduce_push): two sets of */
+  uint64_t stage_off;        /* world * piece_bytes; outputs are y_local / res_out_local                                */
+  uint64_t piece_bytes;
 } oob_norm_args_t;
 int oob_fused_norm(oob_comm* c, int algo, const oob_norm_args_t* a, int max_ctas, void* stream);
 

@@ -28,8 +28,6 @@ namespace oob {
 namespace {
 
 constexpr int kPushThreads = 512;
-constexpr int kPushCallSlot = 0;  // call-epoch words of the pad: calls made so far, and blocks of the running call done
-constexpr int kPushDoneSlot = 1;
 
 // Block b of every rank owns the same stripe of the message (whole 16-byte packs; the last block also takes the
 // elements that do not fill a pack), so one barrier between the blocks of equal index is all the ordering needed,

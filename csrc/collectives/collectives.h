@@ -46,7 +46,16 @@ enum NormAlgo : int {
   kNormArTwoShotNvls = 3, // same with multimem.ld_reduce / multimem.st
   kNormRs = 4,            // reduce-scatter by rows + residual + norm; outputs stay local (sequence-parallel form)
   kNormRsNvls = 5,
+  kNormArPush = 6,        // decode sizes: every rank pushes its rows to all ranks, ONE rank barrier, every rank sums the
+                          // pieces locally and normalises every row (staging area as for the push all-reduce)
+  kNormArPushNvls = 7,    // same, pushed with multimem.st
 };
+
+// Call-epoch words of the signal pad shared by the push kernels (allreduce_push.cu, fused_norm.cu): the number of push
+// calls this rank has made (its parity selects the set of pieces a call uses) and the blocks of the running call
+// that have finished.
+constexpr int kPushCallSlot = 0;
+constexpr int kPushDoneSlot = 1;
 
 struct NormArgs {
   int dtype;              // kF16 / kBF16
@@ -62,6 +71,8 @@ struct NormArgs {
   PeerPtrs res_out;       // x_sum + residual, same placement rule as y (p[rank]==nullptr to skip)
   void* res_out_local;
   size_t res_out_local_emu_stride;
+  PeerPtrs staging;       // push algorithms: two sets of world * piece_bytes (registered)
+  size_t piece_bytes;     // >= rows * hidden * sizeof(T), a multiple of 16
 };
 
 cudaError_t launch_fused_norm(const CommCtx& ctx, int algo, const NormArgs& args, int max_ctas, cudaStream_t stream);

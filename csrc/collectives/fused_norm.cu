@@ -159,6 +159,148 @@ __global__ void __launch_bounds__(kNormThreads) fused_norm_kernel(CommCtx ctx_pa
   if constexpr (kComm) rank_barrier(ctx, blockIdx.x, 41);
 }
 
+// One-barrier all-reduce + residual + RMSNorm for decode-sized messages.  Block b of every rank owns rows b, b + G, ...:
+// it pushes its rows of this rank's partial sums into piece `rank` of the staging area on all ranks, meets block b of
+// the other ranks once, and then sums the `world` pieces of its rows from LOCAL memory (fp32, rank order), adds the
+// residual, normalises and writes the outputs locally.  Every rank normalises every row, so nothing has to be
+// broadcast afterwards.  The staging area holds two sets of pieces that consecutive push calls alternate between
+// (call counter on the device, shared with allreduce_push.cu), which is what makes a closing barrier unnecessary.
+template <typename T, int PPT, int NR, bool MC>
+__global__ void __launch_bounds__(kNormThreads) push_norm_kernel(CommCtx ctx_param, NormArgs a) {
+  const CommCtx ctx = resolve_ctx(ctx_param);
+  const int world = ctx.world, rank = ctx.rank;
+  using PT = PackTraits<T>;
+  constexpr int E = 8;
+  const int packs_per_row = a.hidden / E;
+  const size_t row_bytes = size_t(a.hidden) * sizeof(T);
+
+  __shared__ uint32_t s_set;
+  if (threadIdx.x == 0) s_set = ptx::ld_relaxed_sys(call_epoch_ptr(ctx, kPushCallSlot)) & 1u;
+  __syncthreads();
+  const size_t set_off = size_t(s_set) * size_t(world) * a.piece_bytes;
+  const size_t my_piece = set_off + size_t(rank) * a.piece_bytes;
+
+  const char* x = static_cast<const char*>(a.x.p[rank]);
+  const char* res = a.residual ? static_cast<const char*>(a.residual) + a.residual_emu_stride * blockIdx.y : nullptr;
+  char* y_local = static_cast<char*>(a.y_local) + a.y_local_emu_stride * blockIdx.y;
+  char* ro_local =
+      a.res_out_local ? static_cast<char*>(a.res_out_local) + a.res_out_local_emu_stride * blockIdx.y : nullptr;
+
+  // ---- push this block's rows ------------------------------------------------------------------------------------
+  for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
+    const size_t off = size_t(row) * row_bytes;
+#pragma unroll
+    for (int j = 0; j < PPT; ++j) {
+      const int p = threadIdx.x + j * kNormThreads;
+      if (p < packs_per_row) {
+        const uint4 v = *reinterpret_cast<const uint4*>(x + off + size_t(p) * 16);
+        if constexpr (MC) {
+          ptx::multimem_st_v4(static_cast<char*>(a.staging.mc) + my_piece + off + size_t(p) * 16, v);
+        } else if constexpr (NR > 0) {
+#pragma unroll
+          for (int r = 1; r < NR; ++r)
+            ptx::st_v4(static_cast<char*>(a.staging.p[(rank + r) % NR]) + my_piece + off + size_t(p) * 16, v);
+        } else {
+          for (int r = 1; r < world; ++r)
+            ptx::st_v4(static_cast<char*>(a.staging.p[(rank + r) % world]) + my_piece + off + size_t(p) * 16, v);
+        }
+      }
+    }
+  }
+
+  // Norm weight for this thread's packs (loaded while the pushes travel).
+  float w[PPT][E];
+#pragma unroll
+  for (int j = 0; j < PPT; ++j) {
+    const int p = threadIdx.x + j * kNormThreads;
+    if (p < packs_per_row)
+      PT::unpack(*reinterpret_cast<const uint4*>(static_cast<const char*>(a.weight) + size_t(p) * 16), w[j]);
+  }
+
+  if (!rank_barrier(ctx, blockIdx.x, 42)) return;
+
+  // ---- sum the pieces of this block's rows from local memory, add the residual, normalise -------------------------
+  // The own contribution is taken from x: a rank's own multicast store is not ordered with its loads, and without
+  // the switch the own piece is not pushed at all.
+  const char* mine = static_cast<const char*>(a.staging.p[rank]) + set_off;
+  for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
+    const size_t off = size_t(row) * row_bytes;
+    float v[PPT][E];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PPT; ++j) {
+      const int p = threadIdx.x + j * kNormThreads;
+      if (p < packs_per_row) {
+        const size_t po = off + size_t(p) * 16;
+#pragma unroll
+        for (int i = 0; i < E; ++i) v[j][i] = 0.f;
+        if constexpr (NR > 0) {
+          uint4 raw[NR];
+#pragma unroll
+          for (int r = 0; r < NR; ++r)
+            raw[r] = r == rank ? *reinterpret_cast<const uint4*>(x + po)
+                               : ptx::ld_relaxed_sys_v4(mine + size_t(r) * a.piece_bytes + po);
+#pragma unroll
+          for (int r = 0; r < NR; ++r) {
+            float f[E];
+            PT::unpack(raw[r], f);
+#pragma unroll
+            for (int i = 0; i < E; ++i) v[j][i] += f[i];
+          }
+        } else {
+          for (int r = 0; r < world; ++r) {
+            float f[E];
+            PT::unpack(r == rank ? *reinterpret_cast<const uint4*>(x + po)
+                                 : ptx::ld_relaxed_sys_v4(mine + size_t(r) * a.piece_bytes + po),
+                       f);
+#pragma unroll
+            for (int i = 0; i < E; ++i) v[j][i] += f[i];
+          }
+        }
+        if (res != nullptr) {
+          float rf[E];
+          PT::unpack(ptx::ld_nc_v4(res + po), rf);
+#pragma unroll
+          for (int i = 0; i < E; ++i) v[j][i] += rf[i];
+        }
+        // The normalisation sees the residual stream as it is stored (rounded).
+        const uint4 ro = PT::pack(v[j]);
+        if (ro_local != nullptr) {
+          PT::unpack(ro, v[j]);
+          ptx::st_v4(ro_local + po, ro);
+        } else if (res != nullptr) {
+          PT::unpack(ro, v[j]);
+        }
+#pragma unroll
+        for (int i = 0; i < E; ++i) ss += v[j][i] * v[j][i];
+      }
+    }
+    const float total = block_sum(ss);
+    const float scale = rsqrtf(total / float(a.hidden) + a.eps);
+#pragma unroll
+    for (int j = 0; j < PPT; ++j) {
+      const int p = threadIdx.x + j * kNormThreads;
+      if (p < packs_per_row) {
+        float o[E];
+#pragma unroll
+        for (int i = 0; i < E; ++i) o[i] = v[j][i] * scale * w[j][i];
+        ptx::st_v4(y_local + off + size_t(p) * 16, PT::pack(o));
+      }
+    }
+  }
+
+  // The block that finishes last moves the rank on to the other set of pieces.
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* ticket = call_epoch_ptr(ctx, kPushDoneSlot);
+    if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+      *ticket = 0;
+      atomicAdd(call_epoch_ptr(ctx, kPushCallSlot), 1u);
+      __threadfence();
+    }
+  }
+}
+
 template <typename K>
 cudaError_t launch_k(K kernel, const CommCtx& ctx, int ctas, const NormArgs& a, cudaStream_t stream) {
   if (ctx.emu_table != nullptr) {
@@ -187,6 +329,10 @@ cudaError_t dispatch_algo(int algo, const CommCtx& ctx, int ctas, const NormArgs
       return launch_k(fused_norm_kernel<T, PPT, NR, kNormRs>, ctx, ctas, a, stream);
     case kNormRsNvls:
       return launch_k(fused_norm_kernel<T, PPT, 0, kNormRsNvls>, ctx, ctas, a, stream);
+    case kNormArPush:
+      return launch_k(push_norm_kernel<T, PPT, NR, false>, ctx, ctas, a, stream);
+    case kNormArPushNvls:
+      return launch_k(push_norm_kernel<T, PPT, NR, true>, ctx, ctas, a, stream);
   }
   return cudaErrorInvalidValue;
 }
@@ -224,8 +370,12 @@ cudaError_t launch_fused_norm(const CommCtx& ctx, int algo, const NormArgs& a, i
   const bool mc = (algo == kNormArTwoShotNvls || algo == kNormRsNvls);
   if (mc && a.x.mc == nullptr) return cudaErrorInvalidValue;
   if (algo == kNormArTwoShotNvls && a.y.mc == nullptr) return cudaErrorInvalidValue;
+  const bool push = (algo == kNormArPush || algo == kNormArPushNvls);
+  if (push && (a.y_local == nullptr || a.piece_bytes < size_t(a.rows) * a.hidden * 2 || (a.piece_bytes & 15) ||
+               a.staging.p[ctx.rank] == nullptr || (algo == kNormArPushNvls && a.staging.mc == nullptr)))
+    return cudaErrorInvalidValue;
   int rows = a.rows;
-  if (algo >= kNormArTwoShot) rows = (a.rows + ctx.world - 1) / ctx.world;
+  if (algo >= kNormArTwoShot && !push) rows = (a.rows + ctx.world - 1) / ctx.world;
   int ctas = max_ctas < 1 ? 1 : max_ctas;
   // Communicating launches are bounded by the barrier slots of the pad; the local one may fill the GPU
   // (one row per CTA at a time, eight resident CTAs per SM hide the three dependent passes over a row).

@@ -970,6 +970,14 @@ int oob_fused_norm(oob_comm* c, int algo, const oob_norm_args_t* a, int max_ctas
     n.res_out_local = a->res_out_local;
     n.res_out_local_emu_stride = c->emulated ? a->emu_stride_local : 0;
   }
+  if (algo == OOB_NORM_AR_PUSH || algo == OOB_NORM_AR_PUSH_NVLS) {
+    if ((a->piece_bytes & 15) || a->piece_bytes < norm_bytes || (a->stage_off & 15) ||
+        !c->peer_ptrs(a->stage_reg, a->stage_off, 2 * a->piece_bytes * c->world, &n.staging))
+      return set_error(OOB_ERR_INVALID,
+                       "bad staging area (16-byte aligned, piece_bytes >= the message, 2 * world * piece_bytes registered)");
+    n.piece_bytes = a->piece_bytes;
+    if (algo == OOB_NORM_AR_PUSH_NVLS && n.staging.mc == nullptr) algo = OOB_NORM_AR_PUSH;
+  }
   if (max_ctas <= 0) max_ctas = 32;
   cudaError_t e = launch_fused_norm(c->make_ctx(), algo, n, max_ctas, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "fused norm launch");

@@ -33,6 +33,7 @@ AR_ONESHOT_P2P, AR_TWOSHOT_P2P, AR_TWOSHOT_NVLS, AR_ONESHOT_NVLS = 0, 1, 2, 3
 RS_P2P, RS_NVLS = 0, 1
 AG_PUSH_P2P, AG_PUSH_NVLS, AG_PULL_P2P = 0, 1, 2
 NORM_LOCAL, NORM_AR_ONESHOT, NORM_AR_TWOSHOT, NORM_AR_TWOSHOT_NVLS, NORM_RS, NORM_RS_NVLS = range(6)
+NORM_AR_PUSH, NORM_AR_PUSH_NVLS = 6, 7
 GEMM_PLAIN, GEMM_AR, GEMM_RS_NORM, GEMM_AG = range(4)
 EPILOGUE_NONE, EPILOGUE_SWIGLU, EPILOGUE_ROPE_KV = range(3)
 FLAG_NO_NVLS, FLAG_LEGACY_IPC = 1, 2
@@ -64,7 +65,8 @@ class NormArgs(Structure):
     _fields_ = [("dtype", c_int), ("rows", c_int), ("hidden", c_int), ("eps", c_float), ("x_reg", c_int),
                 ("x_off", c_uint64), ("residual", c_void_p), ("weight", c_void_p), ("y_reg", c_int),
                 ("y_off", c_uint64), ("y_local", c_void_p), ("res_out_reg", c_int), ("res_out_off", c_uint64),
-                ("res_out_local", c_void_p), ("emu_stride_local", c_uint64)]
+                ("res_out_local", c_void_p), ("emu_stride_local", c_uint64), ("stage_reg", c_int), ("stage_off", c_uint64),
+                ("piece_bytes", c_uint64)]
 
 
 class GemmArgs(Structure):

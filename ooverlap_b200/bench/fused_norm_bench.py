@@ -82,7 +82,12 @@ def main() -> int:
 
         base = dict(bench="fused_allreduce_rmsnorm", world=world, rows=rows, hidden=H, bytes=rows * H * 2, dtype="bf16",
                     nvls=int(comm.nvls))
+        def ours_fused_32():
+            return fused_allreduce_rmsnorm(comm, x, w, args.eps, res, max_ctas=32)
+
         arms = [("ours_fused", ours_fused), ("ours_unfused", ours_unfused), ("nccl+torch", nccl_torch)]
+        if rows * H * 2 > (1 << 20):
+            arms.insert(1, ("ours_fused_32ctas", ours_fused_32))
         if rows * H * 2 <= comm.config.push_max_bytes:
             arms.insert(1, ("ours_push+norm", ours_push_norm))
         for name, fn in arms:

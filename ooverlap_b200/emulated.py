@@ -157,7 +157,8 @@ class EmulatedGroup:
     def fused_norm(self, algo: int, *, x_off: int, rows: int, hidden: int, dtype: torch.dtype, weight: torch.Tensor,
                    eps: float, residual: Optional[torch.Tensor] = None, y_off: Optional[int] = None,
                    y_local: Optional[torch.Tensor] = None, res_out_off: Optional[int] = None,
-                   res_out_local: Optional[torch.Tensor] = None, local_stride_bytes: int = 0, max_ctas: int = 8) -> None:
+                   res_out_local: Optional[torch.Tensor] = None, local_stride_bytes: int = 0, max_ctas: int = 8,
+                   stage_off: Optional[int] = None, piece_bytes: int = 0) -> None:
         a = _lib.NormArgs()
         a.dtype, a.rows, a.hidden, a.eps = dtype_code(dtype), rows, hidden, eps
         a.x_reg, a.x_off = 0, x_off
@@ -169,4 +170,5 @@ class EmulatedGroup:
         a.res_out_off = res_out_off or 0
         a.res_out_local = res_out_local.data_ptr() if res_out_local is not None else None
         a.emu_stride_local = local_stride_bytes
+        a.stage_reg, a.stage_off, a.piece_bytes = 0, stage_off or 0, piece_bytes  # push algorithms only
         _lib.check(_lib.lib().oob_fused_norm(self._h, algo, ctypes.byref(a), max_ctas, _stream()))

@@ -58,10 +58,10 @@ def fused_allreduce_rmsnorm(comm, x: torch.Tensor, weight: torch.Tensor, eps: fl
     """``y = rmsnorm(all_reduce(x) + residual) * weight`` in one kernel.
 
     ``x`` ([rows, hidden], registered memory) holds this rank's partial sums.
-    Decode-sized messages (up to ``config.push_max_bytes``, when the communicator has a slot ring) take the one-barrier
-    push all-reduce followed by the local residual + RMSNorm kernel; larger ones the two-shot fused kernel (rank r
-    reduces and normalises its rows and broadcasts them), through NVLS when the communicator has it; fewer rows than
-    ranks the one-shot fused kernel.  ``algo`` forces one of the fused kernels.  Returns ``(y, new_residual)``; with
+    Decode-sized messages (up to ``config.push_max_bytes``) take the push kernel (every rank pushes its rows to all
+    ranks, the ranks meet once, every rank sums and normalises every row locally); larger ones the two-shot fused
+    kernel (rank r reduces and normalises its rows and broadcasts them), through NVLS when the communicator has it;
+    fewer rows than ranks the one-shot fused kernel.  ``algo`` forces one of the fused kernels.  Returns ``(y, new_residual)``; with
     the two-shot forms both live in registered memory."""
     if comm.world == 1:
         return rmsnorm(x, weight, eps, residual, out=out, residual_out=residual_out)
@@ -69,23 +69,16 @@ def fused_allreduce_rmsnorm(comm, x: torch.Tensor, weight: torch.Tensor, eps: fl
     if loc is None:
         raise ValueError("x must live in registered memory (comm.empty / slot pools / comm.register)")
     rows, hidden = x.shape
+    nbytes = x.numel() * x.element_size()
+    piece = (nbytes + 255) // 256 * 256
     if algo is None:
-        nbytes = x.numel() * x.element_size()
-        # Decode-sized messages: the one-barrier push all-reduce followed by the local residual + RMSNorm kernel
-        # (measured on 8 x B200, 16 KiB .. 256 KiB: 19 - 22 us against 34 - 40 us for the one-shot fused kernel, whose
-        # single CTA per row pulls every peer's copy between two barriers).
-        summed = None
-        if not getattr(comm, "emulated", False) and nbytes <= comm.config.push_max_bytes:
-            summed = comm.all_reduce_push(x)
-        if summed is not None:
-            if residual is not None:
-                return rmsnorm(summed, weight, eps, residual, out=out, residual_out=residual_out)
-            y = rmsnorm(summed, weight, eps, None, out=out)
-            if residual_out is not None:
-                residual_out.copy_(summed)
-                summed = residual_out
-            return y, summed  # without a residual the sum itself is the new residual stream
-        if rows < comm.world:
+        # Decode-sized messages: every rank pushes its rows to all ranks, one barrier, every rank sums and normalises
+        # every row locally (measured on 8 x B200 at 16 - 256 KiB: the one-shot fused kernel, whose single CTA per row
+        # pulls every peer's copy between two barriers, took 34 - 40 us; push all-reduce + local norm 19 - 22 us).
+        if (not getattr(comm, "emulated", False) and nbytes <= comm.config.push_max_bytes
+                and comm._push_staging(piece) is not None):
+            algo = _lib.NORM_AR_PUSH_NVLS if comm.nvls else _lib.NORM_AR_PUSH
+        elif rows < comm.world:
             algo = _lib.NORM_AR_ONESHOT
         else:
             algo = _lib.NORM_AR_TWOSHOT_NVLS if (comm.nvls and loc[0] == 0) else _lib.NORM_AR_TWOSHOT
@@ -95,10 +88,15 @@ def fused_allreduce_rmsnorm(comm, x: torch.Tensor, weight: torch.Tensor, eps: fl
     a.residual = residual.data_ptr() if residual is not None else None
     a.weight = weight.data_ptr()
     a.res_out_reg = -1
-    if algo == _lib.NORM_AR_ONESHOT:
+    if algo in (_lib.NORM_AR_ONESHOT, _lib.NORM_AR_PUSH, _lib.NORM_AR_PUSH_NVLS):
         y = out if out is not None else torch.empty_like(x)
         ro = residual_out if residual_out is not None else torch.empty_like(x)
         a.y_local, a.res_out_local = y.data_ptr(), ro.data_ptr()
+        if algo != _lib.NORM_AR_ONESHOT:
+            stage = comm._push_staging(piece)
+            if stage is None:
+                raise ValueError("message too large for the staging area of the push kernels (config.push_max_bytes)")
+            a.stage_reg, a.stage_off, a.piece_bytes = 0, stage, piece
     else:
         y = out if out is not None and comm.heap_offset(out) is not None else comm.scratch_view(
             ("norm_y", x.dtype, tuple(x.shape)), x.shape, x.dtype)
@@ -106,7 +104,9 @@ def fused_allreduce_rmsnorm(comm, x: torch.Tensor, weight: torch.Tensor, eps: fl
             comm.scratch_view(("norm_r", x.dtype, tuple(x.shape)), x.shape, x.dtype))
         a.y_reg, a.y_off = 0, comm.heap_offset(y)
         a.res_out_reg, a.res_out_off = 0, comm.heap_offset(ro)
-    _lib.check(_lib.lib().oob_fused_norm(comm._h, algo, ctypes.byref(a), max_ctas or 32, _stream()))
+    # One row per CTA at a time: a large message needs many CTAs to keep enough loads in flight through the switch.
+    _lib.check(_lib.lib().oob_fused_norm(comm._h, algo, ctypes.byref(a), max_ctas or (32 if nbytes <= (1 << 20) else 128),
+                                         _stream()))
     return y, ro
 
 
