@@ -47,3 +47,24 @@ def test_tuned_solution_overrides_the_rule():
     assert plan(8, 512, 8192, False, "auto", None, None, None, dict(sol, kernel="pair"))[4] == "pair"
     with pytest.raises(ValueError):
         plan(8, 512, 8192, False, "auto", None, None, None, {"strategy": "bogus"})
+
+
+def test_autotune_candidate_list():
+    """What strategy="autotune" measures: the unfused pair, the two-SM kernel over CTA budgets (through the switch when
+    there is one; with peer loads too between two ranks), the one-SM kernel, and from four ranks on its in-switch pull
+    and, for tall outputs, the slab pipeline."""
+    from types import SimpleNamespace
+    from ooverlap_b200.ops.overlap import GemmAllReduce
+
+    def cands(world, nvls, M):
+        op = SimpleNamespace(comm=SimpleNamespace(world=world, nvls=nvls), M=M)
+        return GemmAllReduce._candidates(op)
+
+    c8 = cands(8, True, 8192)
+    assert c8[0] == ("unfused", None, None, None)
+    assert [c for c in c8 if c[1] == "pair"] == [("fused", "pair", 1, n) for n in (4, 8, 16, 24, 32)]
+    assert ("fused", "one_sm", 0, 16) in c8 and ("fused", "one_sm", 2, 16) in c8 and ("chunked", None, None, None) in c8
+    assert ("chunked", None, None, None) not in cands(8, True, 512)
+    c2 = cands(2, True, 8192)
+    assert ("fused", "pair", 0, 8) in c2 and ("fused", "pair", 1, 8) in c2 and ("fused", "one_sm", 2, 16) not in c2
+    assert all(c[2] == 0 for c in cands(4, False, 2048) if c[1] == "pair")
