@@ -241,6 +241,7 @@ int oob_topology_json(char* buf, uint64_t cap, int run_probes);
 #define OOB_TOPO_NO_MULTIMEM_PROBE 16u
 #define OOB_TOPO_REQUIRE_PEER 32u
 #define OOB_TOPO_TEXT 64u
+#define OOB_TOPO_NO_BULK_PROBE 128u   /* skip the bulk-store (cp.async.bulk shared -> peer global) probe */
 int oob_topology_describe(char* buf, uint64_t cap, unsigned flags, const int* devices, int n_devices);
 
 /* Node-local rendezvous on its own (host only): all-gather of small blobs,

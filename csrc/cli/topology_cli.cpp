@@ -2,8 +2,8 @@
 //
 // Capability parity: ooverlap_topology_cli (src/topology/topology_cli.cpp:24-114): --json, --no-enable-peer,
 // --require-peer, --no-probe, --no-atomic-probe and a device list.  Its --no-tma-probe switches off the probe of
-// the data path it uses between GPUs; here that path is multimem and 128-bit ld/st, so the matching switches are
-// --no-multimem-probe and --no-copy-probe.  --no-shm is accepted and ignored: no host-staged transport exists here.
+// the data path it uses between GPUs; here that path is multimem, 128-bit ld/st and bulk stores, so the matching
+// switches are --no-multimem-probe, --no-copy-probe and --no-bulk-probe (--no-tma-probe is accepted as its alias).  --no-shm is accepted and ignored: no host-staged transport exists here.
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -13,13 +13,14 @@
 static void usage(const char* argv0) {
   std::printf(
       "usage: %s [--json] [--no-probe] [--no-enable-peer] [--no-atomic-probe] [--no-copy-probe]\n"
-      "          [--no-multimem-probe] [--require-peer] [--no-shm] [device ...]\n"
+      "          [--no-multimem-probe] [--no-bulk-probe] [--require-peer] [--no-shm] [device ...]\n"
       "  --json               JSON document instead of the table\n"
       "  --no-probe           attributes only: no kernel runs, no memory is allocated\n"
       "  --no-enable-peer     do not switch peer access on (implies no per-pair probes)\n"
       "  --no-atomic-probe    skip the remote-atomic probe\n"
       "  --no-copy-probe      skip the timed 64 MiB peer copy\n"
       "  --no-multimem-probe  skip the multicast (NVLS) probe\n"
+      "  --no-bulk-probe      skip the bulk-store probe (shared memory -> peer memory; alias --no-tma-probe)\n"
       "  --require-peer       exit 1 unless every listed pair has peer access\n"
       "  device ...           indices to describe (default: all visible devices)\n",
       argv0);
@@ -36,6 +37,7 @@ int main(int argc, char** argv) {
     else if (!std::strcmp(a, "--no-atomic-probe")) flags |= OOB_TOPO_NO_ATOMIC_PROBE;
     else if (!std::strcmp(a, "--no-copy-probe")) flags |= OOB_TOPO_NO_COPY_PROBE;
     else if (!std::strcmp(a, "--no-multimem-probe")) flags |= OOB_TOPO_NO_MULTIMEM_PROBE;
+    else if (!std::strcmp(a, "--no-bulk-probe") || !std::strcmp(a, "--no-tma-probe")) flags |= OOB_TOPO_NO_BULK_PROBE;
     else if (!std::strcmp(a, "--require-peer")) flags |= OOB_TOPO_REQUIRE_PEER;
     else if (!std::strcmp(a, "--no-shm")) continue;
     else if (!std::strcmp(a, "--help") || !std::strcmp(a, "-h")) {

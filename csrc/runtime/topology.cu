@@ -7,7 +7,7 @@
 // :183-219 (NUMA node from sysfs), :1328 (JSON dump) and the probe kernels in
 // src/topology/topology_probe.cu:108-238.  The bulk-copy-engine probes of the
 // reference are replaced by what this library actually uses between GPUs:
-// 128-bit ld/st, system-scope atomics and multimem (a live probe through a
+// 128-bit ld/st, system-scope atomics, bulk stores from shared memory and multimem (a live probe through a
 // multicast object over all listed devices: multimem.st, multimem.red and
 // multimem.ld_reduce, each checked from every device's own memory).
 // Host-staged "Shm" transport is not probed: on an NVSwitch machine every pair
@@ -46,6 +46,26 @@ __global__ void probe_atomic_kernel(uint32_t* remote, uint32_t* result) {
 __global__ void probe_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, size_t n) {
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x)
     ptx::st_v4(dst + i, ptx::ld_nc_v4(src + i));
+}
+
+// Untiled bulk store (the copy engine path the one-SM fused GEMM uses for its pushed tiles, here without a tensor map):
+// 4 KiB from shared memory of an SM of the source device into memory of the destination device, then a load back.
+__global__ void probe_bulk_store_kernel(uint32_t* remote, uint32_t* result, uint32_t token) {
+  __shared__ __align__(128) uint32_t tile[1024];
+  for (int i = threadIdx.x; i < 1024; i += blockDim.x) tile[i] = token + uint32_t(i);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes before the async-proxy read
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(remote),
+                 "r"(static_cast<uint32_t>(__cvta_generic_to_shared(tile))), "r"(4096u)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    __threadfence_system();
+    uint32_t bad = 0;
+    for (int i = 0; i < 1024; i += 101) bad += ptx::ld_relaxed_sys(remote + i) != token + uint32_t(i);
+    result[0] = bad;
+  }
 }
 
 // One thread: store a token to word 0 of every bound device, add 5 to word 1 of every bound device.
@@ -87,7 +107,7 @@ void append(std::string* s, const char* fmt, ...) {
 }
 
 struct PairProbe {
-  int ldst = -1, atomic = -1;  // -1 not run, 0 failed, 1 ok
+  int ldst = -1, atomic = -1, bulk = -1;  // -1 not run, 0 failed, 1 ok
   double copy_gbs = 0.0;
 };
 
@@ -100,8 +120,8 @@ PairProbe probe_pair(int src, int dst, unsigned flags) {
   const bool copy = !(flags & OOB_TOPO_NO_COPY_PROBE);
   const size_t big = size_t(64) << 20;
   cudaSetDevice(dst);
-  if (cudaMalloc(&remote, 256) != cudaSuccess || (copy && cudaMalloc(&big_remote, big) != cudaSuccess)) goto done;
-  cudaMemset(remote, 0, 256);
+  if (cudaMalloc(&remote, 8192) != cudaSuccess || (copy && cudaMalloc(&big_remote, big) != cudaSuccess)) goto done;
+  cudaMemset(remote, 0, 8192);
   cudaDeviceSynchronize();
   cudaSetDevice(src);
   {
@@ -121,6 +141,12 @@ PairProbe probe_pair(int src, int dst, unsigned flags) {
     probe_atomic_kernel<<<1, 1>>>(remote, result);
     if (cudaDeviceSynchronize() != cudaSuccess) goto done;
     out.atomic = (result[0] == 0xB200u && result[1] == 0xB200u + 7u) ? 1 : 0;
+  }
+  if (!(flags & OOB_TOPO_NO_BULK_PROBE)) {
+    result[0] = 0xffffffffu;
+    probe_bulk_store_kernel<<<1, 128>>>(remote + 1024, result, 0xB2000000u);  // 4 KiB past the words of the other probes
+    if (cudaDeviceSynchronize() != cudaSuccess) goto done;
+    out.bulk = result[0] == 0u ? 1 : 0;
   }
   if (copy) {
     cudaEvent_t a, b;
@@ -403,8 +429,8 @@ std::string to_json(const TopoDoc& doc) {
   for (const LinkRow& l : doc.links) {
     append(&s,
            "%s\n    {\"src\": %d, \"dst\": %d, \"p2p\": %d, \"native_atomics\": %d, \"performance_rank\": %d, "
-           "\"kind\": \"%s\", \"probe_ldst\": %d, \"probe_atomic\": %d, \"copy_gbs\": %.1f}",
-           first ? "" : ",", l.src, l.dst, l.p2p, l.atomics, l.rank, l.kind, l.probe.ldst, l.probe.atomic,
+           "\"kind\": \"%s\", \"probe_ldst\": %d, \"probe_atomic\": %d, \"probe_bulk_store\": %d, \"copy_gbs\": %.1f}",
+           first ? "" : ",", l.src, l.dst, l.p2p, l.atomics, l.rank, l.kind, l.probe.ldst, l.probe.atomic, l.probe.bulk,
            l.probe.copy_gbs);
     first = false;
   }
@@ -428,11 +454,12 @@ std::string to_text(const TopoDoc& doc) {
     append(&s, "%-4d %-28.28s %d.%-3d %-4d %-6.1f GB %-4d MB %-5d %-9s %s\n", r.index, r.name.c_str(), r.major, r.minor,
            r.sms, double(r.mem) / 1e9, r.l2 >> 20, r.numa, r.multicast ? "yes" : "no", r.fd ? "yes" : "no");
   if (!doc.links.empty()) {
-    append(&s, "\n%-9s %-7s %-4s %-8s %-5s %-6s %-7s %s\n", "src->dst", "kind", "p2p", "atomics", "rank", "ld/st",
-           "atomic", "copy GB/s");
+    append(&s, "\n%-9s %-7s %-4s %-8s %-5s %-6s %-7s %-5s %s\n", "src->dst", "kind", "p2p", "atomics", "rank", "ld/st",
+           "atomic", "bulk", "copy GB/s");
     for (const LinkRow& l : doc.links)
-      append(&s, "%3d->%-4d %-7s %-4s %-8s %-5d %-6s %-7s %.1f\n", l.src, l.dst, l.kind, l.p2p ? "yes" : "no",
-             l.atomics ? "native" : "no", l.rank, tri(l.probe.ldst), tri(l.probe.atomic), l.probe.copy_gbs);
+      append(&s, "%3d->%-4d %-7s %-4s %-8s %-5d %-6s %-7s %-5s %.1f\n", l.src, l.dst, l.kind, l.p2p ? "yes" : "no",
+             l.atomics ? "native" : "no", l.rank, tri(l.probe.ldst), tri(l.probe.atomic), tri(l.probe.bulk),
+             l.probe.copy_gbs);
   }
   append(&s, "\nall pairs NVLink: %s   all pairs peer access: %s   multimem probe: %s", doc.all_nvlink ? "yes" : "no",
          doc.all_p2p ? "yes" : "no", tri(doc.multimem));

@@ -28,10 +28,11 @@ def build(force: bool = False):
 
 
 def topology(run_probes: bool = False, *, devices=None, enable_peer: bool = True, atomic_probe: bool = True,
-             copy_probe: bool = True, multimem_probe: bool = True, require_peer: bool = False, text: bool = False):
+             copy_probe: bool = True, multimem_probe: bool = True, bulk_probe: bool = True, require_peer: bool = False,
+             text: bool = False):
     """Topology of the visible GPUs (or of ``devices``) as a dict, or as a table when ``text`` is set (the CLI
     ``lib/oob_topology`` prints the same).  ``run_probes`` runs the live probes: per directed pair a remote store / load,
-    a remote atomic and a timed peer copy, and over all devices a multimem store / add / in-switch sum; the keyword
+    a remote atomic, a bulk store from shared memory and a timed peer copy, and over all devices a multimem store / add / in-switch sum; the keyword
     switches take single probes out (``enable_peer=False``: peer access is never switched on, so no per-pair probe
     runs).  ``require_peer`` raises ``OobError`` when a pair has no peer access."""
     import ctypes
@@ -41,6 +42,7 @@ def topology(run_probes: bool = False, *, devices=None, enable_peer: bool = True
     flags |= 0 if atomic_probe else _lib.TOPO_NO_ATOMIC_PROBE
     flags |= 0 if copy_probe else _lib.TOPO_NO_COPY_PROBE
     flags |= 0 if multimem_probe else _lib.TOPO_NO_MULTIMEM_PROBE
+    flags |= 0 if bulk_probe else _lib.TOPO_NO_BULK_PROBE
     flags |= _lib.TOPO_REQUIRE_PEER if require_peer else 0
     flags |= _lib.TOPO_TEXT if text else 0
     devs = [int(d) for d in devices] if devices else []

@@ -21,7 +21,7 @@ OOB_OK = 0
 ERR_INVALID, ERR_CUDA, ERR_BOOTSTRAP, ERR_UNSUPPORTED, ERR_NOMEM, ERR_DEVICE_TIMEOUT, ERR_POISONED = -1, -2, -3, -4, -5, -6, -7
 
 TOPO_PROBES, TOPO_NO_ENABLE_PEER, TOPO_NO_ATOMIC_PROBE, TOPO_NO_COPY_PROBE = 1, 2, 4, 8
-TOPO_NO_MULTIMEM_PROBE, TOPO_REQUIRE_PEER, TOPO_TEXT = 16, 32, 64
+TOPO_NO_MULTIMEM_PROBE, TOPO_REQUIRE_PEER, TOPO_TEXT, TOPO_NO_BULK_PROBE = 16, 32, 64, 128
 
 LOG_SINK = ctypes.CFUNCTYPE(None, c_int, c_char_p)
 LOG_ERROR, LOG_WARN, LOG_INFO, LOG_DEBUG = 0, 1, 2, 3

@@ -23,7 +23,7 @@ def test_cli_switches_parse():
     bad = _cli("--bogus")
     assert bad.returncode == 2 and "unknown option" in bad.stderr
     r = _cli("--json", "--no-probe", "--no-enable-peer", "--no-atomic-probe", "--no-copy-probe", "--no-multimem-probe",
-             "--no-shm")
+             "--no-bulk-probe", "--no-tma-probe", "--no-shm")
     assert r.returncode == 0, r.stderr
     doc = json.loads(r.stdout)
     assert doc["device_count"] == len(doc["devices"]) and doc["probe_multimem"] == -1
@@ -55,7 +55,7 @@ def test_probes_pass_on_every_pair():
         assert d["cc"] == "10.0" and d["sms"] >= 100 and d["memory_bytes"] > (100 << 30)
     for l in doc["links"]:
         assert l["p2p"] == 1 and l["kind"] == "nvlink", l
-        assert l["probe_ldst"] == 1 and l["probe_atomic"] == 1 and l["copy_gbs"] > 100.0, l
+        assert l["probe_ldst"] == 1 and l["probe_atomic"] == 1 and l["probe_bulk_store"] == 1 and l["copy_gbs"] > 100.0, l
     if n >= 2:
         assert doc["all_pairs_nvlink"] and doc["all_pairs_p2p"]
         assert doc["probe_multimem"] == 1, doc["probe_multimem_note"]
