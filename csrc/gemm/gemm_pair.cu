@@ -896,14 +896,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(MODE == kGemmPlain ?
           }
           __syncwarp();
           if (*abort) break;
-          constexpr int PF = 3;
+          // (one chunk ahead in the fused kernels: their 384 threads leave 168 registers per thread)
+          constexpr int PF = THREADS > kThreadsPlainP ? 1 : 3;
           const float4* src1 = sk_slot(plan.sk_ws, p_first + 1, int(cta), q) + lane;
           float4 pre[PF][8];
 #pragma unroll
           for (int c = 0; c < PF; ++c)
 #pragma unroll
             for (int i = 0; i < 8; ++i) pre[c][i] = __ldcg(src1 + (c * 8 + i) * 32);
-#pragma unroll
+#pragma unroll(PF == 1 ? 1 : kTileN / 32)
           for (int c = 0; c < kTileN / 32; ++c) {
             uint32_t r[32];
             ptx::tmem_ld_32x32b_x32(t_addr + c * 32, r);

@@ -123,15 +123,20 @@ def _auto_rule(world: int, out_bytes: int, emulated: bool):
     * two ranks: fused; outputs of 64 MiB and more on the two-SM kernel reducing in place through the switch with 24
       communication CTAs, smaller ones on the one-SM kernel that pushes partial tiles (it starts reducing earlier, which
       is what counts for one or two waves of tiles);
-    * four ranks and more (measured at eight): up to 16 MiB the one-SM kernel with the in-switch pull (59 against
-      78 us unfused at M = 512); up to 64 MiB this library's GEMM followed by its in-switch all-reduce (131 us at
-      M = 2048; the fused variants are within 2 %); above that the two-SM kernel reducing in place through the switch
-      with 8 communication CTAs (374 against 393 us unfused at M = 8192)."""
+    * four ranks (measured): up to 16 MiB the one-SM kernel with pushed tiles (59 us at M = 512); above that the two-SM
+      kernel reducing in place through the switch with 16 communication CTAs (130 / 360 us at M = 2048 / 8192 against
+      150 / 500 us for the GEMM followed by the all-reduce);
+    * eight ranks (measured): up to 16 MiB the one-SM kernel with the in-switch pull (59 against 78 us unfused at
+      M = 512); up to 64 MiB this library's GEMM followed by its in-switch all-reduce (131 us at M = 2048; the fused
+      variants are within 2 %); above that the two-SM kernel reducing in place through the switch with 8 communication
+      CTAs (374 against 393 us unfused at M = 8192)."""
     big = out_bytes > (64 << 20)
     if emulated:
         return "fused", None, None, None
     if world < 4:
         return ("fused", 1, 24, "pair") if big else ("fused", None, 16, "one_sm")
+    if world < 8:
+        return ("fused", 0, 16, "one_sm") if out_bytes <= (16 << 20) else ("fused", 1, 16, "pair")
     if big:
         return "fused", 1, 8, "pair"
     if out_bytes <= (16 << 20):
@@ -444,12 +449,15 @@ class GemmReduceScatterNorm:
 
 
 class AllGatherGemm:
-    """Defaults from the 8-GPU measurements of the 70B FFN shapes: the two-SM kernel, 8 pusher CTAs, whole tiles only
-    (``stream_k=-1``: a stream-K tail makes the last pairs depend on two late chunks instead of one and cost 50 us
-    there; 0 lets the plain-GEMM rule decide, 1 forces the tail)."""
+    """Defaults from the measurements of the 70B FFN shapes: the two-SM kernel, 8 pusher CTAs; the stream-K tail by the
+    plain-GEMM rule up to four ranks (381 against 448 us at tp4) and whole tiles only from eight on (242 against
+    296 us at tp8, where a tail makes the last pairs depend on several late chunks at once).  ``stream_k``: None = that
+    default, 0 = the plain-GEMM rule, 1 = always, -1 = never."""
 
     def __init__(self, comm, M: int, K: int, dtype: torch.dtype, *, comm_ctas: int = 8, max_ctas: int = 0,
-                 use_nvls: Optional[bool] = None, kernel: Optional[str] = None, stream_k: int = -1):
+                 use_nvls: Optional[bool] = None, kernel: Optional[str] = None, stream_k: Optional[int] = None):
+        if stream_k is None:
+            stream_k = 0 if comm.world <= 4 else -1
         self.use_nvls = use_nvls
         self.kernel = _kernel_code(kernel)
         self.stream_k = stream_k

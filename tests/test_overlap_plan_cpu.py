@@ -11,7 +11,9 @@ def test_measured_choices_on_nvswitch():
     assert plan(8, 2048, 8192, False)[0] == "unfused"
     # ... above 64 MiB the two-SM kernel that reduces in place through the switch, 8 communication CTAs
     assert plan(8, 8192, 8192, False) == ("fused", 1, 1, 8, "pair")
-    assert plan(4, 2048, 8192, False)[0] == "unfused" and plan(4, 8192, 8192, False)[0] == "fused"
+    # four ranks: pushed tiles for one partial wave, the two-SM kernel through the switch (16 CTAs) above
+    assert plan(4, 512, 8192, False) == ("fused", 1, 0, 16, "one_sm")
+    assert plan(4, 2048, 8192, False) == ("fused", 1, 1, 16, "pair") and plan(4, 8192, 8192, False)[3:] == (16, "pair")
     # two ranks: always a fused kernel; one or two waves of tiles on the one-SM kernel with pushed tiles, 64 MiB and
     # more on the two-SM kernel that reduces in place through the switch with 24 communication CTAs
     assert plan(2, 512, 8192, False) == ("fused", 1, None, 16, "one_sm")
