@@ -384,6 +384,23 @@ class GemmAllReduce:
         return self.output()
 
 
+def wave_aligned_comm_ctas(M: int, N: int, sms: int = 148, lo: int = 4, hi: int = 24) -> int:
+    """Communication CTAs for a fused op on the two-SM kernel such that the GEMM loses no wave to them: the GEMM runs
+    on ``sms / 2 - c / 2`` CTA pairs and takes ``ceil(tiles / pairs)`` waves of 256 x 256 tiles; among the budgets
+    ``lo .. hi`` (even) that reach the smallest wave count the LARGEST is returned, since those reducers are free.
+    Example: 4096 x 8192 is 512 tiles; 74 .. 65 pairs need 8 waves and so do 64 pairs, so 20 CTAs cost the GEMM nothing."""
+    tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    best, best_waves = lo, None
+    for c in range(lo, hi + 1, 2):
+        pairs = (sms - c) // 2
+        if pairs < 1:
+            break
+        waves = -(-tiles // pairs)
+        if best_waves is None or waves < best_waves or (waves == best_waves and c > best):
+            best, best_waves = c, waves
+    return best
+
+
 class GemmReduceScatterNorm:
     """``weight=None`` gives the plain GEMM->reduce-scatter (+ optional residual add).  Defaults from the 8-GPU
     measurements of the 70B FFN shapes: the two-SM kernel, reduction through the switch, 8 communication CTAs (more

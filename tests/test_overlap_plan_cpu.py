@@ -70,3 +70,15 @@ def test_autotune_candidate_list():
     c2 = cands(2, True, 8192)
     assert ("fused", "pair", 0, 8) in c2 and ("fused", "pair", 1, 8) in c2 and ("fused", "one_sm", 2, 16) not in c2
     assert all(c[2] == 0 for c in cands(4, False, 2048) if c[1] == "pair")
+
+
+def test_wave_aligned_communication_ctas():
+    from ooverlap_b200.ops.overlap import wave_aligned_comm_ctas as f
+    assert f(4096, 8192) == 20          # 512 tiles: 64 pairs still need 8 waves, 63 would need 9
+    assert f(8192, 8192) == 10          # 1024 tiles: 15 waves on 72 .. 69 pairs, 16 from 68 pairs down
+    assert f(512, 8192) == 20           # 64 tiles fit one wave on 64 pairs
+    assert f(256, 256) == 24            # one tile: every budget is free
+    for M, N in ((4096, 8192), (2048, 8192), (4096, 28672)):
+        c = f(M, N)
+        tiles = (M // 256) * (N // 256)
+        assert 4 <= c <= 24 and -(-tiles // ((148 - c) // 2)) == min(-(-tiles // ((148 - k) // 2)) for k in range(4, 25, 2))
