@@ -227,7 +227,11 @@ class GemmAllReduce:
         nvls = bool(getattr(self.comm, "nvls", False))
         world = self.comm.world
         cands = [("unfused", None, None, None)]
-        for c in (4, 8, 16, 24, 32):
+        budgets = [4, 8, 16, 24, 32]
+        aligned = wave_aligned_comm_ctas(self.M, self.N)
+        if aligned not in budgets:
+            budgets = sorted(budgets + [aligned])  # the largest budget that costs the GEMM no extra wave of tiles
+        for c in budgets:
             if nvls:
                 cands.append(("fused", "pair", 1, c))
             if not nvls or world == 2:

@@ -59,12 +59,12 @@ def test_autotune_candidate_list():
     from ooverlap_b200.ops.overlap import GemmAllReduce
 
     def cands(world, nvls, M):
-        op = SimpleNamespace(comm=SimpleNamespace(world=world, nvls=nvls), M=M)
+        op = SimpleNamespace(comm=SimpleNamespace(world=world, nvls=nvls), M=M, N=8192)
         return GemmAllReduce._candidates(op)
 
     c8 = cands(8, True, 8192)
     assert c8[0] == ("unfused", None, None, None)
-    assert [c for c in c8 if c[1] == "pair"] == [("fused", "pair", 1, n) for n in (4, 8, 16, 24, 32)]
+    assert [c for c in c8 if c[1] == "pair"] == [("fused", "pair", 1, n) for n in (4, 8, 10, 16, 24, 32)]  # 10: wave-aligned
     assert ("fused", "one_sm", 0, 16) in c8 and ("fused", "one_sm", 2, 16) in c8 and ("chunked", None, None, None) in c8
     assert ("chunked", None, None, None) not in cands(8, True, 512)
     c2 = cands(2, True, 8192)
