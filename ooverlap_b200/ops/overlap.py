@@ -159,10 +159,15 @@ class GemmAllReduce:
                       is exposed.  For large M from four ranks on;
       * ``"autotune"`` decided at the first call: every fused variant and the unfused pair are checked and timed on the
                       real operands, all ranks agree on the fastest (see ``_autotune``; ``tuning`` holds the table);
-      * ``"auto"``    (default) what measured best on B200 / NVSwitch: between two ranks the fused kernel; from four
-                      ranks on the unfused pair for messages up to 64 MiB (a single wave or few waves of tiles leave
-                      nothing to overlap and the NVLS all-reduce moves the message once per direction) and the fused
-                      kernel with peer pushes above.
+      * ``"auto"``    (default) a tuned solution for the shape when one is packaged or named by
+                      ``OOB_OVERLAP_SOLUTIONS``, else the rule derived from the measurements on B200 / NVSwitch
+                      (``_auto_rule``): small outputs on the one-SM fused kernel, large ones on the two-SM fused kernel
+                      that reduces in place through the switch, and at eight ranks the unfused pair in between.
+
+    ``kernel`` picks the fused kernel: "pair" (two-SM mainloop, 256x256 tiles; the epilogue writes the partial product
+    into this rank's copy of the output, reducers reduce it in place: ``use_nvls`` 1 = through the switch, 0 = peer
+    loads and stores) or "one_sm" (128x256 tiles pushed to their owner rank; ``use_nvls`` 0 = peer pushes + peer
+    broadcast, 1 = multimem broadcast of the result, 2 = tiles stay local and the owner pulls their in-switch sum).
     """
 
     def __init__(self, comm, M: int, N: int, dtype: torch.dtype, *, comm_ctas: Optional[int] = None, max_ctas: int = 0,
