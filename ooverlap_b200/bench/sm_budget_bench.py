@@ -38,11 +38,13 @@ PER_GRAPH = 4
 def _time_pair(main_fn, side_fn, side_stream, reps):
     """Runs side_fn on the side stream and main_fn on the current stream, forked from one event and joined at the end,
     from a CUDA graph.  Returns (us_main, us_side, us_both) per call, max over ranks."""
-    main = torch.cuda.current_stream()
     fork, joined = torch.cuda.Event(), torch.cuda.Event()
     ev = {k: [torch.cuda.Event(enable_timing=True) for _ in range(2)] for k in ("main", "side")}
 
     def body(timed: bool):
+        # The stream that is current NOW: inside torch.cuda.graph(...) that is the capture stream, and only work forked
+        # from it is captured.
+        main = torch.cuda.current_stream()
         fork.record(main)
         if side_fn is not None:
             side_stream.wait_event(fork)
