@@ -259,7 +259,7 @@ class GemmAllReduce:
         cands = self._candidates()
         agreed = []
         ref = None
-        iters = 6
+        iters = 10
         INF = 1 << 60
         def agree(value: int) -> list:
             """Host-side exchange of one value per rank; recovers the communicator on all ranks if any rank's device
