@@ -93,7 +93,7 @@ class OoverlapAllReduce:
         # Ring of result / staging slots.  A slot holds a whole prefill chunk of a hidden-8192 model (8192 tokens x
         # 16 KiB = 128 MiB), so that such an all-reduce is one copy into the slot and one in-place all-reduce instead of
         # sixteen slot-sized pieces; decode-sized messages go through the push kernel and only land in a slot.
-        self.rr_slots = _env_int("VLLM_OOVERLAP_RR_SLOTS", 8)
+        self.rr_slots = _env_int("VLLM_OOVERLAP_RR_SLOTS", 16)
         self.rr_capacity = _env_int("VLLM_OOVERLAP_RR_CAPACITY_BYTES", 128 << 20)
         self.ag_dtype = _env_dtype("VLLM_OOVERLAP_AG_DTYPE", "bf16")
         self.ag_slots = _env_int("VLLM_OOVERLAP_AG_SLOTS", 4)
