@@ -134,6 +134,14 @@ int oob_all_gather(oob_comm* c, int dtype, int algo, int out_reg, uint64_t out_o
  * the heap has a multicast alias.  Moves (world - 1) x the message per rank: for messages up to a few hundred KiB. */
 int oob_allreduce_push(oob_comm* c, int dtype, int op, int stage_reg, uint64_t stage_off, uint64_t piece_bytes,
                        const void* in_local, void* out_local, uint64_t count, int use_nvls, int max_ctas, void* stream);
+/* The lowest-latency all-reduce, for messages of a few KiB to a few tens of KiB: no barrier and no fence.  Every rank
+ * stores its input into its piece of the staging area on all ranks as 8-byte cells {4 data bytes, 4 flag bytes = number
+ * of this call}; receivers spin on the cells and sum them in rank order (fp32) into `out_local`.  The staging area
+ * (stage_reg, stage_off) holds TWO sets of world * piece_bytes bytes, piece_bytes a multiple of 16 and at least 8 bytes
+ * per 32-bit word of the message.  It must be zeroed on every rank before the first call (with a host barrier after
+ * the zeroing) and nothing but this entry point may write to it.  Every rank must make the same sequence of calls. */
+int oob_allreduce_ll(oob_comm* c, int dtype, int op, int stage_reg, uint64_t stage_off, uint64_t piece_bytes,
+                     const void* in_local, void* out_local, uint64_t count, int use_nvls, int max_ctas, void* stream);
 
 /* All-to-all: `src_local` holds `world` chunks of count_per_peer elements; chunk j goes to rank j and lands as
  * chunk (this rank) of its registered output buffer (world * count_per_peer elements).  No counterpart in the

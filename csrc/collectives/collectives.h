@@ -32,6 +32,13 @@ cudaError_t launch_allreduce_push(const CommCtx& ctx, int dtype, int op, bool us
                                   size_t piece_bytes, const void* in_local, size_t in_emu_stride, void* out_local,
                                   size_t out_emu_stride, size_t count, int max_ctas, cudaStream_t stream);
 
+// Flag-in-data all-reduce without a barrier for messages up to a few tens of KiB (allreduce_ll.cu).  The staging area
+// (two sets of world * piece_bytes, piece_bytes >= 8 bytes per 32-bit word of the message) must be zeroed once before
+// its first use and written by this kernel only.
+cudaError_t launch_allreduce_ll(const CommCtx& ctx, int dtype, int op, bool use_mc, const PeerPtrs& staging,
+                                size_t piece_bytes, const void* in_local, size_t in_emu_stride, void* out_local,
+                                size_t out_emu_stride, size_t count, int max_ctas, cudaStream_t stream);
+
 // Rank r's chunk j (chunk_bytes each, `src_local` holds `world` of them) lands as chunk r of rank j's registered
 // `out` buffer (all_to_all.cu).
 cudaError_t launch_all_to_all(const CommCtx& ctx, const PeerPtrs& out, const void* src_local, size_t src_emu_stride,
@@ -56,6 +63,9 @@ enum NormAlgo : int {
 // that have finished.
 constexpr int kPushCallSlot = 0;
 constexpr int kPushDoneSlot = 1;
+// The same pair of words for the flag-in-data all-reduce (allreduce_ll.cu), whose call number is also the flag value.
+constexpr int kLlCallSlot = 2;
+constexpr int kLlDoneSlot = 3;
 
 struct NormArgs {
   int dtype;              // kF16 / kBF16

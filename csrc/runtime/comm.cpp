@@ -898,6 +898,31 @@ int oob_allreduce_push(oob_comm* c, int dtype, int op, int stage_reg, uint64_t s
   return OOB_OK;
 }
 
+int oob_allreduce_ll(oob_comm* c, int dtype, int op, int stage_reg, uint64_t stage_off, uint64_t piece_bytes,
+                     const void* in_local, void* out_local, uint64_t count, int use_nvls, int max_ctas, void* stream) {
+  int rc = check_comm(c);
+  if (rc != OOB_OK) return rc;
+  if (count == 0) return OOB_OK;
+  if (dtype != OOB_F16 && dtype != OOB_BF16 && dtype != OOB_F32) return set_error(OOB_ERR_INVALID, "bad dtype");
+  if (op != OOB_SUM && op != OOB_MIN && op != OOB_MAX) return set_error(OOB_ERR_INVALID, "bad reduction");
+  if (in_local == nullptr || out_local == nullptr) return set_error(OOB_ERR_INVALID, "null input or output");
+  const uint64_t esize = dtype == OOB_F32 ? 4 : 2;
+  const uint64_t words = (count * esize + 3) / 4;
+  if ((piece_bytes & 15) || words * 8 > piece_bytes)
+    return set_error(OOB_ERR_INVALID, "piece_bytes must be a multiple of 16 and hold 8 bytes per 32-bit word of the message");
+  if ((reinterpret_cast<uintptr_t>(in_local) | reinterpret_cast<uintptr_t>(out_local)) & (esize - 1))
+    return set_error(OOB_ERR_INVALID, "input and output must be aligned to their element size");
+  PeerPtrs st;
+  if ((stage_off & 15) || !c->peer_ptrs(stage_reg, stage_off, 2 * piece_bytes * c->world, &st))
+    return set_error(OOB_ERR_INVALID, "bad staging area (16-byte aligned, 2 * world * piece_bytes inside the registration)");
+  const bool mc = use_nvls != 0 && st.mc != nullptr;
+  const uint64_t emu_stride = c->emulated ? count * esize : 0;
+  cudaError_t e = launch_allreduce_ll(c->make_ctx(), dtype, op, mc, st, piece_bytes, in_local, emu_stride, out_local,
+                                      emu_stride, count, max_ctas, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "flag-in-data all-reduce launch");
+  return OOB_OK;
+}
+
 int oob_all_to_all(oob_comm* c, int dtype, int out_reg, uint64_t out_off, const void* src_local, uint64_t count_per_peer,
                    int max_ctas, void* stream) {
   int rc = check_comm(c);

@@ -133,6 +133,7 @@ def _declare(lib) -> None:
     lib.oob_all_gather.argtypes = [P, c_int, c_int, c_int, c_uint64, P, P, c_uint64, c_int, P]
     lib.oob_all_to_all.argtypes = [P, c_int, c_int, c_uint64, P, c_uint64, c_int, P]
     lib.oob_allreduce_push.argtypes = [P, c_int, c_int, c_int, c_uint64, c_uint64, P, P, c_uint64, c_int, c_int, P]
+    lib.oob_allreduce_ll.argtypes = [P, c_int, c_int, c_int, c_uint64, c_uint64, P, P, c_uint64, c_int, c_int, P]
     lib.oob_fused_norm.argtypes = [P, c_int, POINTER(NormArgs), c_int, P]
     lib.oob_gemm.argtypes = [P, POINTER(GemmArgs), P]
     lib.oob_gemm_plan_splits.argtypes = [c_int, c_int, c_int, c_int, c_int]

@@ -87,6 +87,7 @@ class Communicator:
         self._ar_pool: Optional[SlotPool] = None
         self._ag_pool: Optional[SlotPool] = None
         self._push_arena = None  # (heap offset, piece capacity) of the push kernels' staging area
+        self._ll_arena = None    # (heap offset, piece capacity) of the flag-in-data kernel's staging area
         self._counter_next = 0
         if devices is None:
             import torch.distributed as dist
@@ -496,6 +497,15 @@ class Communicator:
             for off in self._ar_pool.offsets:
                 self.free(off)
         self._ar_pool = SlotPool(dtype, int(capacity_bytes), [self.alloc(capacity_bytes) for _ in range(slot_count)])
+        if self._ll_arena is None and self.config.ll_max_bytes > 0 and self.world > 1:
+            # Staging area of the flag-in-data all-reduce: 8 bytes per 32-bit word of the message, two sets of `world`
+            # pieces.  It must read as zero on every rank before any rank stores into it: zero, then meet on the host.
+            piece = (2 * self.config.ll_max_bytes + 255) // 256 * 256
+            off = self.alloc(2 * self.world * piece)
+            self.view(off, (2 * self.world * piece,), torch.uint8).zero_()
+            torch.cuda.synchronize()
+            self.barrier()
+            self._ll_arena = (off, piece)
 
     def init_all_gather_slots(self, dtype: torch.dtype, capacity_bytes: int, slot_count: int) -> None:
         if self._ag_pool is not None:
@@ -571,9 +581,11 @@ class Communicator:
 
     def all_reduce_push(self, x: torch.Tensor, op: str = "sum", *, max_ctas: int = 0,
                         use_nvls: Optional[bool] = None) -> Optional[torch.Tensor]:
-        """One-barrier all-reduce of a small tensor (see ``oob_allreduce_push``): every rank pushes ``x`` into its
-        piece of a staging area on all ranks, the ranks meet once, each sums the pieces locally into the next ring
-        slot, which is returned (valid until the ring wraps).  The staging area belongs to the push kernels alone and
+        """Low-latency all-reduce of a small tensor into the next ring slot, which is returned (valid until the ring
+        wraps).  Up to ``config.ll_max_bytes`` (64 KiB) the flag-in-data kernel (``oob_allreduce_ll``: 8-byte cells of
+        data + call number, receivers spin on the cells, no barrier); above that the one-barrier push kernel
+        (``oob_allreduce_push``): every rank pushes ``x`` into its piece of a staging area on all ranks, the ranks meet
+        once, each sums the pieces locally.  The staging area belongs to the push kernels alone and
         holds two sets of pieces that consecutive calls alternate between (decided on the device), so calls may follow
         one another at once, also as replays of captured CUDA graphs.  None when the push path does not apply: no
         ring, a message above ``config.push_max_bytes``, or one that does not fit a slot."""
@@ -584,8 +596,9 @@ class Communicator:
         piece = (nbytes + 255) // 256 * 256
         if nbytes == 0 or nbytes > self.config.push_max_bytes or piece > pool.capacity_bytes:
             return None
-        stage = self._push_staging(piece)
-        if stage is None:
+        use_ll = self._ll_arena is not None and nbytes <= self.config.ll_max_bytes and 2 * piece <= self._ll_arena[1]
+        stage = None if use_ll else self._push_staging(piece)
+        if stage is None and not use_ll:
             return None
         off = pool.offsets[pool.next_index]
         key = ("push", off, tuple(x.shape), x.dtype)
@@ -596,6 +609,14 @@ class Communicator:
             out = self._view_cache[key] = self.view(off, tuple(x.shape), x.dtype)
         pool.advance()
         nvls = self.nvls if use_nvls is None else (bool(use_nvls) and self.nvls)
+        if use_ll:
+            # A few KiB to a few tens of KiB: cells of 4 data bytes + 4 flag bytes, no barrier (see oob_allreduce_ll).
+            _lib.check(_lib.lib().oob_allreduce_ll(self._h, dtype_code(x.dtype), op_code(op), 0, self._ll_arena[0],
+                                                   self._ll_arena[1], ctypes.c_void_p(x.data_ptr()),
+                                                   ctypes.c_void_p(out.data_ptr()), x.numel(),
+                                                   1 if (use_nvls and self.nvls) else 0,  # peer stores unless asked
+                                                   max_ctas or self.config.max_ctas, ctypes.c_void_p(_current_stream_ptr())))
+            return out
         _lib.check(_lib.lib().oob_allreduce_push(self._h, dtype_code(x.dtype), op_code(op), 0, stage, piece,
                                                  ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()), x.numel(),
                                                  1 if nvls else 0, max_ctas or self.config.max_ctas,

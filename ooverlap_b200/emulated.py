@@ -130,6 +130,16 @@ class EmulatedGroup:
                                                  ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()),
                                                  x.shape[1], 0, max_ctas, _stream()))
 
+    def all_reduce_ll(self, stage_off: int, piece_bytes: int, x: torch.Tensor, out: torch.Tensor, op: str = "sum", *,
+                      max_ctas: int = 4) -> None:
+        """Flag-in-data all-reduce without a barrier: ``x`` and ``out`` are ``[world, count]``; the staging area is two
+        sets of ``world * piece_bytes`` (8 bytes per 32-bit word of a row) at ``stage_off`` of every rank's heap and
+        must be zero before its first use."""
+        assert x.shape[0] == self.world and out.shape == x.shape and x.is_contiguous() and out.is_contiguous()
+        _lib.check(_lib.lib().oob_allreduce_ll(self._h, dtype_code(x.dtype), op_code(op), 0, stage_off, piece_bytes,
+                                               ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+                                               x.shape[1], 0, max_ctas, _stream()))
+
     def reduce_scatter(self, in_off: int, count: int, dtype: torch.dtype, out_local: torch.Tensor, op: str = "sum", *,
                        algo: int = _lib.RS_P2P, max_ctas: int = 4) -> None:
         """``out_local`` is ``[world, ceil(count / world)]``; row r receives rank r's partition."""

@@ -112,6 +112,10 @@ class LocalGroup:
         return self.each(lambda r, c: c.all_to_all(xs[r], None if outs is None else outs[r], **kw))
 
     # ------------------------------------------------------------------ host-side collectives
+    def init_round_robin_slots(self, dtype: torch.dtype, capacity_bytes: int, slot_count: int) -> None:
+        """Slot ring on every rank (the ranks meet on the host while they set it up)."""
+        self._host_collective(lambda r: self.comms[r].init_round_robin_slots(dtype, capacity_bytes, slot_count))
+
     def barrier(self) -> None:
         self._host_collective(lambda r: self.comms[r].barrier())
 

@@ -65,6 +65,7 @@ class Config:
     ar_slot_bytes: int
     ag_slots: int              # OOB_AG_SLOTS, OOB_AG_SLOT_BYTES: all-gather pool
     ag_slot_bytes: int
+    ll_max_bytes: int          # OOB_LL_MAX_BYTES: round-robin all-reduces up to this size take the flag-in-data kernel
     push_max_bytes: int        # OOB_PUSH_MAX_BYTES: round-robin all-reduces up to this size take the one-barrier push
                                # kernel (0 = never)
 
@@ -82,5 +83,6 @@ class Config:
             ar_slot_bytes=_int("OOB_AR_SLOT_BYTES", 8 << 20),
             ag_slots=_int("OOB_AG_SLOTS", 4),
             ag_slot_bytes=_int("OOB_AG_SLOT_BYTES", 64 << 20),
+            ll_max_bytes=_int("OOB_LL_MAX_BYTES", 64 << 10),
             push_max_bytes=_int("OOB_PUSH_MAX_BYTES", 256 << 10),
         )

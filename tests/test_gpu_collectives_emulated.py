@@ -203,3 +203,30 @@ def test_all_reduce_push_one_barrier(group, n, dtype, op):
             assert torch.equal(out[r], out[0])
     for s in reversed(stages):
         group.free(s)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("n", [1, 2, 7, 8, 4096, 4097, 32768])
+@pytest.mark.parametrize("op", ["sum", "max"])
+def test_all_reduce_flag_in_data(group, n, dtype, op):
+    """No barrier: every rank stores 8-byte cells of data + call number into its piece on all ranks, receivers spin on
+    the cells.  The same zeroed staging area serves six calls in a row (two sets of cells, alternated by the call
+    counter on the device); odd counts leave half a word at the end."""
+    esize = torch.empty((), dtype=dtype).element_size()
+    words = (n * esize + 3) // 4
+    piece = (8 * words + 255) // 256 * 256
+    stage = group.alloc(2 * group.world * piece)
+    for r in range(group.world):
+        group.view(stage, (2 * group.world * piece,), torch.uint8, r).zero_()
+    torch.cuda.synchronize()
+    for it in range(6):
+        gen = torch.Generator(device="cuda").manual_seed(n * 10 + it)
+        x = (torch.rand(group.world, n, device="cuda", generator=gen) * 2 - 1).to(dtype)
+        out = torch.zeros_like(x)
+        group.all_reduce_ll(stage, piece, x, out, op, max_ctas=3 if it % 2 else 1)
+        group.check_status()
+        want = _reduce(list(x), op)
+        for r in range(group.world):
+            assert (out[r].float() - want).abs().max().item() <= TOL[dtype] * group.world, (it, r)
+            assert torch.equal(out[r], out[0])
+    group.free(stage)
