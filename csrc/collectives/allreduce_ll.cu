@@ -293,9 +293,11 @@ cudaError_t launch_allreduce_ll(const CommCtx& ctx, int dtype, int op, bool use_
   const size_t words = (count * esize + 3) / 4;
   if (words * 8 > piece_bytes) return cudaErrorInvalidValue;
   if (use_mc && staging.mc == nullptr) return cudaErrorInvalidValue;
-  size_t need = (words + 4 * kLlThreads - 1) / (4 * kLlThreads);  // about four words per thread
+  // One word per thread while the CTAs last: a thread's words are polled one after the other, and at these sizes the
+  // polls, not the bytes, are the cost (2-GPU measurement: 16 KiB on 2 CTAs 8.6 us, 1 KiB on one CTA 6.2 us).
+  size_t need = (words + kLlThreads - 1) / kLlThreads;
   if (need < 1) need = 1;
-  int ctas = max_ctas < 1 ? 8 : max_ctas;
+  int ctas = max_ctas < 1 ? 16 : max_ctas;
   if (ctas > kMaxCommBlocks) ctas = kMaxCommBlocks;
   if (static_cast<size_t>(ctas) > need) ctas = static_cast<int>(need);
   const char* in = static_cast<const char*>(in_local);
