@@ -90,11 +90,13 @@ class OoverlapAllReduce:
         self.group = group
         self.debug = os.environ.get("VLLM_OOVERLAP_DEBUG", "0") not in ("", "0")
         self.rr_dtype = _env_dtype("VLLM_OOVERLAP_RR_DTYPE", "bf16")
-        # Ring of result / staging slots.  A slot holds a whole prefill chunk of a hidden-8192 model (8192 tokens x
-        # 16 KiB = 128 MiB), so that such an all-reduce is one copy into the slot and one in-place all-reduce instead of
-        # sixteen slot-sized pieces; decode-sized messages go through the push kernel and only land in a slot.
-        self.rr_slots = _env_int("VLLM_OOVERLAP_RR_SLOTS", 16)
-        self.rr_capacity = _env_int("VLLM_OOVERLAP_RR_CAPACITY_BYTES", 128 << 20)
+        # Ring of result / staging slots.  A slot holds a whole prefill chunk of a hidden-8192 model (16384 tokens x
+        # 16 KiB = 256 MiB), so that such an all-reduce is one copy into the slot and one in-place all-reduce whose
+        # result is handed out as it lies in the slot; with 128 MiB slots the TP4 engine run reduced every prefill chunk
+        # in two pieces with two extra copies out.  Decode-sized messages go through the flag-in-data / push kernels
+        # and only land in a slot.
+        self.rr_slots = _env_int("VLLM_OOVERLAP_RR_SLOTS", 8)
+        self.rr_capacity = _env_int("VLLM_OOVERLAP_RR_CAPACITY_BYTES", 256 << 20)
         self.ag_dtype = _env_dtype("VLLM_OOVERLAP_AG_DTYPE", "bf16")
         self.ag_slots = _env_int("VLLM_OOVERLAP_AG_SLOTS", 4)
         self.ag_capacity = _env_int("VLLM_OOVERLAP_AG_CAPACITY_BYTES", 64 << 20)
