@@ -49,7 +49,9 @@ typedef enum {
   OOB_NORM_RS = 4,
   OOB_NORM_RS_NVLS = 5,
   OOB_NORM_AR_PUSH = 6,      /* decode sizes: push + one barrier + local sum and norm of every row; needs stage_* */
-  OOB_NORM_AR_PUSH_NVLS = 7
+  OOB_NORM_AR_PUSH_NVLS = 7,
+  OOB_NORM_AR_LL = 8         /* the smallest messages: 8-byte cells of data + call number, no barrier; stage_* names the
+                                zeroed staging area of oob_allreduce_ll, piece_bytes >= 2 x the message */
 } oob_norm_algo_t;
 typedef enum { OOB_GEMM_PLAIN = 0, OOB_GEMM_AR = 1, OOB_GEMM_RS_NORM = 2, OOB_GEMM_AG = 3 } oob_gemm_mode_t;
 

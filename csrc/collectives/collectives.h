@@ -56,6 +56,8 @@ enum NormAlgo : int {
   kNormArPush = 6,        // decode sizes: every rank pushes its rows to all ranks, ONE rank barrier, every rank sums the
                           // pieces locally and normalises every row (staging area as for the push all-reduce)
   kNormArPushNvls = 7,    // same, pushed with multimem.st
+  kNormArLl = 8,          // the smallest messages: rows travel as 8-byte cells of data + call number, no barrier at all
+                          // (staging area, cell format and call counter of allreduce_ll.cu)
 };
 
 // Call-epoch words of the signal pad shared by the push kernels (allreduce_push.cu, fused_norm.cu): the number of push

@@ -301,6 +301,155 @@ __global__ void __launch_bounds__(kNormThreads) push_norm_kernel(CommCtx ctx_par
   }
 }
 
+// The same op without any barrier, for the smallest messages (a few rows): the rows travel as 8-byte cells of 4 data
+// bytes + the call number (the cell format, staging area and call counter of allreduce_ll.cu), and every rank spins
+// on the cells of its peers before it sums and normalises.  Block b of every rank owns rows b, b + G, ...
+template <typename T, int PPT, int NR>
+__global__ void __launch_bounds__(kNormThreads) ll_norm_kernel(CommCtx ctx_param, NormArgs a) {
+  const CommCtx ctx = resolve_ctx(ctx_param);
+  const int world = ctx.world, rank = ctx.rank;
+  using PT = PackTraits<T>;
+  constexpr int E = 8;
+  const int packs_per_row = a.hidden / E;
+  const size_t row_bytes = size_t(a.hidden) * sizeof(T);
+
+  __shared__ uint32_t s_seq;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    s_seq = ptx::ld_relaxed_sys(call_epoch_ptr(ctx, kLlCallSlot));
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint32_t flag = s_seq + 1u;
+  const size_t set_off = size_t(s_seq & 1u) * size_t(world) * a.piece_bytes;
+  const size_t my_piece = set_off + size_t(rank) * a.piece_bytes;
+
+  const char* x = static_cast<const char*>(a.x.p[rank]);
+  const char* res = a.residual ? static_cast<const char*>(a.residual) + a.residual_emu_stride * blockIdx.y : nullptr;
+  char* y_local = static_cast<char*>(a.y_local) + a.y_local_emu_stride * blockIdx.y;
+  char* ro_local =
+      a.res_out_local ? static_cast<char*>(a.res_out_local) + a.res_out_local_emu_stride * blockIdx.y : nullptr;
+
+  // ---- store this block's rows as cells into piece `rank` of every other rank (a pack of 16 bytes = four cells) ----
+  for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
+    const size_t off = size_t(row) * row_bytes;
+#pragma unroll
+    for (int j = 0; j < PPT; ++j) {
+      const int p = threadIdx.x + j * kNormThreads;
+      if (p < packs_per_row) {
+        const uint4 v = *reinterpret_cast<const uint4*>(x + off + size_t(p) * 16);
+        const size_t cell0 = my_piece + 2 * (off + size_t(p) * 16);  // 8 bytes of cell per 4 bytes of data
+        for (int r = 1; r < world; ++r) {
+          char* dst = static_cast<char*>(a.staging.p[(rank + r) % world]) + cell0;
+          asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(v.x), "r"(flag) : "memory");
+          asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + 8), "r"(v.y), "r"(flag) : "memory");
+          asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + 16), "r"(v.z), "r"(flag) : "memory");
+          asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst + 24), "r"(v.w), "r"(flag) : "memory");
+        }
+      }
+    }
+  }
+
+  float w[PPT][E];
+#pragma unroll
+  for (int j = 0; j < PPT; ++j) {
+    const int p = threadIdx.x + j * kNormThreads;
+    if (p < packs_per_row)
+      PT::unpack(*reinterpret_cast<const uint4*>(static_cast<const char*>(a.weight) + size_t(p) * 16), w[j]);
+  }
+
+  // ---- spin on the peers' cells of this block's rows, sum in rank order, add the residual, normalise --------------
+  const char* mine = static_cast<const char*>(a.staging.p[rank]) + set_off;
+  const uint64_t t0 = ptx::globaltimer_ns();
+  bool ok = true;
+  for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
+    const size_t off = size_t(row) * row_bytes;
+    float v[PPT][E];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PPT; ++j) {
+      const int p = threadIdx.x + j * kNormThreads;
+      if (p < packs_per_row) {
+        const size_t po = off + size_t(p) * 16;
+#pragma unroll
+        for (int i = 0; i < E; ++i) v[j][i] = 0.f;
+        for (int r = 0; r < world; ++r) {
+          uint4 raw;
+          if (r == rank) {
+            raw = *reinterpret_cast<const uint4*>(x + po);  // the own contribution never travels
+          } else {
+            const char* cell = mine + size_t(r) * a.piece_bytes + 2 * po;
+            uint4 c0, c1;  // two 16-byte loads = four cells {d, f, d, f}
+            uint32_t spins = 0;
+            while (true) {
+              c0 = ptx::ld_relaxed_sys_v4(cell);
+              c1 = ptx::ld_relaxed_sys_v4(cell + 16);
+              if (c0.y == flag && c0.w == flag && c1.y == flag && c1.w == flag) break;
+              if (++spins > 32) __nanosleep(20);
+              if ((spins & 255u) == 0u) {
+                if (ptx::globaltimer_ns() - t0 > ctx.timeout_ns) {
+                  report_error(ctx, kDevTimeoutCounter, r, flag, c0.y, 45);
+                  ok = false;
+                  break;
+                }
+                if (*reinterpret_cast<volatile uint32_t*>(ctx.pad[rank] + kPadErrorFlagOffset) != 0) {
+                  ok = false;
+                  break;
+                }
+              }
+            }
+            if (!ok) break;
+            raw = make_uint4(c0.x, c0.z, c1.x, c1.z);
+          }
+          float f[E];
+          PT::unpack(raw, f);
+#pragma unroll
+          for (int i = 0; i < E; ++i) v[j][i] += f[i];
+        }
+        if (ok && res != nullptr) {
+          float rf[E];
+          PT::unpack(ptx::ld_nc_v4(res + po), rf);
+#pragma unroll
+          for (int i = 0; i < E; ++i) v[j][i] += rf[i];
+        }
+        const uint4 ro = PT::pack(v[j]);
+        if (ro_local != nullptr) {
+          PT::unpack(ro, v[j]);
+          if (ok) ptx::st_v4(ro_local + po, ro);
+        } else if (res != nullptr) {
+          PT::unpack(ro, v[j]);
+        }
+#pragma unroll
+        for (int i = 0; i < E; ++i) ss += v[j][i] * v[j][i];
+      }
+    }
+    // Every thread reaches the block-wide sum, also after a timeout (the row is then not written).
+    const float total = block_sum(ss);
+    const float scale = rsqrtf(total / float(a.hidden) + a.eps);
+#pragma unroll
+    for (int j = 0; j < PPT; ++j) {
+      const int p = threadIdx.x + j * kNormThreads;
+      if (p < packs_per_row && ok) {
+        float o[E];
+#pragma unroll
+        for (int i = 0; i < E; ++i) o[i] = v[j][i] * scale * w[j][i];
+        ptx::st_v4(y_local + off + size_t(p) * 16, PT::pack(o));
+      }
+    }
+  }
+  if (!ok) s_ok = 0;
+  __syncthreads();
+  if (!s_ok) return;  // the call counter stays: recover() zeroes it together with the peers'
+  if (threadIdx.x == 0) {
+    uint32_t* ticket = call_epoch_ptr(ctx, kLlDoneSlot);
+    if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+      *ticket = 0;
+      atomicAdd(call_epoch_ptr(ctx, kLlCallSlot), 1u);
+      __threadfence();
+    }
+  }
+}
+
 template <typename K>
 cudaError_t launch_k(K kernel, const CommCtx& ctx, int ctas, const NormArgs& a, cudaStream_t stream) {
   if (ctx.emu_table != nullptr) {
@@ -333,6 +482,8 @@ cudaError_t dispatch_algo(int algo, const CommCtx& ctx, int ctas, const NormArgs
       return launch_k(push_norm_kernel<T, PPT, NR, false>, ctx, ctas, a, stream);
     case kNormArPushNvls:
       return launch_k(push_norm_kernel<T, PPT, NR, true>, ctx, ctas, a, stream);
+    case kNormArLl:
+      return launch_k(ll_norm_kernel<T, PPT, NR>, ctx, ctas, a, stream);
   }
   return cudaErrorInvalidValue;
 }
@@ -370,8 +521,9 @@ cudaError_t launch_fused_norm(const CommCtx& ctx, int algo, const NormArgs& a, i
   const bool mc = (algo == kNormArTwoShotNvls || algo == kNormRsNvls);
   if (mc && a.x.mc == nullptr) return cudaErrorInvalidValue;
   if (algo == kNormArTwoShotNvls && a.y.mc == nullptr) return cudaErrorInvalidValue;
-  const bool push = (algo == kNormArPush || algo == kNormArPushNvls);
-  if (push && (a.y_local == nullptr || a.piece_bytes < size_t(a.rows) * a.hidden * 2 || (a.piece_bytes & 15) ||
+  const bool push = (algo == kNormArPush || algo == kNormArPushNvls || algo == kNormArLl);
+  if (push && (a.y_local == nullptr ||
+               a.piece_bytes < size_t(a.rows) * a.hidden * 2 * (algo == kNormArLl ? 2 : 1) || (a.piece_bytes & 15) ||
                a.staging.p[ctx.rank] == nullptr || (algo == kNormArPushNvls && a.staging.mc == nullptr)))
     return cudaErrorInvalidValue;
   int rows = a.rows;

@@ -995,8 +995,8 @@ int oob_fused_norm(oob_comm* c, int algo, const oob_norm_args_t* a, int max_ctas
     n.res_out_local = a->res_out_local;
     n.res_out_local_emu_stride = c->emulated ? a->emu_stride_local : 0;
   }
-  if (algo == OOB_NORM_AR_PUSH || algo == OOB_NORM_AR_PUSH_NVLS) {
-    if ((a->piece_bytes & 15) || a->piece_bytes < norm_bytes || (a->stage_off & 15) ||
+  if (algo == OOB_NORM_AR_PUSH || algo == OOB_NORM_AR_PUSH_NVLS || algo == OOB_NORM_AR_LL) {
+    if ((a->piece_bytes & 15) || a->piece_bytes < norm_bytes * (algo == OOB_NORM_AR_LL ? 2 : 1) || (a->stage_off & 15) ||
         !c->peer_ptrs(a->stage_reg, a->stage_off, 2 * a->piece_bytes * c->world, &n.staging))
       return set_error(OOB_ERR_INVALID,
                        "bad staging area (16-byte aligned, piece_bytes >= the message, 2 * world * piece_bytes registered)");

@@ -33,7 +33,7 @@ AR_ONESHOT_P2P, AR_TWOSHOT_P2P, AR_TWOSHOT_NVLS, AR_ONESHOT_NVLS = 0, 1, 2, 3
 RS_P2P, RS_NVLS = 0, 1
 AG_PUSH_P2P, AG_PUSH_NVLS, AG_PULL_P2P = 0, 1, 2
 NORM_LOCAL, NORM_AR_ONESHOT, NORM_AR_TWOSHOT, NORM_AR_TWOSHOT_NVLS, NORM_RS, NORM_RS_NVLS = range(6)
-NORM_AR_PUSH, NORM_AR_PUSH_NVLS = 6, 7
+NORM_AR_PUSH, NORM_AR_PUSH_NVLS, NORM_AR_LL = 6, 7, 8
 GEMM_PLAIN, GEMM_AR, GEMM_RS_NORM, GEMM_AG = range(4)
 EPILOGUE_NONE, EPILOGUE_SWIGLU, EPILOGUE_ROPE_KV = range(3)
 FLAG_NO_NVLS, FLAG_LEGACY_IPC = 1, 2

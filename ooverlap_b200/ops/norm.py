@@ -58,8 +58,10 @@ def fused_allreduce_rmsnorm(comm, x: torch.Tensor, weight: torch.Tensor, eps: fl
     """``y = rmsnorm(all_reduce(x) + residual) * weight`` in one kernel.
 
     ``x`` ([rows, hidden], registered memory) holds this rank's partial sums.
-    Decode-sized messages (up to ``config.push_max_bytes``) take the push kernel (every rank pushes its rows to all
-    ranks, the ranks meet once, every rank sums and normalises every row locally); larger ones the two-shot fused
+    A few rows (up to ``config.ll_max_bytes``, when the communicator has a slot ring) travel as 8-byte cells of data +
+    call number and need no barrier at all; decode-sized messages up to ``config.push_max_bytes`` take the push kernel
+    (every rank pushes its rows to all ranks, the ranks meet once, every rank sums and normalises every row locally);
+    larger ones the two-shot fused
     kernel (rank r reduces and normalises its rows and broadcasts them), through NVLS when the communicator has it;
     fewer rows than ranks the one-shot fused kernel.  ``algo`` forces one of the fused kernels.  Returns ``(y, new_residual)``; with
     the two-shot forms both live in registered memory."""
@@ -75,7 +77,11 @@ def fused_allreduce_rmsnorm(comm, x: torch.Tensor, weight: torch.Tensor, eps: fl
         # Decode-sized messages: every rank pushes its rows to all ranks, one barrier, every rank sums and normalises
         # every row locally (measured on 8 x B200 at 16 - 256 KiB: the one-shot fused kernel, whose single CTA per row
         # pulls every peer's copy between two barriers, took 34 - 40 us; push all-reduce + local norm 19 - 22 us).
-        if (not getattr(comm, "emulated", False) and nbytes <= comm.config.push_max_bytes
+        ll = getattr(comm, "_ll_arena", None)
+        if (not getattr(comm, "emulated", False) and ll is not None and nbytes <= comm.config.ll_max_bytes
+                and 2 * piece <= ll[1]):
+            algo = _lib.NORM_AR_LL  # a few rows: cells of data + call number, no barrier at all
+        elif (not getattr(comm, "emulated", False) and nbytes <= comm.config.push_max_bytes
                 and comm._push_staging(piece) is not None):
             algo = _lib.NORM_AR_PUSH_NVLS if comm.nvls else _lib.NORM_AR_PUSH
         elif rows < comm.world:
@@ -88,11 +94,16 @@ def fused_allreduce_rmsnorm(comm, x: torch.Tensor, weight: torch.Tensor, eps: fl
     a.residual = residual.data_ptr() if residual is not None else None
     a.weight = weight.data_ptr()
     a.res_out_reg = -1
-    if algo in (_lib.NORM_AR_ONESHOT, _lib.NORM_AR_PUSH, _lib.NORM_AR_PUSH_NVLS):
+    if algo in (_lib.NORM_AR_ONESHOT, _lib.NORM_AR_PUSH, _lib.NORM_AR_PUSH_NVLS, _lib.NORM_AR_LL):
         y = out if out is not None else torch.empty_like(x)
         ro = residual_out if residual_out is not None else torch.empty_like(x)
         a.y_local, a.res_out_local = y.data_ptr(), ro.data_ptr()
-        if algo != _lib.NORM_AR_ONESHOT:
+        if algo == _lib.NORM_AR_LL:
+            ll = getattr(comm, "_ll_arena", None)
+            if ll is None or 2 * piece > ll[1]:
+                raise ValueError("no flag-in-data staging area of that size (init_round_robin_slots, config.ll_max_bytes)")
+            a.stage_reg, a.stage_off, a.piece_bytes = 0, ll[0], ll[1]
+        elif algo != _lib.NORM_AR_ONESHOT:
             stage = comm._push_staging(piece)
             if stage is None:
                 raise ValueError("message too large for the staging area of the push kernels (config.push_max_bytes)")

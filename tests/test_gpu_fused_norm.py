@@ -33,7 +33,7 @@ def test_local_rmsnorm(shape, dtype):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("algo", [_lib.NORM_AR_ONESHOT, _lib.NORM_AR_TWOSHOT, _lib.NORM_AR_PUSH])
+@pytest.mark.parametrize("algo", [_lib.NORM_AR_ONESHOT, _lib.NORM_AR_TWOSHOT, _lib.NORM_AR_PUSH, _lib.NORM_AR_LL])
 @pytest.mark.parametrize("rows", [1, 5, 64])
 def test_allreduce_residual_rmsnorm(world, algo, rows):
     from ooverlap_b200 import EmulatedGroup
@@ -50,12 +50,16 @@ def test_allreduce_residual_rmsnorm(world, algo, rows):
     residual = residual1.unsqueeze(0).repeat(world, 1, 1).contiguous()  # replicated on every rank
     w = (1 + 0.02 * torch.randn(hidden, device="cuda")).to(dtype)
     want_y, want_s = _oracle(xs, residual1, w, eps, dtype)
-    if algo in (_lib.NORM_AR_ONESHOT, _lib.NORM_AR_PUSH):
+    if algo in (_lib.NORM_AR_ONESHOT, _lib.NORM_AR_PUSH, _lib.NORM_AR_LL):
         y = torch.zeros(world, rows, hidden, device="cuda", dtype=dtype)
         ro = torch.zeros_like(y)
-        piece = (nbytes + 255) // 256 * 256
-        stage = g.alloc(2 * world * piece) if algo == _lib.NORM_AR_PUSH else None
-        for _ in range(3 if algo == _lib.NORM_AR_PUSH else 1):  # the push kernel alternates between its two sets of pieces
+        piece = (nbytes + 255) // 256 * 256 * (2 if algo == _lib.NORM_AR_LL else 1)  # cells: 8 bytes per 4 of data
+        stage = g.alloc(2 * world * piece) if algo != _lib.NORM_AR_ONESHOT else None
+        if algo == _lib.NORM_AR_LL:  # the flag-in-data staging area must read as zero before its first use
+            for r in range(world):
+                g.view(stage, (2 * world * piece,), torch.uint8, r).zero_()
+            torch.cuda.synchronize()
+        for _ in range(1 if algo == _lib.NORM_AR_ONESHOT else 3):  # the push kernels alternate between two sets of pieces
             g.fused_norm(algo, x_off=x_off, rows=rows, hidden=hidden, dtype=dtype, weight=w, eps=eps, residual=residual,
                          y_local=y, res_out_local=ro, local_stride_bytes=nbytes, stage_off=stage, piece_bytes=piece)
             g.check_status()
