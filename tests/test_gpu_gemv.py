@@ -1,16 +1,9 @@
 """CUDA-core streaming GEMM for one to four rows against a plain PyTorch fp32 reference and against the
-tensor-core path.
-
-Written after the last hardware run of this build: the module only runs with OOB_RUN_UNVALIDATED=1 until it has
-passed on a GPU once."""
-import os
-
+tensor-core path."""
 import pytest
 import torch
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("OOB_RUN_UNVALIDATED", "0") in ("", "0"),
-                                 reason="not yet run on hardware; set OOB_RUN_UNVALIDATED=1")]
+pytestmark = [pytest.mark.gpu]
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
