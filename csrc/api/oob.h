@@ -141,7 +141,8 @@ int oob_allreduce_push(oob_comm* c, int dtype, int op, int stage_reg, uint64_t s
  * of this call}; receivers spin on the cells and sum them in rank order (fp32) into `out_local`.  The staging area
  * (stage_reg, stage_off) holds TWO sets of world * piece_bytes bytes, piece_bytes a multiple of 16 and at least 8 bytes
  * per 32-bit word of the message.  It must be zeroed on every rank before the first call (with a host barrier after
- * the zeroing) and nothing but this entry point may write to it.  Every rank must make the same sequence of calls. */
+ * the zeroing) and again before oob_comm_recover (which restarts the call numbers), and nothing but this entry point
+ * may write to it.  Every rank must make the same sequence of calls. */
 int oob_allreduce_ll(oob_comm* c, int dtype, int op, int stage_reg, uint64_t stage_off, uint64_t piece_bytes,
                      const void* in_local, void* out_local, uint64_t count, int use_nvls, int max_ctas, void* stream);
 

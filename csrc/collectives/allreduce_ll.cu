@@ -8,7 +8,9 @@
 // sets (call counter on the device, so CUDA-graph replays alternate too).  A rank that has finished call k + 1 has seen
 // every peer's cells of call k + 1, so every peer has started call k + 1 and therefore finished reading call k: the
 // set of call k is free for call k + 2 without any barrier.  Flags only grow, and nothing else ever writes to the
-// area (it is zeroed once, when it is allocated), so a cell can never show the flag of a call that has not written it.
+// area (it is zeroed when it is allocated and whenever the call counter is reset), so a cell can never show the flag
+// of a call that has not written it.  The 32-bit call number wraps after 2^32 calls; a cell can then alias only if
+// it has not been written for a whole period and its first writer afterwards happens to carry exactly the old number.
 //
 // Cost: twice the bytes of the message per peer, which is why this is for messages of a few KiB to 64 KiB; above
 // that the push kernel with one barrier (allreduce_push.cu) moves the plain bytes.

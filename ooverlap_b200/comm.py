@@ -292,7 +292,20 @@ class Communicator:
             _lib.check(_lib.lib().oob_comm_status(self._h, None))
 
     def recover(self) -> None:
-        """Collective: clears flags and status on every rank after a device timeout."""
+        """Collective: clears flags and status on every rank after a device timeout.
+
+        The call numbers of the flag-in-data all-reduce start again from zero, so its cells are zeroed too: a cell
+        left over from before the recovery could otherwise show the number of a later call that has not written it
+        yet.  The ranks meet on the host first (no kernel of any rank still stores into this rank's cells) and again
+        inside the native call (no rank launches before every rank's cells are zero)."""
+        if self._h is None:
+            return
+        if self._ll_arena is not None:
+            torch.cuda.synchronize()
+            self.barrier()
+            off, piece = self._ll_arena
+            self.view(off, (2 * self.world * piece,), torch.uint8).zero_()
+            torch.cuda.synchronize()
         _lib.check(_lib.lib().oob_comm_recover(self._h))
 
     def set_timeout_ms(self, ms: int) -> None:

@@ -134,7 +134,7 @@ class EmulatedGroup:
                       max_ctas: int = 4) -> None:
         """Flag-in-data all-reduce without a barrier: ``x`` and ``out`` are ``[world, count]``; the staging area is two
         sets of ``world * piece_bytes`` (8 bytes per 32-bit word of a row) at ``stage_off`` of every rank's heap and
-        must be zero before its first use."""
+        must be zero before its first use and again after ``recover()`` (the call numbers restart from zero)."""
         assert x.shape[0] == self.world and out.shape == x.shape and x.is_contiguous() and out.is_contiguous()
         _lib.check(_lib.lib().oob_allreduce_ll(self._h, dtype_code(x.dtype), op_code(op), 0, stage_off, piece_bytes,
                                                ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()),

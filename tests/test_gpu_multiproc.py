@@ -315,6 +315,46 @@ def test_absent_peer_is_detected_and_recovered():
             assert detected is not None and f"peer {world - 1}" in detected
 
 
+def _rank_recover_then_flag_in_data(rank, world, key):
+    """recover() restarts the call numbers of the flag-in-data all-reduce, so it has to zero the cells as well: the
+    third call before the recovery is a long message, the third call after it too, and the two calls in between are
+    short, so without the zeroing the long one would find its own number in cells that nobody has written since."""
+    import os
+    os.environ["OOB_DISABLE_NVLS"] = "1"
+    from ooverlap_b200 import Communicator
+    torch.cuda.set_device(rank)
+    comm = Communicator(list(range(world)), rank, key, heap_bytes=64 << 20)
+    comm.init_round_robin_slots(torch.bfloat16, 1 << 20, 4)
+    results = []
+
+    def calls(scale):
+        for n in (256, 256, 16384):
+            x = torch.full((n,), scale * (rank + 1), device="cuda", dtype=torch.bfloat16)
+            got = comm.all_reduce_push(x)
+            torch.cuda.synchronize()
+            results.append(bool((got.float() == scale * world * (world + 1) / 2).all().item()))
+
+    calls(1.0)
+    comm.check_status()
+    comm.recover()
+    calls(2.0)
+    comm.check_status()
+    comm.barrier()
+    comm.close()
+    return results
+
+
+@needs_multi
+def test_recover_zeroes_the_flag_in_data_cells():
+    world = min(_world(), 4)
+    res = run_ranks(_rank_recover_then_flag_in_data, world, ("mr_" + uuid.uuid4().hex[:10],), timeout=300)
+    assert len(res) == world, res
+    for r in range(world):
+        kind, val = res[r]
+        assert kind == "ok", val
+        assert all(val), val
+
+
 def _rank_llama(rank, world, key, port, cfg_name="TINY"):
     import os
     import torch.distributed as dist

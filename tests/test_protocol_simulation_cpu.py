@@ -14,6 +14,9 @@ role; every ``yield`` is a point where any other role may run) and executed unde
                               (csrc/gemm/gemm_pair.cu: signal warp, draw_ticket_warp, pair_ar_reducer)
 * push all-reduce             one barrier per call; two sets of pieces selected by a call counter that the last block
                               of a call bumps; ranks run ahead into later calls (csrc/collectives/allreduce_push.cu)
+* flag-in-data all-reduce     no barrier: 8-byte cells of data + call number, two sets, message lengths that differ
+                              from call to call, and the restart of the call numbers by recover()
+                              (csrc/collectives/allreduce_ll.cu)
 * last-arriver split-K sum    per-quadrant arrival counter re-armed by the CTA that completes it
                               (csrc/gemm/gemm_kernel.cuh, csrc/gemm/gemm_skinny.cu)
 
@@ -455,3 +458,90 @@ def test_push_all_reduce_with_one_set_is_caught():
     """With a single set of pieces a rank that runs ahead overwrites a piece its peer has not summed yet."""
     with pytest.raises(AssertionError):
         _run_push(2, 1, sets=1, calls=4, seeds=200)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# flag-in-data all-reduce: NO barrier; 8-byte cells {data, call number}; two sets of cells selected by the call counter;
+# message lengths differ from call to call; recover() restarts the call numbers
+# (csrc/collectives/allreduce_ll.cu, ll_norm_kernel in csrc/collectives/fused_norm.cu, Communicator.recover)
+# ---------------------------------------------------------------------------------------------------------------------
+class CellState:
+    def __init__(self, world, words, sets):
+        self.world, self.words, self.sets = world, words, sets
+        self.calls = [0] * world
+        # cells[rank][set][source][word] = (data, flag); data is the (era, call) that stored it
+        self.cells = [[[[(None, 0)] * words for _ in range(world)] for _ in range(sets)] for _ in range(world)]
+        self.done = [dict() for _ in range(world)]   # (era, call) -> True once the rank's kernel of that call has ended
+
+    def restart(self, zero_cells):
+        """What recover() does between two host barriers (no kernel of any rank is running)."""
+        self.calls = [0] * self.world
+        if zero_cells:
+            for per_rank in self.cells:
+                for per_set in per_rank:
+                    for src in range(self.world):
+                        per_set[src] = [(None, 0)] * self.words
+
+
+def cell_kernel(st, rank, era, call, length, prev):
+    """One single-block kernel of call `call` (of `length` words) on `rank`; `prev` is the rank's previous kernel."""
+    while prev is not None and not st.done[rank].get(prev):
+        yield "blocked"
+    seq = st.calls[rank]
+    flag, s = seq + 1, seq % st.sets
+    yield
+    for w in range(length):                       # store the words, flag attached, into piece `rank` of every peer
+        for peer in range(st.world):
+            if peer != rank:
+                st.cells[peer][s][rank][w] = ((era, call), flag)
+                yield
+    for w in range(length):                       # poll the peers' cells of the same words
+        for src in range(st.world):
+            if src == rank:
+                continue
+            while st.cells[rank][s][src][w][1] != flag:
+                yield "blocked"
+            data = st.cells[rank][s][src][w][0]
+            assert data == (era, call), (rank, src, w, "wanted", (era, call), "summed", data)
+            yield
+    st.calls[rank] = seq + 1
+    st.done[rank][(era, call)] = True
+    yield
+
+
+def _run_cells(world, sets, lengths_by_era, zero_on_restart, seeds):
+    words = max(max(ls) for ls in lengths_by_era)
+    for seed in range(seeds):
+        rng = random.Random(seed * 32452843 + world)
+        st = CellState(world, words, sets)
+        for era, lengths in enumerate(lengths_by_era):
+            if era > 0:
+                st.restart(zero_on_restart)
+            roles = []
+            for r in range(world):
+                prev = None
+                for c, n in enumerate(lengths):
+                    roles.append(cell_kernel(st, r, era, c, n, prev))
+                    prev = (era, c)
+            run_schedule(roles, rng, max_steps=2000000)
+            assert st.calls == [len(lengths)] * world
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_flag_in_data_cells_need_no_barrier_with_two_sets(world):
+    _run_cells(world, sets=2, lengths_by_era=[[3, 1, 4, 2, 4, 1, 3]], zero_on_restart=True, seeds=120)
+
+
+def test_flag_in_data_cells_with_one_set_are_caught():
+    """With one set a rank that runs ahead overwrites cells of the call its peer is still summing."""
+    with pytest.raises(AssertionError):
+        _run_cells(2, sets=1, lengths_by_era=[[2, 2, 2, 2]], zero_on_restart=True, seeds=300)
+
+
+def test_restarting_the_call_numbers_needs_zeroed_cells():
+    """After the call numbers restart, a long message whose number matches one from before finds stale cells unless
+    the cells were zeroed; with the zeroing the same sequence is clean."""
+    eras = [[1, 1, 4], [1, 1, 4]]
+    _run_cells(2, sets=2, lengths_by_era=eras, zero_on_restart=True, seeds=100)
+    with pytest.raises(AssertionError):
+        _run_cells(2, sets=2, lengths_by_era=eras, zero_on_restart=False, seeds=100)
