@@ -600,7 +600,8 @@ class Communicator:
         (``oob_allreduce_push``): every rank pushes ``x`` into its piece of a staging area on all ranks, the ranks meet
         once, each sums the pieces locally.  The staging area belongs to the push kernels alone and
         holds two sets of pieces that consecutive calls alternate between (decided on the device), so calls may follow
-        one another at once, also as replays of captured CUDA graphs.  None when the push path does not apply: no
+        one another at once, also as replays of captured CUDA graphs, as long as a rank's calls run one after the
+        other (one stream, or streams ordered by events).  None when the push path does not apply: no
         ring, a message above ``config.push_max_bytes``, or one that does not fit a slot."""
         pool = self._ar_pool
         if pool is None or not x.is_cuda or not x.is_contiguous() or x.dtype != pool.dtype:
