@@ -24,8 +24,8 @@ Environment (names follow the reference's ``VLLM_OOVERLAP_*`` family):
                                  comparison arms of the serving benchmark.
   VLLM_OOVERLAP_STRICT           1 (default): a tensor the ooverlap backend cannot take raises; 0: it is counted as
                                  declined and handed to vLLM's own chain (the counts are logged when the group closes)
-  VLLM_OOVERLAP_RR_SLOTS         all-reduce ring slots (default 32)
-  VLLM_OOVERLAP_RR_CAPACITY_BYTES  bytes per slot (default 8 MiB)
+  VLLM_OOVERLAP_RR_SLOTS         all-reduce ring slots (default 16)
+  VLLM_OOVERLAP_RR_CAPACITY_BYTES  bytes per slot (default 128 MiB)
   VLLM_OOVERLAP_RR_DTYPE         bf16 | fp16 | fp32 (default bf16)
   VLLM_OOVERLAP_AG_SLOTS / _AG_CAPACITY_BYTES / _AG_DTYPE   all-gather pool (4 x 64 MiB, bf16)
   VLLM_OOVERLAP_BROKER_KEY       fixed rendezvous key (default: a UUID broadcast over the CPU group)
@@ -90,13 +90,14 @@ class OoverlapAllReduce:
         self.group = group
         self.debug = os.environ.get("VLLM_OOVERLAP_DEBUG", "0") not in ("", "0")
         self.rr_dtype = _env_dtype("VLLM_OOVERLAP_RR_DTYPE", "bf16")
-        # Ring of result / staging slots.  A slot holds a whole prefill chunk of a hidden-8192 model (16384 tokens x
-        # 16 KiB = 256 MiB), so that such an all-reduce is one copy into the slot and one in-place all-reduce whose
-        # result is handed out as it lies in the slot; with 128 MiB slots the TP4 engine run reduced every prefill chunk
-        # in two pieces with two extra copies out.  Decode-sized messages go through the flag-in-data / push kernels
-        # and only land in a slot.
-        self.rr_slots = _env_int("VLLM_OOVERLAP_RR_SLOTS", 8)
-        self.rr_capacity = _env_int("VLLM_OOVERLAP_RR_CAPACITY_BYTES", 256 << 20)
+        # Ring of result / staging slots.  A slot holds 8192 tokens of a hidden-8192 model (8192 x 16 KiB = 128 MiB), so
+        # that a prefill chunk of that size is one copy into the slot and one in-place all-reduce whose result is handed
+        # out as it lies in the slot; a larger tensor is reduced in slot-sized pieces (a 16384-token chunk: two pieces
+        # and two copies out; VLLM_OOVERLAP_RR_CAPACITY_BYTES=268435456 with VLLM_OOVERLAP_RR_SLOTS=8 makes it one, a
+        # setting that has not run inside the engine yet).  Decode-sized messages go through the flag-in-data / push
+        # kernels and only land in a slot.
+        self.rr_slots = _env_int("VLLM_OOVERLAP_RR_SLOTS", 16)
+        self.rr_capacity = _env_int("VLLM_OOVERLAP_RR_CAPACITY_BYTES", 128 << 20)
         self.ag_dtype = _env_dtype("VLLM_OOVERLAP_AG_DTYPE", "bf16")
         self.ag_slots = _env_int("VLLM_OOVERLAP_AG_SLOTS", 4)
         self.ag_capacity = _env_int("VLLM_OOVERLAP_AG_CAPACITY_BYTES", 64 << 20)
@@ -280,7 +281,7 @@ _row_parallel_backend: Optional["OoverlapAllReduce"] = None  # the tensor-parall
 @torch.library.custom_op("ooverlap_b200::row_parallel_linear", mutates_args=())
 def row_parallel_linear_op(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """``all_reduce(x @ weight.T)`` over the tensor-parallel group through the registered backend.  The result lives
-    in a slot of the backend's ring: it must be consumed before the ring wraps (32 slots by default)."""
+    in a slot of the backend's ring: it must be consumed before the ring wraps (16 slots by default)."""
     backend = _row_parallel_backend
     out = backend.row_parallel(x, weight) if backend is not None else None
     if out is None:
