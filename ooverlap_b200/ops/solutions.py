@@ -2,8 +2,8 @@
 
 A solution file is a JSON object ``{"<op>:<M>x<N>x<K>:tp<world>:<dtype>": {"strategy": ..., "comm_ctas": ...,
 "use_nvls": ..., "kernel": ..., "us": ...}, ...}`` written by ``ooverlap_b200.bench.tune_overlap``.  ``GemmAllReduce``
-consults the file named by ``OOB_OVERLAP_SOLUTIONS``, else the packaged ``policy/overlap_solutions.json`` (the tuner's
-result on 8 x B200 / NVSwitch for the headline shapes), before falling back to its built-in rule;
+consults the file named by ``OOB_OVERLAP_SOLUTIONS``, else the packaged ``policy/overlap_solutions.json`` (the measured
+winners for the headline shapes on 2, 4 and 8 x B200 / NVSwitch), before falling back to its built-in rule;
 ``OOB_OVERLAP_SOLUTIONS=none`` turns the lookup off.
 
 Capability parity: the reference saves one solution JSON per (M, N, K, backend) with the searched segment sizes,

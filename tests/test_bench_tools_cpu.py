@@ -59,9 +59,37 @@ def test_solutions_roundtrip(tmp_path, monkeypatch):
     assert solutions.lookup("gemm_ar", 512, 8192, 8192, 8, "fp16", path) is None
     monkeypatch.setenv("OOB_OVERLAP_SOLUTIONS", path)
     assert solutions.lookup("gemm_ar", 8192, 8192, 8192, 8, "fp16")["us"] == 417.0
-    monkeypatch.delenv("OOB_OVERLAP_SOLUTIONS")
+    monkeypatch.setenv("OOB_OVERLAP_SOLUTIONS", "none")
     assert solutions.lookup("gemm_ar", 8192, 8192, 8192, 8, "fp16") is None
+    monkeypatch.delenv("OOB_OVERLAP_SOLUTIONS")
+    assert solutions.lookup("gemm_ar", 8192, 8192, 8192, 8, "fp16")["us"] != 417.0  # the packaged table
+    assert solutions.lookup("gemm_ar", 1000, 8192, 8192, 8, "fp16") is None
     assert solutions.load(str(tmp_path / "missing.json")) == {}
+
+
+def test_packaged_overlap_solutions_plan_to_runnable_configurations(monkeypatch):
+    """Every entry of the packaged table is a measured winner for a headline shape and resolves, through the same
+    planner that GemmAllReduce uses, to a configuration the kernels accept."""
+    import json
+    from ooverlap_b200.ops.overlap import plan_gemm_all_reduce
+    monkeypatch.delenv("OOB_OVERLAP_SOLUTIONS", raising=False)
+    table = json.load(open(solutions.PACKAGED))
+    entries = {k: v for k, v in table.items() if k.startswith("gemm_ar:")}
+    assert len(entries) == 9 and isinstance(table["_about"], str)
+    for k, v in entries.items():
+        _, shape, tp, dtype = k.split(":")
+        M, N, K = (int(x) for x in shape.split("x"))
+        world = int(tp[2:])
+        assert solutions.lookup("gemm_ar", M, N, 0, world, dtype) == v
+        assert v["us"] <= v["unfused_us"] and v["measured_by"]
+        strategy, chunks, use_nvls, comm_ctas, kernel = plan_gemm_all_reduce(world, M, N, False, "auto", solution=v)
+        assert strategy == v["strategy"]
+        if strategy == "fused":
+            assert kernel == v["kernel"] and comm_ctas == v["comm_ctas"] and use_nvls == v["use_nvls"]
+            assert kernel in ("pair", "one_sm") and 1 <= comm_ctas <= 64 and use_nvls in (0, 1, 2)
+            assert not (kernel == "pair" and use_nvls == 2)  # the two-SM kernel has one path through the switch
+        # what the caller fixes is never overridden by the table
+        assert plan_gemm_all_reduce(world, M, N, False, "unfused", solution=v)[0] == "unfused"
 
 
 def test_gemm_solution_table_lookup_and_profiler_candidates(tmp_path, monkeypatch):
