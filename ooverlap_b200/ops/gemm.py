@@ -128,6 +128,42 @@ def tile_order(order: torch.Tensor) -> list:
     return [dict(unit=u, t_us=(t - t0) / 1e3, pair=int(w >> 32), index=int(w & 0xFFFFFFFF)) for t, u, w in sorted(done)]
 
 
+def stable_tile_waves(records, wave: int) -> dict:
+    """Compares the tile-order records of several launches of one shape (each the output of :func:`tile_order`, or a
+    plain list of unit numbers in completion order) and reports what is reproducible about the order.
+
+    ``wave`` is the number of units that complete together (CTAs of the GEMM grid; for the two-SM kernel
+    2 x pairs, since every CTA of a pair records its half).  A unit's wave in a launch is its position in the
+    completion order divided by ``wave``.  Returns ``waves`` (per unit: its wave when that is the same in every
+    launch, else -1), ``stable_fraction``, ``hint`` (all units ordered by their median wave, then by number: an order
+    that a consumer may rely on at wave granularity) and ``min_group_waves`` (the smallest g such that every unit stays
+    inside the same group of g consecutive waves in every launch: the finest chunking of the output by completion
+    time that holds from launch to launch).
+
+    Capability parity: the monitor rounds of the reference's search (tool/search.py:639-754) keep the tiles that land
+    in the same wave window every time and derive a stable order and a minimum group size from them.  The fused
+    kernels of this library signal every tile on its own and need no such hint; the analysis is for diagnosis and for
+    choosing slab boundaries of the ``chunked`` strategy."""
+    if wave < 1:
+        raise ValueError("wave must be at least 1")
+    orders = [[(r["unit"] if isinstance(r, dict) else int(r)) for r in rec] for rec in records]
+    if not orders or not orders[0]:
+        return dict(waves=[], stable_fraction=0.0, hint=[], min_group_waves=0)
+    units = sorted(orders[0])
+    if any(sorted(o) != units for o in orders):
+        raise ValueError("the records do not cover the same units")
+    pos = [{u: i // wave for i, u in enumerate(o)} for o in orders]
+    per_unit = {u: [p[u] for p in pos] for u in units}
+    waves = [per_unit[u][0] if len(set(per_unit[u])) == 1 else -1 for u in units]
+    n_waves = (len(units) + wave - 1) // wave
+    g = 1
+    while g < n_waves and any(len({w // g for w in ws}) > 1 for ws in per_unit.values()):
+        g += 1
+    median = {u: sorted(ws)[len(ws) // 2] for u, ws in per_unit.items()}
+    return dict(waves=waves, stable_fraction=sum(1 for w in waves if w >= 0) / len(units),
+                hint=sorted(units, key=lambda u: (median[u], u)), min_group_waves=g)
+
+
 def reserve_workspace(splitk_bytes: int = 0) -> None:
     """Allocates the library's GEMM scratch on the current device now: the stream-K workspace of the two-SM kernel and,
     when ``splitk_bytes`` > 0, a split-K workspace of that size (see :func:`splitk_workspace_bytes`).  Call it before

@@ -173,3 +173,28 @@ def test_vllm_plugin_entry_point_is_discoverable_without_an_installation(tmp_pat
     env = dict(os.environ, PYTHONPATH=os.pathsep.join([plug, root]))
     out = subprocess.run([sys.executable, "-c", code], cwd="/", env=env, capture_output=True, text=True)
     assert out.returncode == 0 and "ok" in out.stdout, out.stderr[-800:]
+
+
+def test_stable_tile_waves_over_several_recorded_launches():
+    from ooverlap_b200.ops import stable_tile_waves
+    # 8 units, waves of 2; launch 2 swaps units inside waves (still stable) and launch 3 moves unit 5 across the
+    # boundary between waves 2 and 3
+    a = [0, 1, 2, 3, 4, 5, 6, 7]
+    b = [1, 0, 3, 2, 5, 4, 7, 6]
+    r = stable_tile_waves([a, b], wave=2)
+    assert r["waves"] == [0, 0, 1, 1, 2, 2, 3, 3] and r["stable_fraction"] == 1.0 and r["min_group_waves"] == 1
+    assert r["hint"] == a
+    c = [0, 1, 2, 3, 4, 6, 5, 7]
+    r = stable_tile_waves([a, b, c], wave=2)
+    assert r["waves"] == [0, 0, 1, 1, 2, -1, -1, 3] and r["stable_fraction"] == 0.75
+    assert r["min_group_waves"] == 2          # waves {0,1} and {2,3} hold in every launch
+    assert r["hint"][:4] == [0, 1, 2, 3]
+    # units that move between waves 1 and 2 break groups of two waves; groups of three ({0,1,2} and {3}) hold
+    d = [0, 1, 2, 4, 3, 5, 6, 7]
+    assert stable_tile_waves([a, d], wave=2)["min_group_waves"] == 3
+    # the records of tile_order() are accepted as they are
+    recs = [[dict(unit=u, t_us=float(i), pair=0, index=i) for i, u in enumerate(o)] for o in (a, b)]
+    assert stable_tile_waves(recs, wave=2)["stable_fraction"] == 1.0
+    assert stable_tile_waves([], wave=2)["hint"] == []
+    with pytest.raises(ValueError):
+        stable_tile_waves([a, [0, 1, 2]], wave=2)
