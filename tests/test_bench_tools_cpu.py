@@ -2,6 +2,8 @@
 import json
 import os
 
+import pytest
+
 from ooverlap_b200.bench import aggregate, plot
 from ooverlap_b200.ops import solutions
 
