@@ -200,3 +200,27 @@ def test_stable_tile_waves_over_several_recorded_launches():
     assert stable_tile_waves([], wave=2)["hint"] == []
     with pytest.raises(ValueError):
         stable_tile_waves([a, [0, 1, 2]], wave=2)
+
+
+def test_overlap_tuner_latency_model_orders_the_candidates():
+    """The tuner measures candidates in the order its model predicts; the model must rank a fused kernel whose
+    reduction hides behind the GEMM ahead of the unfused pair, charge peer traffic more than the switch path, and
+    charge the GEMM for the SMs it gives up."""
+    from ooverlap_b200.bench.tune_overlap import candidates, predict_us
+    cands = candidates([8, 16], [0, 1, 2], ["pair", "one_sm"], 8192, 8)
+    assert cands[0]["strategy"] == "unfused" and cands[-1]["strategy"] == "chunked"
+    assert not any(c["kernel"] == "pair" and c["use_nvls"] == 2 for c in cands)  # one switch path in the two-SM kernel
+    assert len([c for c in cands if c["strategy"] == "fused"]) == 2 * 2 + 2 * 3
+    assert all(c["strategy"] != "chunked" for c in candidates([8], [0], ["pair"], 512, 8))
+    assert all(c["strategy"] != "chunked" for c in candidates([8], [0], ["pair"], 8192, 2))
+    t_ar = {8: 300.0, 16: 290.0}
+    p = {(c["strategy"], c["kernel"], c["comm_ctas"], c["use_nvls"]): predict_us(dict(c, slabs=4), 140.0, t_ar, 148, 25.0)
+         for c in cands}
+    assert p[("unfused", "", 0, 0)] == 140.0 + 290.0
+    assert p[("fused", "pair", 16, 1)] == 290.0 + 25.0              # communication-bound: the GEMM hides
+    assert p[("fused", "pair", 16, 0)] > p[("fused", "pair", 16, 1)]  # peer stores move 1.75 x the bytes
+    assert p[("fused", "pair", 16, 1)] < p[("unfused", "", 0, 0)]
+    # compute-bound case: the GEMM pays for the SMs the communication CTAs take
+    q8 = predict_us(dict(strategy="fused", kernel="pair", comm_ctas=8, use_nvls=1), 400.0, {8: 100.0}, 148, 10.0)
+    q32 = predict_us(dict(strategy="fused", kernel="pair", comm_ctas=32, use_nvls=1), 400.0, {32: 100.0}, 148, 10.0)
+    assert q8 == pytest.approx(400.0 * 148 / 140 + 10.0) and q32 > q8
