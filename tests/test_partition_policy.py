@@ -93,3 +93,53 @@ def test_gemm_bookkeeping_helpers(lib):
     assert lib.oob_gemm_counters_needed(_lib.GEMM_AR, 8192, 8192, 8) == 513
     assert lib.oob_gemm_counters_needed(_lib.GEMM_RS_NORM, 4096, 8192, 8) == 9
     assert lib.oob_gemm_counters_needed(_lib.GEMM_AG, 4096, 3584, 8) == 33
+
+
+def test_packaged_policy_loads_and_covers_two_four_and_eight_ranks(lib, monkeypatch):
+    """The measured (algorithm, CTA budget) table that ships with the package parses with the native loader, has
+    points for 2, 4 and 8 ranks with and without NVLS, names only algorithms that exist, and a lookup at one of its
+    points returns that point."""
+    import os
+    monkeypatch.delenv("OOB_MAX_CTAS", raising=False)
+    path = os.path.join(os.path.dirname(_lib.__file__), "policy", "b200_nvswitch.json")
+    data = json.load(open(path))
+    pts = data["points"]
+    assert {p["world"] for p in pts} == {2, 4, 8}
+    assert {p["collective"] for p in pts} == {"all_reduce", "reduce_scatter", "all_gather"}
+    valid = {"all_reduce": {_lib.AR_ONESHOT_P2P, _lib.AR_TWOSHOT_P2P, _lib.AR_ONESHOT_NVLS, _lib.AR_TWOSHOT_NVLS},
+             "reduce_scatter": {_lib.RS_P2P, _lib.RS_NVLS}, "all_gather": {_lib.AG_PUSH_P2P, _lib.AG_PUSH_NVLS}}
+    for p in pts:
+        assert p["algo"] in valid[p["collective"]], p
+        assert 1 <= p["ctas"] <= 160 and p["bytes"] >= 1024 and p["nvls"] in (0, 1), p
+        if not p["nvls"]:
+            assert p["algo"] not in (_lib.AR_ONESHOT_NVLS, _lib.AR_TWOSHOT_NVLS) or p["collective"] != "all_reduce", p
+    for world in (2, 4, 8):
+        assert any(p["world"] == world and p["nvls"] == 1 for p in pts)
+    assert lib.oob_policy_load(path.encode()) == 0
+    try:
+        code = {"all_reduce": 0, "reduce_scatter": 1, "all_gather": 2}
+        for p in pts[:: max(1, len(pts) // 25)]:
+            algo, ctas = _select(lib, p["world"], code[p["collective"]], p["bytes"], p["nvls"])
+            assert (algo, ctas) == (p["algo"], p["ctas"]), p
+    finally:
+        assert lib.oob_policy_load(b"") == 0
+
+
+def test_policy_files_merge_later_file_wins(tmp_path):
+    from ooverlap_b200.bench.collective_sweep import merge_policies
+    a = {"comment": "first", "points": [
+        {"world": 8, "collective": "all_reduce", "nvls": 1, "bytes": 1024, "algo": 3, "ctas": 8},
+        {"world": 8, "collective": "all_reduce", "nvls": 1, "bytes": 2048, "algo": 3, "ctas": 8}]}
+    b = {"comment": "second", "points": [
+        {"world": 8, "collective": "all_reduce", "nvls": 1, "bytes": 2048, "algo": 4, "ctas": 16},
+        {"world": 4, "collective": "all_gather", "nvls": 0, "bytes": 4096, "algo": 0, "ctas": 4}]}
+    pa, pb, out = tmp_path / "a.json", tmp_path / "b.json", tmp_path / "m.json"
+    pa.write_text(json.dumps(a))
+    pb.write_text(json.dumps(b))
+    assert merge_policies([str(pa), str(pb)], str(out)) == 3
+    m = json.load(open(out))
+    assert m["comment"] == "first"
+    assert [(p["world"], p["bytes"], p["algo"]) for p in m["points"]] == [(4, 4096, 0), (8, 1024, 3), (8, 2048, 4)]
+    assert merge_policies([str(pb), str(pa)], str(out), comment="mine") == 3
+    m = json.load(open(out))
+    assert m["comment"] == "mine" and [p["algo"] for p in m["points"] if p["bytes"] == 2048] == [3]
