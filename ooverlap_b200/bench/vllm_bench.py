@@ -188,6 +188,11 @@ def main() -> int:
         if b not in BACKENDS:
             raise SystemExit(f"unknown backend {b!r}")
     orders = list(itertools.permutations(backends)) if args.orders == "all" else [tuple(backends)]
+    if args.out:
+        # what produced the file: command line, versions, GPUs and the environment that steers the backends
+        from ..utils.manifest import write_manifest
+        write_manifest(args.out + ".manifest.json", extra={"bench": "vllm_throughput", "model": args.model, "tp": args.tp,
+                                                           "backends": backends, "orders": len(orders)})
     repo_root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     rc = 0
     with tempfile.TemporaryDirectory(prefix="oob_vllm_") as tmp:

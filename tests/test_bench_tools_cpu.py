@@ -224,3 +224,30 @@ def test_overlap_tuner_latency_model_orders_the_candidates():
     q8 = predict_us(dict(strategy="fused", kernel="pair", comm_ctas=8, use_nvls=1), 400.0, {8: 100.0}, 148, 10.0)
     q32 = predict_us(dict(strategy="fused", kernel="pair", comm_ctas=32, use_nvls=1), 400.0, {32: 100.0}, 148, 10.0)
     assert q8 == pytest.approx(400.0 * 148 / 140 + 10.0) and q32 > q8
+
+
+def test_run_manifest_captures_versions_and_the_steering_environment(tmp_path):
+    import subprocess
+    import sys
+    from ooverlap_b200.utils import manifest
+    env = {"OOB_LOG_LEVEL": "info", "VLLM_FORCE_ALLREDUCE_BACKEND": "ooverlap", "NCCL_DEBUG": "WARN", "HOME": "/h",
+           "CUDA_VISIBLE_DEVICES": "0,1", "VLLM_API_KEY": "abcdef", "VLLM_OOVERLAP_BROKER_KEY": "k1", "PATH": "/bin"}
+    got = manifest.captured_env(env)
+    assert got == {"CUDA_VISIBLE_DEVICES": "0,1", "NCCL_DEBUG": "WARN", "OOB_LOG_LEVEL": "info",
+                   "VLLM_API_KEY": "<6 characters>", "VLLM_FORCE_ALLREDUCE_BACKEND": "ooverlap",
+                   "VLLM_OOVERLAP_BROKER_KEY": "k1"}
+    m = manifest.run_manifest(["prog", "--x"], {"bench": "b"}, env)
+    assert m["argv"] == ["prog", "--x"] and m["bench"] == "b" and m["env"] == got
+    assert m["torch"] and m["python"] and "ooverlap_b200" in m["library"] and m["time_utc"].endswith("Z")
+    path = tmp_path / "m.json"
+    assert manifest.write_manifest(str(path), ["p"])["argv"] == ["p"]
+    assert json.load(open(path))["argv"] == ["p"]
+    # the vLLM benchmark driver writes one beside its output file, also for a dry run
+    out = tmp_path / "v.jsonl"
+    res = subprocess.run([sys.executable, "-m", "ooverlap_b200.bench.vllm_bench", "--dry-run", "--model", "tiny", "--tp", "2",
+                          "--backends", "pynccl,ooverlap", "--orders", "all", "--out", str(out)],
+                         capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-800:]
+    mf = json.load(open(str(out) + ".manifest.json"))
+    assert mf["bench"] == "vllm_throughput" and mf["tp"] == 2 and mf["backends"] == ["pynccl", "ooverlap"]
+    assert mf["orders"] == 2 and "--dry-run" in mf["argv"]
