@@ -55,3 +55,8 @@ def test_build_entry_point_is_a_no_op_when_current():
         assert b"sm_100a" in _lib.lib().oob_version()
     finally:
         sys.path.remove(ROOT)
+
+
+def test_multi_gpu_request_outside_a_launcher_is_refused_before_any_cuda_call():
+    res = _run("--gpus", "2", "--steps", "1", "--warmup", "1")
+    assert res.returncode == 2 and "torch.distributed.run" in res.stderr
