@@ -251,3 +251,53 @@ def test_run_manifest_captures_versions_and_the_steering_environment(tmp_path):
     mf = json.load(open(str(out) + ".manifest.json"))
     assert mf["bench"] == "vllm_throughput" and mf["tp"] == 2 and mf["backends"] == ["pynccl", "ooverlap"]
     assert mf["orders"] == 2 and "--dry-run" in mf["argv"]
+
+
+def test_plot_kinds_and_the_builtin_svg_writer(tmp_path, capsys):
+    import xml.dom.minidom
+    sweep = []
+    for nbytes, nccl_us, ours_us in ((1024, 16.0, 8.0), (1 << 20, 24.0, 16.0), (64 << 20, 190.0, 160.0)):
+        for coll in ("all_reduce", "all_gather"):
+            sweep.append({"collective": coll, "impl": "nccl", "algo": "nccl", "bytes": nbytes, "us": nccl_us,
+                          "bus_gbs": nbytes / nccl_us / 1e3, "ctas": 0})
+            for ctas, f in ((8, 1.0), (32, 1.2)):
+                sweep.append({"collective": coll, "impl": "ours", "algo": "twoshot_nvls", "bytes": nbytes, "us": ours_us * f,
+                              "bus_gbs": nbytes / (ours_us * f) / 1e3, "ctas": ctas})
+    sweep.append({"collective": "all_reduce", "bytes": 1024, "impl": "nccl", "stat": "latency_us", "p50": 17.0})  # no 'us'
+    lat = plot.latency_series(sweep)
+    assert lat["all_reduce"]["twoshot_nvls"] == [(1024, 8.0), (1 << 20, 16.0), (64 << 20, 160.0)]  # best CTA budget
+    eff = plot.efficiency_series(sweep)
+    assert [round(v, 3) for _, v in eff["all_reduce"]["nccl"]] == [0.5, 0.667, 0.842]
+    assert all(v == 1.0 for _, v in eff["all_gather"]["twoshot_nvls"])
+    f = _write(tmp_path / "s.jsonl", sweep)
+    for kind in ("sweep", "latency", "efficiency"):
+        out = tmp_path / f"{kind}.svg"
+        assert plot.main([f, "--kind", kind, "--out", str(out)]) == 0
+        doc = xml.dom.minidom.parse(str(out))
+        assert len(doc.getElementsByTagName("polyline")) == 4           # two collectives x two labels
+        assert len(doc.getElementsByTagName("circle")) == 12
+        for c in doc.getElementsByTagName("circle"):
+            assert 0 <= float(c.getAttribute("cx")) <= 1040 and 0 <= float(c.getAttribute("cy")) <= 340
+        texts = [t.firstChild.data for t in doc.getElementsByTagName("text") if t.firstChild is not None]
+        assert "all_reduce" in texts and "twoshot_nvls" in texts and "1Ki" in texts and "64Mi" in texts
+    assert plot.main([f, "--kind", "latency"]) == 0
+    assert "all_gather nccl 1024:16" in capsys.readouterr().out
+    # serving: median over runs and backend orders, grouped bars; a non-.svg name falls back to .svg without matplotlib
+    serving = [{"model": "m", "tp": 4, "batch": b, "backend": be, "output_tok_s": v}
+               for b, be, v in ((1, "default", 95.0), (1, "ooverlap", 97.0), (1, "ooverlap", 99.0), (64, "default", 1347.0),
+                                (64, "ooverlap", 1322.0))]
+    assert plot.serving_series(serving)[("m", 4, 1)] == {"default": 95.0, "ooverlap": 98.0}
+    g = _write(tmp_path / "v.jsonl", serving)
+    try:
+        import matplotlib  # noqa: F401
+        target, written = tmp_path / "v.svg", tmp_path / "v.svg"
+    except ImportError:
+        target, written = tmp_path / "v.png", tmp_path / "v.svg"
+    assert plot.main([g, "--kind", "serving", "--out", str(target)]) == 0
+    doc = xml.dom.minidom.parse(str(written))
+    bars = [r for r in doc.getElementsByTagName("rect") if r.getAttribute("fill").startswith("#") and r.getAttribute("height") != "10"]
+    assert len(bars) == 4
+    ov = _write(tmp_path / "o.jsonl", [{"op": "gemm_ar", "M": 512, "impl": "ours_fused", "nvls": 1, "us": 50.0},
+                                       {"op": "gemm_ar", "M": 512, "impl": "cublas+nccl", "us": 80.0}])
+    assert plot.main([ov, "--kind", "overlap", "--out", str(tmp_path / "o.svg")]) == 0
+    assert "cublas+nccl" in open(tmp_path / "o.svg").read()
