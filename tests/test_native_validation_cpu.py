@@ -75,3 +75,22 @@ def test_python_wrappers_check_shapes_before_calling_native_code():
         decode.rope_kv_write(qkv, 2, 1, 8, 1, kc2, kc2, cos[:16], sin[:16], 0)  # tables shorter than the cache
     with pytest.raises(ValueError):
         decode.rope_kv_write(qkv, 2, 1, 8, 1, kc2, kc2, cos, sin, torch.zeros(1, dtype=torch.long))  # pos not on the GPU
+
+
+def test_collective_entry_points_refuse_a_null_communicator():
+    """Every entry point that launches on a communicator answers OOB_ERR_INVALID for a null handle, with a message,
+    before it looks at anything else (a caller that lost its handle must not crash the process)."""
+    lib = _lib.lib()
+    calls = [
+        lambda: lib.oob_allreduce(None, _lib.BF16, 0, 0, 0, 0, -1, 0, None, 16, 0, None),
+        lambda: lib.oob_reduce_scatter(None, _lib.BF16, 0, 0, 0, 0, None, 16, 0, None),
+        lambda: lib.oob_all_gather(None, _lib.BF16, 0, 0, 0, None, None, 16, 0, None),
+        lambda: lib.oob_all_to_all(None, _lib.BF16, 0, 0, None, 16, 0, None),
+        lambda: lib.oob_allreduce_push(None, _lib.BF16, 0, 0, 0, 4096, None, None, 16, 0, 0, None),
+        lambda: lib.oob_allreduce_ll(None, _lib.BF16, 0, 0, 0, 4096, None, None, 16, 0, 0, None),
+        lambda: lib.oob_comm_recover(None),
+        lambda: lib.oob_comm_barrier(None),
+    ]
+    for call in calls:
+        assert call() == _lib.ERR_INVALID
+        assert "null communicator" in _lib.last_error()
